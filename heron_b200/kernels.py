@@ -1,0 +1,143 @@
+"""Device-tensor front end of the C ABI: torch tensors in, torch tensors out.
+
+torch is used for device memory and streams only; every function here hands raw device pointers
+to libheron_b200.so and raises ``HeronB200Error`` on a non-zero status.  Operand conventions are
+the reference operators' own: GEMM / batched GEMM take ``B`` as (N, K) (ops/cuda/dense.py:6,
+ops/cuda/batch_matmul.py:8), NHWC conv takes an HWIO filter (ops/cuda/conv2d.py:155).
+"""
+import ctypes
+
+import torch
+
+from . import _lib
+
+_TORCH_CODES = {
+    torch.float16: _lib.HB_F16,
+    torch.float32: _lib.HB_F32,
+    torch.int8: _lib.HB_S8,
+    torch.uint8: _lib.HB_U8,
+    torch.int32: _lib.HB_S32,
+}
+
+TORCH_DTYPES = {
+    "float16": torch.float16,
+    "float32": torch.float32,
+    "int8": torch.int8,
+    "uint8": torch.uint8,
+    "int32": torch.int32,
+}
+
+
+def _code(t):
+    try:
+        return _TORCH_CODES[t.dtype]
+    except KeyError:
+        raise _lib.HeronB200Error(_lib.HB_ERR_DTYPE, "dtype %s" % t.dtype)
+
+
+def _dev(t, name):
+    if not t.is_cuda:
+        raise ValueError("%s must be a CUDA tensor: the kernels have no CPU path" % name)
+    if not t.is_contiguous():
+        raise ValueError("%s must be contiguous" % name)
+    return ctypes.c_void_p(t.data_ptr())
+
+
+def _knobs(knobs):
+    if knobs is None:
+        return None
+    if isinstance(knobs, _lib.HbKnobs):
+        return ctypes.byref(knobs)
+    return ctypes.byref(_lib.HbKnobs.from_dict(knobs))
+
+
+def _stream(t):
+    return ctypes.c_void_p(torch.cuda.current_stream(t.device).cuda_stream)
+
+
+def default_out_dtype(in_dtype):
+    return torch.float32 if in_dtype == torch.float16 else torch.int32
+
+
+def gemm(a, b, out=None, out_dtype=None, knobs=None):
+    """out[M,N] = sum_k a[M,k] * b[N,k]."""
+    M, K = a.shape
+    N, K2 = b.shape
+    if K != K2:
+        raise ValueError("a is (M,K), b is (N,K): K differs")
+    if out is None:
+        out = torch.empty((M, N), dtype=out_dtype or default_out_dtype(a.dtype), device=a.device)
+    rc = _lib.load().hb_gemm(_dev(a, "a"), _dev(b, "b"), _dev(out, "out"), M, K, N, _code(a),
+                             _code(b), _code(out), _knobs(knobs), _stream(a))
+    _lib.check(rc, "hb_gemm")
+    return out
+
+
+def bmm(a, b, out=None, out_dtype=None, knobs=None):
+    """out[b,M,N] = sum_k a[b,M,k] * b[b,N,k]."""
+    B, M, K = a.shape
+    B2, N, K2 = b.shape
+    if K != K2 or B != B2:
+        raise ValueError("a is (B,M,K), b is (B,N,K): shapes differ")
+    if out is None:
+        out = torch.empty((B, M, N), dtype=out_dtype or default_out_dtype(a.dtype), device=a.device)
+    rc = _lib.load().hb_bmm(_dev(a, "a"), _dev(b, "b"), _dev(out, "out"), B, M, K, N, _code(a),
+                            _code(b), _code(out), _knobs(knobs), _stream(a))
+    _lib.check(rc, "hb_bmm")
+    return out
+
+
+def _pair(v):
+    if isinstance(v, int):
+        return v, v
+    a, b = v
+    return int(a), int(b)
+
+
+def conv_out_hw(H, W, KH, KW, stride, padding, dilation):
+    """Output extent of the reference's NHWC conv (ops/cuda/conv2d.py:165-175)."""
+    sh, sw = _pair(stride)
+    dh, dw = _pair(dilation)
+    HO = (H - ((KH - 1) * dh + 1) + 2 * padding) // sh + 1
+    WO = (W - ((KW - 1) * dw + 1) + 2 * padding) // sw + 1
+    return HO, WO
+
+
+def conv2d_nhwc(x, w, stride=1, padding=0, dilation=1, out=None, out_dtype=None, knobs=None):
+    """out[n,y,x,f] = sum pad(x)[n, y*s+ry*d, x*s+rx*d, c] * w[ry,rx,c,f]; w is HWIO."""
+    N, H, W, CI = x.shape
+    KH, KW, CI2, CO = w.shape
+    if CI != CI2:
+        raise ValueError("input channels of x and w differ")
+    sh, sw = _pair(stride)
+    dh, dw = _pair(dilation)
+    HO, WO = conv_out_hw(H, W, KH, KW, stride, padding, dilation)
+    if out is None:
+        out = torch.empty((N, HO, WO, CO), dtype=out_dtype or default_out_dtype(x.dtype),
+                          device=x.device)
+    rc = _lib.load().hb_conv2d_nhwc(_dev(x, "x"), _dev(w, "w"), _dev(out, "out"), N, H, W, CI, CO,
+                                    KH, KW, sh, sw, int(padding), dh, dw, _code(x), _code(w),
+                                    _code(out), _knobs(knobs), _stream(x))
+    _lib.check(rc, "hb_conv2d_nhwc")
+    return out
+
+
+def conv2d_nhwc_packed(x, w_packed, CO, KH, KW, stride=1, padding=0, dilation=1, sco=64, out=None,
+                       scratch=None, knobs=None):
+    """The x86 operator's conv: uint8 NHWC input, int8 filter packed (CO/sco,KH,KW,CI/4,sco,4)."""
+    N, H, W, CI = x.shape
+    sh, sw = _pair(stride)
+    dh, dw = _pair(dilation)
+    HO, WO = conv_out_hw(H, W, KH, KW, stride, padding, dilation)
+    lib = _lib.load()
+    need = lib.hb_conv2d_packed_scratch_bytes(CI, CO, KH, KW)
+    if scratch is None:
+        scratch = torch.empty(need, dtype=torch.int8, device=x.device)
+    if out is None:
+        out = torch.empty((N, HO, WO, CO // sco, sco), dtype=torch.int32, device=x.device)
+    rc = lib.hb_conv2d_nhwc_packed(_dev(x, "x"), _dev(w_packed, "w_packed"), _dev(out, "out"), N, H,
+                                   W, CI, CO, KH, KW, sh, sw, int(padding), dh, dw, int(sco),
+                                   _dev(scratch, "scratch"), scratch.numel(), _knobs(knobs),
+                                   _stream(x))
+    _lib.check(rc, "hb_conv2d_nhwc_packed")
+    return out

@@ -1,0 +1,142 @@
+/*
+ * heron_b200.h — C ABI of libheron_b200.so.
+ *
+ * The library holds hand-written sm_100a kernels (tcgen05 MMA, TMEM accumulators, TMA-fed
+ * shared-memory ring) for the tensor programs that the Heron auto-tuner generates through TVM:
+ * GEMM, batched GEMM and NHWC conv2d, in fp16 -> fp32/fp16 and u8/s8 -> s32.
+ *
+ * What each entry point replaces in the reference: the TVM-built packed function that
+ * Task.instantiate() hands to tvm.build (task/task.py:76-89).  Its arguments are the operator's
+ * input tensors followed by its output tensor (task/task.py:81), all allocated by the caller
+ * (tests/quick_start/dlboost/run.py:52-58); the callee allocates and frees nothing.  The entry
+ * points below keep that contract: plain device pointers and sizes, caller-owned buffers, a CUDA
+ * stream, and an int status in place of a TVMError (runner/measure_methods.py:178-185).
+ *
+ * There is no CPU fallback anywhere in this library: without a Blackwell GPU every compute entry
+ * point returns HB_ERR_DEVICE.
+ */
+#ifndef HERON_B200_H_
+#define HERON_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- status codes ------------------------------------------------------------------------ */
+enum {
+  HB_OK = 0,
+  HB_ERR_SHAPE = 1,   /* a dimension is non-positive or breaks a documented divisibility rule   */
+  HB_ERR_ALIGN = 2,   /* a pointer is not 16-byte aligned, or a row pitch is not a 16-byte multiple */
+  HB_ERR_KNOB = 3,    /* the knob set is outside the kernel's constrained space                  */
+  HB_ERR_LAUNCH = 4,  /* the CUDA runtime or driver refused the launch / tensor-map encoding    */
+  HB_ERR_TIMEOUT = 5, /* a bounded device-side wait ran out; read by hb_last_status            */
+  HB_ERR_DEVICE = 6,  /* no usable sm_100 device                                                 */
+  HB_ERR_DTYPE = 7,   /* dtype combination the kernels do not implement                         */
+  HB_ERR_SCRATCH = 8  /* the caller's scratch buffer is missing or too small                    */
+};
+
+/* ---- element types ----------------------------------------------------------------------- */
+typedef enum {
+  HB_F16 = 0, /* IEEE binary16 */
+  HB_F32 = 1,
+  HB_S8 = 2,
+  HB_U8 = 3,
+  HB_S32 = 4
+} hb_dtype;
+
+/*
+ * Knobs of the kernel family: the tile / stage / raster parameters a tuner may choose.  They
+ * take the place of the reference's wmma fragment and tiling knobs
+ * (schedule/sched_op/gpu_tensorcore_operator.py:282-294, schedule/sched_op/sched_common.py:157-170).
+ * A zero in any field means "library default for this shape".
+ */
+typedef struct {
+  int tile_n;        /* accumulator tile width; multiple of 32 (64 for fp16 output), 32..256      */
+  int stages;        /* depth of the TMA -> MMA shared-memory ring, 1..12                          */
+  int swizzle_bytes; /* bytes of K per ring stage and TMA swizzle span: 32, 64 or 128             */
+  int acc_stages;    /* TMEM accumulator buffers (1 or 2); 2 overlaps epilogue with the next tile */
+  int raster;        /* 0: consecutive tiles walk N first (default); 1: walk M first               */
+  int epilogue;      /* 1: TMEM -> registers -> shared memory -> TMA store; 2: direct global stores */
+  int max_ctas;      /* cap on the persistent grid (0: one CTA per SM)                             */
+  int reserved;
+} hb_knobs;
+
+/* Library / device facts. */
+int hb_version(void);
+/* Number of SMs of the current device, or a negative status. */
+int hb_sm_count(void);
+/* Fills *k with the defaults the library would pick for op (0 gemm, 1 bmm, 2 conv) on a problem
+ * whose GEMM view is (batch, M, N, K) with the given dtypes.  k_inner is the contiguous part of
+ * the reduction: K for gemm/bmm, the input channel count CI for conv. */
+int hb_default_knobs(int op, int batch, int M, int N, int K, int k_inner, hb_dtype in_a,
+                     hb_dtype out, hb_knobs* k);
+/* Checks a knob set against the kernel's own limits (shared memory, TMEM columns, divisibility)
+ * without touching the GPU.  Returns HB_OK or HB_ERR_KNOB; *smem_bytes / *tmem_cols receive the
+ * resources the configuration needs (either may be NULL). */
+int hb_check_knobs(int op, int batch, int M, int N, int K, int k_inner, hb_dtype in_a,
+                   hb_dtype out, const hb_knobs* k, int* smem_bytes, int* tmem_cols);
+
+/*
+ * GEMM: C[M,N] = sum_k A[M,K] * B[N,K]  (B is stored N-major over K, i.e. C = A * B^T).
+ * Replaces the artefact built from ops/cuda/dense.py:4-17 (fp16 inputs; `in_b == in_a`) and
+ * ops/x86/dense.py:6-18 (A uint8, B int8, C int32).  Accepted combinations:
+ *   in_a = in_b = HB_F16, out = HB_F32 or HB_F16 (fp32 accumulation, RN conversion for HB_F16);
+ *   in_a in {HB_U8, HB_S8}, in_b in {HB_U8, HB_S8}, out = HB_S32 (exact).
+ * All three are dense row-major device buffers.  K*sizeof(in) must be a multiple of 16.
+ */
+int hb_gemm(const void* A, const void* B, void* C, int M, int K, int N, hb_dtype in_a,
+            hb_dtype in_b, hb_dtype out, const hb_knobs* knobs, void* stream);
+
+/*
+ * Batched GEMM: C[b,M,N] = sum_k A[b,M,K] * B[b,N,K].  Replaces ops/cuda/batch_matmul.py:5-19 and
+ * ops/x86/batch_matmul.py:6-20.  Same dtype table as hb_gemm.  batch >= 1 here (the reference op
+ * asserts batch > 1 at ops/cuda/batch_matmul.py:6; the Python operator keeps that assert).
+ */
+int hb_bmm(const void* A, const void* B, void* C, int batch, int M, int K, int N, hb_dtype in_a,
+           hb_dtype in_b, hb_dtype out, const hb_knobs* knobs, void* stream);
+
+/*
+ * NHWC conv2d as implicit GEMM:
+ *   out[n,y,x,f] = sum_{ry,rx,rc} pad(in)[n, y*sh + ry*dh, x*sw + rx*dw, rc] * w[ry,rx,rc,f]
+ * with `in` (N,H,W,CI), `w` HWIO (KH,KW,CI,CO) and `out` (N,HO,WO,CO), zero padding `pad` on all
+ * four sides.  Replaces ops/cuda/conv2d.py:137-196; with in_a = HB_U8, in_w = HB_S8 it computes
+ * what ops/x86/conv2d_int8.py:31-93 computes once that op's packed filter is unpacked to HWIO
+ * (see hb_conv2d_nhwc_packed).  CI*sizeof(in) must be a multiple of 32 and CO*sizeof(out) of 16.
+ */
+int hb_conv2d_nhwc(const void* in, const void* w, void* out, int N, int H, int W, int CI, int CO,
+                   int KH, int KW, int stride_h, int stride_w, int pad, int dil_h, int dil_w,
+                   hb_dtype in_a, hb_dtype in_w, hb_dtype out_t, const hb_knobs* knobs,
+                   void* stream);
+
+/*
+ * The x86 operator's own filter format (ops/x86/conv2d_int8.py:36-50): `w_packed` is int8 with
+ * shape (CO/sco, KH, KW, CI/4, sco, 4), sco in {64, 48, 32} ("OhwI64o4i", "OhwI48o4i",
+ * "OhwI32o4i"); input uint8 NHWC, output int32 (N,HO,WO,CO/sco,sco), which is NHWC.  The filter
+ * is unpacked to HWIO into `scratch` (caller-owned device memory of at least
+ * hb_conv2d_packed_scratch_bytes(...) bytes) by a small kernel on the same stream, then the
+ * implicit-GEMM kernel runs on it.
+ */
+size_t hb_conv2d_packed_scratch_bytes(int CI, int CO, int KH, int KW);
+int hb_conv2d_nhwc_packed(const void* in, const void* w_packed, void* out, int N, int H, int W,
+                          int CI, int CO, int KH, int KW, int stride_h, int stride_w, int pad,
+                          int dil_h, int dil_w, int sco, void* scratch, size_t scratch_bytes,
+                          const hb_knobs* knobs, void* stream);
+
+/*
+ * Device-side status of the kernels launched so far on the current device: synchronises the
+ * device, copies the status word (HB_OK or HB_ERR_TIMEOUT) to *status and clears it.  A bounded
+ * wait that ran out leaves the output undefined but the context usable.  Stands in for the
+ * per-candidate error the reference's runner records (runner/measure_methods.py:178-185).
+ */
+int hb_last_status(int* status);
+
+/* Human-readable text for a status code (static storage). */
+const char* hb_status_string(int status);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* HERON_B200_H_ */
