@@ -42,6 +42,13 @@ EXPORTED_SYMBOLS = (
     "hb_conv2d_nhwc",
     "hb_conv2d_packed_scratch_bytes",
     "hb_conv2d_nhwc_packed",
+    "hb_plan_gemm",
+    "hb_plan_bmm",
+    "hb_plan_conv2d_nhwc",
+    "hb_plan_conv2d_nhwc_packed",
+    "hb_plan_launch",
+    "hb_plan_knobs",
+    "hb_plan_destroy",
     "hb_last_status",
     "hb_status_string",
 )
@@ -119,6 +126,21 @@ def load():
     lib.hb_conv2d_nhwc_packed.argtypes = (
         [c_void_p] * 3 + [c_int] * 12 + [c_int, c_void_p, c_size_t, kp, c_void_p]
     )
+    pp = ctypes.POINTER(c_void_p)
+    lib.hb_plan_gemm.restype = c_int
+    lib.hb_plan_gemm.argtypes = [pp] + lib.hb_gemm.argtypes[:-1]
+    lib.hb_plan_bmm.restype = c_int
+    lib.hb_plan_bmm.argtypes = [pp] + lib.hb_bmm.argtypes[:-1]
+    lib.hb_plan_conv2d_nhwc.restype = c_int
+    lib.hb_plan_conv2d_nhwc.argtypes = [pp] + lib.hb_conv2d_nhwc.argtypes[:-1]
+    lib.hb_plan_conv2d_nhwc_packed.restype = c_int
+    lib.hb_plan_conv2d_nhwc_packed.argtypes = [pp] + lib.hb_conv2d_nhwc_packed.argtypes[:-1]
+    lib.hb_plan_launch.restype = c_int
+    lib.hb_plan_launch.argtypes = [c_void_p, c_void_p]
+    lib.hb_plan_knobs.restype = c_int
+    lib.hb_plan_knobs.argtypes = [c_void_p, kp, ip, ip]
+    lib.hb_plan_destroy.restype = None
+    lib.hb_plan_destroy.argtypes = [c_void_p]
     lib.hb_last_status.restype = c_int
     lib.hb_last_status.argtypes = [ip]
     lib.hb_status_string.restype = ctypes.c_char_p

@@ -1,0 +1,50 @@
+"""Builds libheron_b200.so in-tree with nvcc for sm_100a.
+
+    python -m heron_b200.build [--force] [--verbose]
+
+The library is the package's only compute path.  nvcc cross-compiles without a GPU.
+"""
+import os
+import subprocess
+import sys
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+CSRC = os.path.join(HERE, "csrc")
+TARGET = os.path.join(HERE, "libheron_b200.so")
+SOURCES = [os.path.join(CSRC, "hb_api.cu")]
+DEPS = SOURCES + [os.path.join(CSRC, "hb_kernel.cuh"), os.path.join(CSRC, "hb_ptx.cuh"),
+                  os.path.join(HERE, os.pardir, "include", "heron_b200.h")]
+
+NVCC_FLAGS = [
+    "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+    "-shared", "-Xcompiler", "-fPIC", "-cudart", "static",
+]
+
+
+def nvcc():
+    for cand in (os.environ.get("NVCC"), "/usr/local/cuda/bin/nvcc", "nvcc"):
+        if cand and (os.path.sep not in cand or os.path.exists(cand)):
+            return cand
+    return "nvcc"
+
+
+def is_stale():
+    if not os.path.exists(TARGET):
+        return True
+    t = os.path.getmtime(TARGET)
+    return any(os.path.exists(d) and os.path.getmtime(d) > t for d in DEPS)
+
+
+def build(force=False, verbose=False, extra_flags=()):
+    if not force and not is_stale():
+        return TARGET
+    cmd = [nvcc()] + NVCC_FLAGS + list(extra_flags) + ["-o", TARGET] + SOURCES
+    if verbose:
+        print(" ".join(cmd))
+    subprocess.check_call(cmd)
+    return TARGET
+
+
+if __name__ == "__main__":
+    build(force="--force" in sys.argv, verbose=True,
+          extra_flags=["-Xptxas", "-v"] if "--verbose" in sys.argv else [])

@@ -11,6 +11,7 @@
 #include <cstdio>
 #include <cstring>
 #include <mutex>
+#include <new>
 
 namespace {
 
@@ -174,7 +175,7 @@ void resolve_knobs(const Problem& pr, const hb_knobs* in, int sm_count, hb_knobs
     for (int bn = gran; bn <= 256; bn += gran) {
       const long long tiles = tiles_m * ((pr.N + bn - 1) / bn) * pr.batch;
       const long long waves = (tiles + sms - 1) / sms;
-      const long long cost = waves * (bn + 24);
+      const long long cost = waves * (hb::kTileM + bn);  // operand bytes a CTA pulls per tile
       if (best_cost < 0 || cost < best_cost || (cost == best_cost && bn > best)) {
         best_cost = cost;
         best = bn;
@@ -236,16 +237,34 @@ struct ConvGeom {
   int N, H, W, CI, CO, KH, KW, stride_h, stride_w, pad, dil_h, dil_w, HO, WO;
 };
 
-int launch(Driver& d, const Problem& pr, const hb_knobs& k, const ConvGeom* cg, const void* A,
-           const void* B, void* C, cudaStream_t stream) {
+}  // namespace
+
+// A launch-ready kernel configuration: encoded tensor maps, kernel parameters, grid and shared
+// memory size.  The counterpart of the module the reference gets back from tvm.build.
+struct hb_plan {
+  CUtensorMap tmA, tmB, tmC;
+  hb::KParams p;
+  hb_knobs knobs;
+  int grid;
+  int smem;
+  // packed-filter conv only: the unpack kernel that runs first on the same stream
+  const void* packed_w;
+  void* scratch;
+  int unpack_blocks, sco, KH;
+};
+
+namespace {
+
+int build_plan(Driver& d, const Problem& pr, const hb_knobs& k, const ConvGeom* cg, const void* A,
+               const void* B, void* C, hb_plan* plan) {
   const int es = esize(pr.in_a), eo = esize(pr.out);
   const int kind = mma_kind(pr.in_a, pr.in_b, pr.out);
   int smem = 0, tmem_cols = 0;
   int rc = check_knobs(pr, k, &smem, &tmem_cols);
   if (rc != HB_OK) return rc;
 
-  KParams p;
-  std::memset(&p, 0, sizeof(p));
+  std::memset(plan, 0, sizeof(*plan));
+  KParams& p = plan->p;
   p.M = pr.M; p.N = pr.N; p.K = pr.K; p.batch = pr.batch;
   p.BN = k.tile_n; p.SW = k.swizzle_bytes; p.esize_in = es; p.esize_out = eo;
   p.stages = k.stages; p.acc_stages = k.acc_stages; p.tmem_cols = tmem_cols;
@@ -260,8 +279,9 @@ int launch(Driver& d, const Problem& pr, const hb_knobs& k, const ConvGeom* cg, 
   p.idesc = make_idesc(kind, pr.in_a, pr.in_b, k.tile_n, pr.conv);
   p.C = C; p.ldc = pr.N; p.batch_stride_c = static_cast<long long>(pr.M) * pr.N;
 
-  CUtensorMap tmA, tmB, tmC;
-  std::memset(&tmA, 0, sizeof(tmA)); std::memset(&tmB, 0, sizeof(tmB)); std::memset(&tmC, 0, sizeof(tmC));
+  CUtensorMap& tmA = plan->tmA;
+  CUtensorMap& tmB = plan->tmB;
+  CUtensorMap& tmC = plan->tmC;
   if (!pr.conv) {
     p.num_kb = (pr.K + BK - 1) / BK;
     const uint64_t rowA = static_cast<uint64_t>(pr.K) * es;
@@ -314,15 +334,31 @@ int launch(Driver& d, const Problem& pr, const hb_knobs& k, const ConvGeom* cg, 
   int grid = d.sm_count;
   if (k.max_ctas > 0 && k.max_ctas < grid) grid = k.max_ctas;
   if (p.num_tiles < grid) grid = p.num_tiles;
-  if (eo == 2)
-    hb::hb_umma_kernel<2><<<grid, hb::kThreads, smem, stream>>>(tmA, tmB, tmC, p);
+  plan->grid = grid;
+  plan->smem = smem;
+  plan->knobs = k;
+  return HB_OK;
+}
+
+int run_plan(const hb_plan* plan, cudaStream_t stream) {
+  if (plan->packed_w) {
+    hb::hb_unpack_filter_kernel<<<plan->unpack_blocks, 256, 0, stream>>>(
+        static_cast<const int8_t*>(plan->packed_w), static_cast<int8_t*>(plan->scratch), plan->p.N,
+        plan->KH, plan->p.KW, plan->p.CI, plan->sco);
+    if (cudaGetLastError() != cudaSuccess) return HB_ERR_LAUNCH;
+  }
+  if (plan->p.esize_out == 2)
+    hb::hb_umma_kernel<2><<<plan->grid, hb::kThreads, plan->smem, stream>>>(plan->tmA, plan->tmB,
+                                                                             plan->tmC, plan->p);
   else
-    hb::hb_umma_kernel<4><<<grid, hb::kThreads, smem, stream>>>(tmA, tmB, tmC, p);
+    hb::hb_umma_kernel<4><<<plan->grid, hb::kThreads, plan->smem, stream>>>(plan->tmA, plan->tmB,
+                                                                             plan->tmC, plan->p);
   return cudaGetLastError() == cudaSuccess ? HB_OK : HB_ERR_LAUNCH;
 }
 
-int gemm_like(int op, const void* A, const void* B, void* C, int batch, int M, int K, int N,
-              hb_dtype in_a, hb_dtype in_b, hb_dtype out, const hb_knobs* knobs, void* stream) {
+int plan_gemm_like(int op, const void* A, const void* B, void* C, int batch, int M, int K, int N,
+                   hb_dtype in_a, hb_dtype in_b, hb_dtype out, const hb_knobs* knobs,
+                   hb_plan* plan) {
   if (batch <= 0 || M <= 0 || K <= 0 || N <= 0) return HB_ERR_SHAPE;
   if (mma_kind(in_a, in_b, out) < 0) return HB_ERR_DTYPE;
   if ((static_cast<long long>(K) * esize(in_a)) % 16 != 0) return HB_ERR_SHAPE;
@@ -333,7 +369,31 @@ int gemm_like(int op, const void* A, const void* B, void* C, int batch, int M, i
   Problem pr{op, batch, M, N, K, in_a, in_b, out, false, 0};
   hb_knobs k;
   resolve_knobs(pr, knobs, d.sm_count, &k);
-  return launch(d, pr, k, nullptr, A, B, C, static_cast<cudaStream_t>(stream));
+  return build_plan(d, pr, k, nullptr, A, B, C, plan);
+}
+
+int plan_conv(const void* in, const void* w, void* out, int N, int H, int W, int CI, int CO, int KH,
+              int KW, int stride_h, int stride_w, int pad, int dil_h, int dil_w, hb_dtype in_a,
+              hb_dtype in_w, hb_dtype out_t, const hb_knobs* knobs, hb_plan* plan);
+
+int plan_conv_packed(const void* in, const void* w_packed, void* out, int N, int H, int W, int CI,
+                     int CO, int KH, int KW, int stride_h, int stride_w, int pad, int dil_h,
+                     int dil_w, int sco, void* scratch, size_t scratch_bytes, const hb_knobs* knobs,
+                     hb_plan* plan);
+
+template <class BuildFn>
+int new_plan(hb_plan** out, BuildFn build) {
+  if (!out) return HB_ERR_SHAPE;
+  *out = nullptr;
+  hb_plan* plan = new (std::nothrow) hb_plan;
+  if (!plan) return HB_ERR_LAUNCH;
+  const int rc = build(plan);
+  if (rc != HB_OK) {
+    delete plan;
+    return rc;
+  }
+  *out = plan;
+  return HB_OK;
 }
 
 int conv_out_extent(int in, int k, int stride, int pad, int dil) {
@@ -373,18 +433,34 @@ int hb_check_knobs(int op, int batch, int M, int N, int K, int k_inner, hb_dtype
 
 int hb_gemm(const void* A, const void* B, void* C, int M, int K, int N, hb_dtype in_a,
             hb_dtype in_b, hb_dtype out, const hb_knobs* knobs, void* stream) {
-  return gemm_like(0, A, B, C, 1, M, K, N, in_a, in_b, out, knobs, stream);
+  hb_plan plan;
+  const int rc = plan_gemm_like(0, A, B, C, 1, M, K, N, in_a, in_b, out, knobs, &plan);
+  return rc != HB_OK ? rc : run_plan(&plan, static_cast<cudaStream_t>(stream));
 }
 
 int hb_bmm(const void* A, const void* B, void* C, int batch, int M, int K, int N, hb_dtype in_a,
            hb_dtype in_b, hb_dtype out, const hb_knobs* knobs, void* stream) {
-  return gemm_like(1, A, B, C, batch, M, K, N, in_a, in_b, out, knobs, stream);
+  hb_plan plan;
+  const int rc = plan_gemm_like(1, A, B, C, batch, M, K, N, in_a, in_b, out, knobs, &plan);
+  return rc != HB_OK ? rc : run_plan(&plan, static_cast<cudaStream_t>(stream));
 }
 
 int hb_conv2d_nhwc(const void* in, const void* w, void* out, int N, int H, int W, int CI, int CO,
                    int KH, int KW, int stride_h, int stride_w, int pad, int dil_h, int dil_w,
                    hb_dtype in_a, hb_dtype in_w, hb_dtype out_t, const hb_knobs* knobs,
                    void* stream) {
+  hb_plan plan;
+  const int rc = plan_conv(in, w, out, N, H, W, CI, CO, KH, KW, stride_h, stride_w, pad, dil_h,
+                           dil_w, in_a, in_w, out_t, knobs, &plan);
+  return rc != HB_OK ? rc : run_plan(&plan, static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"
+
+namespace {
+int plan_conv(const void* in, const void* w, void* out, int N, int H, int W, int CI, int CO, int KH,
+              int KW, int stride_h, int stride_w, int pad, int dil_h, int dil_w, hb_dtype in_a,
+              hb_dtype in_w, hb_dtype out_t, const hb_knobs* knobs, hb_plan* plan) {
   if (N <= 0 || H <= 0 || W <= 0 || CI <= 0 || CO <= 0 || KH <= 0 || KW <= 0) return HB_ERR_SHAPE;
   if (stride_h <= 0 || stride_w <= 0 || dil_h <= 0 || dil_w <= 0 || pad < 0) return HB_ERR_SHAPE;
   if (mma_kind(in_a, in_w, out_t) < 0) return HB_ERR_DTYPE;
@@ -409,8 +485,36 @@ int hb_conv2d_nhwc(const void* in, const void* w, void* out, int N, int H, int W
   hb_knobs k;
   resolve_knobs(pr, knobs, d.sm_count, &k);
   ConvGeom cg{N, H, W, CI, CO, KH, KW, stride_h, stride_w, pad, dil_h, dil_w, HO, WO};
-  return launch(d, pr, k, &cg, in, w, out, static_cast<cudaStream_t>(stream));
+  return build_plan(d, pr, k, &cg, in, w, out, plan);
 }
+
+int plan_conv_packed(const void* in, const void* w_packed, void* out, int N, int H, int W, int CI,
+                     int CO, int KH, int KW, int stride_h, int stride_w, int pad, int dil_h,
+                     int dil_w, int sco, void* scratch, size_t scratch_bytes, const hb_knobs* knobs,
+                     hb_plan* plan) {
+  if (sco != 64 && sco != 48 && sco != 32) return HB_ERR_SHAPE;
+  if (CI <= 0 || CO <= 0 || KH <= 0 || KW <= 0) return HB_ERR_SHAPE;
+  if (CI % 4 != 0 || CO % sco != 0) return HB_ERR_SHAPE;
+  if (!scratch || scratch_bytes < hb_conv2d_packed_scratch_bytes(CI, CO, KH, KW))
+    return HB_ERR_SCRATCH;
+  if (!w_packed || !aligned16(w_packed) || !aligned16(scratch)) return HB_ERR_ALIGN;
+  const int rc = plan_conv(in, scratch, out, N, H, W, CI, CO, KH, KW, stride_h, stride_w, pad, dil_h,
+                           dil_w, HB_U8, HB_S8, HB_S32, knobs, plan);
+  if (rc != HB_OK) return rc;
+  const long long groups = static_cast<long long>(KH) * KW * (CI / 4) * CO;
+  int blocks = static_cast<int>((groups + 255) / 256);
+  const int cap = driver().sm_count * 8;
+  if (blocks > cap) blocks = cap;
+  plan->packed_w = w_packed;
+  plan->scratch = scratch;
+  plan->unpack_blocks = blocks;
+  plan->sco = sco;
+  plan->KH = KH;
+  return HB_OK;
+}
+}  // namespace
+
+extern "C" {
 
 size_t hb_conv2d_packed_scratch_bytes(int CI, int CO, int KH, int KW) {
   if (CI <= 0 || CO <= 0 || KH <= 0 || KW <= 0) return 0;
@@ -421,23 +525,60 @@ int hb_conv2d_nhwc_packed(const void* in, const void* w_packed, void* out, int N
                           int CI, int CO, int KH, int KW, int stride_h, int stride_w, int pad,
                           int dil_h, int dil_w, int sco, void* scratch, size_t scratch_bytes,
                           const hb_knobs* knobs, void* stream) {
-  if (sco != 64 && sco != 48 && sco != 32) return HB_ERR_SHAPE;
-  if (CI <= 0 || CO <= 0 || KH <= 0 || KW <= 0) return HB_ERR_SHAPE;
-  if (CI % 4 != 0 || CO % sco != 0) return HB_ERR_SHAPE;
-  if (!scratch || scratch_bytes < hb_conv2d_packed_scratch_bytes(CI, CO, KH, KW))
-    return HB_ERR_SCRATCH;
-  if (!w_packed || !aligned16(w_packed) || !aligned16(scratch)) return HB_ERR_ALIGN;
-  Driver& d = driver();
-  if (d.status != HB_OK) return d.status;
-  const long long groups = static_cast<long long>(KH) * KW * (CI / 4) * CO;
-  int blocks = static_cast<int>((groups + 255) / 256);
-  if (blocks > d.sm_count * 8) blocks = d.sm_count * 8;
-  hb::hb_unpack_filter_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const int8_t*>(w_packed), static_cast<int8_t*>(scratch), CO, KH, KW, CI, sco);
-  if (cudaGetLastError() != cudaSuccess) return HB_ERR_LAUNCH;
-  return hb_conv2d_nhwc(in, scratch, out, N, H, W, CI, CO, KH, KW, stride_h, stride_w, pad, dil_h,
-                        dil_w, HB_U8, HB_S8, HB_S32, knobs, stream);
+  hb_plan plan;
+  const int rc = plan_conv_packed(in, w_packed, out, N, H, W, CI, CO, KH, KW, stride_h, stride_w,
+                                  pad, dil_h, dil_w, sco, scratch, scratch_bytes, knobs, &plan);
+  return rc != HB_OK ? rc : run_plan(&plan, static_cast<cudaStream_t>(stream));
 }
+
+int hb_plan_gemm(hb_plan** plan, const void* A, const void* B, void* C, int M, int K, int N,
+                 hb_dtype in_a, hb_dtype in_b, hb_dtype out, const hb_knobs* knobs) {
+  return new_plan(plan, [&](hb_plan* p) {
+    return plan_gemm_like(0, A, B, C, 1, M, K, N, in_a, in_b, out, knobs, p);
+  });
+}
+
+int hb_plan_bmm(hb_plan** plan, const void* A, const void* B, void* C, int batch, int M, int K,
+                int N, hb_dtype in_a, hb_dtype in_b, hb_dtype out, const hb_knobs* knobs) {
+  return new_plan(plan, [&](hb_plan* p) {
+    return plan_gemm_like(1, A, B, C, batch, M, K, N, in_a, in_b, out, knobs, p);
+  });
+}
+
+int hb_plan_conv2d_nhwc(hb_plan** plan, const void* in, const void* w, void* out, int N, int H,
+                        int W, int CI, int CO, int KH, int KW, int stride_h, int stride_w, int pad,
+                        int dil_h, int dil_w, hb_dtype in_a, hb_dtype in_w, hb_dtype out_t,
+                        const hb_knobs* knobs) {
+  return new_plan(plan, [&](hb_plan* p) {
+    return plan_conv(in, w, out, N, H, W, CI, CO, KH, KW, stride_h, stride_w, pad, dil_h, dil_w,
+                     in_a, in_w, out_t, knobs, p);
+  });
+}
+
+int hb_plan_conv2d_nhwc_packed(hb_plan** plan, const void* in, const void* w_packed, void* out,
+                               int N, int H, int W, int CI, int CO, int KH, int KW, int stride_h,
+                               int stride_w, int pad, int dil_h, int dil_w, int sco, void* scratch,
+                               size_t scratch_bytes, const hb_knobs* knobs) {
+  return new_plan(plan, [&](hb_plan* p) {
+    return plan_conv_packed(in, w_packed, out, N, H, W, CI, CO, KH, KW, stride_h, stride_w, pad,
+                            dil_h, dil_w, sco, scratch, scratch_bytes, knobs, p);
+  });
+}
+
+int hb_plan_launch(const hb_plan* plan, void* stream) {
+  if (!plan) return HB_ERR_SHAPE;
+  return run_plan(plan, static_cast<cudaStream_t>(stream));
+}
+
+int hb_plan_knobs(const hb_plan* plan, hb_knobs* knobs, int* grid, int* smem_bytes) {
+  if (!plan || !knobs) return HB_ERR_SHAPE;
+  *knobs = plan->knobs;
+  if (grid) *grid = plan->grid;
+  if (smem_bytes) *smem_bytes = plan->smem;
+  return HB_OK;
+}
+
+void hb_plan_destroy(hb_plan* plan) { delete plan; }
 
 int hb_last_status(int* status) {
   if (!status) return HB_ERR_SHAPE;

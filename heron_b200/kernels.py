@@ -141,3 +141,113 @@ def conv2d_nhwc_packed(x, w_packed, CO, KH, KW, stride=1, padding=0, dilation=1,
                                    _stream(x))
     _lib.check(rc, "hb_conv2d_nhwc_packed")
     return out
+
+
+class Plan:
+    """A launch-ready kernel bound to fixed buffers (hb_plan): build once, launch many times.
+
+    Keeps references to the tensors it was built on so that their memory outlives the plan.
+    """
+
+    def __init__(self, handle, tensors, out):
+        self._handle = handle
+        self._tensors = tensors
+        self.out = out
+
+    def launch(self, stream=None):
+        if stream is None:
+            stream = torch.cuda.current_stream(self.out.device).cuda_stream
+        _lib.check(_lib.load().hb_plan_launch(self._handle, ctypes.c_void_p(stream)), "hb_plan_launch")
+        return self.out
+
+    __call__ = launch
+
+    def knobs(self):
+        """Resolved knobs plus the persistent grid size and dynamic shared memory of the launch."""
+        k = _lib.HbKnobs()
+        grid, smem = ctypes.c_int(0), ctypes.c_int(0)
+        _lib.check(_lib.load().hb_plan_knobs(self._handle, ctypes.byref(k), ctypes.byref(grid),
+                                             ctypes.byref(smem)), "hb_plan_knobs")
+        d = k.to_dict()
+        d["grid"], d["smem_bytes"] = grid.value, smem.value
+        return d
+
+    def close(self):
+        if self._handle is not None:
+            _lib.load().hb_plan_destroy(self._handle)
+            self._handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def plan_gemm(a, b, out=None, out_dtype=None, knobs=None):
+    M, K = a.shape
+    N, K2 = b.shape
+    if K != K2:
+        raise ValueError("a is (M,K), b is (N,K): K differs")
+    if out is None:
+        out = torch.empty((M, N), dtype=out_dtype or default_out_dtype(a.dtype), device=a.device)
+    h = ctypes.c_void_p()
+    rc = _lib.load().hb_plan_gemm(ctypes.byref(h), _dev(a, "a"), _dev(b, "b"), _dev(out, "out"), M,
+                                  K, N, _code(a), _code(b), _code(out), _knobs(knobs))
+    _lib.check(rc, "hb_plan_gemm")
+    return Plan(h, (a, b), out)
+
+
+def plan_bmm(a, b, out=None, out_dtype=None, knobs=None):
+    B, M, K = a.shape
+    B2, N, K2 = b.shape
+    if K != K2 or B != B2:
+        raise ValueError("a is (B,M,K), b is (B,N,K): shapes differ")
+    if out is None:
+        out = torch.empty((B, M, N), dtype=out_dtype or default_out_dtype(a.dtype), device=a.device)
+    h = ctypes.c_void_p()
+    rc = _lib.load().hb_plan_bmm(ctypes.byref(h), _dev(a, "a"), _dev(b, "b"), _dev(out, "out"), B,
+                                 M, K, N, _code(a), _code(b), _code(out), _knobs(knobs))
+    _lib.check(rc, "hb_plan_bmm")
+    return Plan(h, (a, b), out)
+
+
+def plan_conv2d_nhwc(x, w, stride=1, padding=0, dilation=1, out=None, out_dtype=None, knobs=None):
+    N, H, W, CI = x.shape
+    KH, KW, CI2, CO = w.shape
+    if CI != CI2:
+        raise ValueError("input channels of x and w differ")
+    sh, sw = _pair(stride)
+    dh, dw = _pair(dilation)
+    HO, WO = conv_out_hw(H, W, KH, KW, stride, padding, dilation)
+    if out is None:
+        out = torch.empty((N, HO, WO, CO), dtype=out_dtype or default_out_dtype(x.dtype),
+                          device=x.device)
+    h = ctypes.c_void_p()
+    rc = _lib.load().hb_plan_conv2d_nhwc(ctypes.byref(h), _dev(x, "x"), _dev(w, "w"),
+                                         _dev(out, "out"), N, H, W, CI, CO, KH, KW, sh, sw,
+                                         int(padding), dh, dw, _code(x), _code(w), _code(out),
+                                         _knobs(knobs))
+    _lib.check(rc, "hb_plan_conv2d_nhwc")
+    return Plan(h, (x, w), out)
+
+
+def plan_conv2d_nhwc_packed(x, w_packed, CO, KH, KW, stride=1, padding=0, dilation=1, sco=64,
+                            out=None, scratch=None, knobs=None):
+    N, H, W, CI = x.shape
+    sh, sw = _pair(stride)
+    dh, dw = _pair(dilation)
+    HO, WO = conv_out_hw(H, W, KH, KW, stride, padding, dilation)
+    lib = _lib.load()
+    if scratch is None:
+        scratch = torch.empty(lib.hb_conv2d_packed_scratch_bytes(CI, CO, KH, KW), dtype=torch.int8,
+                              device=x.device)
+    if out is None:
+        out = torch.empty((N, HO, WO, CO // sco, sco), dtype=torch.int32, device=x.device)
+    h = ctypes.c_void_p()
+    rc = lib.hb_plan_conv2d_nhwc_packed(ctypes.byref(h), _dev(x, "x"), _dev(w_packed, "w_packed"),
+                                        _dev(out, "out"), N, H, W, CI, CO, KH, KW, sh, sw,
+                                        int(padding), dh, dw, int(sco), _dev(scratch, "scratch"),
+                                        scratch.numel(), _knobs(knobs))
+    _lib.check(rc, "hb_plan_conv2d_nhwc_packed")
+    return Plan(h, (x, w_packed, scratch), out)

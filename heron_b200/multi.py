@@ -1,0 +1,115 @@
+"""multi.py — two things under the reference's module name.
+
+1. ``Job``: the reference's helper that runs a function in a forked child with a timeout and
+   kills the child's process tree afterwards (multi.py:11-49); the tuners use it for sampling.
+2. The batch-parallel partitioner that the B200 build adds: batched GEMM shards its batch and
+   NHWC conv shards its images over the GPUs of one box, one process per GPU.  Shards are
+   independent (no exchange during compute); where a caller wants the whole output, every rank's
+   kernel writes its shard straight into its slice of a full-size buffer and one in-place
+   all-gather over that buffer (NCCL over NVLink, or gloo on CPU ranks) completes it.
+"""
+import multiprocessing as _multi
+import signal
+
+multi = _multi.get_context("fork")
+
+
+class Job:
+    def __init__(self, func, attach_info, timeout=10):
+        self.func = func
+        self.attach_info = attach_info
+        self.timeout = timeout
+
+    def start(self, inputs):
+        self.queue = multi.Queue(2)
+        self.process = multi.Process(target=exec, args=(self.func, self.queue, inputs))
+        self.process.start()
+
+    def get(self):
+        try:
+            res = self.queue.get(block=True, timeout=self.timeout)
+        except Exception:
+            res = 0
+        if self.process.is_alive():
+            kill_child_processes(self.process.pid)
+            self.process.terminate()
+        self.process.join()
+        self.queue.close()
+        self.queue.join_thread()
+        del self.process
+        del self.queue
+        return res
+
+
+def exec(func, queue, args):
+    queue.put(func(*args))
+
+
+def kill_child_processes(parent_pid, sig=signal.SIGTERM):
+    import psutil
+    try:
+        parent = psutil.Process(parent_pid)
+    except psutil.NoSuchProcess:
+        return
+    for process in parent.children(recursive=True):
+        try:
+            process.send_signal(sig)
+        except psutil.NoSuchProcess:
+            return
+
+
+# ---- batch-parallel partitioning --------------------------------------------------------------
+
+# Position of the sharded leading dimension in each operator's case arguments
+# (gemm [M,K,N] does not shard; bmm [batch,M,K,N]; conv [N,H,W,CI,CO,KH,KW,stride,pad,dil,...]).
+SHARD_ARG = {"bmm": 0, "c2d_nhwc": 0, "c2d": 0}
+
+
+def partition(extent, world):
+    """Contiguous split of ``extent`` units over ``world`` ranks: [(start, count)] per rank.
+    The first ``extent % world`` ranks get one extra unit."""
+    if world <= 0 or extent < 0:
+        raise ValueError("need world > 0 and extent >= 0")
+    base, extra = divmod(extent, world)
+    out, start = [], 0
+    for r in range(world):
+        cnt = base + (1 if r < extra else 0)
+        out.append((start, cnt))
+        start += cnt
+    return out
+
+
+def shard_case(op_name, case_args, rank, world):
+    """Case arguments of rank ``rank``'s shard, plus (start, count) of its units."""
+    if op_name not in SHARD_ARG:
+        raise ValueError("operator %r has no batch-like dimension to shard: run replicas" % op_name)
+    pos = SHARD_ARG[op_name]
+    start, count = partition(int(case_args[pos]), world)[rank]
+    args = list(case_args)
+    args[pos] = count
+    return args, (start, count)
+
+
+def shard_slice(full, rank, world):
+    """View of rank ``rank``'s slice of a tensor whose leading dimension is the sharded one."""
+    start, count = partition(full.shape[0], world)[rank]
+    return full[start:start + count]
+
+
+def gather_output(full, rank, world, group=None):
+    """Completes ``full`` on every rank: each rank has already written its own slice.
+
+    Equal shards use one in-place ``all_gather_into_tensor``; ragged shards (extent not a
+    multiple of world) fall back to one broadcast per rank.  No copy precedes the collective.
+    """
+    import torch.distributed as dist
+    parts = partition(full.shape[0], world)
+    if world == 1:
+        return full
+    if len({c for _, c in parts}) == 1:
+        dist.all_gather_into_tensor(full, shard_slice(full, rank, world), group=group)
+    else:
+        for r, (start, count) in enumerate(parts):
+            if count:
+                dist.broadcast(full[start:start + count], src=r, group=group)
+    return full

@@ -1,0 +1,2 @@
+from .measure_methods import (MeasureErrorNo, MeasureResult, measure_handle, perf_from_cost, reduce_costs,
+                              time_launches)

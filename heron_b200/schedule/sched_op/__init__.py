@@ -1,0 +1,184 @@
+"""Schedule rules of the B200 kernel family.
+
+The reference walks a TVM schedule with rules that each apply a primitive *and* register the
+knobs / constraints it implies (schedule/sched_op/gpu_tensorcore_operator.py:362-414,
+schedule/primitives.py:5-37).  The rules here do the second half for the hand-written kernels:
+every rule declares the knobs it owns and the constraints that tie them to the SM's limits, and
+when a solved point is replayed (``Task.instantiate``) reads the values back into
+``ctx.kernel_knobs``, from which the kernel is launched.
+"""
+from ...utils import genKey
+from ..constraints.primitives import EQ
+
+ELEM_BYTES = {"float16": 2, "float32": 4, "int8": 1, "uint8": 1, "int32": 4}
+
+
+class SchedOp:
+    def __init__(self, name):
+        self.name = name
+
+    def perform(self, s, stage_name, ctx):
+        raise NotImplementedError
+
+
+def _problem(s, stage_name):
+    for out in s.outputs:
+        if out.op.name == stage_name:
+            return out
+    raise KeyError(stage_name)
+
+
+def _gemm_view(out):
+    """(batch, M, N, K, k_inner) of the operator's implicit GEMM."""
+    p = out.op.params
+    if out.op.kind == "gemm":
+        return 1, p["M"], p["N"], p["K"], p["K"]
+    if out.op.kind == "bmm":
+        return p["batch"], p["M"], p["N"], p["K"], p["K"]
+    N, HO, WO = out.shape[0], out.shape[1], out.shape[2]
+    return 1, N * HO * WO, p["CO"], p["KH"] * p["KW"] * p["CI"], p["CI"]
+
+
+class tileOp(SchedOp):
+    """Accumulator tile: 128 x tile_n, and the K extent of a ring stage (= TMA swizzle span)."""
+
+    def perform(self, s, stage_name, ctx):
+        km = ctx.knob_manager
+        out = _problem(s, stage_name)
+        p = out.op.params
+        es, eo = ELEM_BYTES[p["in_dtype"]], ELEM_BYTES[p["out_dtype"]]
+        _, M, N, K, k_inner = _gemm_view(out)
+        conv = out.op.kind.startswith("conv")
+        tile_n = genKey("P", stage_name, "n", param_name="tile_n")
+        swz = genKey("P", stage_name, "k", param_name="swizzle_bytes")
+        a_bytes = genKey("V", stage_name, "m", var_name="a_stage_bytes")
+        b_bytes = genKey("V", stage_name, "n", var_name="b_stage_bytes")
+        stage_bytes = genKey("V", stage_name, "k", var_name="stage_bytes")
+        if km.is_building:
+            step = 64 if eo == 2 else 32
+            # Swizzle spans the kernel accepts for this shape: conv blocks must not straddle
+            # two filter taps, so the span has to divide the channel bytes.
+            spans = [sw for sw in (32, 64, 128) if not conv or (k_inner * es) % sw == 0]
+            if not conv and K * es < 128:
+                spans = [sw for sw in spans if sw <= max(32, 1 << ((K * es - 1).bit_length()))] or [32]
+            gran = step
+            if conv:
+                gran = max(step, min(spans) // es)
+            n_cands = [n for n in range(gran, 257, gran)]
+            km.define_value(tile_n, min(n_cands), max(n_cands), n_cands[-1], True)
+            km.addCandidates(tile_n, n_cands)
+            km.define_value(swz, min(spans), max(spans), max(spans), True)
+            km.addCandidates(swz, spans)
+            lim = ctx.limits["max_shared_memory_per_block"]
+            km.define_value(a_bytes, 1, lim, ctx.limits["tile_m"] * max(spans))
+            km.define_value(b_bytes, 1, lim, n_cands[-1] * max(spans))
+            km.define_value(stage_bytes, 1, lim, (ctx.limits["tile_m"] + n_cands[-1]) * max(spans))
+            km.addProd([ctx.limits["tile_m"], swz], a_bytes)
+            km.addProd([tile_n, swz], b_bytes)
+            km.addSUM(stage_bytes, [a_bytes, b_bytes])
+            if conv:
+                # MN-major filter tiles come in whole swizzle spans of output channels.
+                chunk = genKey("V", stage_name, "n", var_name="b_chunk_bytes")
+                nchunk = genKey("V", stage_name, "n", var_name="b_chunks")
+                km.define_value(chunk, 1, 256 * es, 256 * es)
+                km.define_value(nchunk, 1, 256, 1)
+                km.addProd([tile_n, es], chunk)
+                km.addProd([nchunk, swz], chunk)
+        ctx.kernel_knobs["tile_n"] = km.get_val(tile_n)
+        ctx.kernel_knobs["swizzle_bytes"] = km.get_val(swz)
+        ctx.addSchedDesc("\n## tile 128 x %s, %s bytes of K per stage\n"
+                         % (ctx.kernel_knobs["tile_n"], ctx.kernel_knobs["swizzle_bytes"]))
+
+
+class pipelineOp(SchedOp):
+    """Depth of the TMA -> MMA ring and number of TMEM accumulator buffers."""
+
+    def perform(self, s, stage_name, ctx):
+        km = ctx.knob_manager
+        stages = genKey("P", stage_name, "k", param_name="stages")
+        acc = genKey("P", stage_name, "n", param_name="acc_stages")
+        ring = genKey("V", stage_name, "k", var_name="ring_bytes")
+        cols = genKey("V", stage_name, "n", var_name="tmem_columns")
+        tile_n = genKey("P", stage_name, "n", param_name="tile_n")
+        stage_bytes = genKey("V", stage_name, "k", var_name="stage_bytes")
+        if km.is_building:
+            lim = ctx.limits["max_shared_memory_per_block"]
+            km.define_value(stages, 1, ctx.limits["max_stages"], 4, True)
+            km.define_value(acc, 1, 2, 2, True)
+            km.define_value(ring, 1, lim, lim)
+            km.define_value(cols, 1, ctx.limits["tmem_columns"], ctx.limits["tmem_columns"])
+            km.addProd([stages, stage_bytes], ring)
+            km.addProd([acc, tile_n], cols)
+        ctx.kernel_knobs["stages"] = km.get_val(stages)
+        ctx.kernel_knobs["acc_stages"] = km.get_val(acc)
+        ctx.addSchedDesc("## ring of %s stages, %s accumulator buffers\n"
+                         % (ctx.kernel_knobs["stages"], ctx.kernel_knobs["acc_stages"]))
+
+
+class epilogueOp(SchedOp):
+    """Accumulator write-back path and the shared-memory total it leaves for the ring."""
+
+    def perform(self, s, stage_name, ctx):
+        km = ctx.knob_manager
+        out = _problem(s, stage_name)
+        p = out.op.params
+        eo = ELEM_BYTES[p["out_dtype"]]
+        _, M, N, K, _ = _gemm_view(out)
+        epi = genKey("P", stage_name, "n", param_name="epilogue")
+        epi_bytes = genKey("V", stage_name, "n", var_name="epilogue_bytes")
+        smem = genKey("V", stage_name, "k", var_name="shared_mem_size")
+        ring = genKey("V", stage_name, "k", var_name="ring_bytes")
+        if km.is_building:
+            lim = ctx.limits["max_shared_memory_per_block"]
+            # 1: shared-memory staging + TMA store (needs 16-byte output rows); 2: direct stores.
+            modes = [1, 2] if (N * eo) % 16 == 0 else [2]
+            km.define_value(epi, min(modes), max(modes), modes[0], True)
+            km.addCandidates(epi, modes)
+            km.define_value(epi_bytes, 0, ctx.limits["epilogue_staging_bytes"], 0)
+            staging = [ctx.limits["epilogue_staging_bytes"], 0]
+            for idx, mode in enumerate(modes):
+                cond = (epi + "_cand%d" % idx).replace("P#", "O#")
+                km.solver.primitives.append(EQ([epi_bytes, staging[mode - 1]], cond=cond))
+            km.define_value(smem, 1, lim, lim)
+            km.addSUM(smem, [ring, epi_bytes, ctx.limits["smem_slack_bytes"]])
+            if smem not in km.mems:
+                km.mems.append(smem)
+        ctx.kernel_knobs["epilogue"] = km.get_val(epi)
+        ctx.addSchedDesc("## epilogue mode %s\n" % ctx.kernel_knobs["epilogue"])
+
+
+class rasterOp(SchedOp):
+    """Order in which the persistent CTAs walk the tile grid."""
+
+    def perform(self, s, stage_name, ctx):
+        km = ctx.knob_manager
+        raster = genKey("P", stage_name, "m", param_name="raster")
+        if km.is_building:
+            km.define_value(raster, 0, 1, 0, True)
+        ctx.kernel_knobs["raster"] = km.get_val(raster)
+        ctx.addSchedDesc("## raster %s\n" % ctx.kernel_knobs["raster"])
+
+
+_METHODS = {
+    "tileOp": tileOp,
+    "pipelineOp": pipelineOp,
+    "epilogueOp": epilogueOp,
+    "rasterOp": rasterOp,
+}
+
+
+def get_op_methods(_type):
+    """Rule table of a code-generation type (schedule/sched_op/__init__.py:12-21).  Both targets on
+    the hot path launch the same kernel family, so they share one table."""
+    if _type in ("GPU_TENSOR_CORE", "CPU"):
+        return _METHODS
+    raise ValueError("Unsupportted code gen type %s" % _type)
+
+
+def sched_via_rule(_type, ctx, s):
+    """Applies every rule to every output stage, recording (rule, stage) on the knob manager so
+    that ``Task.instantiate`` can replay them (schedule/sched_op/__init__.py:23-30)."""
+    get_op_methods(_type)
+    for out in s.outputs:
+        for rule in ("tileOp", "pipelineOp", "epilogueOp", "rasterOp"):
+            ctx.addSched(rule, out.op.name, s)

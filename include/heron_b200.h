@@ -126,6 +126,32 @@ int hb_conv2d_nhwc_packed(const void* in, const void* w_packed, void* out, int N
                           const hb_knobs* knobs, void* stream);
 
 /*
+ * Plans.  A plan is what the reference gets back from tvm.build on an instantiated schedule
+ * (tests/quick_start/dlboost/run.py:44-46) and then calls many times under time_evaluator
+ * (run.py:60-62): the encoded TMA tensor maps, the resolved knobs and the launch geometry for one
+ * problem on fixed buffers.  Creating one costs three tensor-map encodings on the host and no
+ * device work; hb_plan_launch only enqueues the kernel(s) and may be captured in a CUDA graph.
+ * The argument lists are those of the immediate entry points above minus the stream.
+ */
+typedef struct hb_plan hb_plan;
+int hb_plan_gemm(hb_plan** plan, const void* A, const void* B, void* C, int M, int K, int N,
+                 hb_dtype in_a, hb_dtype in_b, hb_dtype out, const hb_knobs* knobs);
+int hb_plan_bmm(hb_plan** plan, const void* A, const void* B, void* C, int batch, int M, int K,
+                int N, hb_dtype in_a, hb_dtype in_b, hb_dtype out, const hb_knobs* knobs);
+int hb_plan_conv2d_nhwc(hb_plan** plan, const void* in, const void* w, void* out, int N, int H,
+                        int W, int CI, int CO, int KH, int KW, int stride_h, int stride_w, int pad,
+                        int dil_h, int dil_w, hb_dtype in_a, hb_dtype in_w, hb_dtype out_t,
+                        const hb_knobs* knobs);
+int hb_plan_conv2d_nhwc_packed(hb_plan** plan, const void* in, const void* w_packed, void* out,
+                               int N, int H, int W, int CI, int CO, int KH, int KW, int stride_h,
+                               int stride_w, int pad, int dil_h, int dil_w, int sco, void* scratch,
+                               size_t scratch_bytes, const hb_knobs* knobs);
+int hb_plan_launch(const hb_plan* plan, void* stream);
+/* The knobs after defaults were resolved, the persistent grid and the dynamic shared memory. */
+int hb_plan_knobs(const hb_plan* plan, hb_knobs* knobs, int* grid, int* smem_bytes);
+void hb_plan_destroy(hb_plan* plan);
+
+/*
  * Device-side status of the kernels launched so far on the current device: synchronises the
  * device, copies the status word (HB_OK or HB_ERR_TIMEOUT) to *status and clears it.  A bounded
  * wait that ran out leaves the output undefined but the context usable.  Stands in for the

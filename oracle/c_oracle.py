@@ -1,0 +1,129 @@
+"""ctypes front end of heron_oracle.c (numpy arrays in, numpy arrays out).  TEST INFRASTRUCTURE ONLY."""
+import ctypes
+import os
+
+import numpy as np
+
+from . import build as _build
+
+_lib = None
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        if not os.path.exists(_build.ORACLE_SO):
+            _build.build()
+        _lib = ctypes.CDLL(_build.ORACLE_SO)
+        _lib.oracle_half_to_float.restype = ctypes.c_float
+        _lib.oracle_half_to_float.argtypes = [ctypes.c_uint16]
+        _lib.oracle_float_to_half.restype = ctypes.c_uint16
+        _lib.oracle_float_to_half.argtypes = [ctypes.c_float]
+    return _lib
+
+
+def _p(a):
+    return a.ctypes.data_as(ctypes.c_void_p)
+
+
+def _signed(a):
+    if a.dtype == np.int8:
+        return 1
+    if a.dtype == np.uint8:
+        return 0
+    raise TypeError("expected uint8 / int8, got %s" % a.dtype)
+
+
+def _c(a):
+    return np.ascontiguousarray(a)
+
+
+def gemm_int(a, b):
+    a, b = _c(a), _c(b)
+    M, K = a.shape
+    N = b.shape[0]
+    out = np.empty((M, N), dtype=np.int32)
+    lib().oracle_gemm_i8(_p(a), _p(b), _p(out), M, K, N, _signed(a), _signed(b))
+    return out
+
+
+def bmm_int(a, b):
+    a, b = _c(a), _c(b)
+    B, M, K = a.shape
+    N = b.shape[1]
+    out = np.empty((B, M, N), dtype=np.int32)
+    lib().oracle_bmm_i8(_p(a), _p(b), _p(out), B, M, K, N, _signed(a), _signed(b))
+    return out
+
+
+def gemm_f16(a, b):
+    a, b = _c(a), _c(b)
+    assert a.dtype == np.float16 and b.dtype == np.float16
+    M, K = a.shape
+    N = b.shape[0]
+    out = np.empty((M, N), dtype=np.float32)
+    lib().oracle_gemm_f16(_p(a), _p(b), _p(out), M, K, N)
+    return out
+
+
+def bmm_f16(a, b):
+    a, b = _c(a), _c(b)
+    B, M, K = a.shape
+    N = b.shape[1]
+    out = np.empty((B, M, N), dtype=np.float32)
+    lib().oracle_bmm_f16(_p(a), _p(b), _p(out), B, M, K, N)
+    return out
+
+
+def _pair(v):
+    return (v, v) if isinstance(v, int) else (int(v[0]), int(v[1]))
+
+
+def _out_hw(H, W, KH, KW, stride, pad, dilation):
+    sh, sw = _pair(stride)
+    dh, dw = _pair(dilation)
+    L = lib()
+    return (L.oracle_conv_out_extent(H, KH, sh, pad, dh), L.oracle_conv_out_extent(W, KW, sw, pad, dw))
+
+
+def conv2d_nhwc_int(x, w, stride=1, pad=0, dilation=1):
+    x, w = _c(x), _c(w)
+    N, H, W, CI = x.shape
+    KH, KW, _, CO = w.shape
+    sh, sw = _pair(stride)
+    dh, dw = _pair(dilation)
+    HO, WO = _out_hw(H, W, KH, KW, stride, pad, dilation)
+    out = np.empty((N, HO, WO, CO), dtype=np.int32)
+    lib().oracle_conv2d_nhwc_i8(_p(x), _p(w), _p(out), N, H, W, CI, CO, KH, KW, sh, sw, pad, dh, dw,
+                                _signed(x), _signed(w))
+    return out
+
+
+def conv2d_nhwc_f16(x, w, stride=1, pad=0, dilation=1, out_dtype=np.float32):
+    x, w = _c(x), _c(w)
+    assert x.dtype == np.float16 and w.dtype == np.float16
+    N, H, W, CI = x.shape
+    KH, KW, _, CO = w.shape
+    sh, sw = _pair(stride)
+    dh, dw = _pair(dilation)
+    HO, WO = _out_hw(H, W, KH, KW, stride, pad, dilation)
+    half = np.dtype(out_dtype) == np.float16
+    out = np.empty((N, HO, WO, CO), dtype=np.float16 if half else np.float32)
+    lib().oracle_conv2d_nhwc_f16(_p(x), _p(w), _p(out), N, H, W, CI, CO, KH, KW, sh, sw, pad, dh, dw,
+                                 1 if half else 0)
+    return out
+
+
+def conv2d_nhwc_packed(x, w_packed, stride=1, pad=0, dilation=1):
+    x, w_packed = _c(x), _c(w_packed)
+    assert x.dtype == np.uint8 and w_packed.dtype == np.int8
+    N, H, W, CI = x.shape
+    OC, KH, KW, IC, sco, sci = w_packed.shape
+    assert sci == 4 and IC * 4 == CI
+    sh, sw = _pair(stride)
+    dh, dw = _pair(dilation)
+    HO, WO = _out_hw(H, W, KH, KW, stride, pad, dilation)
+    out = np.empty((N, HO, WO, OC, sco), dtype=np.int32)
+    lib().oracle_conv2d_nhwc_packed(_p(x), _p(w_packed), _p(out), N, H, W, CI, OC * sco, KH, KW, sh,
+                                    sw, pad, dh, dw, sco)
+    return out

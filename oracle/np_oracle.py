@@ -1,0 +1,115 @@
+"""numpy restatement of the reference's operator math.  TEST INFRASTRUCTURE ONLY.
+
+PARITY UNPINNED: the reference ships no golden tensor values for these operators and cannot run
+in this environment (it needs Apache TVM, un-vendored and un-pinned); what this file follows is
+the arithmetic of the reference's ``te.compute`` bodies, cited per function.  It exists beside the
+C restatement (heron_oracle.c) so that the two, written independently in different styles
+(vectorised matmul / explicit im2col here, scalar loops there), can be checked against each other.
+
+Integer results are exact int32 (computed in int64, checked to fit); fp16 inputs are widened to
+float64 and accumulated there.
+"""
+import numpy as np
+
+
+def _as_i64(x):
+    if x.dtype not in (np.uint8, np.int8):
+        raise TypeError("integer oracle takes uint8 / int8 operands, got %s" % x.dtype)
+    return x.astype(np.int64)
+
+
+def _to_i32(acc):
+    if acc.size and (acc.max() > np.iinfo(np.int32).max or acc.min() < np.iinfo(np.int32).min):
+        raise OverflowError("sum leaves int32: the reference's int32 accumulation would wrap")
+    return acc.astype(np.int32)
+
+
+def gemm_int(a, b):
+    """out[i,j] = sum_k int32(a[i,k]) * int32(b[j,k]); ops/x86/dense.py:14-18, ops/cuda/dense.py:12-17."""
+    return _to_i32(_as_i64(a) @ _as_i64(b).T)
+
+
+def bmm_int(a, b):
+    """out[n,i,j] = sum_k a[n,i,k] * b[n,j,k]; ops/x86/batch_matmul.py:15-20."""
+    return _to_i32(np.einsum("bik,bjk->bij", _as_i64(a), _as_i64(b)))
+
+
+def gemm_f16(a, b):
+    """fp16 operands (B is (N,K)), float64 accumulation, float32 result; ops/cuda/dense.py:12-17."""
+    assert a.dtype == np.float16 and b.dtype == np.float16
+    return (a.astype(np.float64) @ b.astype(np.float64).T).astype(np.float32)
+
+
+def bmm_f16(a, b):
+    """ops/cuda/batch_matmul.py:14-19 with fp16 operands."""
+    assert a.dtype == np.float16 and b.dtype == np.float16
+    return np.einsum("bik,bjk->bij", a.astype(np.float64), b.astype(np.float64)).astype(np.float32)
+
+
+def _pair(v):
+    return (v, v) if isinstance(v, int) else (int(v[0]), int(v[1]))
+
+
+def conv_out_extent(size, k, stride, pad, dil):
+    """(size - dilated_k + 2*pad) // stride + 1; ops/cuda/conv2d.py:165-175."""
+    return (size - ((k - 1) * dil + 1) + 2 * pad) // stride + 1
+
+
+def _im2col(x, KH, KW, stride, pad, dilation):
+    """(N,H,W,C) -> (N*HO*WO, KH*KW*C) with K ordered (ry, rx, rc) as the reference reduces."""
+    sh, sw = _pair(stride)
+    dh, dw = _pair(dilation)
+    N, H, W, C = x.shape
+    HO = conv_out_extent(H, KH, sh, pad, dh)
+    WO = conv_out_extent(W, KW, sw, pad, dw)
+    xp = np.zeros((N, H + 2 * pad, W + 2 * pad, C), dtype=x.dtype)
+    xp[:, pad:pad + H, pad:pad + W, :] = x
+    cols = np.empty((N, HO, WO, KH, KW, C), dtype=x.dtype)
+    for ry in range(KH):
+        for rx in range(KW):
+            cols[:, :, :, ry, rx, :] = xp[:, ry * dh: ry * dh + (HO - 1) * sh + 1: sh,
+                                          rx * dw: rx * dw + (WO - 1) * sw + 1: sw, :]
+    return cols.reshape(N * HO * WO, KH * KW * C), (N, HO, WO)
+
+
+def conv2d_nhwc_int(x, w, stride=1, pad=0, dilation=1):
+    """uint8/int8 NHWC input, HWIO filter, int32 output; ops/cuda/conv2d.py:168-196."""
+    KH, KW, CI, CO = w.shape
+    cols, (N, HO, WO) = _im2col(x, KH, KW, stride, pad, dilation)
+    out = _as_i64(cols) @ _as_i64(w).reshape(KH * KW * CI, CO)
+    return _to_i32(out).reshape(N, HO, WO, CO)
+
+
+def conv2d_nhwc_f16(x, w, stride=1, pad=0, dilation=1, out_dtype=np.float32):
+    """fp16 NHWC conv with float64 accumulation; rounded to float32, then to fp16 if asked."""
+    assert x.dtype == np.float16 and w.dtype == np.float16
+    KH, KW, CI, CO = w.shape
+    cols, (N, HO, WO) = _im2col(x, KH, KW, stride, pad, dilation)
+    out = cols.astype(np.float64) @ w.astype(np.float64).reshape(KH * KW * CI, CO)
+    out = out.astype(np.float32).reshape(N, HO, WO, CO)
+    return out.astype(np.float16) if np.dtype(out_dtype) == np.float16 else out
+
+
+def pack_filter_x86(w_hwio, sco=64, sci=4):
+    """HWIO int8 filter -> the x86 operator's (CO/sco, KH, KW, CI/sci, sco, sci) layout
+    (ops/x86/conv2d_int8.py:36-50)."""
+    KH, KW, CI, CO = w_hwio.shape
+    assert CO % sco == 0 and CI % sci == 0
+    w = w_hwio.reshape(KH, KW, CI // sci, sci, CO // sco, sco)
+    return np.ascontiguousarray(w.transpose(4, 0, 1, 2, 5, 3))
+
+
+def unpack_filter_x86(w_packed):
+    """Inverse of pack_filter_x86."""
+    OC, KH, KW, IC, sco, sci = w_packed.shape
+    w = w_packed.transpose(1, 2, 3, 5, 0, 4)
+    return np.ascontiguousarray(w.reshape(KH, KW, IC * sci, OC * sco))
+
+
+def conv2d_nhwc_packed(x, w_packed, stride=1, pad=0, dilation=1):
+    """The x86 operator: uint8 input, packed int8 filter, int32 output (N,HO,WO,CO/sco,sco);
+    ops/x86/conv2d_int8.py:74-93."""
+    OC, KH, KW, IC, sco, sci = w_packed.shape
+    out = conv2d_nhwc_int(x, unpack_filter_x86(w_packed), stride, pad, dilation)
+    N, HO, WO, CO = out.shape
+    return out.reshape(N, HO, WO, OC, sco)

@@ -1,0 +1,47 @@
+"""Loader of tests/golden/kat.npz (see tests/golden/make_golden.py for what the cases are)."""
+import os
+
+import numpy as np
+
+_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "kat.npz")
+
+
+def load_cases():
+    data = np.load(_PATH)
+    cases = {}
+    for key in data.files:
+        name, field = key.split("/")
+        cases.setdefault(name, {})[field] = data[key]
+    for case in cases.values():
+        for f in ("stride", "pad", "dil"):
+            if f in case:
+                case[f] = int(case[f])
+    return cases
+
+
+def run_case(name, case, gemm_int, bmm_int, gemm_f16, conv_int, conv_f16, conv_packed):
+    """Dispatches a golden case to an implementation's functions and returns its output."""
+    if name.startswith("gemm_f16"):
+        return gemm_f16(case["a"], case["b"])
+    if name.startswith("gemm"):
+        return gemm_int(case["a"], case["b"])
+    if name.startswith("bmm"):
+        return bmm_int(case["a"], case["b"])
+    if name.startswith("conv_packed"):
+        return conv_packed(case["x"], case["w"], case["stride"], case["pad"], case["dil"])
+    if name.startswith("conv_f16"):
+        return conv_f16(case["x"], case["w"], case["stride"], case["pad"], case["dil"], case["out"].dtype)
+    return conv_int(case["x"], case["w"], case["stride"], case["pad"], case["dil"])
+
+
+def assert_matches(name, got, want):
+    """Bit-exact for integers and for fp16 outputs of exactly representable sums; 1e-2 of the
+    largest magnitude for floating point (the benchmark's stated tolerance)."""
+    assert got.shape == want.shape, name
+    if want.dtype.kind in "iu":
+        assert got.dtype == want.dtype, name
+        assert np.array_equal(got, want), name
+    else:
+        scale = max(float(np.abs(want.astype(np.float64)).max()), 1e-30)
+        err = float(np.abs(got.astype(np.float64) - want.astype(np.float64)).max()) / scale
+        assert err <= 1e-2, (name, err)

@@ -1,0 +1,126 @@
+"""The C ABI on a machine without a GPU: the library loads, exports every symbol the header
+declares, answers the host-only queries, and refuses to compute (no CPU fallback)."""
+import ctypes
+import os
+import re
+
+import numpy as np
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def header_symbols():
+    text = open(os.path.join(ROOT, "include", "heron_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(hb_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_exports_match_header(hb_lib):
+    from heron_b200 import _lib
+    declared = header_symbols()
+    assert declared, "no declarations found in include/heron_b200.h"
+    assert sorted(_lib.EXPORTED_SYMBOLS) == declared
+    for name in declared:
+        assert hasattr(hb_lib, name), name
+
+
+def test_version_and_status_strings(hb_lib):
+    from heron_b200 import _lib
+    assert hb_lib.hb_version() >= 100
+    for code in range(0, 9):
+        assert _lib.status_string(code)
+    assert "unknown" in _lib.status_string(99)
+
+
+def test_default_knobs_are_inside_the_space(hb_lib):
+    from heron_b200 import _lib
+    cases = [
+        (0, 1, 64, 64, 64, 64, _lib.HB_U8, _lib.HB_S32),
+        (0, 1, 4096, 4096, 4096, 4096, _lib.HB_F16, _lib.HB_F32),
+        (1, 192, 512, 512, 64, 64, _lib.HB_S8, _lib.HB_S32),
+        (2, 1, 100352, 64, 576, 64, _lib.HB_F16, _lib.HB_F16),
+        (2, 1, 50176, 512, 4608, 512, _lib.HB_U8, _lib.HB_S32),
+        (2, 1, 324, 64, 144, 16, _lib.HB_F16, _lib.HB_F32),
+    ]
+    for op, batch, M, N, K, kin, tin, tout in cases:
+        k = _lib.HbKnobs()
+        assert hb_lib.hb_default_knobs(op, batch, M, N, K, kin, tin, tout, ctypes.byref(k)) == 0
+        smem, cols = ctypes.c_int(0), ctypes.c_int(0)
+        rc = hb_lib.hb_check_knobs(op, batch, M, N, K, kin, tin, tout, ctypes.byref(k),
+                                   ctypes.byref(smem), ctypes.byref(cols))
+        assert rc == 0, (op, M, N, K, k.to_dict())
+        assert 0 < smem.value <= 232448 and cols.value in (32, 64, 128, 256, 512)
+    # the quoted configuration keeps the widest tile
+    k = _lib.HbKnobs()
+    hb_lib.hb_default_knobs(0, 1, 4096, 4096, 4096, 4096, _lib.HB_F16, _lib.HB_F32, ctypes.byref(k))
+    assert k.tile_n == 256 and k.swizzle_bytes == 128 and k.acc_stages == 2
+
+
+@pytest.mark.parametrize("bad", [
+    dict(tile_n=48), dict(tile_n=288), dict(stages=13), dict(swizzle_bytes=96),
+    dict(tile_n=256, stages=12), dict(acc_stages=3), dict(raster=2), dict(epilogue=3),
+])
+def test_check_knobs_rejects(hb_lib, bad):
+    from heron_b200 import _lib
+    k = _lib.HbKnobs.from_dict(bad)
+    rc = hb_lib.hb_check_knobs(0, 1, 4096, 4096, 4096, 4096, _lib.HB_F16, _lib.HB_F32, ctypes.byref(k), None, None)
+    assert rc == _lib.HB_ERR_KNOB
+
+
+def test_fp16_output_needs_64_column_tiles(hb_lib):
+    from heron_b200 import _lib
+    k = _lib.HbKnobs.from_dict(dict(tile_n=96))
+    assert hb_lib.hb_check_knobs(0, 1, 512, 512, 512, 512, _lib.HB_F16, _lib.HB_F16, ctypes.byref(k), None, None) == _lib.HB_ERR_KNOB
+    assert hb_lib.hb_check_knobs(0, 1, 512, 512, 512, 512, _lib.HB_F16, _lib.HB_F32, ctypes.byref(k), None, None) == 0
+
+
+def test_argument_errors_come_before_the_device(hb_lib):
+    """Shape / dtype / alignment errors are reported without touching a GPU."""
+    from heron_b200 import _lib
+    buf = np.zeros(4096, dtype=np.uint8)
+    p = ctypes.c_void_p(buf.ctypes.data & ~15)
+    assert hb_lib.hb_gemm(p, p, p, 0, 64, 64, _lib.HB_U8, _lib.HB_S8, _lib.HB_S32, None, None) == _lib.HB_ERR_SHAPE
+    assert hb_lib.hb_gemm(p, p, p, 64, 24, 64, _lib.HB_U8, _lib.HB_S8, _lib.HB_S32, None, None) == _lib.HB_ERR_SHAPE
+    assert hb_lib.hb_gemm(p, p, p, 64, 64, 64, _lib.HB_F16, _lib.HB_S8, _lib.HB_S32, None, None) == _lib.HB_ERR_DTYPE
+    assert hb_lib.hb_gemm(p, p, p, 64, 64, 64, _lib.HB_U8, _lib.HB_S8, _lib.HB_F32, None, None) == _lib.HB_ERR_DTYPE
+    odd = ctypes.c_void_p((buf.ctypes.data & ~15) + 8)
+    assert hb_lib.hb_gemm(odd, p, p, 64, 64, 64, _lib.HB_U8, _lib.HB_S8, _lib.HB_S32, None, None) == _lib.HB_ERR_ALIGN
+    assert hb_lib.hb_gemm(None, p, p, 64, 64, 64, _lib.HB_U8, _lib.HB_S8, _lib.HB_S32, None, None) == _lib.HB_ERR_ALIGN
+    # conv: channel bytes must be a multiple of 32, stride <= 8
+    args = [p, p, p, 1, 8, 8, 8, 16, 3, 3, 1, 1, 1, 1, 1, _lib.HB_F16, _lib.HB_F16, _lib.HB_F32, None, None]
+    assert hb_lib.hb_conv2d_nhwc(*args) == _lib.HB_ERR_SHAPE
+    args[6] = 16
+    args[10] = 9
+    assert hb_lib.hb_conv2d_nhwc(*args) == _lib.HB_ERR_SHAPE
+    # packed conv: scratch too small
+    rc = hb_lib.hb_conv2d_nhwc_packed(p, p, p, 1, 7, 7, 64, 64, 3, 3, 1, 1, 1, 1, 1, 64, p, 16, None, None)
+    assert rc == _lib.HB_ERR_SCRATCH
+    assert hb_lib.hb_conv2d_packed_scratch_bytes(64, 64, 3, 3) == 3 * 3 * 64 * 64
+
+
+def test_no_cpu_fallback(hb_lib):
+    """Without a usable sm_100 device a well-formed call reports HB_ERR_DEVICE instead of
+    computing anywhere else."""
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("a GPU is present; the refusal is what a CPU-only host shows")
+    from heron_b200 import _lib
+    buf = np.zeros(1 << 16, dtype=np.uint8)
+    p = ctypes.c_void_p((buf.ctypes.data + 15) & ~15)
+    assert hb_lib.hb_gemm(p, p, p, 64, 64, 64, _lib.HB_U8, _lib.HB_S8, _lib.HB_S32, None, None) == _lib.HB_ERR_DEVICE
+    assert hb_lib.hb_sm_count() == -_lib.HB_ERR_DEVICE
+    v = ctypes.c_int(0)
+    assert hb_lib.hb_last_status(ctypes.byref(v)) == _lib.HB_ERR_DEVICE
+    h = ctypes.c_void_p()
+    assert hb_lib.hb_plan_gemm(ctypes.byref(h), p, p, p, 64, 64, 64, _lib.HB_U8, _lib.HB_S8, _lib.HB_S32, None) == _lib.HB_ERR_DEVICE
+    assert not h.value
+
+
+def test_front_end_refuses_cpu_tensors(hb_lib):
+    import torch
+    from heron_b200 import kernels
+    a = torch.zeros(64, 64, dtype=torch.uint8)
+    b = torch.zeros(64, 64, dtype=torch.int8)
+    with pytest.raises(ValueError, match="no CPU path"):
+        kernels.gemm(a, b, out=torch.zeros(64, 64, dtype=torch.int32))

@@ -1,0 +1,363 @@
+"""Parity of the sm_100a kernels with the oracle, through the C ABI (ctypes), on a B200.
+
+Bit-exact for the integer paths; for fp16 inputs with fp32 accumulation the bound is a maximum
+error of 1e-2 relative to the largest magnitude of the oracle's output (the benchmark's stated
+tolerance) — observed errors are around 1e-6 (fp32 output) and 5e-4 (fp16 output).
+"""
+import random
+
+import numpy as np
+import pytest
+import torch
+
+from golden_util import assert_matches, load_cases, run_case
+from oracle import np_oracle as npo
+
+pytestmark = pytest.mark.gpu
+
+FP_TOL = 1e-2
+
+
+@pytest.fixture(scope="module")
+def K(hb_lib):
+    assert torch.cuda.is_available(), "GPU tests need a B200"
+    from heron_b200 import kernels
+    assert hb_lib.hb_sm_count() > 0, "libheron_b200.so found no sm_100 device"
+    return kernels
+
+
+@pytest.fixture(scope="module")
+def co(oracle_libs):
+    from oracle import c_oracle
+    return c_oracle
+
+
+@pytest.fixture(autouse=True)
+def _status_clean(hb_lib):
+    yield
+    from heron_b200 import _lib
+    assert _lib.last_status() == 0, "a bounded device-side wait ran out"
+
+
+def dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def poison(shape, dtype):
+    """Output buffers start as 0xCD bytes so that an unwritten tile cannot pass."""
+    t = torch.empty(shape, dtype=dtype, device="cuda")
+    t.view(torch.uint8).fill_(0xCD)
+    return t
+
+
+_T = {np.dtype(np.float32): torch.float32, np.dtype(np.float16): torch.float16, np.dtype(np.int32): torch.int32}
+
+
+def check(got_t, want, what=""):
+    got = got_t.cpu().numpy()
+    assert got.shape == want.shape, what
+    if want.dtype.kind in "iu":
+        assert np.array_equal(got, want), "%s: %d mismatches" % (what, int((got != want).sum()))
+    else:
+        scale = max(float(np.abs(want.astype(np.float64)).max()), 1e-30)
+        err = float(np.abs(got.astype(np.float64) - want.astype(np.float64)).max()) / scale
+        assert np.isfinite(got.astype(np.float32)).all(), what
+        assert err <= FP_TOL, (what, err)
+
+
+def k_gemm(K, a, b, out_dtype=None, knobs=None):
+    od = out_dtype or (np.float32 if a.dtype == np.float16 else np.int32)
+    out = poison((a.shape[0], b.shape[0]), _T[np.dtype(od)])
+    K.gemm(dev(a), dev(b), out=out, knobs=knobs)
+    return out
+
+
+def k_bmm(K, a, b, knobs=None):
+    od = torch.float32 if a.dtype == np.float16 else torch.int32
+    out = poison((a.shape[0], a.shape[1], b.shape[1]), od)
+    K.bmm(dev(a), dev(b), out=out, knobs=knobs)
+    return out
+
+
+def k_conv(K, x, w, stride, pad, dil, out_dtype=None, knobs=None):
+    od = np.dtype(out_dtype or (np.float32 if x.dtype == np.float16 else np.int32))
+    HO, WO = K.conv_out_hw(x.shape[1], x.shape[2], w.shape[0], w.shape[1], stride, pad, dil)
+    out = poison((x.shape[0], HO, WO, w.shape[3]), _T[od])
+    K.conv2d_nhwc(dev(x), dev(w), stride=stride, padding=pad, dilation=dil, out=out, knobs=knobs)
+    return out
+
+
+def k_conv_packed(K, x, wp, stride, pad, dil, knobs=None):
+    OC, KH, KW, IC, sco, _ = wp.shape
+    return K.conv2d_nhwc_packed(dev(x), dev(wp), OC * sco, KH, KW, stride=stride, padding=pad, dilation=dil,
+                                sco=sco, knobs=knobs)
+
+
+def rand_i8(rng, shape, signed):
+    return rng.integers(-128, 128, shape).astype(np.int8) if signed else rng.integers(0, 256, shape, dtype=np.uint8)
+
+
+# ---- committed golden cases ---------------------------------------------------------------
+def test_golden_cases(K):
+    for name, case in load_cases().items():
+        got = run_case(
+            name, case,
+            lambda a, b: k_gemm(K, a, b), lambda a, b: k_bmm(K, a, b), lambda a, b: k_gemm(K, a, b),
+            lambda x, w, s, p, d: k_conv(K, x, w, s, p, d),
+            lambda x, w, s, p, d, od: k_conv(K, x, w, s, p, d, out_dtype=od),
+            lambda x, w, s, p, d: k_conv_packed(K, x, w, s, p, d))
+        assert_matches(name, got.cpu().numpy(), case["out"])
+
+
+# ---- GEMM ---------------------------------------------------------------------------------
+@pytest.mark.parametrize("M,N,Kd", [(64, 64, 64), (1, 16, 16), (128, 256, 128), (129, 257, 144), (300, 200, 80),
+                                    (512, 512, 512), (1000, 136, 1040), (128, 36, 64)])
+@pytest.mark.parametrize("a_signed,b_signed", [(False, True), (True, True), (False, False), (True, False)])
+def test_gemm_int8_exact(K, co, M, N, Kd, a_signed, b_signed):
+    rng = np.random.default_rng(M * 7 + N * 3 + Kd + a_signed * 2 + b_signed)
+    a, b = rand_i8(rng, (M, Kd), a_signed), rand_i8(rng, (N, Kd), b_signed)
+    check(k_gemm(K, a, b), co.gemm_int(a, b), "gemm int8 %s" % ((M, N, Kd),))
+
+
+@pytest.mark.parametrize("M,N,Kd", [(64, 64, 64), (128, 64, 8), (130, 260, 72), (512, 384, 1024), (2048, 512, 256)])
+@pytest.mark.parametrize("out_dtype", [np.float32, np.float16])
+def test_gemm_fp16(K, co, M, N, Kd, out_dtype):
+    rng = np.random.default_rng(M + N + Kd)
+    a = (rng.standard_normal((M, Kd)) / np.sqrt(Kd)).astype(np.float16)
+    b = rng.standard_normal((N, Kd)).astype(np.float16)
+    if out_dtype == np.float16 and N % 8 != 0:
+        pytest.skip("fp16 rows must be 16-byte multiples for this case's epilogue")
+    check(k_gemm(K, a, b, out_dtype=out_dtype), co.gemm_f16(a, b).astype(out_dtype), "gemm f16")
+
+
+@pytest.mark.parametrize("knobs", [
+    dict(tile_n=32), dict(tile_n=96, stages=2), dict(tile_n=256, stages=1), dict(tile_n=128, acc_stages=1),
+    dict(swizzle_bytes=64), dict(swizzle_bytes=32, tile_n=64), dict(epilogue=2), dict(epilogue=2, tile_n=160),
+    dict(raster=1), dict(max_ctas=3), dict(tile_n=224, stages=3, raster=1),
+])
+def test_gemm_every_knob_gives_the_same_bits(K, co, knobs):
+    rng = np.random.default_rng(42)
+    a, b = rand_i8(rng, (640, 192), False), rand_i8(rng, (480, 192), True)
+    check(k_gemm(K, a, b, knobs=knobs), co.gemm_int(a, b), str(knobs))
+
+
+def test_gemm_rejects_bad_arguments(K):
+    from heron_b200._lib import HB_ERR_KNOB, HB_ERR_SHAPE, HeronB200Error
+    a, b = torch.zeros(64, 24, dtype=torch.uint8, device="cuda"), torch.zeros(64, 24, dtype=torch.int8, device="cuda")
+    with pytest.raises(HeronB200Error) as e:
+        K.gemm(a, b)  # K bytes not a multiple of 16
+    assert e.value.status == HB_ERR_SHAPE
+    a, b = torch.zeros(64, 64, dtype=torch.uint8, device="cuda"), torch.zeros(64, 64, dtype=torch.int8, device="cuda")
+    with pytest.raises(HeronB200Error) as e:
+        K.gemm(a, b, knobs=dict(tile_n=48))
+    assert e.value.status == HB_ERR_KNOB
+    with pytest.raises(HeronB200Error) as e:
+        K.gemm(a[:, :60].contiguous()[:, :48].contiguous(), b[:, :48].contiguous(), knobs=dict(tile_n=256, stages=12))
+    assert e.value.status == HB_ERR_KNOB
+
+
+# ---- batched GEMM ---------------------------------------------------------------------------
+@pytest.mark.parametrize("B,M,N,Kd", [(2, 64, 64, 64), (3, 200, 96, 48), (5, 130, 40, 16), (12, 512, 512, 64)])
+def test_bmm_int8_exact(K, co, B, M, N, Kd):
+    rng = np.random.default_rng(B + M + N)
+    a, b = rand_i8(rng, (B, M, Kd), True), rand_i8(rng, (B, N, Kd), True)
+    check(k_bmm(K, a, b), co.bmm_int(a, b), "bmm")
+
+
+def test_bmm_fp16(K, co):
+    rng = np.random.default_rng(8)
+    a = (rng.standard_normal((4, 150, 64)) / 8).astype(np.float16)
+    b = rng.standard_normal((4, 72, 64)).astype(np.float16)
+    check(k_bmm(K, a, b), co.bmm_f16(a, b), "bmm f16")
+
+
+# ---- conv -----------------------------------------------------------------------------------
+CONV_CASES = [
+    # N, H, W, CI, CO, KH, KW, stride, pad, dil
+    (2, 8, 8, 64, 64, 3, 3, 1, 1, 1),
+    (2, 8, 8, 64, 64, 1, 1, 1, 0, 1),
+    (3, 7, 7, 128, 128, 3, 3, 1, 1, 1),
+    (4, 14, 14, 128, 256, 3, 3, 2, 1, 1),
+    (4, 14, 14, 32, 64, 3, 3, 1, 2, 2),
+    (1, 9, 11, 32, 96, 3, 3, (2, 1), 1, 1),
+    (5, 5, 5, 32, 32, 5, 5, 1, 2, 1),
+    (2, 12, 12, 64, 32, 3, 3, 3, 0, 1),
+    (1, 3, 3, 32, 32, 3, 3, 1, 0, 1),
+    (8, 56, 56, 64, 64, 3, 3, 1, 1, 1),
+]
+
+
+@pytest.mark.parametrize("case", CONV_CASES)
+def test_conv_int8_exact(K, co, case):
+    N, H, W, CI, CO, KH, KW, s, p, d = case
+    rng = np.random.default_rng(hash(case[:7]) % 1000)
+    x, w = rand_i8(rng, (N, H, W, CI), False), rand_i8(rng, (KH, KW, CI, CO), True)
+    check(k_conv(K, x, w, s, p, d), co.conv2d_nhwc_int(x, w, s, p, d), str(case))
+
+
+@pytest.mark.parametrize("case", CONV_CASES + [(4, 9, 9, 16, 64, 3, 3, 1, 1, 1)])
+@pytest.mark.parametrize("out_dtype", [np.float32, np.float16])
+def test_conv_fp16(K, co, case, out_dtype):
+    N, H, W, CI, CO, KH, KW, s, p, d = case
+    rng = np.random.default_rng(hash(case[:7]) % 1000 + 1)
+    x = rng.standard_normal((N, H, W, CI)).astype(np.float16)
+    w = (rng.standard_normal((KH, KW, CI, CO)) / np.sqrt(KH * KW * CI)).astype(np.float16)
+    check(k_conv(K, x, w, s, p, d, out_dtype=out_dtype), co.conv2d_nhwc_f16(x, w, s, p, d, out_dtype), str(case))
+
+
+def test_conv_s8_activations(K, co):
+    rng = np.random.default_rng(77)
+    x, w = rand_i8(rng, (2, 6, 6, 64), True), rand_i8(rng, (3, 3, 64, 64), True)
+    check(k_conv(K, x, w, 1, 1, 1), co.conv2d_nhwc_int(x, w, 1, 1, 1), "s8 x s8 conv")
+
+
+@pytest.mark.parametrize("sco,fmt", [(64, "OhwI64o4i"), (48, "OhwI48o4i"), (32, "OhwI32o4i")])
+def test_conv_packed_x86_format(K, co, sco, fmt):
+    rng = np.random.default_rng(sco)
+    x = rand_i8(rng, (3, 7, 7, 64), False)
+    w = rand_i8(rng, (3, 3, 64, 192), True)
+    wp = npo.pack_filter_x86(w, sco)
+    got = k_conv_packed(K, x, wp, 1, 1, 1)
+    assert tuple(got.shape) == (3, 7, 7, 192 // sco, sco)
+    check(got, co.conv2d_nhwc_packed(x, wp, 1, 1, 1), fmt)
+
+
+def test_conv_rejects_unsupported_channels(K):
+    from heron_b200._lib import HB_ERR_SHAPE, HeronB200Error
+    x = torch.zeros(1, 5, 5, 16, dtype=torch.uint8, device="cuda")  # 16 bytes of channels
+    w = torch.zeros(3, 3, 16, 16, dtype=torch.int8, device="cuda")
+    with pytest.raises(HeronB200Error) as e:
+        K.conv2d_nhwc(x, w, 1, 1, 1)
+    assert e.value.status == HB_ERR_SHAPE
+
+
+# ---- through the reference-facing interface ----------------------------------------------------
+def _task(registry, op, args, codegen):
+    from heron_b200.config import Config
+    from heron_b200.task import Task
+    t = Task("T", registry.getOpFromName(op), args, "cuda")
+    cfg = Config()
+    cfg.codegen_type = codegen
+    cfg.log_dir = None
+    t.config = cfg
+    t.make_stage_schedules()
+    return t
+
+
+def test_task_random_knob_points_agree(K, co):
+    """Eight random feasible points of the knob space all produce the oracle's bits."""
+    from heron_b200.ops import cuda as heron_cuda
+    t = _task(heron_cuda, "bmm", [6, 384, 64, 320, "int8", "int32"], "GPU_TENSOR_CORE")
+    rng = np.random.default_rng(21)
+    a, b = rand_i8(rng, (6, 384, 64), True), rand_i8(rng, (6, 320, 64), True)
+    want = co.bmm_int(a, b)
+    random.seed(21)
+    ta, tb = dev(a), dev(b)
+    for _ in range(8):
+        t.knob_manager.randSample()
+        handle, args = t.instantiate(t.knob_manager)
+        out = poison(args[-1].shape, torch.int32)
+        handle(ta, tb, out)
+        check(out, want, str(handle.knobs))
+
+
+def test_quick_start_config_through_x86_interface(K, co):
+    """Configuration 1: the DL Boost quick-start GEMM (64^3, uint8 x int8 -> int32)."""
+    from heron_b200.ops import x86 as heron_cpu
+    from heron_b200.workloads import make_inputs
+    t = _task(heron_cpu, "gemm", [64, 64, 64, "int8", "int32"], "CPU")
+    t.knob_manager.randSample()
+    handle, args = t.instantiate(t.knob_manager)
+    a, b = make_inputs("cfg1_gemm_u8s8_64")
+    assert (a.dtype, b.dtype) == (np.uint8, np.int8)
+    out = poison(args[-1].shape, torch.int32)
+    plan = handle.plan(dev(a), dev(b), out)
+    plan.launch()
+    first = out.clone()
+    out.view(torch.uint8).fill_(0xCD)
+    plan.launch()
+    assert torch.equal(first, out), "relaunching a plan changed the result"
+    check(out, co.gemm_int(a, b), "cfg1")
+
+
+# ---- the benchmark configurations at full size -----------------------------------------------
+def test_cfg2_gemm_fp16_4096_full_size(K, co):
+    """Full 4096^3: 48 sampled rows against the oracle, every element through a row-sum identity
+    sum_j C[i,j] = sum_k A[i,k] * (sum_j B[j,k]) evaluated in float64."""
+    from heron_b200.workloads import make_inputs
+    a, b = make_inputs("cfg2_gemm_f16_4096")
+    out = k_gemm(K, a, b)
+    rows = np.random.default_rng(2).choice(4096, 48, replace=False)
+    want = co.gemm_f16(a[rows], b)
+    check(out[torch.from_numpy(rows).cuda()], want, "cfg2 sampled rows")
+    got = out.cpu().numpy().astype(np.float64)
+    colsum_b = b.astype(np.float64).sum(axis=0)
+    want_rowsum = a.astype(np.float64) @ colsum_b
+    assert np.abs(got.sum(axis=1) - want_rowsum).max() <= 1e-3 * np.abs(b.astype(np.float64)).sum() / 4096 * 64
+    rowsum_a = a.astype(np.float64).sum(axis=0)
+    want_colsum = b.astype(np.float64) @ rowsum_a
+    assert np.abs(got.sum(axis=0) - want_colsum).max() <= 1e-2 * max(1.0, np.abs(want_colsum).max())
+
+
+def test_cfg4_bmm_int8_full_size(K, co):
+    """Full 192 x 512 x 64 x 512: four whole batches bit-exact against the oracle, every element
+    through exact integer row- and column-sum identities."""
+    from heron_b200.workloads import make_inputs
+    a, b = make_inputs("cfg4_bmm_s8_attention")
+    out = k_bmm(K, a, b)
+    for bi in (0, 77, 130, 191):
+        check(out[bi], co.gemm_int(a[bi], b[bi]), "cfg4 batch %d" % bi)
+    got = out.cpu().numpy().astype(np.int64)
+    a64, b64 = a.astype(np.int64), b.astype(np.int64)
+    assert np.array_equal(got.sum(axis=2), np.einsum("bik,bk->bi", a64, b64.sum(axis=1)))
+    assert np.array_equal(got.sum(axis=1), np.einsum("bjk,bk->bj", b64, a64.sum(axis=1)))
+
+
+def test_cfg3_conv_fp16_full_size(K, co):
+    from heron_b200.workloads import make_inputs
+    x, w = make_inputs("cfg3_conv_f16_resnet_s2")
+    out = k_conv(K, x, w, 1, 1, 1, out_dtype=np.float16)
+    for n in (0, 13, 31):
+        check(out[n:n + 1], co.conv2d_nhwc_f16(x[n:n + 1], w, 1, 1, 1, np.float16), "cfg3 image %d" % n)
+    # channel-sum identity over every output element, in float64 against the fp16-rounded result
+    got = out.cpu().numpy().astype(np.float64).sum(axis=3)
+    wsum = w.astype(np.float64).sum(axis=3, keepdims=True)
+    xp = np.pad(x.astype(np.float64), ((0, 0), (1, 1), (1, 1), (0, 0)))
+    want = np.zeros(got.shape)
+    for ry in range(3):
+        for rx in range(3):
+            want += (xp[:, ry:ry + 56, rx:rx + 56, :] * wsum[ry, rx, :, 0]).sum(axis=3)
+    assert np.abs(got - want).max() <= 64 * 2e-3 * np.abs(out.cpu().numpy().astype(np.float64)).max()
+
+
+def test_cfg5_conv_int8_full_size(K, co):
+    """Full N=1024: six whole images bit-exact against the oracle, every element through the
+    exact channel-sum identity sum_f out[n,y,x,f] = conv(in, sum_f w)."""
+    from heron_b200.workloads import make_inputs
+    x, w = make_inputs("cfg5_conv_u8s8_resnet_s4")
+    out = k_conv(K, x, w, 1, 1, 1)
+    for n in (0, 1, 511, 512, 1000, 1023):
+        check(out[n:n + 1], co.conv2d_nhwc_int(x[n:n + 1], w, 1, 1, 1), "cfg5 image %d" % n)
+    got = out.cpu().numpy().astype(np.int64).sum(axis=3)
+    wsum = w.astype(np.int64).sum(axis=3)  # (3,3,512)
+    xp = np.pad(x.astype(np.int64), ((0, 0), (1, 1), (1, 1), (0, 0)))
+    want = np.zeros(got.shape, dtype=np.int64)
+    for ry in range(3):
+        for rx in range(3):
+            want += (xp[:, ry:ry + 7, rx:rx + 7, :] * wsum[ry, rx]).sum(axis=3)
+    assert np.array_equal(got, want)
+
+
+def test_cfg5_through_the_x86_operator(K, co):
+    """The same layer through the DL Boost operator's interface: packed filter, 5-D output."""
+    from heron_b200.ops import x86 as heron_cpu
+    from heron_b200.workloads import conv_inputs, rng_for
+    t = _task(heron_cpu, "c2d", [16, 7, 7, 512, 512, 3, 3, 1, 1, 1, "OhwI64o4i", "uint8", "int32"], "CPU")
+    t.knob_manager.randSample()
+    handle, args = t.instantiate(t.knob_manager)
+    x, w = conv_inputs(16, 7, 7, 512, 512, 3, 3, "uint8", rng_for(5))
+    wp = npo.pack_filter_x86(w, 64)
+    assert tuple(args[1].shape) == wp.shape
+    out = poison(args[-1].shape, torch.int32)
+    handle(dev(x), dev(wp), out)
+    check(out, co.conv2d_nhwc_packed(x, wp, 1, 1, 1), "x86 c2d")

@@ -1,0 +1,152 @@
+"""The oracle against itself: C restatement vs numpy restatement vs the committed golden cases,
+plus the timed CPU baseline against both.  CPU only."""
+import numpy as np
+import pytest
+from hypothesis import given, settings, strategies as st
+
+from golden_util import assert_matches, load_cases, run_case
+from oracle import np_oracle as npo
+
+
+@pytest.fixture(scope="module")
+def co(oracle_libs):
+    from oracle import c_oracle
+    return c_oracle
+
+
+@pytest.fixture(scope="module")
+def dl(oracle_libs):
+    from oracle import dlboost
+    return dlboost
+
+
+def test_golden_numpy():
+    for name, case in load_cases().items():
+        got = run_case(name, case, npo.gemm_int, npo.bmm_int, npo.gemm_f16, npo.conv2d_nhwc_int,
+                       npo.conv2d_nhwc_f16, npo.conv2d_nhwc_packed)
+        assert_matches(name, got, case["out"])
+
+
+def test_golden_c(co):
+    for name, case in load_cases().items():
+        got = run_case(name, case, co.gemm_int, co.bmm_int, co.gemm_f16, co.conv2d_nhwc_int,
+                       co.conv2d_nhwc_f16, co.conv2d_nhwc_packed)
+        assert_matches(name, got, case["out"])
+
+
+def test_golden_fp16_cases_bit_exact_between_oracles(co):
+    """Both restatements accumulate in double, so even the floating-point cases agree to the bit."""
+    for name, case in load_cases().items():
+        if "f16" not in name:
+            continue
+        a = run_case(name, case, None, None, npo.gemm_f16, None, npo.conv2d_nhwc_f16, None)
+        b = run_case(name, case, None, None, co.gemm_f16, None, co.conv2d_nhwc_f16, None)
+        assert np.array_equal(a.view(np.uint16 if a.dtype == np.float16 else np.uint32),
+                              b.view(np.uint16 if b.dtype == np.float16 else np.uint32)), name
+
+
+@settings(max_examples=40, deadline=None)
+@given(M=st.integers(1, 40), K=st.integers(1, 70), N=st.integers(1, 40), a_signed=st.booleans(),
+       b_signed=st.booleans(), seed=st.integers(0, 2 ** 31))
+def test_gemm_int_c_vs_numpy(co, M, K, N, a_signed, b_signed, seed):
+    rng = np.random.default_rng(seed)
+    a = rng.integers(-128, 128, (M, K)).astype(np.int8) if a_signed else rng.integers(0, 256, (M, K), dtype=np.uint8)
+    b = rng.integers(-128, 128, (N, K)).astype(np.int8) if b_signed else rng.integers(0, 256, (N, K), dtype=np.uint8)
+    assert np.array_equal(co.gemm_int(a, b), npo.gemm_int(a, b))
+
+
+@settings(max_examples=40, deadline=None)
+@given(N=st.integers(1, 3), H=st.integers(1, 9), W=st.integers(1, 9), CI=st.sampled_from([4, 8, 16]),
+       CO=st.sampled_from([1, 8, 32]), KH=st.integers(1, 3), KW=st.integers(1, 3),
+       stride=st.integers(1, 3), pad=st.integers(0, 2), dil=st.integers(1, 2),
+       seed=st.integers(0, 2 ** 31))
+def test_conv_int_c_vs_numpy(co, N, H, W, CI, CO, KH, KW, stride, pad, dil, seed):
+    if H + 2 * pad < (KH - 1) * dil + 1 or W + 2 * pad < (KW - 1) * dil + 1:
+        return
+    rng = np.random.default_rng(seed)
+    x = rng.integers(0, 256, (N, H, W, CI), dtype=np.uint8)
+    w = rng.integers(-128, 128, (KH, KW, CI, CO)).astype(np.int8)
+    assert np.array_equal(co.conv2d_nhwc_int(x, w, stride, pad, dil), npo.conv2d_nhwc_int(x, w, stride, pad, dil))
+
+
+def test_conv_against_scipy_correlate():
+    """A third, library implementation of the same sum: per-channel 2-D cross-correlation."""
+    from scipy.signal import correlate2d
+    rng = np.random.default_rng(5)
+    x = rng.integers(0, 256, (1, 6, 7, 3), dtype=np.uint8)
+    w = rng.integers(-128, 128, (3, 3, 3, 2)).astype(np.int8)
+    want = np.zeros((1, 6, 7, 2), dtype=np.int64)
+    for f in range(2):
+        for c in range(3):
+            want[0, :, :, f] += correlate2d(x[0, :, :, c].astype(np.int64), w[:, :, c, f].astype(np.int64),
+                                            mode="same")
+    assert np.array_equal(npo.conv2d_nhwc_int(x, w, 1, 1, 1), want.astype(np.int32))
+
+
+def test_fp16_paths(co):
+    rng = np.random.default_rng(3)
+    a = rng.standard_normal((33, 130)).astype(np.float16)
+    b = rng.standard_normal((17, 130)).astype(np.float16)
+    assert np.array_equal(co.gemm_f16(a, b), npo.gemm_f16(a, b))
+    x = rng.standard_normal((2, 8, 5, 16)).astype(np.float16)
+    w = rng.standard_normal((3, 3, 16, 24)).astype(np.float16)
+    for out_dtype in (np.float32, np.float16):
+        assert np.array_equal(co.conv2d_nhwc_f16(x, w, (2, 1), 1, 1, out_dtype),
+                              npo.conv2d_nhwc_f16(x, w, (2, 1), 1, 1, out_dtype))
+
+
+def test_half_conversion_matches_numpy(co):
+    L = co.lib()
+    halves = np.arange(0, 65536, 13, dtype=np.uint16)
+    floats = halves.view(np.float16).astype(np.float32)
+    for h, f in zip(halves.tolist(), floats.tolist()):
+        got = L.oracle_half_to_float(h)
+        assert (np.isnan(got) and np.isnan(f)) or got == f
+    rng = np.random.default_rng(11)
+    vals = (rng.standard_normal(4000) * rng.choice([1e-8, 1e-5, 1e-2, 1.0, 300.0, 6e4], 4000)).astype(np.float32)
+    with np.errstate(over="ignore"):
+        want = vals.astype(np.float16).view(np.uint16)
+    for v, w in zip(vals.tolist(), want.tolist()):
+        assert L.oracle_float_to_half(v) == w
+
+
+def test_empty_and_degenerate(co):
+    a = np.zeros((0, 8), dtype=np.uint8)
+    b = np.zeros((4, 8), dtype=np.int8)
+    assert co.gemm_int(a, b).shape == (0, 4) and npo.gemm_int(a, b).shape == (0, 4)
+    # a 1x1 window with stride 2 on a 1-pixel image
+    x = np.full((1, 1, 1, 4), 3, dtype=np.uint8)
+    w = np.full((1, 1, 4, 2), -2, dtype=np.int8)
+    assert np.array_equal(co.conv2d_nhwc_int(x, w, 2, 0, 1), np.full((1, 1, 1, 2), -24, dtype=np.int32))
+
+
+def test_filter_packing_roundtrip():
+    rng = np.random.default_rng(2)
+    w = rng.integers(-128, 128, (3, 3, 16, 96)).astype(np.int8)
+    for sco in (32, 48):
+        wp = npo.pack_filter_x86(w, sco)
+        assert wp.shape == (96 // sco, 3, 3, 4, sco, 4)
+        assert np.array_equal(npo.unpack_filter_x86(wp), w)
+
+
+def test_cpu_baseline_matches_oracle(dl):
+    """The timed DL Boost port computes what the oracle computes (VNNI path or its scalar twin)."""
+    rng = np.random.default_rng(9)
+    a = rng.integers(0, 256, (70, 64), dtype=np.uint8)
+    b = rng.integers(-128, 128, (48, 64)).astype(np.int8)
+    assert np.array_equal(dl.GemmU8S8(70, 64, 48)(a, b), npo.gemm_int(a, b))
+    a = rng.integers(-128, 128, (3, 33, 64)).astype(np.int8)
+    b = rng.integers(-128, 128, (3, 32, 64)).astype(np.int8)
+    assert np.array_equal(dl.BmmS8S8(3, 33, 64, 32)(a, b), npo.bmm_int(a, b))
+    x = rng.integers(0, 256, (3, 7, 7, 64), dtype=np.uint8)
+    w = rng.integers(-128, 128, (3, 3, 64, 192)).astype(np.int8)
+    for sco in (64, 48, 32):
+        wp = npo.pack_filter_x86(w, sco)
+        assert np.array_equal(dl.ConvPacked(3, 7, 7, 64, 192, 3, 3, 1, 1, 1, sco)(x, wp),
+                              npo.conv2d_nhwc_packed(x, wp, 1, 1, 1))
+    af = rng.standard_normal((37, 100)).astype(np.float16)
+    bf = rng.standard_normal((19, 100)).astype(np.float16)
+    if dl.has_avx512():
+        got = dl.GemmF16(37, 100, 19)(af, bf)
+        want = npo.gemm_f16(af, bf)
+        assert np.abs(got - want).max() <= 1e-3 * np.abs(want).max()
