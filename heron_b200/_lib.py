@@ -65,10 +65,13 @@ class HbKnobs(ctypes.Structure):
         ("raster", ctypes.c_int),
         ("epilogue", ctypes.c_int),
         ("max_ctas", ctypes.c_int),
+        ("cta_group", ctypes.c_int),
+        ("l2_prefetch", ctypes.c_int),
         ("reserved", ctypes.c_int),
     ]
 
-    FIELDS = ("tile_n", "stages", "swizzle_bytes", "acc_stages", "raster", "epilogue", "max_ctas")
+    FIELDS = ("tile_n", "stages", "swizzle_bytes", "acc_stages", "raster", "epilogue", "max_ctas",
+              "cta_group", "l2_prefetch", "reserved")
 
     @classmethod
     def from_dict(cls, d):

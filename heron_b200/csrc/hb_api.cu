@@ -64,12 +64,17 @@ Driver& driver() {
       return;
     d.im2col = reinterpret_cast<EncodeIm2colFn>(fn);
     // Opt in to the large dynamic shared-memory carve-out once per instantiation.
-    if (cudaFuncSetAttribute(hb::hb_umma_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             kSmemLimit) != cudaSuccess)
-      return;
-    if (cudaFuncSetAttribute(hb::hb_umma_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             kSmemLimit) != cudaSuccess)
-      return;
+    const void* kernels[6] = {
+        reinterpret_cast<const void*>(&hb::hb_umma_kernel<4, 1, 0>),
+        reinterpret_cast<const void*>(&hb::hb_umma_kernel<2, 1, 0>),
+        reinterpret_cast<const void*>(&hb::hb_umma_kernel<4, 1, 1>),
+        reinterpret_cast<const void*>(&hb::hb_umma_kernel<4, 2, 0>),
+        reinterpret_cast<const void*>(&hb::hb_umma_kernel<2, 2, 0>),
+        reinterpret_cast<const void*>(&hb::hb_umma_kernel<4, 2, 1>)};
+    for (const void* k : kernels)
+      if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit) !=
+          cudaSuccess)
+        return;
     d.status = HB_OK;
   });
   return d;
@@ -117,7 +122,7 @@ int next_pow2_cols(int c) {
 
 // Instruction descriptor of tcgen05.mma (32 bit): accumulator format bits 4..5, A/B formats bits
 // 7..9 / 10..12, A/B major bits 15/16, N/8 in bits 17..22, M/16 in bits 24..28.
-uint32_t make_idesc(int kind, hb_dtype a, hb_dtype b, int tile_n, bool b_mn_major) {
+uint32_t make_idesc(int kind, hb_dtype a, hb_dtype b, int tile_m, int tile_n, bool b_mn_major) {
   uint32_t d = 0;
   if (kind == 0) {
     d |= 1u << 4;  // fp32 accumulator; A and B formats 0 = fp16
@@ -129,7 +134,7 @@ uint32_t make_idesc(int kind, hb_dtype a, hb_dtype b, int tile_n, bool b_mn_majo
   d |= 0u << 15;                       // A is K-major
   d |= (b_mn_major ? 1u : 0u) << 16;   // B major
   d |= static_cast<uint32_t>(tile_n >> 3) << 17;
-  d |= static_cast<uint32_t>(hb::kTileM >> 4) << 24;
+  d |= static_cast<uint32_t>(tile_m >> 4) << 24;
   return d;
 }
 
@@ -141,7 +146,8 @@ struct Problem {
   int CI;  // conv only
 };
 
-int stage_bytes(int tile_n, int sw) { return (hb::kTileM + tile_n) * sw; }
+// Ring-stage bytes of one CTA: 128 rows of A plus this CTA's share of B's tile_n rows.
+int stage_bytes(int tile_n, int sw, int cg) { return (hb::kTileM + tile_n / cg) * sw; }
 
 // Resolves zeros in *in to defaults for this problem.
 void resolve_knobs(const Problem& pr, const hb_knobs* in, int sm_count, hb_knobs* out) {
@@ -161,21 +167,33 @@ void resolve_knobs(const Problem& pr, const hb_knobs* in, int sm_count, hb_knobs
       k.swizzle_bytes = kbytes > 64 ? 128 : (kbytes > 32 ? 64 : 32);
     }
   }
+  if (k.cta_group == 0) {
+    // CTA pairs pay off when the K loop is long enough to amortise the cross-CTA hand-offs of a
+    // tile and when each CTA of the pair still gets a whole B chunk of a tile no wider than N.
+    const int sw = k.swizzle_bytes ? k.swizzle_bytes : 128;
+    const long long kblocks = (static_cast<long long>(pr.K) * es + sw - 1) / sw;
+    const int min_pair_n = pr.conv ? 2 * sw / es : 64;
+    k.cta_group = (pr.M > hb::kTileM && kblocks >= 8 && pr.N >= min_pair_n) ? 2 : 1;
+  }
   if (k.epilogue == 0) {
     // Default: TMA store whenever the output rows are 16-byte multiples.
     k.epilogue = ((static_cast<long long>(pr.N) * eo) % 16 == 0) ? 1 : 2;
   }
   if (k.tile_n == 0) {
     const int step = (eo == 2) ? 64 : 32;
-    const int chunk = pr.conv ? k.swizzle_bytes / es : step;  // MN-major B needs whole chunks
+    // MN-major B needs whole swizzle-span chunks of columns in every CTA of the group
+    const int chunk = pr.conv ? k.cta_group * k.swizzle_bytes / es : step;
     const int gran = chunk > step ? chunk : step;
-    const long long tiles_m = (pr.M + hb::kTileM - 1) / hb::kTileM;
+    const int rows = hb::kTileM * k.cta_group;
+    const long long tiles_m = (pr.M + rows - 1) / rows;
+    const int units = sms / k.cta_group;
     long long best_cost = -1;
     int best = gran;
     for (int bn = gran; bn <= 256; bn += gran) {
       const long long tiles = tiles_m * ((pr.N + bn - 1) / bn) * pr.batch;
-      const long long waves = (tiles + sms - 1) / sms;
-      const long long cost = waves * (hb::kTileM + bn);  // operand bytes a CTA pulls per tile
+      const long long waves = (tiles + units - 1) / units;
+      // operand bytes a CTA pulls per tile
+      const long long cost = waves * (hb::kTileM + bn / k.cta_group);
       if (best_cost < 0 || cost < best_cost || (cost == best_cost && bn > best)) {
         best_cost = cost;
         best = bn;
@@ -186,11 +204,12 @@ void resolve_knobs(const Problem& pr, const hb_knobs* in, int sm_count, hb_knobs
   if (k.acc_stages == 0) k.acc_stages = (2 * k.tile_n <= 512) ? 2 : 1;
   if (k.stages == 0) {
     const int epi = k.epilogue == 1 ? hb::kEpiWarps * 2 * hb::kEpiBufBytes : 0;
-    int s = (kSmemLimit - kSmemSlack - epi) / stage_bytes(k.tile_n, k.swizzle_bytes);
+    int s = (kSmemLimit - kSmemSlack - epi) / stage_bytes(k.tile_n, k.swizzle_bytes, k.cta_group);
     if (s > 8) s = 8;
     if (s < 1) s = 1;
     k.stages = s;
   }
+  if (k.l2_prefetch == 0) k.l2_prefetch = -1;
   *out = k;
 }
 
@@ -206,12 +225,15 @@ int check_knobs(const Problem& pr, const hb_knobs& k, int* smem_bytes, int* tmem
   if (k.epilogue != 1 && k.epilogue != 2) return HB_ERR_KNOB;
   if (k.epilogue == 1 && (static_cast<long long>(pr.N) * eo) % 16 != 0) return HB_ERR_KNOB;
   if (k.max_ctas < 0) return HB_ERR_KNOB;
+  if (k.cta_group != 1 && k.cta_group != 2) return HB_ERR_KNOB;
+  if (k.l2_prefetch < -1 || k.l2_prefetch > 64) return HB_ERR_KNOB;
   if (pr.conv) {
     if ((pr.CI * es) % k.swizzle_bytes != 0) return HB_ERR_KNOB;
-    if ((k.tile_n * es) % k.swizzle_bytes != 0) return HB_ERR_KNOB;  // whole MN-major chunks
+    // whole MN-major chunks in every CTA of the group
+    if ((k.tile_n / k.cta_group * es) % k.swizzle_bytes != 0) return HB_ERR_KNOB;
   }
   const int epi = k.epilogue == 1 ? hb::kEpiWarps * 2 * hb::kEpiBufBytes : 0;
-  const int smem = k.stages * stage_bytes(k.tile_n, k.swizzle_bytes) + epi + kSmemSlack;
+  const int smem = k.stages * stage_bytes(k.tile_n, k.swizzle_bytes, k.cta_group) + epi + kSmemSlack;
   if (smem > kSmemLimit) return HB_ERR_KNOB;
   if (smem_bytes) *smem_bytes = smem;
   if (tmem_cols) *tmem_cols = next_pow2_cols(k.acc_stages * k.tile_n);
@@ -268,7 +290,8 @@ int build_plan(Driver& d, const Problem& pr, const hb_knobs& k, const ConvGeom* 
   p.M = pr.M; p.N = pr.N; p.K = pr.K; p.batch = pr.batch;
   p.BN = k.tile_n; p.SW = k.swizzle_bytes; p.esize_in = es; p.esize_out = eo;
   p.stages = k.stages; p.acc_stages = k.acc_stages; p.tmem_cols = tmem_cols;
-  p.tiles_m = (pr.M + hb::kTileM - 1) / hb::kTileM;
+  const int cgrp = k.cta_group;
+  p.tiles_m = (pr.M + hb::kTileM * cgrp - 1) / (hb::kTileM * cgrp);
   p.tiles_n = (pr.N + k.tile_n - 1) / k.tile_n;
   const long long ntiles = static_cast<long long>(p.tiles_m) * p.tiles_n * pr.batch;
   if (ntiles > 0x7fffffffLL) return HB_ERR_SHAPE;
@@ -276,7 +299,9 @@ int build_plan(Driver& d, const Problem& pr, const hb_knobs& k, const ConvGeom* 
   const int BK = k.swizzle_bytes / es;
   p.raster = k.raster; p.kind = kind; p.b_mn_major = pr.conv ? 1 : 0; p.a_im2col = pr.conv ? 1 : 0;
   p.epilogue = k.epilogue == 1 ? 1 : 0;
-  p.idesc = make_idesc(kind, pr.in_a, pr.in_b, k.tile_n, pr.conv);
+  p.l2_prefetch = (!pr.conv && k.l2_prefetch > 0) ? k.l2_prefetch : 0;
+  p.probe = k.reserved;  // diagnostic modes: 1 = no reloads, 2 = no MMAs (results undefined)
+  p.idesc = make_idesc(kind, pr.in_a, pr.in_b, hb::kTileM * cgrp, k.tile_n, pr.conv);
   p.C = C; p.ldc = pr.N; p.batch_stride_c = static_cast<long long>(pr.M) * pr.N;
 
   CUtensorMap& tmA = plan->tmA;
@@ -288,8 +313,8 @@ int build_plan(Driver& d, const Problem& pr, const hb_knobs& k, const ConvGeom* 
     rc = encode_tiled3(d, &tmA, pr.in_a, A, pr.K, pr.M, pr.batch, rowA, rowA * pr.M, BK, hb::kTileM,
                        k.swizzle_bytes);
     if (rc != HB_OK) return rc;
-    rc = encode_tiled3(d, &tmB, pr.in_b, B, pr.K, pr.N, pr.batch, rowA, rowA * pr.N, BK, k.tile_n,
-                       k.swizzle_bytes);
+    rc = encode_tiled3(d, &tmB, pr.in_b, B, pr.K, pr.N, pr.batch, rowA, rowA * pr.N, BK,
+                       k.tile_n / cgrp, k.swizzle_bytes);
     if (rc != HB_OK) return rc;
   } else {
     p.HO = cg->HO; p.WO = cg->WO; p.KW = cg->KW; p.CI = cg->CI;
@@ -331,14 +356,35 @@ int build_plan(Driver& d, const Problem& pr, const hb_knobs& k, const ConvGeom* 
     if (rc != HB_OK) return rc;
   }
 
-  int grid = d.sm_count;
-  if (k.max_ctas > 0 && k.max_ctas < grid) grid = k.max_ctas;
-  if (p.num_tiles < grid) grid = p.num_tiles;
-  plan->grid = grid;
+  int units = d.sm_count / cgrp;  // CTAs, or CTA pairs, resident at once
+  if (cgrp == 2) {
+    cudaLaunchConfig_t cfg;
+    std::memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = dim3(d.sm_count / 2 * 2);
+    cfg.blockDim = dim3(hb::kThreads);
+    cfg.dynamicSmemBytes = smem;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = 2; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr; cfg.numAttrs = 1;
+    int clusters = 0;
+    const void* fn = eo == 2 ? reinterpret_cast<const void*>(&hb::hb_umma_kernel<2, 2, 0>)
+                             : (kind == 0 ? reinterpret_cast<const void*>(&hb::hb_umma_kernel<4, 2, 0>)
+                                          : reinterpret_cast<const void*>(&hb::hb_umma_kernel<4, 2, 1>));
+    if (cudaOccupancyMaxActiveClusters(&clusters, fn, &cfg) == cudaSuccess && clusters > 0 &&
+        clusters < units)
+      units = clusters;
+  }
+  if (k.max_ctas > 0 && k.max_ctas / cgrp < units) units = k.max_ctas / cgrp > 0 ? k.max_ctas / cgrp : 1;
+  if (p.num_tiles < units) units = p.num_tiles;
+  plan->grid = units * cgrp;
   plan->smem = smem;
   plan->knobs = k;
   return HB_OK;
 }
+
+template <int OUT_BYTES, int CG, int KIND>
+int launch_kernel(const hb_plan* plan, cudaStream_t stream);
 
 int run_plan(const hb_plan* plan, cudaStream_t stream) {
   if (plan->packed_w) {
@@ -347,13 +393,32 @@ int run_plan(const hb_plan* plan, cudaStream_t stream) {
         plan->KH, plan->p.KW, plan->p.CI, plan->sco);
     if (cudaGetLastError() != cudaSuccess) return HB_ERR_LAUNCH;
   }
-  if (plan->p.esize_out == 2)
-    hb::hb_umma_kernel<2><<<plan->grid, hb::kThreads, plan->smem, stream>>>(plan->tmA, plan->tmB,
-                                                                             plan->tmC, plan->p);
-  else
-    hb::hb_umma_kernel<4><<<plan->grid, hb::kThreads, plan->smem, stream>>>(plan->tmA, plan->tmB,
-                                                                             plan->tmC, plan->p);
-  return cudaGetLastError() == cudaSuccess ? HB_OK : HB_ERR_LAUNCH;
+  const bool half_out = plan->p.esize_out == 2;
+  const bool i8 = plan->p.kind == 1;
+  if (plan->knobs.cta_group == 2) {
+    if (half_out) return launch_kernel<2, 2, 0>(plan, stream);
+    return i8 ? launch_kernel<4, 2, 1>(plan, stream) : launch_kernel<4, 2, 0>(plan, stream);
+  }
+  if (half_out) return launch_kernel<2, 1, 0>(plan, stream);
+  return i8 ? launch_kernel<4, 1, 1>(plan, stream) : launch_kernel<4, 1, 0>(plan, stream);
+}
+
+template <int OUT_BYTES, int CG, int KIND>
+int launch_kernel(const hb_plan* plan, cudaStream_t stream) {
+  cudaLaunchConfig_t cfg;
+  std::memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3(plan->grid);
+  cfg.blockDim = dim3(hb::kThreads);
+  cfg.dynamicSmemBytes = plan->smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeClusterDimension;
+  attr.val.clusterDim.x = CG; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  const cudaError_t e = cudaLaunchKernelEx(&cfg, hb::hb_umma_kernel<OUT_BYTES, CG, KIND>, plan->tmA,
+                                           plan->tmB, plan->tmC, plan->p);
+  return e == cudaSuccess ? HB_OK : HB_ERR_LAUNCH;
 }
 
 int plan_gemm_like(int op, const void* A, const void* B, void* C, int batch, int M, int K, int N,

@@ -13,6 +13,15 @@
 // Two accumulator buffers in TMEM let the MMA warp start the next tile while the epilogue warps
 // drain the previous one.
 //
+// With CG = 2 the two CTAs of a cluster share every MMA (tcgen05 cta_group::2): the pair owns a
+// 256 x BN tile, each CTA stages its own 128 rows of A and its own half of B's BN rows, the
+// leader CTA (cluster rank 0) issues the instruction for both and each CTA's TMEM receives its
+// 128 x BN half of the accumulator.  A CTA then pulls a third less operand data per flop than
+// alone, which is what the large tensor-bound shapes are limited by.  Loads of both CTAs
+// complete on the leader's "full" barrier; the leader's commits arrive on both CTAs' "empty"
+// and "accumulator full" barriers; both CTAs' epilogue warps arrive on the leader's
+// "accumulator empty" barrier.
+//
 // Operand layouts in shared memory are the canonical swizzled UMMA layouts, written by TMA:
 //   A, K-major:   rows = M index, each row SW bytes of K (SW = 32/64/128 = TMA swizzle span);
 //   B, K-major:   rows = N index, same (GEMM / BMM: B is stored (N, K));
@@ -42,7 +51,7 @@ struct KParams {
   int BN, SW, esize_in, esize_out;
   int stages, acc_stages, tmem_cols;
   int tiles_m, tiles_n, num_tiles, num_kb;
-  int raster, kind, b_mn_major, a_im2col, epilogue;
+  int raster, kind, b_mn_major, a_im2col, epilogue, l2_prefetch, probe;
   uint32_t idesc;
   // conv geometry (a_im2col only)
   int HO, WO, KW, CI, kb_per_tap, stride_h, stride_w, dil_h, dil_w, pad;
@@ -73,7 +82,7 @@ __device__ __forceinline__ void mbar_wait_drain(uint32_t bar, uint32_t parity) {
   }
 }
 
-template <int OUT_BYTES>
+template <int OUT_BYTES, int CG, int KIND>
 __global__ void __launch_bounds__(kThreads, 1)
 hb_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                const __grid_constant__ CUtensorMap tmC, const KParams p) {
@@ -82,8 +91,11 @@ hb_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem = smem_raw + (smem_base - smem_u32(smem_raw));
 
+  const uint32_t cta_rank = (CG == 2) ? cluster_ctarank() : 0u;
+  const bool leader = cta_rank == 0u;
+  const int bn_cta = p.BN / CG;  // rows of B (columns of the tile) this CTA stages
   const int a_bytes = kTileM * p.SW;
-  const int b_bytes = p.BN * p.SW;
+  const int b_bytes = bn_cta * p.SW;
   const uint32_t sA = smem_base;
   const uint32_t sB = sA + p.stages * a_bytes;
   const uint32_t sEpi = sB + p.stages * b_bytes;
@@ -102,7 +114,7 @@ hb_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(smem_u32(&bars->tmem_full[a]), 1);
-      mbar_init(smem_u32(&bars->tmem_empty[a]), kEpiWarps);
+      mbar_init(smem_u32(&bars->tmem_empty[a]), kEpiWarps * CG);
     }
     mbar_init(smem_u32(&bars->drain), 1);
     bars->abort_flag = 0;
@@ -111,34 +123,38 @@ hb_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     prefetch_tmap(&tmB);
     if (p.epilogue) prefetch_tmap(&tmC);
   }
-  if (warp == 1) {
-    tmem_alloc(smem_u32(&bars->tmem_base), static_cast<uint32_t>(p.tmem_cols));
-    tmem_relinquish();
-  }
+  if (warp == 1) tmem_alloc_cg<CG>(smem_u32(&bars->tmem_base), static_cast<uint32_t>(p.tmem_cols));
   tc_fence_before();
   __syncthreads();
+  if (CG == 2) cluster_sync();  // the peer's barriers exist before anything arrives on them
   tc_fence_after();
   const uint32_t tmem_base = bars->tmem_base;
 
   const int tiles_per_batch = p.tiles_m * p.tiles_n;
+  const int first_tile = blockIdx.x / CG;  // a pair of CTAs walks the tile list together
+  const int tile_step = gridDim.x / CG;
+  const int tile_rows = kTileM * CG;
 
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------------------
-    if (lane == 0) {
+    // elect.sync (not "lane == 0") picks the issuing lane: the compiler then knows the branch
+    // runs on exactly one lane and keeps descriptors and coordinates in uniform registers,
+    // which is what the TMA and MMA instructions read their operands from.
+    if (elect_one()) {
       int stage = 0;
       uint32_t phase = 0;
       long long issued = 0;
       bool ok = true;
       const int chunk_cols = p.SW / p.esize_in;               // MN-major B: columns per chunk
-      const int n_chunks = p.b_mn_major ? p.BN / chunk_cols : 1;
-      const uint32_t tx_bytes = static_cast<uint32_t>(a_bytes + b_bytes);
-      for (int t = blockIdx.x; ok && t < p.num_tiles; t += gridDim.x) {
+      const int n_chunks = p.b_mn_major ? bn_cta / chunk_cols : 1;
+      const uint32_t tx_bytes = static_cast<uint32_t>(a_bytes + b_bytes) * CG;
+      for (int t = first_tile; ok && t < p.num_tiles; t += tile_step) {
         const int b = t / tiles_per_batch;
         const int r = t - b * tiles_per_batch;
         const int mb = p.raster ? (r % p.tiles_m) : (r / p.tiles_n);
         const int nb = p.raster ? (r / p.tiles_m) : (r % p.tiles_n);
-        const int m0 = mb * kTileM;
-        const int n0 = nb * p.BN;
+        const int m0 = mb * tile_rows + static_cast<int>(cta_rank) * kTileM;
+        const int n0 = nb * p.BN + static_cast<int>(cta_rank) * bn_cta;
         int pix_w = 0, pix_h = 0, pix_n = 0;
         if (p.a_im2col) {
           const int hw = p.HO * p.WO;
@@ -150,12 +166,23 @@ hb_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           pix_h = y * p.stride_h - p.pad;
         }
         for (int kb = 0; kb < p.num_kb; ++kb) {
-          const uint32_t full = smem_u32(&bars->full[stage]);
+          const uint32_t full_local = smem_u32(&bars->full[stage]);
+          const uint32_t full = (CG == 2) ? mapa(full_local, 0) : full_local;  // the leader's barrier
           if (!mbar_wait(smem_u32(&bars->empty[stage]), phase ^ 1u, abort_flag)) {
             ok = false;
             break;
           }
-          mbar_arrive_expect_tx(full, tx_bytes);
+          if (p.probe == 1 && issued >= p.stages) {
+            // diagnostic: operands stay as first loaded; only the barrier protocol runs
+            if (leader) mbar_arrive(full_local);
+            ++issued;
+            if (++stage == p.stages) {
+              stage = 0;
+              phase ^= 1u;
+            }
+            continue;
+          }
+          if (leader) mbar_arrive_expect_tx(full_local, tx_bytes);
           const uint32_t dA = sA + stage * a_bytes;
           const uint32_t dB = sB + stage * b_bytes;
           int krow;  // first K index of this block in B's K dimension
@@ -164,19 +191,23 @@ hb_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             const int cc = kb - tap * p.kb_per_tap;
             const int ry = tap / p.KW;
             const int rx = tap - ry * p.KW;
-            tma_load_im2col_4d(dA, &tmA, full, cc * BK, pix_w, pix_h, pix_n,
-                               static_cast<uint16_t>(rx * p.dil_w),
-                               static_cast<uint16_t>(ry * p.dil_h));
+            tma_load_im2col_4d_cg<CG>(dA, &tmA, full, cc * BK, pix_w, pix_h, pix_n,
+                                      static_cast<uint16_t>(rx * p.dil_w),
+                                      static_cast<uint16_t>(ry * p.dil_h));
             krow = tap * p.CI + cc * BK;
           } else {
-            tma_load_3d(dA, &tmA, full, kb * BK, m0, b);
+            tma_load_3d_cg<CG>(dA, &tmA, full, kb * BK, m0, b);
             krow = kb * BK;
+            if (p.l2_prefetch > 0 && kb + p.l2_prefetch < p.num_kb) {
+              tma_prefetch_3d(&tmA, (kb + p.l2_prefetch) * BK, m0, b);
+              tma_prefetch_3d(&tmB, (kb + p.l2_prefetch) * BK, n0, b);
+            }
           }
           if (p.b_mn_major) {
             for (int j = 0; j < n_chunks; ++j)
-              tma_load_3d(dB + j * (BK * p.SW), &tmB, full, n0 + j * chunk_cols, krow, b);
+              tma_load_3d_cg<CG>(dB + j * (BK * p.SW), &tmB, full, n0 + j * chunk_cols, krow, b);
           } else {
-            tma_load_3d(dB, &tmB, full, krow, n0, b);
+            tma_load_3d_cg<CG>(dB, &tmB, full, krow, n0, b);
           }
           ++issued;
           if (++stage == p.stages) {
@@ -187,71 +218,92 @@ hb_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       }
       if (!ok) {
         // Wait (bounded) for the loads that are still in flight before shared memory goes away.
-        const int pending = issued < p.stages ? static_cast<int>(issued) : p.stages;
-        for (int i = 0; i < pending; ++i) {
-          if (--stage < 0) {
-            stage = p.stages - 1;
-            phase ^= 1u;
+        // A full barrier completes only when both CTAs' loads of that stage have landed, so the
+        // leader's wait covers the peer's copies too; the peer, which cannot poll the leader's
+        // barrier, gives its own copies a fixed grace period instead.
+        if (leader) {
+          const int pending = issued < p.stages ? static_cast<int>(issued) : p.stages;
+          for (int i = 0; i < pending; ++i) {
+            if (--stage < 0) {
+              stage = p.stages - 1;
+              phase ^= 1u;
+            }
+            mbar_wait_drain(smem_u32(&bars->full[stage]), phase);
           }
-          mbar_wait_drain(smem_u32(&bars->full[stage]), phase);
+        } else {
+          const long long t0 = clock64();
+          while (clock64() - t0 < 4000000LL) {
+          }
         }
       }
     }
     __syncwarp();
   } else if (warp == 1) {
-    // ------------------------------ MMA issuer --------------------------------------------
-    if (lane == 0) {
+    // ------------------------------ MMA issuer (leader CTA only) ---------------------------
+    if (elect_one() && leader) {
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
+      // Descriptors are built once per kernel (high word) and once per stage (low word); the
+      // four MMAs of a stage differ only by a constant added to the 14-bit start-address field.
       const uint32_t layout_type = p.SW == 128 ? 2u : (p.SW == 64 ? 4u : 6u);
       const uint32_t sbo = 8u * p.SW;                // bytes between 8-row groups
       const int n_mma = p.SW / 32;                   // MMAs per ring stage (32 bytes of K each)
       const int umma_k = 32 / p.esize_in;            // 16 (fp16) or 32 (int8)
       const uint32_t b_lbo = p.b_mn_major ? static_cast<uint32_t>(BK * p.SW) : 16u;
-      const uint32_t b_step = p.b_mn_major ? static_cast<uint32_t>(umma_k * p.SW) : 32u;
-      for (int t = blockIdx.x; ok && t < p.num_tiles; t += gridDim.x) {
+      const uint32_t b_step16 = (p.b_mn_major ? static_cast<uint32_t>(umma_k * p.SW) : 32u) >> 4;
+      const uint64_t desc_hi =
+          static_cast<uint64_t>(((sbo >> 4) & 0x3FFFu) | (1u << 14) | (layout_type << 29)) << 32;
+      const uint32_t a_lo_fixed = (16u >> 4) << 16;
+      const uint32_t b_lo_fixed = ((b_lbo >> 4) & 0x3FFFu) << 16;
+      const uint32_t idesc = p.idesc;
+      const int num_kb = p.num_kb, stages = p.stages, acc_stages = p.acc_stages, probe = p.probe;
+      const uint32_t a16 = static_cast<uint32_t>(a_bytes) >> 4, b16 = static_cast<uint32_t>(b_bytes) >> 4;
+      const uint32_t full0 = smem_u32(&bars->full[0]), empty0 = smem_u32(&bars->empty[0]);
+      for (int t = first_tile; ok && t < p.num_tiles; t += tile_step) {
         if (!mbar_wait(smem_u32(&bars->tmem_empty[acc]), acc_phase ^ 1u, abort_flag)) {
           ok = false;
           break;
         }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * p.BN);
-        for (int kb = 0; kb < p.num_kb; ++kb) {
-          if (!mbar_wait(smem_u32(&bars->full[stage]), phase, abort_flag)) {
+        uint32_t accum = 0u;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(full0 + 8u * stage, phase, abort_flag)) {
             ok = false;
             break;
           }
           tc_fence_after();
-          const uint32_t aA = sA + stage * a_bytes;
-          const uint32_t aB = sB + stage * b_bytes;
-          for (int k = 0; k < n_mma; ++k) {
-            const uint64_t adesc = make_smem_desc(aA + k * 32u, 16u, sbo, layout_type);
-            const uint64_t bdesc = make_smem_desc(aB + k * b_step, b_lbo, sbo, layout_type);
-            const uint32_t accum = (kb | k) != 0 ? 1u : 0u;
-            if (p.kind == 0)
-              umma_f16(d_tmem, adesc, bdesc, p.idesc, accum);
-            else
-              umma_i8(d_tmem, adesc, bdesc, p.idesc, accum);
+          const uint32_t a_lo = (((sA >> 4) + stage * a16) & 0x3FFFu) | a_lo_fixed;
+          const uint32_t b_lo = (((sB >> 4) + stage * b16) & 0x3FFFu) | b_lo_fixed;
+          if (probe != 2) {
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              if (k < n_mma) {
+                umma_cg<CG, KIND>(d_tmem, desc_hi | (a_lo + 2u * k), desc_hi | (b_lo + b_step16 * k), idesc,
+                                  accum);
+                accum = 1u;
+              }
+            }
           }
-          umma_commit(smem_u32(&bars->empty[stage]));  // stage reusable once these MMAs finish
-          if (++stage == p.stages) {
+          umma_commit_cg<CG>(empty0 + 8u * stage);  // stage reusable once these MMAs finish
+          if (++stage == stages) {
             stage = 0;
             phase ^= 1u;
           }
         }
         if (!ok) break;
-        umma_commit(smem_u32(&bars->tmem_full[acc]));  // accumulator complete
-        if (++acc == p.acc_stages) {
+        umma_commit_cg<CG>(smem_u32(&bars->tmem_full[acc]));  // accumulator complete
+        if (++acc == acc_stages) {
           acc = 0;
           acc_phase ^= 1u;
         }
       }
       if (!ok) {
         // Let every MMA issued so far finish before TMEM is freed.
-        umma_commit(smem_u32(&bars->drain));
+        umma_commit_local<CG>(smem_u32(&bars->drain));
         mbar_wait_drain(smem_u32(&bars->drain), 0u);
       }
     }
@@ -266,12 +318,12 @@ hb_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     uint32_t store_it = 0;
     constexpr int kColsPerStore = 128 / OUT_BYTES;  // 32 (4-byte) or 64 (fp16) columns
     const uint32_t my_buf = sEpi + ew * 2 * kEpiBufBytes;
-    for (int t = blockIdx.x; ok && t < p.num_tiles; t += gridDim.x) {
+    for (int t = first_tile; ok && t < p.num_tiles; t += tile_step) {
       const int b = t / tiles_per_batch;
       const int r = t - b * tiles_per_batch;
       const int mb = p.raster ? (r % p.tiles_m) : (r / p.tiles_n);
       const int nb = p.raster ? (r / p.tiles_m) : (r % p.tiles_n);
-      const int row0 = mb * kTileM + q * 32;
+      const int row0 = mb * tile_rows + static_cast<int>(cta_rank) * kTileM + q * 32;
       const int n0 = nb * p.BN;
       if (!mbar_wait(smem_u32(&bars->tmem_full[acc]), acc_phase, abort_flag)) {
         ok = false;
@@ -308,14 +360,20 @@ hb_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           // Last read of this accumulator: hand it back to the MMA warp before storing.
           tc_fence_before();
           __syncwarp();
-          if (lane == 0) mbar_arrive(smem_u32(&bars->tmem_empty[acc]));
+          if (lane == 0) {
+            if (CG == 2)
+              mbar_arrive_cluster(mapa(smem_u32(&bars->tmem_empty[acc]), 0));
+            else
+              mbar_arrive(smem_u32(&bars->tmem_empty[acc]));
+          }
         }
         const int col = n0 + c0;
         if (p.epilogue) {
           if (col < p.N && row0 < p.M) {
             const uint32_t buf = my_buf + (store_it & 1u) * kEpiBufBytes;
             ++store_it;
-            if (lane == 0) bulk_wait_read<1>();  // the store that last used this buffer has read it
+            const bool issuer = elect_one();
+            if (issuer) bulk_wait_read<1>();  // the store that last used this buffer has read it
             __syncwarp();
             const uint32_t row_addr = buf + lane * 128;
 #pragma unroll
@@ -327,7 +385,7 @@ hb_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             }
             fence_proxy_async_smem();
             __syncwarp();
-            if (lane == 0) {
+            if (issuer) {
               tma_store_3d(&tmC, buf, col, row0, b);
               bulk_commit();
             }
@@ -371,15 +429,17 @@ hb_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         acc_phase ^= 1u;
       }
     }
-    if (p.epilogue && lane == 0) bulk_wait<0>();
+    // every lane may have been the elected issuer of some store: each drains its own groups
+    if (p.epilogue) bulk_wait<0>();
     __syncwarp();
   }
 
   tc_fence_before();
   __syncthreads();
+  if (CG == 2) cluster_sync();  // neither CTA leaves while the other may still touch its barriers
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, static_cast<uint32_t>(p.tmem_cols));
+    tmem_dealloc_cg<CG>(tmem_base, static_cast<uint32_t>(p.tmem_cols));
   }
   if (threadIdx.x == 0 && *abort_flag) atomicExch(&g_hb_status, kErrTimeout);
 }

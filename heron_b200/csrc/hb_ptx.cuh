@@ -189,6 +189,142 @@ __device__ __forceinline__ void tmem_ld_wait() {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+// ---- thread-block clusters (pairs of CTAs that share one MMA) ------------------------------
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// shared::cluster address of `addr` (a shared::cta address of this CTA) in CTA `rank` of the cluster.
+__device__ __forceinline__ uint32_t mapa(uint32_t addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+// One arrival on an mbarrier that may live in another CTA of the cluster.
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr)
+               : "memory");
+}
+
+// ---- cta_group-generic forms --------------------------------------------------------------
+// CG = 1: one CTA owns the MMA.  CG = 2: the two CTAs of a cluster share it; loads of either CTA
+// complete on the leader's mbarrier (`bar` is then a shared::cluster address).
+template <int CG>
+__device__ __forceinline__ void tma_load_3d_cg(uint32_t dst, const CUtensorMap* m, uint32_t bar, int x,
+                                               int y, int z) {
+  if constexpr (CG == 1) {
+    tma_load_3d(dst, m, bar, x, y, z);
+  } else {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+        " [%0], [%1, {%3, %4, %5}], [%2];" ::"r"(dst),
+        "l"(reinterpret_cast<uint64_t>(m)), "r"(bar), "r"(x), "r"(y), "r"(z)
+        : "memory");
+  }
+}
+template <int CG>
+__device__ __forceinline__ void tma_load_im2col_4d_cg(uint32_t dst, const CUtensorMap* m, uint32_t bar,
+                                                      int c, int w, int h, int n, uint16_t off_w,
+                                                      uint16_t off_h) {
+  if constexpr (CG == 1) {
+    tma_load_im2col_4d(dst, m, bar, c, w, h, n, off_w, off_h);
+  } else {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.im2col.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+        " [%0], [%1, {%3, %4, %5, %6}], [%2], {%7, %8};" ::"r"(dst),
+        "l"(reinterpret_cast<uint64_t>(m)), "r"(bar), "r"(c), "r"(w), "r"(h), "r"(n), "h"(off_w),
+        "h"(off_h)
+        : "memory");
+  }
+}
+// L2 prefetch of a tile a few ring stages ahead (no shared memory, no completion to wait for).
+__device__ __forceinline__ void tma_prefetch_3d(const CUtensorMap* m, int x, int y, int z) {
+  asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global.tile [%0, {%1, %2, %3}];" ::"l"(
+                   reinterpret_cast<uint64_t>(m)),
+               "r"(x), "r"(y), "r"(z)
+               : "memory");
+}
+template <int CG>
+__device__ __forceinline__ void tmem_alloc_cg(uint32_t smem_dst, uint32_t ncols) {
+  if constexpr (CG == 1) {
+    tmem_alloc(smem_dst, ncols);
+    tmem_relinquish();
+  } else {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst),
+                 "r"(ncols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+}
+template <int CG>
+__device__ __forceinline__ void tmem_dealloc_cg(uint32_t taddr, uint32_t ncols) {
+  if constexpr (CG == 1) {
+    tmem_dealloc(taddr, ncols);
+  } else {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols)
+                 : "memory");
+  }
+}
+template <int CG, int KIND>
+__device__ __forceinline__ void umma_cg(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                        uint32_t accumulate) {
+  if constexpr (CG == 1) {
+    if constexpr (KIND == 0)
+      umma_f16(d_tmem, adesc, bdesc, idesc, accumulate);
+    else
+      umma_i8(d_tmem, adesc, bdesc, idesc, accumulate);
+  } else if constexpr (KIND == 0) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t"
+        "}\n" ::"r"(d_tmem),
+        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, p;\n\t"
+        "}\n" ::"r"(d_tmem),
+        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+  }
+}
+// Commit to the mbarrier at shared::cta address `bar` in every CTA of the group: one arrival each
+// once all MMAs issued so far have completed.  With two CTAs this is two commits, one per CTA's
+// copy of the barrier (addressed through the cluster window).
+template <int CG>
+__device__ __forceinline__ void umma_commit_cg(uint32_t bar) {
+  if constexpr (CG == 1) {
+    umma_commit(bar);
+  } else {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                     mapa(bar, 0))
+                 : "memory");
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                     mapa(bar, 1))
+                 : "memory");
+  }
+}
+// Commit to this CTA's barrier only (used while draining after an abort).
+template <int CG>
+__device__ __forceinline__ void umma_commit_local(uint32_t bar) {
+  if constexpr (CG == 1) {
+    umma_commit(bar);
+  } else {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                     mapa(bar, 0))
+                 : "memory");
+  }
+}
+
 // ---- descriptors --------------------------------------------------------------------------
 // Shared-memory matrix descriptor (64 bit): start address, leading / stride byte offsets (all in
 // 16-byte units), descriptor version 1 (Blackwell), swizzle mode in bits 61..63.

@@ -51,6 +51,8 @@ class tileOp(SchedOp):
         conv = out.op.kind.startswith("conv")
         tile_n = genKey("P", stage_name, "n", param_name="tile_n")
         swz = genKey("P", stage_name, "k", param_name="swizzle_bytes")
+        cta_group = genKey("P", stage_name, "m", param_name="cta_group")
+        bn_cta = genKey("V", stage_name, "n", var_name="tile_n_per_cta")
         a_bytes = genKey("V", stage_name, "m", var_name="a_stage_bytes")
         b_bytes = genKey("V", stage_name, "n", var_name="b_stage_bytes")
         stage_bytes = genKey("V", stage_name, "k", var_name="stage_bytes")
@@ -69,12 +71,17 @@ class tileOp(SchedOp):
             km.addCandidates(tile_n, n_cands)
             km.define_value(swz, min(spans), max(spans), max(spans), True)
             km.addCandidates(swz, spans)
+            # 1: every CTA owns its MMAs; 2: a CTA pair shares them (256-row tiles, half of the
+            # tile's B rows staged per CTA), which needs more than one 128-row tile of work.
+            km.define_value(cta_group, 1, 2 if M > ctx.limits["tile_m"] else 1, 1, True)
+            km.define_value(bn_cta, 8, 256, n_cands[-1])
+            km.addProd([bn_cta, cta_group], tile_n)
             lim = ctx.limits["max_shared_memory_per_block"]
             km.define_value(a_bytes, 1, lim, ctx.limits["tile_m"] * max(spans))
             km.define_value(b_bytes, 1, lim, n_cands[-1] * max(spans))
             km.define_value(stage_bytes, 1, lim, (ctx.limits["tile_m"] + n_cands[-1]) * max(spans))
             km.addProd([ctx.limits["tile_m"], swz], a_bytes)
-            km.addProd([tile_n, swz], b_bytes)
+            km.addProd([bn_cta, swz], b_bytes)
             km.addSUM(stage_bytes, [a_bytes, b_bytes])
             if conv:
                 # MN-major filter tiles come in whole swizzle spans of output channels.
@@ -82,10 +89,11 @@ class tileOp(SchedOp):
                 nchunk = genKey("V", stage_name, "n", var_name="b_chunks")
                 km.define_value(chunk, 1, 256 * es, 256 * es)
                 km.define_value(nchunk, 1, 256, 1)
-                km.addProd([tile_n, es], chunk)
+                km.addProd([bn_cta, es], chunk)
                 km.addProd([nchunk, swz], chunk)
         ctx.kernel_knobs["tile_n"] = km.get_val(tile_n)
         ctx.kernel_knobs["swizzle_bytes"] = km.get_val(swz)
+        ctx.kernel_knobs["cta_group"] = km.get_val(cta_group)
         ctx.addSchedDesc("\n## tile 128 x %s, %s bytes of K per stage\n"
                          % (ctx.kernel_knobs["tile_n"], ctx.kernel_knobs["swizzle_bytes"]))
 

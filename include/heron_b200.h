@@ -61,6 +61,10 @@ typedef struct {
   int raster;        /* 0: consecutive tiles walk N first (default); 1: walk M first               */
   int epilogue;      /* 1: TMEM -> registers -> shared memory -> TMA store; 2: direct global stores */
   int max_ctas;      /* cap on the persistent grid (0: one CTA per SM)                             */
+  int cta_group;     /* 1: each CTA owns its MMAs (128 x tile_n tiles); 2: CTA pairs share them
+                        (tcgen05 cta_group::2, 256 x tile_n tiles, half of B staged per CTA)        */
+  int l2_prefetch;   /* ring stages ahead of the loads at which operand tiles are prefetched into
+                        L2; 0 = library default, -1 = off (gemm / bmm only)                         */
   int reserved;
 } hb_knobs;
 

@@ -125,8 +125,6 @@ def test_gemm_fp16(K, co, M, N, Kd, out_dtype):
     rng = np.random.default_rng(M + N + Kd)
     a = (rng.standard_normal((M, Kd)) / np.sqrt(Kd)).astype(np.float16)
     b = rng.standard_normal((N, Kd)).astype(np.float16)
-    if out_dtype == np.float16 and N % 8 != 0:
-        pytest.skip("fp16 rows must be 16-byte multiples for this case's epilogue")
     check(k_gemm(K, a, b, out_dtype=out_dtype), co.gemm_f16(a, b).astype(out_dtype), "gemm f16")
 
 
@@ -134,6 +132,8 @@ def test_gemm_fp16(K, co, M, N, Kd, out_dtype):
     dict(tile_n=32), dict(tile_n=96, stages=2), dict(tile_n=256, stages=1), dict(tile_n=128, acc_stages=1),
     dict(swizzle_bytes=64), dict(swizzle_bytes=32, tile_n=64), dict(epilogue=2), dict(epilogue=2, tile_n=160),
     dict(raster=1), dict(max_ctas=3), dict(tile_n=224, stages=3, raster=1),
+    dict(cta_group=1), dict(cta_group=2), dict(cta_group=2, tile_n=64, swizzle_bytes=64), dict(cta_group=1, tile_n=256),
+    dict(cta_group=2, epilogue=2, acc_stages=1), dict(cta_group=2, l2_prefetch=3), dict(cta_group=2, max_ctas=5),
 ])
 def test_gemm_every_knob_gives_the_same_bits(K, co, knobs):
     rng = np.random.default_rng(42)
@@ -152,7 +152,7 @@ def test_gemm_rejects_bad_arguments(K):
         K.gemm(a, b, knobs=dict(tile_n=48))
     assert e.value.status == HB_ERR_KNOB
     with pytest.raises(HeronB200Error) as e:
-        K.gemm(a[:, :60].contiguous()[:, :48].contiguous(), b[:, :48].contiguous(), knobs=dict(tile_n=256, stages=12))
+        K.gemm(a, b, knobs=dict(tile_n=256, stages=12))  # more shared memory than an SM has
     assert e.value.status == HB_ERR_KNOB
 
 
@@ -188,11 +188,12 @@ CONV_CASES = [
 
 
 @pytest.mark.parametrize("case", CONV_CASES)
-def test_conv_int8_exact(K, co, case):
+@pytest.mark.parametrize("cta_group", [1, 2])
+def test_conv_int8_exact(K, co, case, cta_group):
     N, H, W, CI, CO, KH, KW, s, p, d = case
     rng = np.random.default_rng(hash(case[:7]) % 1000)
     x, w = rand_i8(rng, (N, H, W, CI), False), rand_i8(rng, (KH, KW, CI, CO), True)
-    check(k_conv(K, x, w, s, p, d), co.conv2d_nhwc_int(x, w, s, p, d), str(case))
+    check(k_conv(K, x, w, s, p, d, knobs=dict(cta_group=cta_group)), co.conv2d_nhwc_int(x, w, s, p, d), str(case))
 
 
 @pytest.mark.parametrize("case", CONV_CASES + [(4, 9, 9, 16, 64, 3, 3, 1, 1, 1)])
