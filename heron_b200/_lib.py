@@ -19,6 +19,7 @@ HB_ERR_TIMEOUT = 5
 HB_ERR_DEVICE = 6
 HB_ERR_DTYPE = 7
 HB_ERR_SCRATCH = 8
+HB_ERR_STATIC_SCRATCH = 9
 
 # hb_dtype
 HB_F16, HB_F32, HB_S8, HB_U8, HB_S32 = 0, 1, 2, 3, 4
@@ -42,6 +43,8 @@ EXPORTED_SYMBOLS = (
     "hb_conv2d_nhwc",
     "hb_conv2d_packed_scratch_bytes",
     "hb_conv2d_nhwc_packed",
+    "hb_conv2d_packed_noalloc_max_bytes",
+    "hb_conv2d_nhwc_packed_noalloc",
     "hb_plan_gemm",
     "hb_plan_bmm",
     "hb_plan_conv2d_nhwc",
@@ -129,6 +132,10 @@ def load():
     lib.hb_conv2d_nhwc_packed.argtypes = (
         [c_void_p] * 3 + [c_int] * 12 + [c_int, c_void_p, c_size_t, kp, c_void_p]
     )
+    lib.hb_conv2d_packed_noalloc_max_bytes.restype = c_size_t
+    lib.hb_conv2d_packed_noalloc_max_bytes.argtypes = []
+    lib.hb_conv2d_nhwc_packed_noalloc.restype = c_int
+    lib.hb_conv2d_nhwc_packed_noalloc.argtypes = [c_void_p] * 3 + [c_int] * 12 + [c_int, kp, c_void_p]
     pp = ctypes.POINTER(c_void_p)
     lib.hb_plan_gemm.restype = c_int
     lib.hb_plan_gemm.argtypes = [pp] + lib.hb_gemm.argtypes[:-1]

@@ -275,7 +275,36 @@ struct hb_plan {
   int unpack_blocks, sco, KH;
 };
 
+// ---- built-in scratch for callers that cannot allocate ---------------------------------------
+// Device memory that lives inside the library image: every GPU that loads the library keeps
+// these bytes until the process exits.  Host code must not use the array's name as a pointer
+// (on the host it is only a handle for the runtime); set-up asks the runtime for the device
+// address once per device and the kernels get that address as an ordinary argument.
+#define HB_STATIC_SCRATCH_BYTES (4u << 20)
+static __device__ __align__(256) int8_t g_hb_static_scratch[HB_STATIC_SCRATCH_BYTES];
+
 namespace {
+
+constexpr int kMaxDevices = 64;
+void* g_static_scratch_addr[kMaxDevices] = {nullptr};
+std::mutex g_static_scratch_mutex;
+
+// Device address of g_hb_static_scratch on the current device (looked up on first use there).
+int static_scratch_address(void** out) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return HB_ERR_DEVICE;
+  std::lock_guard<std::mutex> lock(g_static_scratch_mutex);
+  if (g_static_scratch_addr[dev] == nullptr) {
+    void* ptr = nullptr;
+    if (cudaGetSymbolAddress(&ptr, g_hb_static_scratch) != cudaSuccess || ptr == nullptr) {
+      cudaGetLastError();  // leave no sticky error behind
+      return HB_ERR_LAUNCH;
+    }
+    g_static_scratch_addr[dev] = ptr;
+  }
+  *out = g_static_scratch_addr[dev];
+  return HB_OK;
+}
 
 int build_plan(Driver& d, const Problem& pr, const hb_knobs& k, const ConvGeom* cg, const void* A,
                const void* B, void* C, hb_plan* plan) {
@@ -596,6 +625,28 @@ int hb_conv2d_nhwc_packed(const void* in, const void* w_packed, void* out, int N
   return rc != HB_OK ? rc : run_plan(&plan, static_cast<cudaStream_t>(stream));
 }
 
+size_t hb_conv2d_packed_noalloc_max_bytes(void) { return HB_STATIC_SCRATCH_BYTES; }
+
+int hb_conv2d_nhwc_packed_noalloc(const void* in, const void* w_packed, void* out, int N, int H,
+                                  int W, int CI, int CO, int KH, int KW, int stride_h,
+                                  int stride_w, int pad, int dil_h, int dil_w, int sco,
+                                  const hb_knobs* knobs, void* stream) {
+  const size_t need = hb_conv2d_packed_scratch_bytes(CI, CO, KH, KW);
+  if (need == 0) return HB_ERR_SHAPE;
+  if (need > HB_STATIC_SCRATCH_BYTES) return HB_ERR_STATIC_SCRATCH;
+  Driver& d = driver();
+  if (d.status != HB_OK) return d.status;
+  void* scratch = nullptr;
+  int rc = static_scratch_address(&scratch);
+  if (rc != HB_OK) return rc;
+  // The unpack kernel rewrites every byte of the scratch the conv kernel will read (the whole
+  // KH*KW*CI*CO filter), so nothing left over from an earlier call can leak into this one.
+  hb_plan plan;
+  rc = plan_conv_packed(in, w_packed, out, N, H, W, CI, CO, KH, KW, stride_h, stride_w, pad, dil_h,
+                        dil_w, sco, scratch, HB_STATIC_SCRATCH_BYTES, knobs, &plan);
+  return rc != HB_OK ? rc : run_plan(&plan, static_cast<cudaStream_t>(stream));
+}
+
 int hb_plan_gemm(hb_plan** plan, const void* A, const void* B, void* C, int M, int K, int N,
                  hb_dtype in_a, hb_dtype in_b, hb_dtype out, const hb_knobs* knobs) {
   return new_plan(plan, [&](hb_plan* p) {
@@ -671,6 +722,8 @@ const char* hb_status_string(int status) {
     case HB_ERR_DEVICE: return "no usable sm_100 device";
     case HB_ERR_DTYPE: return "unsupported dtype combination";
     case HB_ERR_SCRATCH: return "scratch buffer missing or too small";
+    case HB_ERR_STATIC_SCRATCH:
+      return "filter does not fit the library's built-in 4 MiB scratch (hb_conv2d_nhwc_packed_noalloc)";
   }
   return "unknown status";
 }

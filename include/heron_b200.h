@@ -35,7 +35,8 @@ enum {
   HB_ERR_TIMEOUT = 5, /* a bounded device-side wait ran out; read by hb_last_status            */
   HB_ERR_DEVICE = 6,  /* no usable sm_100 device                                                 */
   HB_ERR_DTYPE = 7,   /* dtype combination the kernels do not implement                         */
-  HB_ERR_SCRATCH = 8  /* the caller's scratch buffer is missing or too small                    */
+  HB_ERR_SCRATCH = 8, /* the caller's scratch buffer is missing or too small                    */
+  HB_ERR_STATIC_SCRATCH = 9 /* the problem needs more than the library's built-in scratch array */
 };
 
 /* ---- element types ----------------------------------------------------------------------- */
@@ -128,6 +129,34 @@ int hb_conv2d_nhwc_packed(const void* in, const void* w_packed, void* out, int N
                           int CI, int CO, int KH, int KW, int stride_h, int stride_w, int pad,
                           int dil_h, int dil_w, int sco, void* scratch, size_t scratch_bytes,
                           const hb_knobs* knobs, void* stream);
+
+/*
+ * hb_conv2d_nhwc_packed without a scratch argument and without any allocation.  It has no
+ * counterpart in the reference: it exists because the reference's calling convention has no room
+ * for a workspace.  A built operator there receives exactly its tensors (input, filter, output;
+ * task/task.py:81) and nothing else, so a host that drives this library through that convention
+ * has no pointer to hand over, and it cannot call cudaMalloc either when the call sits inside a
+ * timed measurement loop (cudaMalloc synchronises the device and would be measured) or inside a
+ * region where allocation is forbidden outright, such as a stream capture or a serving loop with
+ * a fixed memory budget.
+ *
+ * The unpacked filter goes into an array that is part of the library image
+ * (hb_conv2d_packed_noalloc_max_bytes() = 4 MiB; every GPU that loads the library holds those
+ * 4 MiB until the process exits).  A filter with KH*KW*CI*CO bytes above that limit is refused
+ * with HB_ERR_STATIC_SCRATCH; use hb_conv2d_nhwc_packed with your own buffer instead.
+ *
+ * The first call on each device looks up the array's device address (cudaGetSymbolAddress);
+ * make that first call outside any stream capture.  All calls on a device share the one array,
+ * which keeps the last call's unpacked filter: every call rewrites all the bytes it later reads,
+ * so nothing needs clearing, but two calls whose kernels can overlap on the GPU (different
+ * streams, no dependency between them) race on it.  Calls on one stream are safe.
+ * The entry point calls no cudaMalloc / cudaFree and no library routine that allocates.
+ */
+size_t hb_conv2d_packed_noalloc_max_bytes(void);
+int hb_conv2d_nhwc_packed_noalloc(const void* in, const void* w_packed, void* out, int N, int H,
+                                  int W, int CI, int CO, int KH, int KW, int stride_h,
+                                  int stride_w, int pad, int dil_h, int dil_w, int sco,
+                                  const hb_knobs* knobs, void* stream);
 
 /*
  * Plans.  A plan is what the reference gets back from tvm.build on an instantiated schedule
