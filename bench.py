@@ -166,6 +166,9 @@ def run_ours(args):
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
     if world > 1:
+        # keep stdout to the one JSON line: NCCL's version banner goes to stdout at VERSION level
+        if os.environ.get("NCCL_DEBUG", "VERSION").upper() == "VERSION":
+            os.environ["NCCL_DEBUG"] = "WARN"
         dist.init_process_group("nccl", device_id=device)
 
     name = args.workload
@@ -262,10 +265,32 @@ def run_ours(args):
     e2e_ms = max(g0.elapsed_time(g1), (time.perf_counter() - w0) * 1e3) / e2e_steps
     barrier()
 
-    times = torch.tensor([elapsed_ms, e2e_ms], dtype=torch.float64, device=device)
+    # ---- sharded runs: compute + in-place all-gather of the whole output, reported separately ------
+    gather_ms = 0.0
+    if shards:
+        from heron_b200.multi import gather_output, shard_slice
+        full_shape = (units_total,) + tuple(targs[-1].shape[1:])
+        full = torch.empty(full_shape, dtype=TORCH_DTYPES[targs[-1].dtype], device=device)
+        gplan = handle.plan(*[to_dev(h, device) for h in host_in], shard_slice(full, rank, world))
+        gsteps = max(3, min(args.steps, 50))
+        for _ in range(3):
+            gplan.launch()
+            gather_output(full, rank, world)
+        barrier()
+        h0, h1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        h0.record()
+        for _ in range(gsteps):
+            gplan.launch()
+            gather_output(full, rank, world)
+        h1.record()
+        barrier()
+        gather_ms = h0.elapsed_time(h1) / gsteps
+        gather_bytes = full.numel() * full.element_size()
+
+    times = torch.tensor([elapsed_ms, e2e_ms, gather_ms], dtype=torch.float64, device=device)
     if world > 1:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
-    elapsed_ms, e2e_ms = float(times[0]), float(times[1])
+    elapsed_ms, e2e_ms, gather_ms = float(times[0]), float(times[1]), float(times[2])
     ms_per_step = elapsed_ms / args.steps
 
     if rank == 0:
@@ -308,6 +333,11 @@ def run_ours(args):
                            "3-stream pipeline of depth 2"},
             "gpu_launches": args.steps,
         }
+        if shards:
+            line["config"]["with_all_gather"] = {
+                "ms_per_step": round(gather_ms, 5),
+                "note": "kernel writes its shard into the full buffer, then one in-place NCCL all-gather; "
+                        "%.1f MB gathered per step" % (gather_bytes / 1e6)}
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline(name, budget_s=args.cpu_seconds)
         print(json.dumps(line), flush=True)
@@ -374,6 +404,7 @@ def time_cpu(fn, budget_s, min_calls=3):
 def cpu_baseline(name, budget_s=8.0):
     from heron_b200.workloads import CONFIGS
     from oracle import dlboost as dl
+    dl.set_threads(os.cpu_count() or 1)
     fn, ops, sample = cpu_problem(name)
     sec, calls = time_cpu(fn, budget_s)
     unit = "TFLOP/s" if CONFIGS[name]["in_dtype"] == "float16" else "TOP/s"
@@ -390,6 +421,7 @@ def run_reference(args):
         return
     from heron_b200.workloads import CONFIGS
     from oracle import dlboost as dl
+    dl.set_threads(os.cpu_count() or 1)  # torch.distributed.run exports OMP_NUM_THREADS=1
     name = args.workload
     cfg = CONFIGS[name]
     fn, ops, sample = cpu_problem(name, args.steps)

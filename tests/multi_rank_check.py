@@ -1,0 +1,62 @@
+"""Body of the multi-GPU check, one process per GPU (launched by tests/test_gpu_multi.py under
+torch.distributed.run).  Each rank computes its shard of a batched GEMM and of an NHWC conv with
+the sm_100a kernels, writing straight into its slice of a full-size output buffer; one in-place
+NCCL all-gather completes the buffer; every rank compares the whole result with the oracle."""
+import os
+import sys
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+
+def main():
+    rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=dev)
+    from heron_b200 import _lib, kernels as K
+    from heron_b200.multi import gather_output, partition, shard_case, shard_slice
+    from oracle import np_oracle as npo
+
+    rng = np.random.default_rng(4242)  # same stream on every rank
+    ok = True
+
+    # batched GEMM, batch 12 (equal shards) and 7 (ragged shards over 2 ranks)
+    for batch in (12, 7):
+        a = rng.integers(-128, 128, (batch, 192, 64)).astype(np.int8)
+        b = rng.integers(-128, 128, (batch, 160, 64)).astype(np.int8)
+        args, (start, count) = shard_case("bmm", [batch, 192, 64, 160], rank, world)
+        full = torch.full((batch, 192, 160), -1, dtype=torch.int32, device=dev)
+        mine = shard_slice(full, rank, world)
+        assert mine.shape[0] == count == args[0]
+        if count:
+            K.bmm(torch.from_numpy(a[start:start + count]).to(dev), torch.from_numpy(b[start:start + count]).to(dev),
+                  out=mine)
+        gather_output(full, rank, world)
+        ok &= bool(np.array_equal(full.cpu().numpy(), npo.bmm_int(a, b)))
+
+    # NHWC conv, 16 images
+    x = rng.integers(0, 256, (16, 7, 7, 64), dtype=np.uint8)
+    w = rng.integers(-128, 128, (3, 3, 64, 128)).astype(np.int8)
+    start, count = partition(16, world)[rank]
+    full = torch.full((16, 7, 7, 128), -1, dtype=torch.int32, device=dev)
+    K.conv2d_nhwc(torch.from_numpy(x[start:start + count]).to(dev), torch.from_numpy(w).to(dev), 1, 1, 1,
+                  out=shard_slice(full, rank, world))
+    gather_output(full, rank, world)
+    ok &= bool(np.array_equal(full.cpu().numpy(), npo.conv2d_nhwc_int(x, w, 1, 1, 1)))
+
+    ok &= _lib.last_status() == 0
+    flag = torch.tensor([1 if ok else 0], device=dev)
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    dist.destroy_process_group()
+    if rank == 0:
+        print("MULTI_RANK_CHECK", "PASS" if int(flag) == 1 else "FAIL", "world", world)
+    sys.exit(0 if int(flag) == 1 else 1)
+
+
+if __name__ == "__main__":
+    main()
