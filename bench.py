@@ -167,8 +167,7 @@ def run_ours(args):
     device = torch.device("cuda", local_rank)
     if world > 1:
         # keep stdout to the one JSON line: NCCL's version banner goes to stdout at VERSION level
-        if os.environ.get("NCCL_DEBUG", "VERSION").upper() == "VERSION":
-            os.environ["NCCL_DEBUG"] = "WARN"
+        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
         dist.init_process_group("nccl", device_id=device)
 
     name = args.workload

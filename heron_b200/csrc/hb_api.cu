@@ -18,7 +18,7 @@ namespace {
 using hb::KParams;
 
 constexpr int kSmemLimit = 232448;  // 227 KiB opt-in dynamic shared memory per CTA on sm_100
-constexpr int kSmemSlack = 1024 /*alignment*/ + 512 /*barriers*/;
+constexpr int kSmemSlack = 2048 /*alignment of the ring and of the epilogue staging*/ + 512 /*barriers*/;
 
 // ---- driver entry points (no link-time dependency on libcuda) -------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,

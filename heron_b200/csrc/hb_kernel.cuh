@@ -98,7 +98,8 @@ hb_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   const int b_bytes = bn_cta * p.SW;
   const uint32_t sA = smem_base;
   const uint32_t sB = sA + p.stages * a_bytes;
-  const uint32_t sEpi = sB + p.stages * b_bytes;
+  // the epilogue staging buffers are 128-byte swizzled: 1024-byte aligned whatever the ring size
+  const uint32_t sEpi = (sB + p.stages * b_bytes + 1023u) & ~1023u;
   const int epi_bytes = p.epilogue ? kEpiWarps * 2 * kEpiBufBytes : 0;
   SmemBars* bars = reinterpret_cast<SmemBars*>(smem + (sEpi - smem_base) + epi_bytes);
   volatile int* abort_flag = &bars->abort_flag;

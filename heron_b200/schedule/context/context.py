@@ -15,7 +15,7 @@ B200_LIMITS = {
     "tile_m": 128,
     "max_stages": 12,
     "epilogue_staging_bytes": 4 * 2 * 4096,
-    "smem_slack_bytes": 1024 + 512,
+    "smem_slack_bytes": 2048 + 512,
     "sm_count": 148,
 }
 

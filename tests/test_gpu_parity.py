@@ -362,3 +362,75 @@ def test_cfg5_through_the_x86_operator(K, co):
     out = poison(args[-1].shape, torch.int32)
     handle(dev(x), dev(wp), out)
     check(out, co.conv2d_nhwc_packed(x, wp, 1, 1, 1), "x86 c2d")
+
+
+def test_tuning_run_on_device_with_the_verify_hook(K, co, tmp_path):
+    """A short CGA run measured with CUDA events, every candidate checked against the oracle
+    through the reference's verify hook (Task.set_verify_func), then the best record re-applied."""
+    import json
+    import os
+    from heron_b200.config import Config
+    from heron_b200.environment import Env
+    from heron_b200.ops import cuda as heron_cuda
+    from heron_b200.runner import LocalRunner, measure_option
+    cfg = Config()
+    cfg.out_name, cfg.opt_method, cfg.max_trials = str(tmp_path), "CGA", 12
+    cfg.measure_time_per_round, cfg.pop_num, cfg.select_num, cfg.iter_walks, cfg.parallel = 6, 24, 12, 2, False
+    cfg.codegen_type = "GPU_TENSOR_CORE"
+    env = Env(measure_option(runner=LocalRunner(number=5, repeat=3)), cfg)
+    task = env.createTask("B", heron_cuda.getOpFromName("bmm"), [4, 256, 64, 256, "int8", "int32"], "cuda")
+
+    def reference(args):
+        rng = np.random.default_rng(5)
+        a, b = rand_i8(rng, (4, 256, 64), True), rand_i8(rng, (4, 256, 64), True)
+        return [a, b], co.bmm_int(a, b)
+
+    task.set_verify_func(reference, rtol=0.0)
+    random.seed(5)
+    np.random.seed(5)
+    env.tune("B")
+    rows = [json.loads(r) for r in open(os.path.join(cfg.log_dir, "records.txt"))]
+    assert len(rows) >= 6 and all(r["perf"] > 0 for r in rows), "a candidate failed or gave a wrong result"
+    handle, args = task.apply_best(os.path.join(cfg.log_dir, "records.txt"))
+    a, b = task.ref_input
+    out = poison(args[-1].shape, torch.int32)
+    handle(dev(a), dev(b), out)
+    check(out, task.ref_output, "best record")
+
+
+@pytest.mark.parametrize("op,args", [
+    ("bmm", [4, 256, 64, 256, "int8", "int32"]),
+    ("gemm", [640, 192, 480, "int8", "int32"]),
+    ("c2d_nhwc", [8, 9, 9, 64, 128, 3, 3, 1, 1, 1, "int8", "int32"]),
+])
+def test_many_random_knob_points(K, co, op, args):
+    """Sixty distinct feasible points of each operator's knob space, all bit-exact.  (A sweep like
+    this found a misaligned epilogue staging buffer for CTA pairs with 32-byte swizzle.)"""
+    from heron_b200.ops import cuda as heron_cuda
+    t = _task(heron_cuda, op, args, "GPU_TENSOR_CORE")
+    rng = np.random.default_rng(len(args))
+    if op == "bmm":
+        ins = [rand_i8(rng, (4, 256, 64), True), rand_i8(rng, (4, 256, 64), True)]
+        want = co.bmm_int(*ins)
+    elif op == "gemm":
+        ins = [rand_i8(rng, (640, 192), True), rand_i8(rng, (480, 192), True)]
+        want = co.gemm_int(*ins)
+    else:
+        ins = [rand_i8(rng, (8, 9, 9, 64), True), rand_i8(rng, (3, 3, 64, 128), True)]
+        want = co.conv2d_nhwc_int(ins[0], ins[1], 1, 1, 1)
+    tin = [dev(i) for i in ins]
+    random.seed(17)
+    seen = set()
+    for _ in range(200):
+        if len(seen) >= 60:
+            break
+        t.knob_manager.randSample()
+        handle, targs = t.instantiate(t.knob_manager)
+        key = tuple(sorted(handle.knobs.items()))
+        if key in seen:
+            continue
+        seen.add(key)
+        out = poison(targs[-1].shape, torch.int32)
+        handle(*tin, out)
+        check(out, want, str(handle.knobs))
+    assert len(seen) >= 40
