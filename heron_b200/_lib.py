@@ -70,11 +70,12 @@ class HbKnobs(ctypes.Structure):
         ("max_ctas", ctypes.c_int),
         ("cta_group", ctypes.c_int),
         ("l2_prefetch", ctypes.c_int),
+        ("conv_algo", ctypes.c_int),
         ("reserved", ctypes.c_int),
     ]
 
     FIELDS = ("tile_n", "stages", "swizzle_bytes", "acc_stages", "raster", "epilogue", "max_ctas",
-              "cta_group", "l2_prefetch", "reserved")
+              "cta_group", "l2_prefetch", "conv_algo", "reserved")
 
     @classmethod
     def from_dict(cls, d):

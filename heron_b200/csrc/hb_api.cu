@@ -5,6 +5,7 @@
 // maps travel as kernel parameters, and the device status word is a __device__ variable.
 #include "../../include/heron_b200.h"
 #include "hb_kernel.cuh"
+#include "hb_conv_strip.cuh"
 
 #include <cuda.h>
 #include <cuda_runtime.h>
@@ -72,6 +73,14 @@ Driver& driver() {
         reinterpret_cast<const void*>(&hb::hb_umma_kernel<2, 2, 0>),
         reinterpret_cast<const void*>(&hb::hb_umma_kernel<4, 2, 1>)};
     for (const void* k : kernels)
+      if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit) !=
+          cudaSuccess)
+        return;
+    const void* strip_kernels[3] = {
+        reinterpret_cast<const void*>(&hb::hb_conv_strip_kernel<4, 0>),
+        reinterpret_cast<const void*>(&hb::hb_conv_strip_kernel<2, 0>),
+        reinterpret_cast<const void*>(&hb::hb_conv_strip_kernel<4, 1>)};
+    for (const void* k : strip_kernels)
       if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit) !=
           cudaSuccess)
         return;
@@ -269,6 +278,9 @@ struct hb_plan {
   hb_knobs knobs;
   int grid;
   int smem;
+  // strip conv (conv_algo 2): its own parameter block; tmA = tiled input map, tmB = filter map
+  bool strip;
+  hb::StripParams sp;
   // packed-filter conv only: the unpack kernel that runs first on the same stream
   const void* packed_w;
   void* scratch;
@@ -422,6 +434,16 @@ int run_plan(const hb_plan* plan, cudaStream_t stream) {
         plan->KH, plan->p.KW, plan->p.CI, plan->sco);
     if (cudaGetLastError() != cudaSuccess) return HB_ERR_LAUNCH;
   }
+  if (plan->strip) {
+    const hb::StripParams& sp = plan->sp;
+    if (sp.esize_out == 2)
+      hb::hb_conv_strip_kernel<2, 0><<<plan->grid, hb::kThreads, plan->smem, stream>>>(plan->tmA, plan->tmB, sp);
+    else if (sp.esize_in == 2)
+      hb::hb_conv_strip_kernel<4, 0><<<plan->grid, hb::kThreads, plan->smem, stream>>>(plan->tmA, plan->tmB, sp);
+    else
+      hb::hb_conv_strip_kernel<4, 1><<<plan->grid, hb::kThreads, plan->smem, stream>>>(plan->tmA, plan->tmB, sp);
+    return cudaGetLastError() == cudaSuccess ? HB_OK : HB_ERR_LAUNCH;
+  }
   const bool half_out = plan->p.esize_out == 2;
   const bool i8 = plan->p.kind == 1;
   if (plan->knobs.cta_group == 2) {
@@ -552,6 +574,84 @@ int hb_conv2d_nhwc(const void* in, const void* w, void* out, int N, int H, int W
 }  // extern "C"
 
 namespace {
+
+// Shared-memory need of the strip algorithm for a geometry, or 0 when it does not apply.
+int strip_smem_bytes(const ConvGeom& g, int es, int eo, hb::StripParams* sp) {
+  if (g.stride_h != 1 || g.stride_w != 1) return 0;
+  if ((g.CI * es) % 128 != 0 || (g.CO * es) % 128 != 0) return 0;
+  if (g.CO > 256 || g.CO % (128 / eo) != 0 || g.CO % 16 != 0) return 0;
+  const int Wp = g.W + 2 * g.pad;
+  if (Wp > 128 || Wp < 1) return 0;
+  const int R = 128 / Wp;
+  const int strip_rows = R + (g.KH - 1) * g.dil_h;
+  if (strip_rows > 256) return 0;
+  const int max_off = (g.KH - 1) * g.dil_h * Wp + (g.KW - 1) * g.dil_w;
+  int px = strip_rows * Wp;
+  if (max_off + 128 > px) px = max_off + 128;
+  const int strip_bytes = (px * 128 + 1023) & ~1023;
+  const int n_cchunks = g.CI * es / 128;
+  const long long filt = static_cast<long long>(g.KH) * g.KW * g.CI * g.CO * es;
+  const long long smem = ((filt + 1023) & ~1023LL) + 2LL * n_cchunks * strip_bytes + 1024 + 256;
+  if (smem > kSmemLimit) return 0;
+  if (sp) {
+    sp->Wp = Wp; sp->R = R; sp->strip_rows = strip_rows; sp->strip_bytes = strip_bytes;
+    sp->n_cchunks = n_cchunks; sp->groups = (g.HO + R - 1) / R;
+  }
+  return static_cast<int>(smem);
+}
+
+int build_strip_plan(Driver& d, const ConvGeom& g, hb_dtype in_a, hb_dtype in_w, hb_dtype out_t,
+                     const hb_knobs& k, const void* in, const void* w, void* out, hb_plan* plan) {
+  const int es = esize(in_a), eo = esize(out_t);
+  std::memset(plan, 0, sizeof(*plan));
+  hb::StripParams& sp = plan->sp;
+  const int smem = strip_smem_bytes(g, es, eo, &sp);
+  if (smem == 0) return HB_ERR_KNOB;
+  const long long tiles = static_cast<long long>(g.N) * sp.groups;
+  if (tiles > 0x7fffffffLL) return HB_ERR_SHAPE;
+  sp.N = g.N; sp.H = g.H; sp.W = g.W; sp.CI = g.CI; sp.CO = g.CO; sp.KH = g.KH; sp.KW = g.KW;
+  sp.pad = g.pad; sp.dil_h = g.dil_h; sp.dil_w = g.dil_w; sp.HO = g.HO; sp.WO = g.WO;
+  sp.num_tiles = static_cast<int>(tiles);
+  sp.esize_in = es; sp.esize_out = eo;
+  sp.tmem_cols = next_pow2_cols(2 * g.CO);
+  const int kind = mma_kind(in_a, in_w, out_t);
+  sp.idesc = make_idesc(kind, in_a, in_w, hb::kTileM, g.CO, true);
+  sp.out = out;
+  sp.probe = k.reserved;
+  // input as a tiled (C, W, H, N) tensor: one box = 128 bytes of channels x padded width x strip rows
+  cuuint64_t dims[4] = {static_cast<cuuint64_t>(g.CI), static_cast<cuuint64_t>(g.W),
+                        static_cast<cuuint64_t>(g.H), static_cast<cuuint64_t>(g.N)};
+  cuuint64_t strides[3] = {static_cast<cuuint64_t>(g.CI) * es, static_cast<cuuint64_t>(g.W) * g.CI * es,
+                           static_cast<cuuint64_t>(g.H) * g.W * g.CI * es};
+  cuuint32_t box[4] = {static_cast<cuuint32_t>(128 / es), static_cast<cuuint32_t>(sp.Wp),
+                       static_cast<cuuint32_t>(sp.strip_rows), 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = d.tiled(&plan->tmA, tmap_dtype(in_a), 4, const_cast<void*>(in), dims, strides, box, estr,
+                       CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                       CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return HB_ERR_LAUNCH;
+  const long long K = static_cast<long long>(g.KH) * g.KW * g.CI;
+  const uint64_t rowB = static_cast<uint64_t>(g.CO) * es;
+  int rc = encode_tiled3(d, &plan->tmB, in_w, w, g.CO, K, 1, rowB, rowB * K, 128 / es, 128 / es, 128);
+  if (rc != HB_OK) return rc;
+  int grid = d.sm_count;
+  if (k.max_ctas > 0 && k.max_ctas < grid) grid = k.max_ctas;
+  if (sp.num_tiles < grid) grid = sp.num_tiles;
+  plan->strip = true;
+  plan->grid = grid;
+  plan->smem = smem;
+  plan->knobs = k;
+  plan->knobs.conv_algo = 2;
+  // fields hb_plan_knobs reports
+  plan->knobs.tile_n = g.CO; plan->knobs.swizzle_bytes = 128; plan->knobs.stages = 2;
+  plan->knobs.acc_stages = 2; plan->knobs.cta_group = 1; plan->knobs.epilogue = 2;
+  // the packed-filter wrapper reads these from the GEMM-view parameter block
+  plan->p.N = g.CO; plan->p.KW = g.KW; plan->p.CI = g.CI; plan->p.esize_out = eo;
+  return HB_OK;
+}
+}  // namespace
+
+namespace {
 int plan_conv(const void* in, const void* w, void* out, int N, int H, int W, int CI, int CO, int KH,
               int KW, int stride_h, int stride_w, int pad, int dil_h, int dil_w, hb_dtype in_a,
               hb_dtype in_w, hb_dtype out_t, const hb_knobs* knobs, hb_plan* plan) {
@@ -576,9 +676,27 @@ int plan_conv(const void* in, const void* w, void* out, int N, int H, int W, int
   Driver& d = driver();
   if (d.status != HB_OK) return d.status;
   Problem pr{2, 1, static_cast<int>(M), CO, static_cast<int>(K), in_a, in_w, out_t, true, CI};
+  ConvGeom cg{N, H, W, CI, CO, KH, KW, stride_h, stride_w, pad, dil_h, dil_w, HO, WO};
+  const int algo = knobs ? knobs->conv_algo : 0;
+  if (algo < 0 || algo > 2) return HB_ERR_KNOB;
+  if (algo != 1) {
+    hb::StripParams probe;
+    std::memset(&probe, 0, sizeof(probe));
+    const bool fits = strip_smem_bytes(cg, es, esize(out_t), &probe) != 0;
+    // Picked by default when the filter has more than one tap (so pixels would otherwise be
+    // re-fetched per tap), tiles fill at least three quarters of the 128 MMA rows, and the whole
+    // reduction is short enough that operand traffic, not tensor time, bounds the kernel.
+    const bool wanted = algo == 2 || (KH * KW > 1 && probe.R * probe.Wp >= 96 && K * es <= 2048);
+    if (algo == 2 && !fits) return HB_ERR_KNOB;
+    if (fits && wanted) {
+      hb_knobs k0;
+      if (knobs) k0 = *knobs; else std::memset(&k0, 0, sizeof(k0));
+      return build_strip_plan(d, cg, in_a, in_w, out_t, k0, in, w, out, plan);
+    }
+  }
   hb_knobs k;
   resolve_knobs(pr, knobs, d.sm_count, &k);
-  ConvGeom cg{N, H, W, CI, CO, KH, KW, stride_h, stride_w, pad, dil_h, dil_w, HO, WO};
+  k.conv_algo = 1;
   return build_plan(d, pr, k, &cg, in, w, out, plan);
 }
 

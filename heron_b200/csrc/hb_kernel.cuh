@@ -277,13 +277,22 @@ hb_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             break;
           }
           tc_fence_after();
-          const uint32_t a_lo = (((sA >> 4) + stage * a16) & 0x3FFFu) | a_lo_fixed;
+          uint32_t a_lo = (((sA >> 4) + stage * a16) & 0x3FFFu) | a_lo_fixed;
+          uint64_t a_hi_extra = 0;
+          if (probe >= 16) {
+            // diagnostic: start the A descriptor `shift` rows (128 bytes each) into the tile,
+            // with (probe >= 32) or without the descriptor's base-offset field set
+            const uint32_t shift = static_cast<uint32_t>(probe & 15);
+            const uint32_t addr = sA + stage * a_bytes + shift * 128u;
+            a_lo = ((addr >> 4) & 0x3FFFu) | a_lo_fixed;
+            if (probe >= 32) a_hi_extra = static_cast<uint64_t>((addr >> 7) & 7u) << 49;
+          }
           const uint32_t b_lo = (((sB >> 4) + stage * b16) & 0x3FFFu) | b_lo_fixed;
           if (probe != 2) {
 #pragma unroll
             for (int k = 0; k < 4; ++k) {
               if (k < n_mma) {
-                umma_cg<CG, KIND>(d_tmem, desc_hi | (a_lo + 2u * k), desc_hi | (b_lo + b_step16 * k), idesc,
+                umma_cg<CG, KIND>(d_tmem, desc_hi | a_hi_extra | (a_lo + 2u * k), desc_hi | (b_lo + b_step16 * k), idesc,
                                   accum);
                 accum = 1u;
               }

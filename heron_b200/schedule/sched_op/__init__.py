@@ -155,6 +155,47 @@ class epilogueOp(SchedOp):
         ctx.addSchedDesc("## epilogue mode %s\n" % ctx.kernel_knobs["epilogue"])
 
 
+class convAlgoOp(SchedOp):
+    """conv only: implicit GEMM with one im2col TMA per tap (1), or resident filter + one padded
+    input strip per tile (2).  The second exists only for stride-1 problems whose filter and two
+    strips fit shared memory and whose padded width fits the 128 MMA rows."""
+
+    def perform(self, s, stage_name, ctx):
+        km = ctx.knob_manager
+        out = _problem(s, stage_name)
+        if out.op.kind != "conv2d_nhwc":
+            return
+        p = out.op.params
+        algo = genKey("P", stage_name, "m", param_name="conv_algo")
+        if km.is_building:
+            es, eo = ELEM_BYTES[p["in_dtype"]], ELEM_BYTES[p["out_dtype"]]
+            km.define_value(algo, 1, 2 if strip_applies(p, es, eo, ctx.limits) else 1, 1, True)
+        ctx.kernel_knobs["conv_algo"] = km.get_val(algo)
+        ctx.addSchedDesc("## conv algorithm %s\n" % ctx.kernel_knobs["conv_algo"])
+
+
+def strip_applies(p, es, eo, limits):
+    """The strip kernel's own feasibility rule (mirrors the library's check)."""
+    sh, sw = p["stride"]
+    dh, dw = p["dilation"]
+    if (sh, sw) != (1, 1):
+        return False
+    CI, CO, KH, KW, pad = p["CI"], p["CO"], p["KH"], p["KW"], p["padding"]
+    if (CI * es) % 128 or (CO * es) % 128 or CO > 256 or CO % (128 // eo) or CO % 16:
+        return False
+    Wp = p["W"] + 2 * pad
+    if Wp > 128:
+        return False
+    R = 128 // Wp
+    strip_rows = R + (KH - 1) * dh
+    if strip_rows > 256:
+        return False
+    px = max(strip_rows * Wp, (KH - 1) * dh * Wp + (KW - 1) * dw + 128)
+    strip_bytes = (px * 128 + 1023) // 1024 * 1024
+    filt = (KH * KW * CI * CO * es + 1023) // 1024 * 1024
+    return filt + 2 * (CI * es // 128) * strip_bytes + 1024 + 256 <= limits["max_shared_memory_per_block"]
+
+
 class rasterOp(SchedOp):
     """Order in which the persistent CTAs walk the tile grid."""
 
@@ -172,6 +213,7 @@ _METHODS = {
     "pipelineOp": pipelineOp,
     "epilogueOp": epilogueOp,
     "rasterOp": rasterOp,
+    "convAlgoOp": convAlgoOp,
 }
 
 
@@ -188,5 +230,5 @@ def sched_via_rule(_type, ctx, s):
     that ``Task.instantiate`` can replay them (schedule/sched_op/__init__.py:23-30)."""
     get_op_methods(_type)
     for out in s.outputs:
-        for rule in ("tileOp", "pipelineOp", "epilogueOp", "rasterOp"):
+        for rule in ("tileOp", "pipelineOp", "epilogueOp", "rasterOp", "convAlgoOp"):
             ctx.addSched(rule, out.op.name, s)

@@ -66,7 +66,10 @@ typedef struct {
                         (tcgen05 cta_group::2, 256 x tile_n tiles, half of B staged per CTA)        */
   int l2_prefetch;   /* ring stages ahead of the loads at which operand tiles are prefetched into
                         L2; 0 = library default, -1 = off (gemm / bmm only)                         */
-  int reserved;
+  int conv_algo;     /* conv only.  1: implicit GEMM, one im2col TMA per filter tap; 2: resident
+                        filter + one padded input strip per tile (stride 1, filter fits shared
+                        memory, padded width <= 128); 0 = library picks                           */
+  int reserved;      /* diagnostic probe modes; leave 0                                            */
 } hb_knobs;
 
 /* Library / device facts. */

@@ -434,3 +434,61 @@ def test_many_random_knob_points(K, co, op, args):
         handle(*tin, out)
         check(out, want, str(handle.knobs))
     assert len(seen) >= 40
+
+
+STRIP_CASES = [
+    # N, H, W, CI, CO, KH, KW, pad, dil  (stride 1; filter + two strips fit shared memory)
+    (2, 8, 8, 64, 64, 3, 3, 1, 1),
+    (8, 56, 56, 64, 64, 3, 3, 1, 1),
+    (2, 12, 12, 64, 64, 3, 3, 0, 1),
+    (1, 100, 100, 64, 64, 1, 1, 0, 1),
+    (3, 13, 9, 64, 128, 3, 3, 2, 2),
+    (2, 57, 31, 128, 64, 3, 1, 1, 1),
+    (2, 126, 5, 64, 64, 3, 3, 1, 1),
+]
+
+
+@pytest.mark.parametrize("case", STRIP_CASES)
+def test_conv_strip_algorithm_fp16(K, co, case):
+    """The resident-filter / halo-strip conv kernel (conv_algo 2) against the oracle, and against
+    the implicit-GEMM kernel (conv_algo 1) on the same inputs."""
+    N, H, W, CI, CO, KH, KW, p, d = case
+    rng = np.random.default_rng(sum(case))
+    x = rng.standard_normal((N, H, W, CI)).astype(np.float16)
+    w = (rng.standard_normal((KH, KW, CI, CO)) / np.sqrt(KH * KW * CI)).astype(np.float16)
+    for od in (np.float32, np.float16):
+        want = co.conv2d_nhwc_f16(x, w, 1, p, d, od)
+        check(k_conv(K, x, w, 1, p, d, out_dtype=od, knobs=dict(conv_algo=2)), want, "strip %s" % (case,))
+        check(k_conv(K, x, w, 1, p, d, out_dtype=od, knobs=dict(conv_algo=1)), want, "im2col %s" % (case,))
+
+
+@pytest.mark.parametrize("case", [(3, 7, 7, 128, 128, 3, 3, 1, 1), (4, 28, 28, 128, 128, 3, 3, 1, 1),
+                                  (2, 30, 30, 256, 128, 1, 1, 0, 1)])
+def test_conv_strip_algorithm_int8(K, co, case):
+    N, H, W, CI, CO, KH, KW, p, d = case
+    rng = np.random.default_rng(sum(case))
+    x, w = rand_i8(rng, (N, H, W, CI), False), rand_i8(rng, (KH, KW, CI, CO), True)
+    check(k_conv(K, x, w, 1, p, d, knobs=dict(conv_algo=2)), co.conv2d_nhwc_int(x, w, 1, p, d), "strip int8")
+
+
+def test_conv_strip_refused_when_it_does_not_apply(K):
+    from heron_b200._lib import HB_ERR_KNOB, HeronB200Error
+    x = torch.zeros(2, 14, 14, 128, dtype=torch.float16, device="cuda")
+    w = torch.zeros(3, 3, 128, 256, dtype=torch.float16, device="cuda")  # 576 KiB filter
+    with pytest.raises(HeronB200Error) as e:
+        K.conv2d_nhwc(x, w, 1, 1, 1, knobs=dict(conv_algo=2))
+    assert e.value.status == HB_ERR_KNOB
+    w = torch.zeros(3, 3, 128, 64, dtype=torch.float16, device="cuda")
+    with pytest.raises(HeronB200Error) as e:
+        K.conv2d_nhwc(x, w, 2, 1, 1, knobs=dict(conv_algo=2))  # stride 2
+    assert e.value.status == HB_ERR_KNOB
+    K.conv2d_nhwc(x, w, 2, 1, 1)  # the default falls back to the implicit-GEMM kernel
+
+
+def test_default_picks_strip_for_resnet_stage2(K):
+    x = torch.zeros(8, 56, 56, 64, dtype=torch.float16, device="cuda")
+    w = torch.zeros(3, 3, 64, 64, dtype=torch.float16, device="cuda")
+    assert K.plan_conv2d_nhwc(x, w, 1, 1, 1).knobs()["conv_algo"] == 2
+    x = torch.zeros(16, 7, 7, 512, dtype=torch.uint8, device="cuda")
+    w = torch.zeros(3, 3, 512, 512, dtype=torch.int8, device="cuda")
+    assert K.plan_conv2d_nhwc(x, w, 1, 1, 1).knobs()["conv_algo"] == 1
