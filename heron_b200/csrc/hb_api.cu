@@ -236,6 +236,7 @@ int check_knobs(const Problem& pr, const hb_knobs& k, int* smem_bytes, int* tmem
   if (k.max_ctas < 0) return HB_ERR_KNOB;
   if (k.cta_group != 1 && k.cta_group != 2) return HB_ERR_KNOB;
   if (k.l2_prefetch < -1 || k.l2_prefetch > 64) return HB_ERR_KNOB;
+  if (k.tail_split != 0 && k.tail_split != 1 && k.tail_split != 2 && k.tail_split != 4) return HB_ERR_KNOB;
   if (pr.conv) {
     if ((pr.CI * es) % k.swizzle_bytes != 0) return HB_ERR_KNOB;
     // whole MN-major chunks in every CTA of the group
@@ -273,7 +274,7 @@ struct ConvGeom {
 // A launch-ready kernel configuration: encoded tensor maps, kernel parameters, grid and shared
 // memory size.  The counterpart of the module the reference gets back from tvm.build.
 struct hb_plan {
-  CUtensorMap tmA, tmB, tmC;
+  CUtensorMap tmA, tmB, tmC, tmB2;
   hb::KParams p;
   hb_knobs knobs;
   int grid;
@@ -417,10 +418,44 @@ int build_plan(Driver& d, const Problem& pr, const hb_knobs& k, const ConvGeom* 
       units = clusters;
   }
   if (k.max_ctas > 0 && k.max_ctas / cgrp < units) units = k.max_ctas / cgrp > 0 ? k.max_ctas / cgrp : 1;
-  if (p.num_tiles < units) units = p.num_tiles;
-  plan->grid = units * cgrp;
   plan->smem = smem;
   plan->knobs = k;
+
+  // Tail balancing: cut the tiles of the last partial wave into column slices when that shortens it.
+  auto slice_ok = [&](int s) {
+    const int bn = k.tile_n / s;
+    if (bn * s != k.tile_n || bn % ((eo == 2) ? 64 : 32) != 0 || (bn / cgrp) % 8 != 0 || bn % 16 != 0) return false;
+    if (pr.conv && ((bn / cgrp) * es) % k.swizzle_bytes != 0) return false;
+    return true;
+  };
+  const int tiles = p.num_tiles;
+  const int tail = tiles % units;
+  int split = 1;
+  if (k.tail_split > 1) {
+    if (!slice_ok(k.tail_split)) return HB_ERR_KNOB;
+    split = tail > 0 ? k.tail_split : 1;
+  } else if (k.tail_split == 0 && tail > 0 && p.num_kb >= 8) {
+    // (short reductions are output-bound: slicing their tiles only adds work items)
+    double best = 1.0;
+    for (int s2 = 2; s2 <= 4; s2 *= 2) {
+      if (!slice_ok(s2)) continue;
+      const double t = static_cast<double>((static_cast<long long>(s2) * tail + units - 1) / units) / s2;
+      if (t < best - 1e-9) { best = t; split = s2; }
+    }
+  }
+  p.split = split;
+  p.whole_tiles = split > 1 ? tiles - tail : tiles;
+  p.num_tiles = p.whole_tiles + (tiles - p.whole_tiles) * split;
+  p.idesc_split = make_idesc(kind, pr.in_a, pr.in_b, hb::kTileM * cgrp, k.tile_n / split, pr.conv);
+  plan->tmB2 = plan->tmB;
+  if (split > 1 && !pr.conv) {
+    const uint64_t rowA = static_cast<uint64_t>(pr.K) * es;
+    rc = encode_tiled3(d, &plan->tmB2, pr.in_b, B, pr.K, pr.N, pr.batch, rowA, rowA * pr.N, BK,
+                       k.tile_n / split / cgrp, k.swizzle_bytes);
+    if (rc != HB_OK) return rc;
+  }
+  plan->knobs.tail_split = split;
+  plan->grid = (p.num_tiles < units ? p.num_tiles : units) * cgrp;
   return HB_OK;
 }
 
@@ -468,7 +503,7 @@ int launch_kernel(const hb_plan* plan, cudaStream_t stream) {
   cfg.attrs = &attr;
   cfg.numAttrs = 1;
   const cudaError_t e = cudaLaunchKernelEx(&cfg, hb::hb_umma_kernel<OUT_BYTES, CG, KIND>, plan->tmA,
-                                           plan->tmB, plan->tmC, plan->p);
+                                           plan->tmB, plan->tmC, plan->tmB2, plan->p);
   return e == cudaSuccess ? HB_OK : HB_ERR_LAUNCH;
 }
 
@@ -591,9 +626,15 @@ int strip_smem_bytes(const ConvGeom& g, int es, int eo, hb::StripParams* sp) {
   const int strip_bytes = (px * 128 + 1023) & ~1023;
   const int n_cchunks = g.CI * es / 128;
   const long long filt = static_cast<long long>(g.KH) * g.KW * g.CI * g.CO * es;
-  const long long smem = ((filt + 1023) & ~1023LL) + 2LL * n_cchunks * strip_bytes + 1024 + 256;
+  long long smem = ((filt + 1023) & ~1023LL) + 2LL * n_cchunks * strip_bytes + 1024 + 256;
   if (smem > kSmemLimit) return 0;
+  int ring = 2;  // deeper when shared memory allows: more strips in flight hide HBM latency
+  while (ring < 4 && smem + static_cast<long long>(n_cchunks) * strip_bytes <= kSmemLimit) {
+    smem += static_cast<long long>(n_cchunks) * strip_bytes;
+    ++ring;
+  }
   if (sp) {
+    sp->ring = ring;
     sp->Wp = Wp; sp->R = R; sp->strip_rows = strip_rows; sp->strip_bytes = strip_bytes;
     sp->n_cchunks = n_cchunks; sp->groups = (g.HO + R - 1) / R;
   }
@@ -643,7 +684,7 @@ int build_strip_plan(Driver& d, const ConvGeom& g, hb_dtype in_a, hb_dtype in_w,
   plan->knobs = k;
   plan->knobs.conv_algo = 2;
   // fields hb_plan_knobs reports
-  plan->knobs.tile_n = g.CO; plan->knobs.swizzle_bytes = 128; plan->knobs.stages = 2;
+  plan->knobs.tile_n = g.CO; plan->knobs.swizzle_bytes = 128; plan->knobs.stages = sp.ring;
   plan->knobs.acc_stages = 2; plan->knobs.cta_group = 1; plan->knobs.epilogue = 2;
   // the packed-filter wrapper reads these from the GEMM-view parameter block
   plan->p.N = g.CO; plan->p.KW = g.KW; plan->p.CI = g.CI; plan->p.esize_out = eo;

@@ -15,7 +15,7 @@
 // address, so a descriptor may start at any 128-byte row.  One tile = R = floor(128 / Wp) output
 // rows of one image = one 128-row MMA per (tap, 32 bytes of channels).
 //
-// Roles as in hb_umma_kernel: warp 0 loads (filter once, then strips into a two-deep ring),
+// Roles as in hb_umma_kernel: warp 0 loads (filter once, then strips into a ring of two to four buffers),
 // warp 1 issues MMAs into one of two TMEM accumulators, warps 2..5 read the accumulator and store
 // the valid positions straight to global memory (each thread owns one output pixel: CO
 // contiguous elements).  All waits are bounded, with the same abort protocol.
@@ -35,6 +35,7 @@ struct StripParams {
   int num_tiles;
   int esize_in, esize_out;
   int tmem_cols;
+  int ring;   // strip buffers in flight (2..4)
   int probe;  // diagnostic: 2 = no MMAs, 3 = epilogue only hands the accumulator back, 4 = strips loaded once
   uint32_t idesc;
   void* out;
@@ -42,8 +43,8 @@ struct StripParams {
 
 struct StripBars {
   uint64_t filt_full;
-  uint64_t strip_full[2];
-  uint64_t strip_empty[2];
+  uint64_t strip_full[4];
+  uint64_t strip_empty[4];
   uint64_t tmem_full[2];
   uint64_t tmem_empty[2];
   uint64_t drain;
@@ -76,7 +77,7 @@ hb_conv_strip_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_cons
   const int strip_total = p.n_cchunks * p.strip_bytes;
   const uint32_t sFilt = smem_base;
   const uint32_t sStrip = sFilt + ((filt_bytes + 1023) & ~1023);
-  StripBars* bars = reinterpret_cast<StripBars*>(smem + (sStrip - smem_base) + 2 * strip_total);
+  StripBars* bars = reinterpret_cast<StripBars*>(smem + (sStrip - smem_base) + p.ring * strip_total);
   volatile int* abort_flag = &bars->abort_flag;
 
   const int warp = threadIdx.x >> 5;
@@ -84,9 +85,11 @@ hb_conv_strip_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_cons
 
   if (threadIdx.x == 0) {
     mbar_init(smem_u32(&bars->filt_full), 1);
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < 4; ++i) {
       mbar_init(smem_u32(&bars->strip_full[i]), 1);
       mbar_init(smem_u32(&bars->strip_empty[i]), 1);
+    }
+    for (int i = 0; i < 2; ++i) {
       mbar_init(smem_u32(&bars->tmem_full[i]), 1);
       mbar_init(smem_u32(&bars->tmem_empty[i]), kEpiWarps);
     }
@@ -129,10 +132,10 @@ hb_conv_strip_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_cons
           break;
         }
         const uint32_t full = smem_u32(&bars->strip_full[buf]);
-        if (p.probe == 4 && issued >= 2) {
+        if (p.probe == 4 && issued >= p.ring) {
           mbar_arrive(full);
           ++issued;
-          if (++buf == 2) {
+          if (++buf == p.ring) {
             buf = 0;
             phase ^= 1u;
           }
@@ -143,17 +146,17 @@ hb_conv_strip_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_cons
           tma_load_4d(sStrip + buf * strip_total + cc * p.strip_bytes, &tmIn, full, cc * BK, -p.pad,
                       y0 - p.pad, n);
         ++issued;
-        if (++buf == 2) {
+        if (++buf == p.ring) {
           buf = 0;
           phase ^= 1u;
         }
       }
       if (!ok) {
         mbar_wait_drain(smem_u32(&bars->filt_full), 0u);
-        const int pending = issued < 2 ? issued : 2;
+        const int pending = issued < p.ring ? issued : p.ring;
         for (int i = 0; i < pending; ++i) {
           if (--buf < 0) {
-            buf = 1;
+            buf = p.ring - 1;
             phase ^= 1u;
           }
           mbar_wait_drain(smem_u32(&bars->strip_full[buf]), phase);
@@ -206,7 +209,7 @@ hb_conv_strip_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_cons
           }
         umma_commit(smem_u32(&bars->strip_empty[buf]));
         umma_commit(smem_u32(&bars->tmem_full[acc]));
-        if (++buf == 2) {
+        if (++buf == p.ring) {
           buf = 0;
           phase ^= 1u;
         }

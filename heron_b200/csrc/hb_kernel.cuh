@@ -52,6 +52,11 @@ struct KParams {
   int stages, acc_stages, tmem_cols;
   int tiles_m, tiles_n, num_tiles, num_kb;
   int raster, kind, b_mn_major, a_im2col, epilogue, l2_prefetch, probe;
+  // Tail balancing: the first `whole_tiles` tiles are 128*CG x BN; each remaining tile is cut into
+  // `split` column slices of BN/split, so that the last, partly filled wave of the persistent
+  // grid is made of shorter work items.  num_tiles counts work items (whole tiles + slices).
+  int whole_tiles, split;
+  uint32_t idesc_split;
   uint32_t idesc;
   // conv geometry (a_im2col only)
   int HO, WO, KW, CI, kb_per_tap, stride_h, stride_w, dil_h, dil_w, pad;
@@ -85,7 +90,8 @@ __device__ __forceinline__ void mbar_wait_drain(uint32_t bar, uint32_t parity) {
 template <int OUT_BYTES, int CG, int KIND>
 __global__ void __launch_bounds__(kThreads, 1)
 hb_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-               const __grid_constant__ CUtensorMap tmC, const KParams p) {
+               const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmB2,
+               const KParams p) {
   extern __shared__ uint8_t smem_raw[];
   // Swizzled TMA boxes and UMMA descriptors want 1024-byte aligned stage bases.
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -135,6 +141,23 @@ hb_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   const int first_tile = blockIdx.x / CG;  // a pair of CTAs walks the tile list together
   const int tile_step = gridDim.x / CG;
   const int tile_rows = kTileM * CG;
+  // work item -> (batch, first row of the pair tile, first column, width)
+  auto decode = [&](int t, int& b, int& m_pair, int& n_first, int& bn) {
+    int slice = 0;
+    bn = p.BN;
+    if (t >= p.whole_tiles) {
+      const int h = t - p.whole_tiles;
+      slice = h % p.split;
+      t = p.whole_tiles + h / p.split;
+      bn = p.BN / p.split;
+    }
+    b = t / tiles_per_batch;
+    const int r = t - b * tiles_per_batch;
+    const int mb = p.raster ? (r % p.tiles_m) : (r / p.tiles_n);
+    const int nb = p.raster ? (r / p.tiles_m) : (r % p.tiles_n);
+    m_pair = mb * tile_rows;
+    n_first = nb * p.BN + slice * bn;
+  };
 
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------------------
@@ -147,15 +170,15 @@ hb_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       long long issued = 0;
       bool ok = true;
       const int chunk_cols = p.SW / p.esize_in;               // MN-major B: columns per chunk
-      const int n_chunks = p.b_mn_major ? bn_cta / chunk_cols : 1;
-      const uint32_t tx_bytes = static_cast<uint32_t>(a_bytes + b_bytes) * CG;
       for (int t = first_tile; ok && t < p.num_tiles; t += tile_step) {
-        const int b = t / tiles_per_batch;
-        const int r = t - b * tiles_per_batch;
-        const int mb = p.raster ? (r % p.tiles_m) : (r / p.tiles_n);
-        const int nb = p.raster ? (r / p.tiles_m) : (r % p.tiles_n);
-        const int m0 = mb * tile_rows + static_cast<int>(cta_rank) * kTileM;
-        const int n0 = nb * p.BN + static_cast<int>(cta_rank) * bn_cta;
+        int b, m_pair, n_first, bn;
+        decode(t, b, m_pair, n_first, bn);
+        const int bn_mine = bn / CG;  // B rows this CTA stages for this work item
+        const int n_chunks = p.b_mn_major ? bn_mine / chunk_cols : 1;
+        const uint32_t tx_bytes = static_cast<uint32_t>(a_bytes + bn_mine * p.SW) * CG;
+        const CUtensorMap* tmBk = (bn == p.BN) ? &tmB : &tmB2;  // K-major B: box rows = bn / CG
+        const int m0 = m_pair + static_cast<int>(cta_rank) * kTileM;
+        const int n0 = n_first + static_cast<int>(cta_rank) * bn_mine;
         int pix_w = 0, pix_h = 0, pix_n = 0;
         if (p.a_im2col) {
           const int hw = p.HO * p.WO;
@@ -201,14 +224,14 @@ hb_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             krow = kb * BK;
             if (p.l2_prefetch > 0 && kb + p.l2_prefetch < p.num_kb) {
               tma_prefetch_3d(&tmA, (kb + p.l2_prefetch) * BK, m0, b);
-              tma_prefetch_3d(&tmB, (kb + p.l2_prefetch) * BK, n0, b);
+              tma_prefetch_3d(tmBk, (kb + p.l2_prefetch) * BK, n0, b);
             }
           }
           if (p.b_mn_major) {
             for (int j = 0; j < n_chunks; ++j)
               tma_load_3d_cg<CG>(dB + j * (BK * p.SW), &tmB, full, n0 + j * chunk_cols, krow, b);
           } else {
-            tma_load_3d_cg<CG>(dB, &tmB, full, krow, n0, b);
+            tma_load_3d_cg<CG>(dB, tmBk, full, krow, n0, b);
           }
           ++issued;
           if (++stage == p.stages) {
@@ -270,6 +293,7 @@ hb_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * p.BN);
+        const uint32_t idesc_t = (t >= p.whole_tiles) ? p.idesc_split : idesc;
         uint32_t accum = 0u;
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(full0 + 8u * stage, phase, abort_flag)) {
@@ -292,7 +316,7 @@ hb_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 #pragma unroll
             for (int k = 0; k < 4; ++k) {
               if (k < n_mma) {
-                umma_cg<CG, KIND>(d_tmem, desc_hi | a_hi_extra | (a_lo + 2u * k), desc_hi | (b_lo + b_step16 * k), idesc,
+                umma_cg<CG, KIND>(d_tmem, desc_hi | a_hi_extra | (a_lo + 2u * k), desc_hi | (b_lo + b_step16 * k), idesc_t,
                                   accum);
                 accum = 1u;
               }
@@ -329,12 +353,9 @@ hb_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     constexpr int kColsPerStore = 128 / OUT_BYTES;  // 32 (4-byte) or 64 (fp16) columns
     const uint32_t my_buf = sEpi + ew * 2 * kEpiBufBytes;
     for (int t = first_tile; ok && t < p.num_tiles; t += tile_step) {
-      const int b = t / tiles_per_batch;
-      const int r = t - b * tiles_per_batch;
-      const int mb = p.raster ? (r % p.tiles_m) : (r / p.tiles_n);
-      const int nb = p.raster ? (r / p.tiles_m) : (r % p.tiles_n);
-      const int row0 = mb * tile_rows + static_cast<int>(cta_rank) * kTileM + q * 32;
-      const int n0 = nb * p.BN;
+      int b, m_pair, n0, bn;
+      decode(t, b, m_pair, n0, bn);
+      const int row0 = m_pair + static_cast<int>(cta_rank) * kTileM + q * 32;
       if (!mbar_wait(smem_u32(&bars->tmem_full[acc]), acc_phase, abort_flag)) {
         ok = false;
         break;
@@ -342,31 +363,37 @@ hb_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       tc_fence_after();
       const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) +
                               static_cast<uint32_t>(acc * p.BN);
-      for (int c0 = 0; c0 < p.BN; c0 += kColsPerStore) {
-        uint32_t v[32];
+      // Software pipeline over 128-byte column chunks: the TMEM load of chunk i+1 is in flight
+      // while chunk i goes through shared memory to its TMA store.
+      uint32_t v[32];
+      uint32_t v2[OUT_BYTES == 2 ? 32 : 1];
+      tmem_ld_32x32(t_addr, v);
+      if (OUT_BYTES == 2) tmem_ld_32x32(t_addr + 32, reinterpret_cast<uint32_t(&)[32]>(v2));
+      for (int c0 = 0; c0 < bn; c0 += kColsPerStore) {
         uint32_t packed[32];  // 128 bytes of output for this thread's row
+        tmem_ld_wait();
         if (OUT_BYTES == 4) {
-          tmem_ld_32x32(t_addr + c0, v);
-          tmem_ld_wait();
 #pragma unroll
           for (int i = 0; i < 32; ++i) packed[i] = v[i];
         } else {
-          tmem_ld_32x32(t_addr + c0, v);
-          tmem_ld_wait();
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
             __half2 h = __floats2half2_rn(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1]));
             packed[i] = *reinterpret_cast<uint32_t*>(&h);
           }
-          tmem_ld_32x32(t_addr + c0 + 32, v);
-          tmem_ld_wait();
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
-            __half2 h = __floats2half2_rn(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1]));
+            __half2 h = __floats2half2_rn(__uint_as_float(v2[(2 * i) % (OUT_BYTES == 2 ? 32 : 1)]),
+                                          __uint_as_float(v2[(2 * i + 1) % (OUT_BYTES == 2 ? 32 : 1)]));
             packed[16 + i] = *reinterpret_cast<uint32_t*>(&h);
           }
         }
-        if (c0 + kColsPerStore >= p.BN) {
+        if (c0 + kColsPerStore < bn) {
+          tmem_ld_32x32(t_addr + c0 + kColsPerStore, v);
+          if (OUT_BYTES == 2)
+            tmem_ld_32x32(t_addr + c0 + kColsPerStore + 32, reinterpret_cast<uint32_t(&)[32]>(v2));
+        }
+        if (c0 + kColsPerStore >= bn) {
           // Last read of this accumulator: hand it back to the MMA warp before storing.
           tc_fence_before();
           __syncwarp();

@@ -69,6 +69,8 @@ typedef struct {
   int conv_algo;     /* conv only.  1: implicit GEMM, one im2col TMA per filter tap; 2: resident
                         filter + one padded input strip per tile (stride 1, filter fits shared
                         memory, padded width <= 128); 0 = library picks                           */
+  int tail_split;    /* the tiles of the last, partly filled wave of the persistent grid are cut into
+                        this many column slices (1, 2 or 4); 0 = library picks                      */
   int reserved;      /* diagnostic probe modes; leave 0                                            */
 } hb_knobs;
 
