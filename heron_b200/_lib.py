@@ -43,6 +43,9 @@ EXPORTED_SYMBOLS = (
     "hb_conv2d_nhwc",
     "hb_conv2d_packed_scratch_bytes",
     "hb_conv2d_nhwc_packed",
+    "hb_conv2d_nchw_scratch_bytes",
+    "hb_conv2d_nchw",
+    "hb_plan_conv2d_nchw",
     "hb_conv2d_packed_noalloc_max_bytes",
     "hb_conv2d_nhwc_packed_noalloc",
     "hb_plan_gemm",
@@ -138,7 +141,13 @@ def load():
     lib.hb_conv2d_packed_noalloc_max_bytes.argtypes = []
     lib.hb_conv2d_nhwc_packed_noalloc.restype = c_int
     lib.hb_conv2d_nhwc_packed_noalloc.argtypes = [c_void_p] * 3 + [c_int] * 12 + [c_int, kp, c_void_p]
+    lib.hb_conv2d_nchw_scratch_bytes.restype = c_size_t
+    lib.hb_conv2d_nchw_scratch_bytes.argtypes = [c_int] * 10 + [c_int, c_int]
+    lib.hb_conv2d_nchw.restype = c_int
+    lib.hb_conv2d_nchw.argtypes = [c_void_p] * 3 + [c_int] * 10 + [c_int] * 3 + [c_void_p, c_size_t, kp, c_void_p]
     pp = ctypes.POINTER(c_void_p)
+    lib.hb_plan_conv2d_nchw.restype = c_int
+    lib.hb_plan_conv2d_nchw.argtypes = [pp] + lib.hb_conv2d_nchw.argtypes[:-1]
     lib.hb_plan_gemm.restype = c_int
     lib.hb_plan_gemm.argtypes = [pp] + lib.hb_gemm.argtypes[:-1]
     lib.hb_plan_bmm.restype = c_int

@@ -282,6 +282,13 @@ struct hb_plan {
   // strip conv (conv_algo 2): its own parameter block; tmA = tiled input map, tmB = filter map
   bool strip;
   hb::StripParams sp;
+  // NCHW conv only: layout transposes before (input, filter) and after (output) the conv kernel
+  struct Glue {
+    const void* src; void* dst;
+    int esize, R, C, Rp, Cp, batch;
+    long long rs, cs, bs;
+  } glue_pre[2], glue_post;
+  int n_glue_pre; bool has_glue_post;
   // packed-filter conv only: the unpack kernel that runs first on the same stream
   const void* packed_w;
   void* scratch;
@@ -462,7 +469,34 @@ int build_plan(Driver& d, const Problem& pr, const hb_knobs& k, const ConvGeom* 
 template <int OUT_BYTES, int CG, int KIND>
 int launch_kernel(const hb_plan* plan, cudaStream_t stream);
 
+int run_glue(const hb_plan::Glue& g, cudaStream_t stream) {
+  dim3 grid((g.Cp + 31) / 32, (g.Rp + 31) / 32, g.batch), block(32, 8);
+  if (grid.y > 65535 || grid.z > 65535) return HB_ERR_SHAPE;
+  if (g.esize == 1)
+    hb::hb_transpose_pad_kernel<uint8_t><<<grid, block, 0, stream>>>(
+        static_cast<const uint8_t*>(g.src), static_cast<uint8_t*>(g.dst), g.R, g.C, g.Rp, g.Cp, g.rs, g.cs, g.bs);
+  else if (g.esize == 2)
+    hb::hb_transpose_pad_kernel<uint16_t><<<grid, block, 0, stream>>>(
+        static_cast<const uint16_t*>(g.src), static_cast<uint16_t*>(g.dst), g.R, g.C, g.Rp, g.Cp, g.rs, g.cs, g.bs);
+  else
+    hb::hb_transpose_pad_kernel<uint32_t><<<grid, block, 0, stream>>>(
+        static_cast<const uint32_t*>(g.src), static_cast<uint32_t*>(g.dst), g.R, g.C, g.Rp, g.Cp, g.rs, g.cs, g.bs);
+  return cudaGetLastError() == cudaSuccess ? HB_OK : HB_ERR_LAUNCH;
+}
+
+int run_main(const hb_plan* plan, cudaStream_t stream);
+
 int run_plan(const hb_plan* plan, cudaStream_t stream) {
+  for (int i = 0; i < plan->n_glue_pre; ++i) {
+    const int rc = run_glue(plan->glue_pre[i], stream);
+    if (rc != HB_OK) return rc;
+  }
+  int rc = run_main(plan, stream);
+  if (rc != HB_OK) return rc;
+  return plan->has_glue_post ? run_glue(plan->glue_post, stream) : HB_OK;
+}
+
+int run_main(const hb_plan* plan, cudaStream_t stream) {
   if (plan->packed_w) {
     hb::hb_unpack_filter_kernel<<<plan->unpack_blocks, 256, 0, stream>>>(
         static_cast<const int8_t*>(plan->packed_w), static_cast<int8_t*>(plan->scratch), plan->p.N,
@@ -552,9 +586,93 @@ int conv_out_extent(int in, int k, int stride, int pad, int dil) {
   return (in - span + 2 * pad) / stride + 1;
 }
 
+
+size_t align256(size_t v) { return (v + 255) & ~static_cast<size_t>(255); }
+
+struct NchwLayout {
+  int CIp, HO, WO;
+  size_t in_bytes, w_bytes, out_bytes, total;
+};
+
+bool nchw_layout(int N, int H, int W, int CI, int CO, int KH, int KW, int sh, int sw, int pad,
+                 hb_dtype in_a, hb_dtype out_t, NchwLayout* L) {
+  const int es = esize(in_a), eo = esize(out_t);
+  if (es == 0 || eo == 0 || N <= 0 || H <= 0 || W <= 0 || CI <= 0 || CO <= 0 || KH <= 0 || KW <= 0 ||
+      sh <= 0 || sw <= 0 || pad < 0)
+    return false;
+  const int gran = 32 / es;  // the NHWC kernels want whole 32-byte channel groups
+  L->CIp = (CI + gran - 1) / gran * gran;
+  L->HO = conv_out_extent(H, KH, sh, pad, 1);
+  L->WO = conv_out_extent(W, KW, sw, pad, 1);
+  if (L->HO <= 0 || L->WO <= 0) return false;
+  L->in_bytes = align256(static_cast<size_t>(N) * H * W * L->CIp * es);
+  L->w_bytes = align256(static_cast<size_t>(KH) * KW * L->CIp * CO * es);
+  L->out_bytes = align256(static_cast<size_t>(N) * L->HO * L->WO * CO * eo);
+  L->total = L->in_bytes + L->w_bytes + L->out_bytes;
+  return true;
+}
+
+int plan_conv_nchw(const void* in, const void* w, void* out, int N, int H, int W, int CI, int CO,
+                   int KH, int KW, int sh, int sw, int pad, hb_dtype in_a, hb_dtype in_w,
+                   hb_dtype out_t, void* scratch, size_t scratch_bytes, const hb_knobs* knobs,
+                   hb_plan* plan) {
+  NchwLayout L;
+  if (!nchw_layout(N, H, W, CI, CO, KH, KW, sh, sw, pad, in_a, out_t, &L)) return HB_ERR_SHAPE;
+  if (esize(in_w) != esize(in_a)) return HB_ERR_DTYPE;
+  if (!scratch || scratch_bytes < L.total) return HB_ERR_SCRATCH;
+  if (!in || !w || !out) return HB_ERR_ALIGN;
+  if ((reinterpret_cast<uintptr_t>(scratch) & 255u) != 0) return HB_ERR_ALIGN;
+  uint8_t* s_in = static_cast<uint8_t*>(scratch);
+  uint8_t* s_w = s_in + L.in_bytes;
+  uint8_t* s_out = s_w + L.w_bytes;
+  const int rc = plan_conv(s_in, s_w, s_out, N, H, W, L.CIp, CO, KH, KW, sh, sw, pad, 1, 1, in_a, in_w,
+                           out_t, knobs, plan);
+  if (rc != HB_OK) return rc;
+  const int es = esize(in_a), eo = esize(out_t);
+  const int T = KH * KW;
+  // input (N, CI, H*W) -> (N, H*W, CIp)
+  plan->glue_pre[0] = hb_plan::Glue{in, s_in, es, CI, H * W, L.CIp, H * W, N,
+                                    static_cast<long long>(H) * W, 1, static_cast<long long>(CI) * H * W};
+  // filter (CO, CI, T) -> (T, CIp, CO)
+  plan->glue_pre[1] = hb_plan::Glue{w, s_w, es, CO, CI, CO, L.CIp, T,
+                                    static_cast<long long>(CI) * T, T, 1};
+  plan->n_glue_pre = 2;
+  // output (N, HO*WO, CO) -> (N, CO, HO*WO)
+  const int P = L.HO * L.WO;
+  plan->glue_post = hb_plan::Glue{s_out, out, eo, P, CO, P, CO, N, CO, 1, static_cast<long long>(P) * CO};
+  plan->has_glue_post = true;
+  return HB_OK;
+}
 }  // namespace
 
 extern "C" {
+
+size_t hb_conv2d_nchw_scratch_bytes(int N, int H, int W, int CI, int CO, int KH, int KW,
+                                    int stride_h, int stride_w, int pad, hb_dtype in_a,
+                                    hb_dtype out_t) {
+  NchwLayout L;
+  return nchw_layout(N, H, W, CI, CO, KH, KW, stride_h, stride_w, pad, in_a, out_t, &L) ? L.total : 0;
+}
+
+int hb_conv2d_nchw(const void* in, const void* w, void* out, int N, int H, int W, int CI, int CO,
+                   int KH, int KW, int stride_h, int stride_w, int pad, hb_dtype in_a,
+                   hb_dtype in_w, hb_dtype out_t, void* scratch, size_t scratch_bytes,
+                   const hb_knobs* knobs, void* stream) {
+  hb_plan plan;
+  const int rc = plan_conv_nchw(in, w, out, N, H, W, CI, CO, KH, KW, stride_h, stride_w, pad, in_a,
+                                in_w, out_t, scratch, scratch_bytes, knobs, &plan);
+  return rc != HB_OK ? rc : run_plan(&plan, static_cast<cudaStream_t>(stream));
+}
+
+int hb_plan_conv2d_nchw(hb_plan** plan, const void* in, const void* w, void* out, int N, int H,
+                        int W, int CI, int CO, int KH, int KW, int stride_h, int stride_w, int pad,
+                        hb_dtype in_a, hb_dtype in_w, hb_dtype out_t, void* scratch,
+                        size_t scratch_bytes, const hb_knobs* knobs) {
+  return new_plan(plan, [&](hb_plan* p) {
+    return plan_conv_nchw(in, w, out, N, H, W, CI, CO, KH, KW, stride_h, stride_w, pad, in_a, in_w,
+                          out_t, scratch, scratch_bytes, knobs, p);
+  });
+}
 
 int hb_version(void) { return 100; }
 

@@ -506,4 +506,28 @@ __global__ void hb_unpack_filter_kernel(const int8_t* __restrict__ packed, int8_
   }
 }
 
+// Batched transpose with zero padding, the layout glue of the NCHW operator:
+//   dst[b][j][i] = (i < R && j < C) ? src[b*src_bs + i*src_rs + j*src_cs] : 0,   j < Cp, i < Rp
+// with dst dense ([Cp][Rp] per batch).  32 x 32 tiles through shared memory so that both the
+// reads (along j when src_cs == 1) and the writes (along i) are coalesced.
+template <typename T>
+__global__ void hb_transpose_pad_kernel(const T* __restrict__ src, T* __restrict__ dst, int R, int C,
+                                        int Rp, int Cp, long long src_rs, long long src_cs,
+                                        long long src_bs) {
+  __shared__ T tile[32][33];
+  const int b = blockIdx.z;
+  const int i0 = blockIdx.y * 32, j0 = blockIdx.x * 32;
+  const T* s = src + static_cast<long long>(b) * src_bs;
+  T* d = dst + static_cast<long long>(b) * Cp * Rp;
+  for (int ii = threadIdx.y; ii < 32; ii += blockDim.y) {
+    const int i = i0 + ii, j = j0 + threadIdx.x;
+    tile[ii][threadIdx.x] = (i < R && j < C) ? s[i * src_rs + j * src_cs] : T(0);
+  }
+  __syncthreads();
+  for (int jj = threadIdx.y; jj < 32; jj += blockDim.y) {
+    const int j = j0 + jj, i = i0 + threadIdx.x;
+    if (j < Cp && i < Rp) d[static_cast<long long>(j) * Rp + i] = tile[threadIdx.x][jj];
+  }
+}
+
 }  // namespace hb

@@ -143,6 +143,42 @@ def conv2d_nhwc_packed(x, w_packed, CO, KH, KW, stride=1, padding=0, dilation=1,
     return out
 
 
+def _nchw_common(x, w, stride, padding, out, out_dtype, scratch):
+    N, CI, H, W = x.shape
+    CO, CI2, KH, KW = w.shape
+    if CI != CI2:
+        raise ValueError("input channels of x and w differ")
+    sh, sw = _pair(stride)
+    HO, WO = conv_out_hw(H, W, KH, KW, stride, padding, 1)
+    if out is None:
+        out = torch.empty((N, CO, HO, WO), dtype=out_dtype or default_out_dtype(x.dtype), device=x.device)
+    need = _lib.load().hb_conv2d_nchw_scratch_bytes(N, H, W, CI, CO, KH, KW, sh, sw, int(padding), _code(x),
+                                                   _code(out))
+    if scratch is None:
+        scratch = torch.empty(need, dtype=torch.uint8, device=x.device)
+    return (N, H, W, CI, CO, KH, KW, sh, sw, int(padding)), out, scratch
+
+
+def conv2d_nchw(x, w, stride=1, padding=0, out=None, out_dtype=None, scratch=None, knobs=None):
+    """out[n,c,p,q] = sum pad(x)[n,ci,p*s+kh,q*s+kw] * w[c,ci,kh,kw]; x NCHW, w OIHW, dilation 1."""
+    dims, out, scratch = _nchw_common(x, w, stride, padding, out, out_dtype, scratch)
+    rc = _lib.load().hb_conv2d_nchw(_dev(x, "x"), _dev(w, "w"), _dev(out, "out"), *dims, _code(x), _code(w),
+                                    _code(out), _dev(scratch, "scratch"), scratch.numel(), _knobs(knobs),
+                                    _stream(x))
+    _lib.check(rc, "hb_conv2d_nchw")
+    return out
+
+
+def plan_conv2d_nchw(x, w, stride=1, padding=0, out=None, out_dtype=None, scratch=None, knobs=None):
+    dims, out, scratch = _nchw_common(x, w, stride, padding, out, out_dtype, scratch)
+    h = ctypes.c_void_p()
+    rc = _lib.load().hb_plan_conv2d_nchw(ctypes.byref(h), _dev(x, "x"), _dev(w, "w"), _dev(out, "out"), *dims,
+                                         _code(x), _code(w), _code(out), _dev(scratch, "scratch"),
+                                         scratch.numel(), _knobs(knobs))
+    _lib.check(rc, "hb_plan_conv2d_nchw")
+    return Plan(h, (x, w, scratch), out)
+
+
 class Plan:
     """A launch-ready kernel bound to fixed buffers (hb_plan): build once, launch many times.
 

@@ -35,6 +35,11 @@ def _gemm_view(out):
         return 1, p["M"], p["N"], p["K"], p["K"]
     if out.op.kind == "bmm":
         return p["batch"], p["M"], p["N"], p["K"], p["K"]
+    if out.op.kind == "conv2d_nchw":
+        N, HO, WO = out.shape[0], out.shape[2], out.shape[3]
+        gran = 32 // ELEM_BYTES[p["in_dtype"]]
+        ci = (p["CI"] + gran - 1) // gran * gran  # channels are zero-padded to 32-byte groups
+        return 1, N * HO * WO, p["CO"], p["KH"] * p["KW"] * ci, ci
     N, HO, WO = out.shape[0], out.shape[1], out.shape[2]
     return 1, N * HO * WO, p["CO"], p["KH"] * p["KW"] * p["CI"], p["CI"]
 

@@ -44,6 +44,10 @@ class KernelHandle:
             fn = K.plan_conv2d_nhwc if planned else K.conv2d_nhwc
             return fn(x, w, stride=p["stride"], padding=p["padding"], dilation=p["dilation"], out=out,
                       knobs=knobs)
+        if kind == "conv2d_nchw":
+            x, w, out = tensors
+            fn = K.plan_conv2d_nchw if planned else K.conv2d_nchw
+            return fn(x, w, stride=p["stride"], padding=p["padding"], out=out, knobs=knobs)
         if kind == "conv2d_nhwc_packed":
             x, w, out = tensors
             fn = K.plan_conv2d_nhwc_packed if planned else K.conv2d_nhwc_packed

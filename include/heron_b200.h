@@ -136,6 +136,25 @@ int hb_conv2d_nhwc_packed(const void* in, const void* w_packed, void* out, int N
                           const hb_knobs* knobs, void* stream);
 
 /*
+ * NCHW conv2d, the operator the reference's network tables use
+ * (ops/cuda/conv2d.py:9-135; tests/figure10/configs/resnet50.json):
+ *   out[n,c,p,q] = sum_{ci,kh,kw} pad(in)[n, ci, p*sh+kh, q*sw+kw] * w[c,ci,kh,kw]
+ * `in` (N,CI,H,W), `w` (CO,CI,KH,KW), `out` (N,CO,HO,WO), dilation 1 (the reference asserts it).
+ * The reference lowers it to an explicit im2col GEMM; here two small transposes bring input and
+ * filter to NHWC / HWIO in `scratch` (channels zero-padded to a 32-byte multiple, which also
+ * covers the reference's CI == 3 special case: its zero-padded filter taps add nothing), the
+ * NHWC kernel runs, and a third transpose writes NCHW.  `scratch` is caller-owned device memory,
+ * 256-byte aligned, of at least hb_conv2d_nchw_scratch_bytes(...) bytes.
+ */
+size_t hb_conv2d_nchw_scratch_bytes(int N, int H, int W, int CI, int CO, int KH, int KW,
+                                    int stride_h, int stride_w, int pad, hb_dtype in_a,
+                                    hb_dtype out_t);
+int hb_conv2d_nchw(const void* in, const void* w, void* out, int N, int H, int W, int CI, int CO,
+                   int KH, int KW, int stride_h, int stride_w, int pad, hb_dtype in_a,
+                   hb_dtype in_w, hb_dtype out_t, void* scratch, size_t scratch_bytes,
+                   const hb_knobs* knobs, void* stream);
+
+/*
  * hb_conv2d_nhwc_packed without a scratch argument and without any allocation.  It has no
  * counterpart in the reference: it exists because the reference's calling convention has no room
  * for a workspace.  A built operator there receives exactly its tensors (input, filter, output;
@@ -184,6 +203,10 @@ int hb_plan_conv2d_nhwc_packed(hb_plan** plan, const void* in, const void* w_pac
                                int N, int H, int W, int CI, int CO, int KH, int KW, int stride_h,
                                int stride_w, int pad, int dil_h, int dil_w, int sco, void* scratch,
                                size_t scratch_bytes, const hb_knobs* knobs);
+int hb_plan_conv2d_nchw(hb_plan** plan, const void* in, const void* w, void* out, int N, int H,
+                        int W, int CI, int CO, int KH, int KW, int stride_h, int stride_w, int pad,
+                        hb_dtype in_a, hb_dtype in_w, hb_dtype out_t, void* scratch,
+                        size_t scratch_bytes, const hb_knobs* knobs);
 int hb_plan_launch(const hb_plan* plan, void* stream);
 /* The knobs after defaults were resolved, the persistent grid and the dynamic shared memory. */
 int hb_plan_knobs(const hb_plan* plan, hb_knobs* knobs, int* grid, int* smem_bytes);

@@ -127,3 +127,21 @@ def conv2d_nhwc_packed(x, w_packed, stride=1, pad=0, dilation=1):
     lib().oracle_conv2d_nhwc_packed(_p(x), _p(w_packed), _p(out), N, H, W, CI, OC * sco, KH, KW, sh,
                                     sw, pad, dh, dw, sco)
     return out
+
+
+def conv2d_nchw(x, w, stride=1, pad=0, out_dtype=None):
+    """NCHW input, OIHW filter; integer operands give int32, fp16 operands float32 (or fp16)."""
+    x, w = _c(x), _c(w)
+    N, CI, H, W = x.shape
+    CO, _, KH, KW = w.shape
+    sh, sw = _pair(stride)
+    HO, WO = _out_hw(H, W, KH, KW, stride, pad, 1)
+    if x.dtype == np.float16:
+        half = out_dtype is not None and np.dtype(out_dtype) == np.float16
+        out = np.empty((N, CO, HO, WO), dtype=np.float16 if half else np.float32)
+        lib().oracle_conv2d_nchw(_p(x), _p(w), _p(out), N, H, W, CI, CO, KH, KW, sh, sw, pad, 2 if half else 1, 0, 0)
+    else:
+        out = np.empty((N, CO, HO, WO), dtype=np.int32)
+        lib().oracle_conv2d_nchw(_p(x), _p(w), _p(out), N, H, W, CI, CO, KH, KW, sh, sw, pad, 0, _signed(x),
+                                 _signed(w))
+    return out

@@ -242,3 +242,44 @@ void oracle_conv2d_nhwc_f16(const uint16_t* in, const uint16_t* w, void* out, in
         }
       }
 }
+
+/*
+ * NCHW conv, the operator of the reference's network tables (ops/cuda/conv2d.py:9-101), written
+ * as the direct sum its im2col GEMM computes:
+ *   out[n,c,p,q] = sum_{ci,kh,kw} pad(in)[n, ci, p*sh+kh, q*sw+kw] * w[c,ci,kh,kw]
+ * `mode` 0: uint8/int8 operands (signedness flags), int32 output.  `mode` 1: binary16 operands,
+ * double accumulation, float output; `mode` 2: the same rounded to binary16.
+ */
+void oracle_conv2d_nchw(const void* in, const void* w, void* out, int N, int H, int W, int CI, int CO,
+                        int KH, int KW, int sh, int sw, int pad, int mode, int in_signed,
+                        int w_signed) {
+  const int HO = oracle_conv_out_extent(H, KH, sh, pad, 1);
+  const int WO = oracle_conv_out_extent(W, KW, sw, pad, 1);
+  for (int n = 0; n < N; ++n)
+    for (int c = 0; c < CO; ++c)
+      for (int p = 0; p < HO; ++p)
+        for (int q = 0; q < WO; ++q) {
+          int32_t iacc = 0;
+          double facc = 0.0;
+          for (int ci = 0; ci < CI; ++ci)
+            for (int kh = 0; kh < KH; ++kh) {
+              const int iy = p * sh + kh - pad;
+              if (iy < 0 || iy >= H) continue;
+              for (int kw = 0; kw < KW; ++kw) {
+                const int ix = q * sw + kw - pad;
+                if (ix < 0 || ix >= W) continue;
+                const size_t ii = (((size_t)n * CI + ci) * H + iy) * W + ix;
+                const size_t wi = (((size_t)c * CI + ci) * KH + kh) * KW + kw;
+                if (mode == 0)
+                  iacc += load_i8(in, ii, in_signed) * load_i8(w, wi, w_signed);
+                else
+                  facc += (double)half_to_float(((const uint16_t*)in)[ii]) *
+                          (double)half_to_float(((const uint16_t*)w)[wi]);
+              }
+            }
+          const size_t oi = (((size_t)n * CO + c) * HO + p) * WO + q;
+          if (mode == 0) ((int32_t*)out)[oi] = iacc;
+          else if (mode == 1) ((float*)out)[oi] = (float)facc;
+          else ((uint16_t*)out)[oi] = float_to_half_rn((float)facc);
+        }
+}

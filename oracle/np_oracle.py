@@ -113,3 +113,37 @@ def conv2d_nhwc_packed(x, w_packed, stride=1, pad=0, dilation=1):
     out = conv2d_nhwc_int(x, unpack_filter_x86(w_packed), stride, pad, dilation)
     N, HO, WO, CO = out.shape
     return out.reshape(N, HO, WO, OC, sco)
+
+
+def _nchw_im2col(x, w, stride, pad):
+    """The reference's own lowering of the NCHW operator (ops/cuda/conv2d.py:51-86): pad the
+    input, build A[MM, MK] with MM = N*HO*WO rows and MK = CI*KH*KW columns ordered (ci, kh, kw),
+    B[CO, MK] from the OIHW filter; C = B . A^T; output[n, c, p, q] = C[c, n*HO*WO + p*WO + q]."""
+    sh, sw = _pair(stride)
+    N, CI, H, W = x.shape
+    CO, _, KH, KW = w.shape
+    HO = conv_out_extent(H, KH, sh, pad, 1)
+    WO = conv_out_extent(W, KW, sw, pad, 1)
+    xp = np.zeros((N, CI, H + 2 * pad, W + 2 * pad), dtype=x.dtype)
+    xp[:, :, pad:pad + H, pad:pad + W] = x
+    A = np.empty((N, HO, WO, CI, KH, KW), dtype=x.dtype)
+    for kh in range(KH):
+        for kw in range(KW):
+            A[:, :, :, :, kh, kw] = xp[:, :, kh: kh + (HO - 1) * sh + 1: sh,
+                                       kw: kw + (WO - 1) * sw + 1: sw].transpose(0, 2, 3, 1)
+    return A.reshape(N * HO * WO, CI * KH * KW), w.reshape(CO, CI * KH * KW), (N, CO, HO, WO)
+
+
+def conv2d_nchw_int(x, w, stride=1, pad=0):
+    """uint8/int8 NCHW input, OIHW filter, int32 NCHW output (ops/cuda/conv2d.py:9-101)."""
+    A, B, (N, CO, HO, WO) = _nchw_im2col(x, w, stride, pad)
+    C = _to_i32(_as_i64(B) @ _as_i64(A).T)
+    return np.ascontiguousarray(C.reshape(CO, N, HO, WO).transpose(1, 0, 2, 3))
+
+
+def conv2d_nchw_f16(x, w, stride=1, pad=0, out_dtype=np.float32):
+    assert x.dtype == np.float16 and w.dtype == np.float16
+    A, B, (N, CO, HO, WO) = _nchw_im2col(x, w, stride, pad)
+    C = (B.astype(np.float64) @ A.astype(np.float64).T).astype(np.float32)
+    out = np.ascontiguousarray(C.reshape(CO, N, HO, WO).transpose(1, 0, 2, 3))
+    return out.astype(np.float16) if np.dtype(out_dtype) == np.float16 else out

@@ -492,3 +492,54 @@ def test_default_picks_strip_for_resnet_stage2(K):
     x = torch.zeros(16, 7, 7, 512, dtype=torch.uint8, device="cuda")
     w = torch.zeros(3, 3, 512, 512, dtype=torch.int8, device="cuda")
     assert K.plan_conv2d_nhwc(x, w, 1, 1, 1).knobs()["conv_algo"] == 1
+
+
+NCHW_CASES = [
+    # N, CI, H, W, CO, KH, KW, stride, pad
+    (2, 3, 32, 32, 64, 7, 7, 2, 3),      # the first-layer shape family (3 input channels)
+    (2, 64, 14, 14, 64, 3, 3, 1, 1),
+    (2, 64, 14, 14, 256, 1, 1, 1, 0),
+    (2, 256, 14, 14, 128, 1, 1, 2, 0),
+    (3, 16, 9, 11, 40, 3, 3, (2, 1), 1),
+]
+
+
+@pytest.mark.parametrize("case", NCHW_CASES)
+def test_conv_nchw_fp16(K, co, case):
+    N, CI, H, W, CO, KH, KW, s, p = case
+    rng = np.random.default_rng(sum(x if isinstance(x, int) else 3 for x in case))
+    x = rng.standard_normal((N, CI, H, W)).astype(np.float16)
+    w = (rng.standard_normal((CO, CI, KH, KW)) / np.sqrt(CI * KH * KW)).astype(np.float16)
+    for od, tdt in ((np.float32, torch.float32), (np.float16, torch.float16)):
+        want = co.conv2d_nchw(x, w, s, p, od)
+        out = poison(want.shape, tdt)
+        K.conv2d_nchw(dev(x), dev(w), stride=s, padding=p, out=out)
+        check(out, want, "nchw %s" % (case,))
+
+
+def test_conv_nchw_int8_and_plan(K, co):
+    rng = np.random.default_rng(12)
+    x, w = rand_i8(rng, (2, 32, 10, 10), False), rand_i8(rng, (48, 32, 3, 3), True)
+    want = co.conv2d_nchw(x, w, 1, 1)
+    out = poison(want.shape, torch.int32)
+    plan = K.plan_conv2d_nchw(dev(x), dev(w), stride=1, padding=1, out=out)
+    plan.launch()
+    check(out, want, "nchw int8")
+    out.view(torch.uint8).fill_(0xCD)
+    plan.launch()
+    check(out, want, "nchw int8 relaunch")
+
+
+def test_conv_nchw_through_the_registry(K, co):
+    """`c2d` of the tensor-core registry, with a ResNet-50 table row scaled down in batch."""
+    from heron_b200.ops import cuda as heron_cuda
+    t = _task(heron_cuda, "c2d", [4, 28, 28, 128, 128, 3, 3, 1, 1, 1, "float16", "float16"], "GPU_TENSOR_CORE")
+    t.knob_manager.randSample()
+    handle, args = t.instantiate(t.knob_manager)
+    assert [a.shape for a in args] == [(4, 128, 28, 28), (128, 128, 3, 3), (4, 128, 28, 28)]
+    rng = np.random.default_rng(3)
+    x = rng.standard_normal(args[0].shape).astype(np.float16)
+    w = (rng.standard_normal(args[1].shape) / 34.0).astype(np.float16)
+    out = poison(args[2].shape, torch.float16)
+    handle(dev(x), dev(w), out)
+    check(out, co.conv2d_nchw(x, w, 1, 1, np.float16), "c2d registry")

@@ -32,6 +32,7 @@ def test_registry_names_and_signatures():
     assert heron_cuda.getOpFromName("bmm").__name__ == "heron_batch_matmul"
     assert heron_cuda.getOpFromName("c2d_nhwc").__name__ == "heron_conv2d_nhwc_tensorcore"
     assert heron_cpu.getOpFromName("c2d").__name__ == "heron_conv2d_nhwc"
+    assert heron_cuda.getOpFromName("c2d").__name__ == "heron_conv2d_nchw_tensorcore"
     with pytest.raises(NotImplementedError):
         heron_cuda.getOpFromName("gemv")
     with pytest.raises(KeyError):

@@ -150,3 +150,22 @@ def test_cpu_baseline_matches_oracle(dl):
         got = dl.GemmF16(37, 100, 19)(af, bf)
         want = npo.gemm_f16(af, bf)
         assert np.abs(got - want).max() <= 1e-3 * np.abs(want).max()
+
+
+def test_nchw_operator_three_ways(co):
+    """The NCHW operator: the reference's im2col formulation (numpy), the direct sum (C), and the
+    NHWC restatement on transposed tensors all agree to the bit."""
+    rng = np.random.default_rng(21)
+    for (N, CI, H, W, CO, KH, KW, s, p) in [(2, 3, 9, 9, 8, 7, 7, 2, 3), (1, 16, 6, 7, 5, 3, 3, 1, 1),
+                                            (2, 32, 5, 5, 16, 1, 1, 2, 0)]:
+        x = rng.integers(0, 256, (N, CI, H, W), dtype=np.uint8)
+        w = rng.integers(-128, 128, (CO, CI, KH, KW)).astype(np.int8)
+        a = npo.conv2d_nchw_int(x, w, s, p)
+        b = co.conv2d_nchw(x, w, s, p)
+        c = npo.conv2d_nhwc_int(np.ascontiguousarray(x.transpose(0, 2, 3, 1)),
+                                np.ascontiguousarray(w.transpose(2, 3, 1, 0)), s, p, 1).transpose(0, 3, 1, 2)
+        assert np.array_equal(a, b) and np.array_equal(a, c)
+        xf = rng.standard_normal((N, CI, H, W)).astype(np.float16)
+        wf = rng.standard_normal((CO, CI, KH, KW)).astype(np.float16)
+        for od in (np.float32, np.float16):
+            assert np.array_equal(npo.conv2d_nchw_f16(xf, wf, s, p, od), co.conv2d_nchw(xf, wf, s, p, od))
