@@ -189,7 +189,7 @@ def run_ours(args):
 
     # Rotating buffer sets: more bytes than L2 (126 MB) between two uses of the same set.
     set_bytes = sum(int(np.prod(a.shape)) * torch.empty(0, dtype=TORCH_DTYPES[a.dtype]).element_size() for a in targs)
-    n_sets = max(2, min(8, int(np.ceil(300e6 / max(set_bytes, 1))) + 1))
+    n_sets = max(2, min(16, int(np.ceil(300e6 / max(set_bytes, 1))) + 1))
     sets = []
     for _ in range(n_sets):
         ins = [to_dev(h, device) for h in host_in]

@@ -40,52 +40,65 @@ struct Driver {
   int status = HB_ERR_DEVICE;
 };
 
+// Per-device set-up (kernel attributes are per device): done the first time a device is current
+// when an entry point runs.  Driver entry points are process-wide.
+constexpr int kMaxDev = 64;
+
+bool setup_device(Driver* d) {
+  cudaDeviceProp prop;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return false;
+  if (cudaGetDeviceProperties(&prop, dev) != cudaSuccess) return false;
+  if (prop.major != 10) return false;
+  d->sm_count = prop.multiProcessorCount;
+  // Opt in to the large dynamic shared-memory carve-out for every kernel instantiation.
+  const void* kernels[9] = {
+      reinterpret_cast<const void*>(&hb::hb_umma_kernel<4, 1, 0>),
+      reinterpret_cast<const void*>(&hb::hb_umma_kernel<2, 1, 0>),
+      reinterpret_cast<const void*>(&hb::hb_umma_kernel<4, 1, 1>),
+      reinterpret_cast<const void*>(&hb::hb_umma_kernel<4, 2, 0>),
+      reinterpret_cast<const void*>(&hb::hb_umma_kernel<2, 2, 0>),
+      reinterpret_cast<const void*>(&hb::hb_umma_kernel<4, 2, 1>),
+      reinterpret_cast<const void*>(&hb::hb_conv_strip_kernel<4, 0>),
+      reinterpret_cast<const void*>(&hb::hb_conv_strip_kernel<2, 0>),
+      reinterpret_cast<const void*>(&hb::hb_conv_strip_kernel<4, 1>)};
+  for (const void* k : kernels)
+    if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit) != cudaSuccess)
+      return false;
+  return true;
+}
+
 Driver& driver() {
-  static Driver d;
-  static std::once_flag once;
-  std::call_once(once, [] {
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess) return;
-    cudaDeviceProp prop;
-    if (cudaGetDeviceProperties(&prop, dev) != cudaSuccess) return;
-    if (prop.major != 10) return;
-    d.sm_count = prop.multiProcessorCount;
-    cudaDriverGetVersion(&d.driver_version);
-    void* fn = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) !=
-            cudaSuccess ||
-        q != cudaDriverEntryPointSuccess || fn == nullptr)
-      return;
-    d.tiled = reinterpret_cast<EncodeTiledFn>(fn);
-    fn = nullptr;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeIm2col", &fn, cudaEnableDefault, &q) !=
-            cudaSuccess ||
-        q != cudaDriverEntryPointSuccess || fn == nullptr)
-      return;
-    d.im2col = reinterpret_cast<EncodeIm2colFn>(fn);
-    // Opt in to the large dynamic shared-memory carve-out once per instantiation.
-    const void* kernels[6] = {
-        reinterpret_cast<const void*>(&hb::hb_umma_kernel<4, 1, 0>),
-        reinterpret_cast<const void*>(&hb::hb_umma_kernel<2, 1, 0>),
-        reinterpret_cast<const void*>(&hb::hb_umma_kernel<4, 1, 1>),
-        reinterpret_cast<const void*>(&hb::hb_umma_kernel<4, 2, 0>),
-        reinterpret_cast<const void*>(&hb::hb_umma_kernel<2, 2, 0>),
-        reinterpret_cast<const void*>(&hb::hb_umma_kernel<4, 2, 1>)};
-    for (const void* k : kernels)
-      if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit) !=
-          cudaSuccess)
-        return;
-    const void* strip_kernels[3] = {
-        reinterpret_cast<const void*>(&hb::hb_conv_strip_kernel<4, 0>),
-        reinterpret_cast<const void*>(&hb::hb_conv_strip_kernel<2, 0>),
-        reinterpret_cast<const void*>(&hb::hb_conv_strip_kernel<4, 1>)};
-    for (const void* k : strip_kernels)
-      if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit) !=
-          cudaSuccess)
-        return;
-    d.status = HB_OK;
-  });
+  static Driver per_device[kMaxDev];
+  static bool tried[kMaxDev] = {false};
+  static Driver none;  // status HB_ERR_DEVICE
+  static std::mutex mu;
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDev) {
+    cudaGetLastError();
+    return none;
+  }
+  std::lock_guard<std::mutex> lock(mu);
+  Driver& d = per_device[dev];
+  if (tried[dev]) return d;
+  tried[dev] = true;
+  if (!setup_device(&d)) {
+    cudaGetLastError();
+    return d;
+  }
+  cudaDriverGetVersion(&d.driver_version);
+  void* fn = nullptr;
+  cudaDriverEntryPointQueryResult q;
+  if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) != cudaSuccess ||
+      q != cudaDriverEntryPointSuccess || fn == nullptr)
+    return d;
+  d.tiled = reinterpret_cast<EncodeTiledFn>(fn);
+  fn = nullptr;
+  if (cudaGetDriverEntryPoint("cuTensorMapEncodeIm2col", &fn, cudaEnableDefault, &q) != cudaSuccess ||
+      q != cudaDriverEntryPointSuccess || fn == nullptr)
+    return d;
+  d.im2col = reinterpret_cast<EncodeIm2colFn>(fn);
+  d.status = HB_OK;
   return d;
 }
 

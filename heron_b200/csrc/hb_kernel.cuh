@@ -356,7 +356,8 @@ hb_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       int b, m_pair, n0, bn;
       decode(t, b, m_pair, n0, bn);
       const int row0 = m_pair + static_cast<int>(cta_rank) * kTileM + q * 32;
-      if (!mbar_wait(smem_u32(&bars->tmem_full[acc]), acc_phase, abort_flag)) {
+      if (!(p.probe == 8 ? mbar_wait(smem_u32(&bars->tmem_full[acc]), acc_phase, abort_flag)
+                         : mbar_wait_relaxed(smem_u32(&bars->tmem_full[acc]), acc_phase, abort_flag))) {
         ok = false;
         break;
       }

@@ -75,6 +75,26 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   }
 }
 
+// The same wait for roles that are off the critical path (the epilogue warps wait a whole K loop
+// for their accumulator): back off with nanosleep between polls so that 128 idle threads do not
+// burn issue slots and power while the tensor pipe works.
+__device__ __forceinline__ bool mbar_wait_relaxed(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  uint32_t polls = 0;
+  while (true) {
+    __nanosleep(polls < 8 ? 32 : 256);
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((++polls & 63u) == 0u) {
+      if (*abort_flag) return false;
+      if (clock64() - t0 > HB_WAIT_LIMIT_CYCLES) {
+        *abort_flag = 1;
+        return false;
+      }
+    }
+  }
+}
+
 // ---- proxy fences -------------------------------------------------------------------------
 __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
