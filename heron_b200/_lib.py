@@ -34,6 +34,7 @@ DTYPE_CODES = {
 
 # Every symbol include/heron_b200.h declares; the CPU test-suite checks the library exports them.
 EXPORTED_SYMBOLS = (
+    "hb_kernel_limits",
     "hb_version",
     "hb_sm_count",
     "hb_default_knobs",
@@ -92,6 +93,21 @@ class HbKnobs(ctypes.Structure):
         return {name: int(getattr(self, name)) for name in self.FIELDS}
 
 
+class HbLimits(ctypes.Structure):
+    """Mirror of ``hb_limits``."""
+
+    _fields_ = [(n, ctypes.c_int) for n in
+                ("max_shared_memory_per_block", "tmem_columns", "tile_m", "max_stages",
+                 "epilogue_staging_bytes", "smem_slack_bytes", "static_scratch_bytes", "reserved")]
+
+
+def kernel_limits():
+    """The library's own SM limits as a dict (needs the built library, not a GPU)."""
+    lim = HbLimits()
+    check(load().hb_kernel_limits(ctypes.byref(lim)), "hb_kernel_limits")
+    return {n: int(getattr(lim, n)) for n, _ in HbLimits._fields_ if n != "reserved"}
+
+
 class HeronB200Error(RuntimeError):
     """A non-zero status from the library (the stand-in for the reference's TVMError)."""
 
@@ -119,6 +135,8 @@ def load():
     ip = ctypes.POINTER(c_int)
     lib.hb_version.restype = c_int
     lib.hb_version.argtypes = []
+    lib.hb_kernel_limits.restype = c_int
+    lib.hb_kernel_limits.argtypes = [ctypes.POINTER(HbLimits)]
     lib.hb_sm_count.restype = c_int
     lib.hb_sm_count.argtypes = []
     lib.hb_default_knobs.restype = c_int

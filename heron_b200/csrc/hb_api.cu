@@ -689,6 +689,19 @@ int hb_plan_conv2d_nchw(hb_plan** plan, const void* in, const void* w, void* out
 
 int hb_version(void) { return 100; }
 
+int hb_kernel_limits(hb_limits* out) {
+  if (!out) return HB_ERR_SHAPE;
+  out->max_shared_memory_per_block = kSmemLimit;
+  out->tmem_columns = 512;
+  out->tile_m = hb::kTileM;
+  out->max_stages = hb::kMaxStages;
+  out->epilogue_staging_bytes = hb::kEpiWarps * 2 * hb::kEpiBufBytes;
+  out->smem_slack_bytes = kSmemSlack;
+  out->static_scratch_bytes = static_cast<int>(HB_STATIC_SCRATCH_BYTES);
+  out->reserved = 0;
+  return HB_OK;
+}
+
 int hb_sm_count(void) {
   Driver& d = driver();
   return d.status == HB_OK ? d.sm_count : -d.status;

@@ -40,7 +40,13 @@ class Env:
     def get_build_kwargs(self, task):
         # The reference asks TVM for the GPU's limits (threads, shared memory); the constraint
         # model here refers to the B200's SM limits.
-        self.build_kwargs = {"limits": dict(B200_LIMITS)}
+        limits = dict(B200_LIMITS)
+        try:  # prefer the numbers the built library reports over the table in the package
+            from . import _lib
+            limits.update(_lib.kernel_limits())
+        except ImportError:
+            pass
+        self.build_kwargs = {"limits": limits}
 
     def tune(self, task_name, pretrained=False):
         self.init_dir()

@@ -96,16 +96,37 @@ def shard_slice(full, rank, world):
     return full[start:start + count]
 
 
-def gather_output(full, rank, world, group=None):
+class ShardMismatch(RuntimeError):
+    """Ranks disagree on the extent or layout of the tensor they are about to gather."""
+
+
+def check_same_extent(full, world, group=None):
+    """Host-side guard (one small all-reduce): every rank must hold a full buffer of the same
+    shape, otherwise the in-place gather would write past a smaller rank's slices."""
+    import torch
+    import torch.distributed as dist
+    dims = list(full.shape) + [0] * (8 - full.dim())
+    lo = torch.tensor(dims, dtype=torch.int64, device=full.device)
+    hi = lo.clone()
+    dist.all_reduce(lo, op=dist.ReduceOp.MIN, group=group)
+    dist.all_reduce(hi, op=dist.ReduceOp.MAX, group=group)
+    if not torch.equal(lo, hi):
+        raise ShardMismatch("ranks hold full buffers of different shapes: min %s max %s"
+                            % (lo.tolist()[:full.dim()], hi.tolist()[:full.dim()]))
+
+
+def gather_output(full, rank, world, group=None, check=False):
     """Completes ``full`` on every rank: each rank has already written its own slice.
 
     Equal shards use one in-place ``all_gather_into_tensor``; ragged shards (extent not a
     multiple of world) fall back to one broadcast per rank.  No copy precedes the collective.
     """
     import torch.distributed as dist
-    parts = partition(full.shape[0], world)
     if world == 1:
         return full
+    if check:
+        check_same_extent(full, world, group)
+    parts = partition(full.shape[0], world)
     if len({c for _, c in parts}) == 1:
         dist.all_gather_into_tensor(full, shard_slice(full, rank, world), group=group)
     else:

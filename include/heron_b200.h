@@ -74,6 +74,23 @@ typedef struct {
   int reserved;      /* diagnostic probe modes; leave 0                                            */
 } hb_knobs;
 
+/*
+ * The SM limits the kernels' knob space is built from, so that a host-side constraint model
+ * (the reference registers thread and shared-memory limits the same way,
+ * schedule/context/cuda_context.py:25-63) states the same bounds as hb_check_knobs.
+ */
+typedef struct {
+  int max_shared_memory_per_block; /* opt-in dynamic shared memory per CTA, bytes              */
+  int tmem_columns;                /* 32-bit accumulator columns per SM                         */
+  int tile_m;                      /* rows of one CTA's accumulator tile                        */
+  int max_stages;                  /* deepest TMA -> MMA ring                                   */
+  int epilogue_staging_bytes;      /* shared memory the TMA-store epilogue takes                */
+  int smem_slack_bytes;            /* alignment padding + barriers                              */
+  int static_scratch_bytes;        /* capacity of the built-in scratch of the no-alloc entry    */
+  int reserved;
+} hb_limits;
+int hb_kernel_limits(hb_limits* out);
+
 /* Library / device facts. */
 int hb_version(void);
 /* Number of SMs of the current device, or a negative status. */

@@ -125,3 +125,13 @@ def test_front_end_refuses_cpu_tensors(hb_lib):
     b = torch.zeros(64, 64, dtype=torch.int8)
     with pytest.raises(ValueError, match="no CPU path"):
         kernels.gemm(a, b, out=torch.zeros(64, 64, dtype=torch.int32))
+
+
+def test_library_limits_match_the_constraint_model(hb_lib):
+    from heron_b200 import _lib
+    from heron_b200.schedule.context import B200_LIMITS
+    lim = _lib.kernel_limits()
+    for key in ("max_shared_memory_per_block", "tmem_columns", "tile_m", "max_stages", "epilogue_staging_bytes",
+                "smem_slack_bytes"):
+        assert lim[key] == B200_LIMITS[key], key
+    assert lim["static_scratch_bytes"] == hb_lib.hb_conv2d_packed_noalloc_max_bytes()

@@ -543,3 +543,16 @@ def test_conv_nchw_through_the_registry(K, co):
     out = poison(args[2].shape, torch.float16)
     handle(dev(x), dev(w), out)
     check(out, co.conv2d_nchw(x, w, 1, 1, np.float16), "c2d registry")
+
+
+def test_x86_batched_gemm_through_the_registry(K, co):
+    from heron_b200.ops import x86 as heron_cpu
+    t = _task(heron_cpu, "bmm", [3, 130, 64, 96, "float16", "float16"], "CPU")  # dtype arguments are ignored
+    t.knob_manager.randSample()
+    handle, args = t.instantiate(t.knob_manager)
+    assert [a.dtype for a in args] == ["uint8", "int8", "int32"]
+    rng = np.random.default_rng(31)
+    a, b = rand_i8(rng, (3, 130, 64), False), rand_i8(rng, (3, 96, 64), True)
+    out = poison(args[-1].shape, torch.int32)
+    handle(dev(a), dev(b), out)
+    check(out, co.bmm_int(a, b), "x86 bmm")

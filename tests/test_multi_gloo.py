@@ -50,3 +50,70 @@ def test_two_rank_shard_and_gather(extent):
         p.join(timeout=60)
         assert p.exitcode == 0
     assert sorted(results) == [(0, True), (1, True)]
+
+
+def _mismatch_worker(rank, world, port, q):
+    sys.path.insert(0, ROOT)
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from heron_b200.multi import ShardMismatch, gather_output
+        # rank 1 was handed a wrong total (5 units instead of 6)
+        full = torch.zeros((6 if rank == 0 else 5, 4), dtype=torch.int32)
+        try:
+            gather_output(full, rank, world, check=True)
+            q.put((rank, "no error"))
+        except ShardMismatch:
+            q.put((rank, "mismatch"))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_wrong_shard_size_is_caught_on_the_host():
+    """Failure injection on the host: a rank with a wrong extent is reported by every rank before
+    any data moves."""
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 29500 + (os.getpid() + 77) % 2000
+    procs = [ctx.Process(target=_mismatch_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = sorted(q.get(timeout=120) for _ in range(2))
+    for p in procs:
+        p.join(timeout=60)
+    assert results == [(0, "mismatch"), (1, "mismatch")]
+
+
+def _absent_worker(rank, world, port, q):
+    import datetime
+    sys.path.insert(0, ROOT)
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=5))
+    if rank == 1:
+        q.put((rank, "left"))  # leaves between steps, nothing in flight
+        return
+    from heron_b200.multi import gather_output
+    full = torch.zeros((6, 4), dtype=torch.int32)
+    try:
+        gather_output(full, rank, world)
+        q.put((rank, "no error"))
+    except Exception as exc:  # the short process-group timeout ends the collective with an error
+        q.put((rank, "error:" + type(exc).__name__))
+
+
+def test_rank_that_leaves_ends_the_collective_with_an_error():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 29500 + (os.getpid() + 191) % 2000
+    procs = [ctx.Process(target=_absent_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = dict(q.get(timeout=120) for _ in range(2))
+    for p in procs:
+        p.join(timeout=60)
+        if p.is_alive():
+            p.terminate()
+    assert results[1] == "left"
+    assert results[0].startswith("error:")
