@@ -362,7 +362,8 @@ int build_plan(Driver& d, const Problem& pr, const hb_knobs& k, const ConvGeom* 
   p.raster = k.raster; p.kind = kind; p.b_mn_major = pr.conv ? 1 : 0; p.a_im2col = pr.conv ? 1 : 0;
   p.epilogue = k.epilogue == 1 ? 1 : 0;
   p.l2_prefetch = (!pr.conv && k.l2_prefetch > 0) ? k.l2_prefetch : 0;
-  p.probe = k.reserved;  // diagnostic modes: 1 = no reloads, 2 = no MMAs (results undefined)
+  p.probe = k.reserved;  // diagnostic modes
+  if (k.reserved == 12) p.wait_limit_cycles = 200000000LL;  // ~0.1 s: the timeout test should be quick: 1 = no reloads, 2 = no MMAs (results undefined)
   p.idesc = make_idesc(kind, pr.in_a, pr.in_b, hb::kTileM * cgrp, k.tile_n, pr.conv);
   p.C = C; p.ldc = pr.N; p.batch_stride_c = static_cast<long long>(pr.M) * pr.N;
 

@@ -36,6 +36,7 @@ struct StripParams {
   int esize_in, esize_out;
   int tmem_cols;
   int ring;   // strip buffers in flight (2..4)
+  long long wait_limit_cycles;
   int probe;  // diagnostic: 2 = no MMAs, 3 = epilogue only hands the accumulator back, 4 = strips loaded once
   uint32_t idesc;
   void* out;
@@ -79,6 +80,7 @@ hb_conv_strip_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_cons
   const uint32_t sStrip = sFilt + ((filt_bytes + 1023) & ~1023);
   StripBars* bars = reinterpret_cast<StripBars*>(smem + (sStrip - smem_base) + p.ring * strip_total);
   volatile int* abort_flag = &bars->abort_flag;
+  const WaitCtx wctx{abort_flag, p.wait_limit_cycles > 0 ? p.wait_limit_cycles : HB_WAIT_LIMIT_CYCLES};
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -127,7 +129,7 @@ hb_conv_strip_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_cons
       for (int t = blockIdx.x; ok && t < p.num_tiles; t += gridDim.x) {
         const int n = t / p.groups;
         const int y0 = (t - n * p.groups) * p.R;
-        if (!mbar_wait(smem_u32(&bars->strip_empty[buf]), phase ^ 1u, abort_flag)) {
+        if (!mbar_wait(smem_u32(&bars->strip_empty[buf]), phase ^ 1u, wctx)) {
           ok = false;
           break;
         }
@@ -167,7 +169,7 @@ hb_conv_strip_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_cons
   } else if (warp == 1) {
     // ------------------------------ MMA issuer --------------------------------------------
     if (elect_one()) {
-      bool ok = mbar_wait(smem_u32(&bars->filt_full), 0u, abort_flag);
+      bool ok = mbar_wait(smem_u32(&bars->filt_full), 0u, wctx);
       int buf = 0, acc = 0;
       uint32_t phase = 0, acc_phase = 0;
       const int umma_k = 32 / p.esize_in;
@@ -179,8 +181,8 @@ hb_conv_strip_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_cons
       const uint32_t b_step16 = static_cast<uint32_t>(umma_k * 128) >> 4;
       const uint32_t idesc = p.idesc;
       for (int t = blockIdx.x; ok && t < p.num_tiles; t += gridDim.x) {
-        if (!mbar_wait(smem_u32(&bars->tmem_empty[acc]), acc_phase ^ 1u, abort_flag) ||
-            !mbar_wait(smem_u32(&bars->strip_full[buf]), phase, abort_flag)) {
+        if (!mbar_wait(smem_u32(&bars->tmem_empty[acc]), acc_phase ^ 1u, wctx) ||
+            !mbar_wait(smem_u32(&bars->strip_full[buf]), phase, wctx)) {
           ok = false;
           break;
         }
@@ -238,7 +240,7 @@ hb_conv_strip_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_cons
       const int n = t / p.groups;
       const int y = (t - n * p.groups) * p.R + py;
       const bool valid = py < p.R && y < p.HO && px < p.WO;
-      if (!mbar_wait(smem_u32(&bars->tmem_full[acc]), acc_phase, abort_flag)) {
+      if (!mbar_wait(smem_u32(&bars->tmem_full[acc]), acc_phase, wctx)) {
         ok = false;
         break;
       }

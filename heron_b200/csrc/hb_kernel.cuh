@@ -57,6 +57,7 @@ struct KParams {
   // grid is made of shorter work items.  num_tiles counts work items (whole tiles + slices).
   int whole_tiles, split;
   uint32_t idesc_split;
+  long long wait_limit_cycles;  // 0: the default bound on every mbarrier wait
   uint32_t idesc;
   // conv geometry (a_im2col only)
   int HO, WO, KW, CI, kb_per_tap, stride_h, stride_w, dil_h, dil_w, pad;
@@ -109,6 +110,7 @@ hb_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   const int epi_bytes = p.epilogue ? kEpiWarps * 2 * kEpiBufBytes : 0;
   SmemBars* bars = reinterpret_cast<SmemBars*>(smem + (sEpi - smem_base) + epi_bytes);
   volatile int* abort_flag = &bars->abort_flag;
+  const WaitCtx wctx{abort_flag, p.wait_limit_cycles > 0 ? p.wait_limit_cycles : HB_WAIT_LIMIT_CYCLES};
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -170,7 +172,9 @@ hb_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       long long issued = 0;
       bool ok = true;
       const int chunk_cols = p.SW / p.esize_in;               // MN-major B: columns per chunk
-      for (int t = first_tile; ok && t < p.num_tiles; t += tile_step) {
+      // diagnostic 12: the producer stays silent, so the consumers' bounded waits run out and the
+      // abort path (drain, TMEM release, status word) is what the launch exercises
+      for (int t = first_tile; ok && t < p.num_tiles && p.probe != 12; t += tile_step) {
         int b, m_pair, n_first, bn;
         decode(t, b, m_pair, n_first, bn);
         const int bn_mine = bn / CG;  // B rows this CTA stages for this work item
@@ -192,7 +196,7 @@ hb_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         for (int kb = 0; kb < p.num_kb; ++kb) {
           const uint32_t full_local = smem_u32(&bars->full[stage]);
           const uint32_t full = (CG == 2) ? mapa(full_local, 0) : full_local;  // the leader's barrier
-          if (!mbar_wait(smem_u32(&bars->empty[stage]), phase ^ 1u, abort_flag)) {
+          if (!mbar_wait(smem_u32(&bars->empty[stage]), phase ^ 1u, wctx)) {
             ok = false;
             break;
           }
@@ -287,7 +291,7 @@ hb_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       const uint32_t a16 = static_cast<uint32_t>(a_bytes) >> 4, b16 = static_cast<uint32_t>(b_bytes) >> 4;
       const uint32_t full0 = smem_u32(&bars->full[0]), empty0 = smem_u32(&bars->empty[0]);
       for (int t = first_tile; ok && t < p.num_tiles; t += tile_step) {
-        if (!mbar_wait(smem_u32(&bars->tmem_empty[acc]), acc_phase ^ 1u, abort_flag)) {
+        if (!mbar_wait(smem_u32(&bars->tmem_empty[acc]), acc_phase ^ 1u, wctx)) {
           ok = false;
           break;
         }
@@ -296,7 +300,7 @@ hb_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         const uint32_t idesc_t = (t >= p.whole_tiles) ? p.idesc_split : idesc;
         uint32_t accum = 0u;
         for (int kb = 0; kb < num_kb; ++kb) {
-          if (!mbar_wait(full0 + 8u * stage, phase, abort_flag)) {
+          if (!mbar_wait(full0 + 8u * stage, phase, wctx)) {
             ok = false;
             break;
           }
@@ -356,8 +360,8 @@ hb_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       int b, m_pair, n0, bn;
       decode(t, b, m_pair, n0, bn);
       const int row0 = m_pair + static_cast<int>(cta_rank) * kTileM + q * 32;
-      if (!(p.probe == 8 ? mbar_wait(smem_u32(&bars->tmem_full[acc]), acc_phase, abort_flag)
-                         : mbar_wait_relaxed(smem_u32(&bars->tmem_full[acc]), acc_phase, abort_flag))) {
+      if (!(p.probe == 8 ? mbar_wait(smem_u32(&bars->tmem_full[acc]), acc_phase, wctx)
+                         : mbar_wait_relaxed(smem_u32(&bars->tmem_full[acc]), acc_phase, wctx))) {
         ok = false;
         break;
       }

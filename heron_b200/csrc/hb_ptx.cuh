@@ -55,11 +55,17 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 
 // Bounded wait.  `abort_flag` lives in shared memory and is shared by every role of the CTA:
 // whoever runs out of patience sets it, everybody else sees it within a few hundred polls and
-// leaves its loop too.  The limit is in SM clock cycles (about two seconds at 2 GHz).
+// leaves its loop too.  The limit is in SM clock cycles (about two seconds at 2 GHz by default;
+// a launch may ask for a shorter one).
 #ifndef HB_WAIT_LIMIT_CYCLES
 #define HB_WAIT_LIMIT_CYCLES (4000000000LL)
 #endif
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+struct WaitCtx {
+  volatile int* abort_flag;
+  long long limit_cycles;
+};
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const WaitCtx& w) {
+  volatile int* abort_flag = w.abort_flag;
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   uint32_t polls = 0;
@@ -67,7 +73,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     if (mbar_try_wait(bar, parity)) return true;
     if ((++polls & 63u) == 0u) {
       if (*abort_flag) return false;
-      if (clock64() - t0 > HB_WAIT_LIMIT_CYCLES) {
+      if (clock64() - t0 > w.limit_cycles) {
         *abort_flag = 1;
         return false;
       }
@@ -78,7 +84,8 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
 // The same wait for roles that are off the critical path (the epilogue warps wait a whole K loop
 // for their accumulator): back off with nanosleep between polls so that 128 idle threads do not
 // burn issue slots and power while the tensor pipe works.
-__device__ __forceinline__ bool mbar_wait_relaxed(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+__device__ __forceinline__ bool mbar_wait_relaxed(uint32_t bar, uint32_t parity, const WaitCtx& w) {
+  volatile int* abort_flag = w.abort_flag;
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   uint32_t polls = 0;
@@ -87,7 +94,7 @@ __device__ __forceinline__ bool mbar_wait_relaxed(uint32_t bar, uint32_t parity,
     if (mbar_try_wait(bar, parity)) return true;
     if ((++polls & 63u) == 0u) {
       if (*abort_flag) return false;
-      if (clock64() - t0 > HB_WAIT_LIMIT_CYCLES) {
+      if (clock64() - t0 > w.limit_cycles) {
         *abort_flag = 1;
         return false;
       }

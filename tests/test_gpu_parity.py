@@ -556,3 +556,22 @@ def test_x86_batched_gemm_through_the_registry(K, co):
     out = poison(args[-1].shape, torch.int32)
     handle(dev(a), dev(b), out)
     check(out, co.bmm_int(a, b), "x86 bmm")
+
+
+def test_bounded_wait_runs_out_cleanly(K, co):
+    """Failure detection without a fault: a diagnostic launch whose producer warp stays silent, so
+    the MMA and epilogue warps' bounded waits run out (0.1 s limit for this launch).  The kernel
+    must return by itself, leave HB_ERR_TIMEOUT in the status word, free its TMEM and leave the
+    context usable: the next launch on the same device is correct."""
+    from heron_b200 import _lib
+    rng = np.random.default_rng(1)
+    a, b = rand_i8(rng, (256, 128), False), rand_i8(rng, (256, 128), True)
+    ta, tb = dev(a), dev(b)
+    out = poison((256, 256), torch.int32)
+    K.gemm(ta, tb, out=out, knobs=dict(cta_group=1, reserved=12))
+    assert _lib.last_status() == _lib.HB_ERR_TIMEOUT
+    assert _lib.last_status() == 0  # reading clears it
+    for _ in range(3):  # TMEM was released: full-size allocations succeed again
+        K.gemm(ta, tb, out=out, knobs=dict(cta_group=1, tile_n=256))
+        check(out, co.gemm_int(a, b), "after timeout")
+    assert _lib.last_status() == 0
