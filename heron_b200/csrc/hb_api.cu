@@ -424,7 +424,7 @@ int build_plan(Driver& d, const Problem& pr, const hb_knobs& k, const ConvGeom* 
     cudaLaunchConfig_t cfg;
     std::memset(&cfg, 0, sizeof(cfg));
     cfg.gridDim = dim3(d.sm_count / 2 * 2);
-    cfg.blockDim = dim3(hb::kThreads);
+    cfg.blockDim = dim3(hb::kUmmaThreads);
     cfg.dynamicSmemBytes = smem;
     cudaLaunchAttribute attr;
     attr.id = cudaLaunchAttributeClusterDimension;
@@ -542,7 +542,7 @@ int launch_kernel(const hb_plan* plan, cudaStream_t stream) {
   cudaLaunchConfig_t cfg;
   std::memset(&cfg, 0, sizeof(cfg));
   cfg.gridDim = dim3(plan->grid);
-  cfg.blockDim = dim3(hb::kThreads);
+  cfg.blockDim = dim3(hb::kUmmaThreads);
   cfg.dynamicSmemBytes = plan->smem;
   cfg.stream = stream;
   cudaLaunchAttribute attr;

