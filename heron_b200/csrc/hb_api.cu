@@ -571,15 +571,6 @@ int plan_gemm_like(int op, const void* A, const void* B, void* C, int batch, int
   return build_plan(d, pr, k, nullptr, A, B, C, plan);
 }
 
-int plan_conv(const void* in, const void* w, void* out, int N, int H, int W, int CI, int CO, int KH,
-              int KW, int stride_h, int stride_w, int pad, int dil_h, int dil_w, hb_dtype in_a,
-              hb_dtype in_w, hb_dtype out_t, const hb_knobs* knobs, hb_plan* plan);
-
-int plan_conv_packed(const void* in, const void* w_packed, void* out, int N, int H, int W, int CI,
-                     int CO, int KH, int KW, int stride_h, int stride_w, int pad, int dil_h,
-                     int dil_w, int sco, void* scratch, size_t scratch_bytes, const hb_knobs* knobs,
-                     hb_plan* plan);
-
 template <class BuildFn>
 int new_plan(hb_plan** out, BuildFn build) {
   if (!out) return HB_ERR_SHAPE;
@@ -600,6 +591,161 @@ int conv_out_extent(int in, int k, int stride, int pad, int dil) {
   return (in - span + 2 * pad) / stride + 1;
 }
 
+
+
+// Shared-memory need of the strip algorithm for a geometry, or 0 when it does not apply.
+int strip_smem_bytes(const ConvGeom& g, int es, int eo, hb::StripParams* sp) {
+  if (g.stride_h != 1 || g.stride_w != 1) return 0;
+  if ((g.CI * es) % 128 != 0 || (g.CO * es) % 128 != 0) return 0;
+  if (g.CO > 256 || g.CO % (128 / eo) != 0 || g.CO % 16 != 0) return 0;
+  const int Wp = g.W + 2 * g.pad;
+  if (Wp > 128 || Wp < 1) return 0;
+  const int R = 128 / Wp;
+  const int strip_rows = R + (g.KH - 1) * g.dil_h;
+  if (strip_rows > 256) return 0;
+  const int max_off = (g.KH - 1) * g.dil_h * Wp + (g.KW - 1) * g.dil_w;
+  int px = strip_rows * Wp;
+  if (max_off + 128 > px) px = max_off + 128;
+  const int strip_bytes = (px * 128 + 1023) & ~1023;
+  const int n_cchunks = g.CI * es / 128;
+  const long long filt = static_cast<long long>(g.KH) * g.KW * g.CI * g.CO * es;
+  long long smem = ((filt + 1023) & ~1023LL) + 2LL * n_cchunks * strip_bytes + 1024 + 256;
+  if (smem > kSmemLimit) return 0;
+  int ring = 2;  // deeper when shared memory allows: more strips in flight hide HBM latency
+  while (ring < 4 && smem + static_cast<long long>(n_cchunks) * strip_bytes <= kSmemLimit) {
+    smem += static_cast<long long>(n_cchunks) * strip_bytes;
+    ++ring;
+  }
+  if (sp) {
+    sp->ring = ring;
+    sp->Wp = Wp; sp->R = R; sp->strip_rows = strip_rows; sp->strip_bytes = strip_bytes;
+    sp->n_cchunks = n_cchunks; sp->groups = (g.HO + R - 1) / R;
+  }
+  return static_cast<int>(smem);
+}
+
+int build_strip_plan(Driver& d, const ConvGeom& g, hb_dtype in_a, hb_dtype in_w, hb_dtype out_t,
+                     const hb_knobs& k, const void* in, const void* w, void* out, hb_plan* plan) {
+  const int es = esize(in_a), eo = esize(out_t);
+  std::memset(plan, 0, sizeof(*plan));
+  hb::StripParams& sp = plan->sp;
+  const int smem = strip_smem_bytes(g, es, eo, &sp);
+  if (smem == 0) return HB_ERR_KNOB;
+  const long long tiles = static_cast<long long>(g.N) * sp.groups;
+  if (tiles > 0x7fffffffLL) return HB_ERR_SHAPE;
+  sp.N = g.N; sp.H = g.H; sp.W = g.W; sp.CI = g.CI; sp.CO = g.CO; sp.KH = g.KH; sp.KW = g.KW;
+  sp.pad = g.pad; sp.dil_h = g.dil_h; sp.dil_w = g.dil_w; sp.HO = g.HO; sp.WO = g.WO;
+  sp.num_tiles = static_cast<int>(tiles);
+  sp.esize_in = es; sp.esize_out = eo;
+  sp.tmem_cols = next_pow2_cols(2 * g.CO);
+  const int kind = mma_kind(in_a, in_w, out_t);
+  sp.idesc = make_idesc(kind, in_a, in_w, hb::kTileM, g.CO, true);
+  sp.out = out;
+  sp.probe = k.reserved;
+  // input as a tiled (C, W, H, N) tensor: one box = 128 bytes of channels x padded width x strip rows
+  cuuint64_t dims[4] = {static_cast<cuuint64_t>(g.CI), static_cast<cuuint64_t>(g.W),
+                        static_cast<cuuint64_t>(g.H), static_cast<cuuint64_t>(g.N)};
+  cuuint64_t strides[3] = {static_cast<cuuint64_t>(g.CI) * es, static_cast<cuuint64_t>(g.W) * g.CI * es,
+                           static_cast<cuuint64_t>(g.H) * g.W * g.CI * es};
+  cuuint32_t box[4] = {static_cast<cuuint32_t>(128 / es), static_cast<cuuint32_t>(sp.Wp),
+                       static_cast<cuuint32_t>(sp.strip_rows), 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = d.tiled(&plan->tmA, tmap_dtype(in_a), 4, const_cast<void*>(in), dims, strides, box, estr,
+                       CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                       CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return HB_ERR_LAUNCH;
+  const long long K = static_cast<long long>(g.KH) * g.KW * g.CI;
+  const uint64_t rowB = static_cast<uint64_t>(g.CO) * es;
+  int rc = encode_tiled3(d, &plan->tmB, in_w, w, g.CO, K, 1, rowB, rowB * K, 128 / es, 128 / es, 128);
+  if (rc != HB_OK) return rc;
+  int grid = d.sm_count;
+  if (k.max_ctas > 0 && k.max_ctas < grid) grid = k.max_ctas;
+  if (sp.num_tiles < grid) grid = sp.num_tiles;
+  plan->strip = true;
+  plan->grid = grid;
+  plan->smem = smem;
+  plan->knobs = k;
+  plan->knobs.conv_algo = 2;
+  // fields hb_plan_knobs reports
+  plan->knobs.tile_n = g.CO; plan->knobs.swizzle_bytes = 128; plan->knobs.stages = sp.ring;
+  plan->knobs.acc_stages = 2; plan->knobs.cta_group = 1; plan->knobs.epilogue = 2;
+  // the packed-filter wrapper reads these from the GEMM-view parameter block
+  plan->p.N = g.CO; plan->p.KW = g.KW; plan->p.CI = g.CI; plan->p.esize_out = eo;
+  return HB_OK;
+}
+
+int plan_conv(const void* in, const void* w, void* out, int N, int H, int W, int CI, int CO, int KH,
+              int KW, int stride_h, int stride_w, int pad, int dil_h, int dil_w, hb_dtype in_a,
+              hb_dtype in_w, hb_dtype out_t, const hb_knobs* knobs, hb_plan* plan) {
+  if (N <= 0 || H <= 0 || W <= 0 || CI <= 0 || CO <= 0 || KH <= 0 || KW <= 0) return HB_ERR_SHAPE;
+  if (stride_h <= 0 || stride_w <= 0 || dil_h <= 0 || dil_w <= 0 || pad < 0) return HB_ERR_SHAPE;
+  if (mma_kind(in_a, in_w, out_t) < 0) return HB_ERR_DTYPE;
+  const int es = esize(in_a);
+  if ((CI * es) % 32 != 0) return HB_ERR_SHAPE;
+  if ((static_cast<long long>(CO) * es) % 16 != 0) return HB_ERR_SHAPE;
+  // im2col-mode TMA limits: 8-bit signed corners, 8-bit tap offsets, traversal stride <= 8.
+  if (pad > 127 || (KW - 1) * dil_w > 255 || (KH - 1) * dil_h > 255) return HB_ERR_SHAPE;
+  if (pad - (KW - 1) * dil_w < -128 || pad - (KH - 1) * dil_h < -128) return HB_ERR_SHAPE;
+  if (stride_h > 8 || stride_w > 8) return HB_ERR_SHAPE;
+  const int HO = conv_out_extent(H, KH, stride_h, pad, dil_h);
+  const int WO = conv_out_extent(W, KW, stride_w, pad, dil_w);
+  if (HO <= 0 || WO <= 0) return HB_ERR_SHAPE;
+  const long long M = static_cast<long long>(N) * HO * WO;
+  const long long K = static_cast<long long>(KH) * KW * CI;
+  if (M > 0x7fffffffLL || K > 0x7fffffffLL) return HB_ERR_SHAPE;
+  if (!in || !w || !out) return HB_ERR_ALIGN;
+  if (!aligned16(in) || !aligned16(w) || !aligned16(out)) return HB_ERR_ALIGN;
+  Driver& d = driver();
+  if (d.status != HB_OK) return d.status;
+  Problem pr{2, 1, static_cast<int>(M), CO, static_cast<int>(K), in_a, in_w, out_t, true, CI};
+  ConvGeom cg{N, H, W, CI, CO, KH, KW, stride_h, stride_w, pad, dil_h, dil_w, HO, WO};
+  const int algo = knobs ? knobs->conv_algo : 0;
+  if (algo < 0 || algo > 2) return HB_ERR_KNOB;
+  if (algo != 1) {
+    hb::StripParams probe;
+    std::memset(&probe, 0, sizeof(probe));
+    const bool fits = strip_smem_bytes(cg, es, esize(out_t), &probe) != 0;
+    // Picked by default when the filter has more than one tap (so pixels would otherwise be
+    // re-fetched per tap), tiles fill at least three quarters of the 128 MMA rows, and the whole
+    // reduction is short enough that operand traffic, not tensor time, bounds the kernel.
+    const bool wanted = algo == 2 || (KH * KW > 1 && probe.R * probe.Wp >= 96 && K * es <= 2048);
+    if (algo == 2 && !fits) return HB_ERR_KNOB;
+    if (fits && wanted) {
+      hb_knobs k0;
+      if (knobs) k0 = *knobs; else std::memset(&k0, 0, sizeof(k0));
+      return build_strip_plan(d, cg, in_a, in_w, out_t, k0, in, w, out, plan);
+    }
+  }
+  hb_knobs k;
+  resolve_knobs(pr, knobs, d.sm_count, &k);
+  k.conv_algo = 1;
+  return build_plan(d, pr, k, &cg, in, w, out, plan);
+}
+
+int plan_conv_packed(const void* in, const void* w_packed, void* out, int N, int H, int W, int CI,
+                     int CO, int KH, int KW, int stride_h, int stride_w, int pad, int dil_h,
+                     int dil_w, int sco, void* scratch, size_t scratch_bytes, const hb_knobs* knobs,
+                     hb_plan* plan) {
+  if (sco != 64 && sco != 48 && sco != 32) return HB_ERR_SHAPE;
+  if (CI <= 0 || CO <= 0 || KH <= 0 || KW <= 0) return HB_ERR_SHAPE;
+  if (CI % 4 != 0 || CO % sco != 0) return HB_ERR_SHAPE;
+  if (!scratch || scratch_bytes < hb_conv2d_packed_scratch_bytes(CI, CO, KH, KW))
+    return HB_ERR_SCRATCH;
+  if (!w_packed || !aligned16(w_packed) || !aligned16(scratch)) return HB_ERR_ALIGN;
+  const int rc = plan_conv(in, scratch, out, N, H, W, CI, CO, KH, KW, stride_h, stride_w, pad, dil_h,
+                           dil_w, HB_U8, HB_S8, HB_S32, knobs, plan);
+  if (rc != HB_OK) return rc;
+  const long long groups = static_cast<long long>(KH) * KW * (CI / 4) * CO;
+  int blocks = static_cast<int>((groups + 255) / 256);
+  const int cap = driver().sm_count * 8;
+  if (blocks > cap) blocks = cap;
+  plan->packed_w = w_packed;
+  plan->scratch = scratch;
+  plan->unpack_blocks = blocks;
+  plan->sco = sco;
+  plan->KH = KH;
+  return HB_OK;
+}
 
 size_t align256(size_t v) { return (v + 255) & ~static_cast<size_t>(255); }
 
@@ -751,168 +897,6 @@ int hb_conv2d_nhwc(const void* in, const void* w, void* out, int N, int H, int W
   return rc != HB_OK ? rc : run_plan(&plan, static_cast<cudaStream_t>(stream));
 }
 
-}  // extern "C"
-
-namespace {
-
-// Shared-memory need of the strip algorithm for a geometry, or 0 when it does not apply.
-int strip_smem_bytes(const ConvGeom& g, int es, int eo, hb::StripParams* sp) {
-  if (g.stride_h != 1 || g.stride_w != 1) return 0;
-  if ((g.CI * es) % 128 != 0 || (g.CO * es) % 128 != 0) return 0;
-  if (g.CO > 256 || g.CO % (128 / eo) != 0 || g.CO % 16 != 0) return 0;
-  const int Wp = g.W + 2 * g.pad;
-  if (Wp > 128 || Wp < 1) return 0;
-  const int R = 128 / Wp;
-  const int strip_rows = R + (g.KH - 1) * g.dil_h;
-  if (strip_rows > 256) return 0;
-  const int max_off = (g.KH - 1) * g.dil_h * Wp + (g.KW - 1) * g.dil_w;
-  int px = strip_rows * Wp;
-  if (max_off + 128 > px) px = max_off + 128;
-  const int strip_bytes = (px * 128 + 1023) & ~1023;
-  const int n_cchunks = g.CI * es / 128;
-  const long long filt = static_cast<long long>(g.KH) * g.KW * g.CI * g.CO * es;
-  long long smem = ((filt + 1023) & ~1023LL) + 2LL * n_cchunks * strip_bytes + 1024 + 256;
-  if (smem > kSmemLimit) return 0;
-  int ring = 2;  // deeper when shared memory allows: more strips in flight hide HBM latency
-  while (ring < 4 && smem + static_cast<long long>(n_cchunks) * strip_bytes <= kSmemLimit) {
-    smem += static_cast<long long>(n_cchunks) * strip_bytes;
-    ++ring;
-  }
-  if (sp) {
-    sp->ring = ring;
-    sp->Wp = Wp; sp->R = R; sp->strip_rows = strip_rows; sp->strip_bytes = strip_bytes;
-    sp->n_cchunks = n_cchunks; sp->groups = (g.HO + R - 1) / R;
-  }
-  return static_cast<int>(smem);
-}
-
-int build_strip_plan(Driver& d, const ConvGeom& g, hb_dtype in_a, hb_dtype in_w, hb_dtype out_t,
-                     const hb_knobs& k, const void* in, const void* w, void* out, hb_plan* plan) {
-  const int es = esize(in_a), eo = esize(out_t);
-  std::memset(plan, 0, sizeof(*plan));
-  hb::StripParams& sp = plan->sp;
-  const int smem = strip_smem_bytes(g, es, eo, &sp);
-  if (smem == 0) return HB_ERR_KNOB;
-  const long long tiles = static_cast<long long>(g.N) * sp.groups;
-  if (tiles > 0x7fffffffLL) return HB_ERR_SHAPE;
-  sp.N = g.N; sp.H = g.H; sp.W = g.W; sp.CI = g.CI; sp.CO = g.CO; sp.KH = g.KH; sp.KW = g.KW;
-  sp.pad = g.pad; sp.dil_h = g.dil_h; sp.dil_w = g.dil_w; sp.HO = g.HO; sp.WO = g.WO;
-  sp.num_tiles = static_cast<int>(tiles);
-  sp.esize_in = es; sp.esize_out = eo;
-  sp.tmem_cols = next_pow2_cols(2 * g.CO);
-  const int kind = mma_kind(in_a, in_w, out_t);
-  sp.idesc = make_idesc(kind, in_a, in_w, hb::kTileM, g.CO, true);
-  sp.out = out;
-  sp.probe = k.reserved;
-  // input as a tiled (C, W, H, N) tensor: one box = 128 bytes of channels x padded width x strip rows
-  cuuint64_t dims[4] = {static_cast<cuuint64_t>(g.CI), static_cast<cuuint64_t>(g.W),
-                        static_cast<cuuint64_t>(g.H), static_cast<cuuint64_t>(g.N)};
-  cuuint64_t strides[3] = {static_cast<cuuint64_t>(g.CI) * es, static_cast<cuuint64_t>(g.W) * g.CI * es,
-                           static_cast<cuuint64_t>(g.H) * g.W * g.CI * es};
-  cuuint32_t box[4] = {static_cast<cuuint32_t>(128 / es), static_cast<cuuint32_t>(sp.Wp),
-                       static_cast<cuuint32_t>(sp.strip_rows), 1};
-  cuuint32_t estr[4] = {1, 1, 1, 1};
-  CUresult r = d.tiled(&plan->tmA, tmap_dtype(in_a), 4, const_cast<void*>(in), dims, strides, box, estr,
-                       CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                       CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) return HB_ERR_LAUNCH;
-  const long long K = static_cast<long long>(g.KH) * g.KW * g.CI;
-  const uint64_t rowB = static_cast<uint64_t>(g.CO) * es;
-  int rc = encode_tiled3(d, &plan->tmB, in_w, w, g.CO, K, 1, rowB, rowB * K, 128 / es, 128 / es, 128);
-  if (rc != HB_OK) return rc;
-  int grid = d.sm_count;
-  if (k.max_ctas > 0 && k.max_ctas < grid) grid = k.max_ctas;
-  if (sp.num_tiles < grid) grid = sp.num_tiles;
-  plan->strip = true;
-  plan->grid = grid;
-  plan->smem = smem;
-  plan->knobs = k;
-  plan->knobs.conv_algo = 2;
-  // fields hb_plan_knobs reports
-  plan->knobs.tile_n = g.CO; plan->knobs.swizzle_bytes = 128; plan->knobs.stages = sp.ring;
-  plan->knobs.acc_stages = 2; plan->knobs.cta_group = 1; plan->knobs.epilogue = 2;
-  // the packed-filter wrapper reads these from the GEMM-view parameter block
-  plan->p.N = g.CO; plan->p.KW = g.KW; plan->p.CI = g.CI; plan->p.esize_out = eo;
-  return HB_OK;
-}
-}  // namespace
-
-namespace {
-int plan_conv(const void* in, const void* w, void* out, int N, int H, int W, int CI, int CO, int KH,
-              int KW, int stride_h, int stride_w, int pad, int dil_h, int dil_w, hb_dtype in_a,
-              hb_dtype in_w, hb_dtype out_t, const hb_knobs* knobs, hb_plan* plan) {
-  if (N <= 0 || H <= 0 || W <= 0 || CI <= 0 || CO <= 0 || KH <= 0 || KW <= 0) return HB_ERR_SHAPE;
-  if (stride_h <= 0 || stride_w <= 0 || dil_h <= 0 || dil_w <= 0 || pad < 0) return HB_ERR_SHAPE;
-  if (mma_kind(in_a, in_w, out_t) < 0) return HB_ERR_DTYPE;
-  const int es = esize(in_a);
-  if ((CI * es) % 32 != 0) return HB_ERR_SHAPE;
-  if ((static_cast<long long>(CO) * es) % 16 != 0) return HB_ERR_SHAPE;
-  // im2col-mode TMA limits: 8-bit signed corners, 8-bit tap offsets, traversal stride <= 8.
-  if (pad > 127 || (KW - 1) * dil_w > 255 || (KH - 1) * dil_h > 255) return HB_ERR_SHAPE;
-  if (pad - (KW - 1) * dil_w < -128 || pad - (KH - 1) * dil_h < -128) return HB_ERR_SHAPE;
-  if (stride_h > 8 || stride_w > 8) return HB_ERR_SHAPE;
-  const int HO = conv_out_extent(H, KH, stride_h, pad, dil_h);
-  const int WO = conv_out_extent(W, KW, stride_w, pad, dil_w);
-  if (HO <= 0 || WO <= 0) return HB_ERR_SHAPE;
-  const long long M = static_cast<long long>(N) * HO * WO;
-  const long long K = static_cast<long long>(KH) * KW * CI;
-  if (M > 0x7fffffffLL || K > 0x7fffffffLL) return HB_ERR_SHAPE;
-  if (!in || !w || !out) return HB_ERR_ALIGN;
-  if (!aligned16(in) || !aligned16(w) || !aligned16(out)) return HB_ERR_ALIGN;
-  Driver& d = driver();
-  if (d.status != HB_OK) return d.status;
-  Problem pr{2, 1, static_cast<int>(M), CO, static_cast<int>(K), in_a, in_w, out_t, true, CI};
-  ConvGeom cg{N, H, W, CI, CO, KH, KW, stride_h, stride_w, pad, dil_h, dil_w, HO, WO};
-  const int algo = knobs ? knobs->conv_algo : 0;
-  if (algo < 0 || algo > 2) return HB_ERR_KNOB;
-  if (algo != 1) {
-    hb::StripParams probe;
-    std::memset(&probe, 0, sizeof(probe));
-    const bool fits = strip_smem_bytes(cg, es, esize(out_t), &probe) != 0;
-    // Picked by default when the filter has more than one tap (so pixels would otherwise be
-    // re-fetched per tap), tiles fill at least three quarters of the 128 MMA rows, and the whole
-    // reduction is short enough that operand traffic, not tensor time, bounds the kernel.
-    const bool wanted = algo == 2 || (KH * KW > 1 && probe.R * probe.Wp >= 96 && K * es <= 2048);
-    if (algo == 2 && !fits) return HB_ERR_KNOB;
-    if (fits && wanted) {
-      hb_knobs k0;
-      if (knobs) k0 = *knobs; else std::memset(&k0, 0, sizeof(k0));
-      return build_strip_plan(d, cg, in_a, in_w, out_t, k0, in, w, out, plan);
-    }
-  }
-  hb_knobs k;
-  resolve_knobs(pr, knobs, d.sm_count, &k);
-  k.conv_algo = 1;
-  return build_plan(d, pr, k, &cg, in, w, out, plan);
-}
-
-int plan_conv_packed(const void* in, const void* w_packed, void* out, int N, int H, int W, int CI,
-                     int CO, int KH, int KW, int stride_h, int stride_w, int pad, int dil_h,
-                     int dil_w, int sco, void* scratch, size_t scratch_bytes, const hb_knobs* knobs,
-                     hb_plan* plan) {
-  if (sco != 64 && sco != 48 && sco != 32) return HB_ERR_SHAPE;
-  if (CI <= 0 || CO <= 0 || KH <= 0 || KW <= 0) return HB_ERR_SHAPE;
-  if (CI % 4 != 0 || CO % sco != 0) return HB_ERR_SHAPE;
-  if (!scratch || scratch_bytes < hb_conv2d_packed_scratch_bytes(CI, CO, KH, KW))
-    return HB_ERR_SCRATCH;
-  if (!w_packed || !aligned16(w_packed) || !aligned16(scratch)) return HB_ERR_ALIGN;
-  const int rc = plan_conv(in, scratch, out, N, H, W, CI, CO, KH, KW, stride_h, stride_w, pad, dil_h,
-                           dil_w, HB_U8, HB_S8, HB_S32, knobs, plan);
-  if (rc != HB_OK) return rc;
-  const long long groups = static_cast<long long>(KH) * KW * (CI / 4) * CO;
-  int blocks = static_cast<int>((groups + 255) / 256);
-  const int cap = driver().sm_count * 8;
-  if (blocks > cap) blocks = cap;
-  plan->packed_w = w_packed;
-  plan->scratch = scratch;
-  plan->unpack_blocks = blocks;
-  plan->sco = sco;
-  plan->KH = KH;
-  return HB_OK;
-}
-}  // namespace
-
-extern "C" {
 
 size_t hb_conv2d_packed_scratch_bytes(int CI, int CO, int KH, int KW) {
   if (CI <= 0 || CO <= 0 || KH <= 0 || KW <= 0) return 0;
