@@ -34,8 +34,8 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustain
 # DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) from the ncu captures
 # summarised under profiles/; None where no capture has been taken.
 NCU_TRAFFIC_BYTES = {
-    "cfg2_gemm_f16_4096": 125e6,        # profiles/gemm_f16_4096_ncu.md
-    "cfg4_bmm_s8_attention": 155.3e6,   # profiles/other_configs_ncu.md
+    "cfg2_gemm_f16_4096": 125e6,
+    "cfg4_bmm_s8_attention": 155.3e6,
     "cfg3_conv_f16_resnet_s2": 12.9e6,
     "cfg5_conv_u8s8_resnet_s4": 74.8e6,
     "cfg1_gemm_u8s8_64": None,
