@@ -9,8 +9,8 @@ from .runner.runner import Runner
 from .schedule.context import B200_LIMITS
 from .schedule.sched_op import get_op_methods
 from .task.task import Task
-from .tuner import (CGATuner, ConstrainedRandomWalkerSATuner, CRandTuner, GATuner, RandomWalkSATuner, RCGATuner,
-                    SDGATuner)
+from .tuner import (CGATuner, ConstrainedRandomWalkerSATuner, CRandTuner, GATuner, IDEATuner, RandomWalkSATuner,
+                    RCGATuner, SDGATuner, SRGATuner)
 from .utils import mkdir
 
 _TUNERS = {
@@ -19,6 +19,8 @@ _TUNERS = {
     "RCGA": RCGATuner,
     "GA": GATuner,
     "SDGA": SDGATuner,
+    "SRGA": SRGATuner,
+    "IDEA": IDEATuner,
     "SA": RandomWalkSATuner,
     "CSA": ConstrainedRandomWalkerSATuner,
 }

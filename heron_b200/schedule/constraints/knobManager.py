@@ -272,6 +272,34 @@ class KnobManager:
             self.solved_knob_vals_phenotype[key] = phenotype[idx]
         return phenotype, valid
 
+    def SBX_crossover_and_mutation(self, m1, m2, feasible):
+        """Simulated binary crossover + polynomial mutation over every model variable, snapped to
+        the values seen feasible for that variable; the child may violate constraints, its
+        per-constraint violations are returned (knobManager.py:382-423; used by IDEA)."""
+        import math
+        eta_c, eta_m = 15, 20
+        chrom, res = {}, []
+        for key in m1.solved_knob_vals_genotype.keys():
+            x1, x2 = m1.solved_knob_vals_genotype[key], m2.solved_knob_vals_genotype[key]
+            cands = feasible.get(key) or [x1, x2]
+            u = random.random()
+            sign = float(random.randint(0, 1) * 2 - 1)
+            beta = math.pow(2 * u, 1 / eta_c + 1) if u <= 0.5 else math.pow(1 / (2 * (1 - u + 1e-8)), 1 / eta_c + 1)
+            x = 0.5 * ((1 + sign * beta) * x1 + (1 - sign * beta) * x2)
+            x = min(cands, key=lambda t: abs(t - x))
+            if random.random() < 0.1:
+                span = max(cands) - min(cands)
+                r = random.random()
+                delta = math.pow(2 * r, 1 / (eta_m + 1)) - 1 if r < 0.5 else 1 - math.pow(2 * (1 - r), 1 / (eta_m + 1))
+                x = min(cands, key=lambda t: abs(t - (x + span * delta)))
+            chrom[key] = x
+            res.append(x)
+        violations, valid = self.solver.MultiSATScore(chrom)
+        self.solved_knob_vals_genotype = chrom
+        self.solved_knob_vals_phenotype = chrom
+        self._valid = valid
+        return res, valid, violations
+
     def constrained_random_walk(self, knob_manager, ratio):
         keys = list(knob_manager.solved_knob_vals_genotype.keys())
         preserve_num = int(ratio * len(keys))

@@ -88,6 +88,37 @@ class SDGATuner(GATuner):
         return self._breed("SATDecoding", samples, task, self.feasible)
 
 
+class SRGATuner(GATuner):
+    """GA over all variables with stochastic ranking between fitness and constraint violation
+    (ga_tuner.py:113-152 of the reference)."""
+
+    def Selection(self, pop, num):
+        return self.RankSelection(pop, num)
+
+    def RankPop(self, pop):
+        sweeps, pf = 10, 0.45
+        order = list(pop)
+        for _ in range(sweeps):
+            swapped = False
+            for j in range(len(order) - 1):
+                a, b = order[j], order[j + 1]
+                va, vb = a.violation or 0, b.violation or 0
+                by_fitness = (va == 0 and vb == 0) or random.random() < pf
+                if (by_fitness and a.predict < b.predict) or (not by_fitness and va > vb):
+                    order[j], order[j + 1] = b, a
+                    swapped = True
+            if not swapped:
+                break
+        return order
+
+    def crossoverAndMutate(self, samples, task):
+        res = self._breed("UnconstrainedAll", samples, task, self.feasible)
+        for s in res:  # infeasible children keep a (penalised) predicted fitness for the ranking
+            if not s.valid and s.point is not None:
+                s.predict = float(self.predict([s])[0]) if self.cost_model is not None else 0.0
+        return res
+
+
 def crossoverAndMutateSequential(kind, num, samples, task, args):
     res = []
     for _ in range(num):
@@ -104,6 +135,8 @@ def crossoverAndMutateSequential(kind, num, samples, task, args):
             point, valid, violation = km.crossover_and_mutate_all(m1, m2, args)
         elif kind == "SATDecoding":
             point, valid = km.satdecoding_crossover_and_mutate(m1, m2, args)
+        elif kind == "SBX":
+            point, valid, child.violations = km.SBX_crossover_and_mutation(m1, m2, args)
         else:
             raise ValueError(kind)
         child.violation = violation

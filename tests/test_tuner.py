@@ -42,7 +42,7 @@ def make_env(tmp_path, method, trials=48):
     return env
 
 
-@pytest.mark.parametrize("method", ["CGA", "CRAND", "SA", "GA", "SDGA"])
+@pytest.mark.parametrize("method", ["CGA", "CRAND", "SA", "GA", "SDGA", "SRGA", "IDEA"])
 def test_tuning_loop_improves_and_writes_records(tmp_path, method):
     random.seed(7)
     np.random.seed(7)
