@@ -100,6 +100,9 @@ def conv_out_hw(H, W, KH, KW, stride, padding, dilation):
     dh, dw = _pair(dilation)
     HO = (H - ((KH - 1) * dh + 1) + 2 * padding) // sh + 1
     WO = (W - ((KW - 1) * dw + 1) + 2 * padding) // sw + 1
+    if HO <= 0 or WO <= 0:
+        # the window does not fit the padded image: the library's own answer, before any allocation
+        raise _lib.HeronB200Error(_lib.HB_ERR_SHAPE, "conv output extent %d x %d" % (HO, WO))
     return HO, WO
 
 

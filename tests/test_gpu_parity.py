@@ -575,3 +575,68 @@ def test_bounded_wait_runs_out_cleanly(K, co):
         K.gemm(ta, tb, out=out, knobs=dict(cta_group=1, tile_n=256))
         check(out, co.gemm_int(a, b), "after timeout")
     assert _lib.last_status() == 0
+
+
+# ---- property tests over random small shapes ------------------------------------------------------
+from hypothesis import HealthCheck, given, settings, strategies as st  # noqa: E402
+
+_prop = settings(max_examples=40, deadline=None, suppress_health_check=[HealthCheck.function_scoped_fixture])
+
+
+@_prop
+@given(M=st.integers(1, 300), N=st.integers(1, 300), K16=st.integers(1, 20), a_signed=st.booleans(),
+       cta_group=st.sampled_from([0, 1, 2]), seed=st.integers(0, 2 ** 20))
+def test_gemm_int8_random_shapes(K, co, M, N, K16, a_signed, cta_group, seed):
+    """Any M, any N (rows that are not 16-byte multiples take the direct-store epilogue), K a
+    multiple of 16 bytes."""
+    rng = np.random.default_rng(seed)
+    a, b = rand_i8(rng, (M, 16 * K16), a_signed), rand_i8(rng, (N, 16 * K16), True)
+    check(k_gemm(K, a, b, knobs=dict(cta_group=cta_group)), co.gemm_int(a, b), "gemm %s" % ((M, N, 16 * K16),))
+
+
+@_prop
+@given(B=st.integers(1, 5), M=st.integers(1, 200), N=st.integers(1, 40), K8=st.integers(1, 12),
+       seed=st.integers(0, 2 ** 20))
+def test_bmm_fp16_random_shapes(K, co, B, M, N, K8, seed):
+    rng = np.random.default_rng(seed)
+    Kd = 8 * K8
+    a = (rng.standard_normal((B, M, Kd)) / np.sqrt(Kd)).astype(np.float16)
+    b = rng.standard_normal((B, 4 * N, Kd)).astype(np.float16)
+    check(k_bmm(K, a, b), co.bmm_f16(a, b), "bmm %s" % ((B, M, 4 * N, Kd),))
+
+
+@_prop
+@given(N=st.integers(1, 4), H=st.integers(1, 20), W=st.integers(1, 20), CI=st.sampled_from([32, 64, 96]),
+       CO16=st.integers(1, 6), KH=st.integers(1, 5), KW=st.integers(1, 5), sh=st.integers(1, 3), sw=st.integers(1, 3),
+       pad=st.integers(0, 3), dil=st.integers(1, 2), algo=st.sampled_from([0, 1]), seed=st.integers(0, 2 ** 20))
+def test_conv_int8_random_geometry(K, co, N, H, W, CI, CO16, KH, KW, sh, sw, pad, dil, algo, seed):
+    """Strides, paddings, dilations and window sizes at random, including windows larger than the
+    image plus padding (rejected) and one-pixel outputs."""
+    span_h, span_w = (KH - 1) * dil + 1, (KW - 1) * dil + 1
+    rng = np.random.default_rng(seed)
+    x, w = rand_i8(rng, (N, H, W, CI), False), rand_i8(rng, (KH, KW, CI, 16 * CO16), True)
+    if H + 2 * pad < span_h or W + 2 * pad < span_w:
+        from heron_b200._lib import HB_ERR_SHAPE, HeronB200Error
+        with pytest.raises(HeronB200Error) as e:
+            K.conv2d_nhwc(dev(x), dev(w), (sh, sw), pad, dil)
+        assert e.value.status == HB_ERR_SHAPE
+        return
+    got = k_conv(K, x, w, (sh, sw), pad, dil, knobs=dict(conv_algo=algo))
+    check(got, co.conv2d_nhwc_int(x, w, (sh, sw), pad, dil), "conv %s" % ((N, H, W, CI, 16 * CO16, KH, KW, sh, sw, pad, dil),))
+
+
+@_prop
+@given(N=st.integers(1, 3), H=st.integers(1, 40), W=st.integers(1, 40), CO=st.sampled_from([64, 128]),
+       KH=st.integers(1, 3), KW=st.integers(1, 3), pad=st.integers(0, 2), dil=st.integers(1, 2),
+       half_out=st.booleans(), seed=st.integers(0, 2 ** 20))
+def test_conv_strip_random_geometry(K, co, N, H, W, CO, KH, KW, pad, dil, half_out, seed):
+    """The strip kernel over random stride-1 geometries: ragged last row groups, windows that
+    overhang the padding, one-row images, dilation."""
+    if H + 2 * pad < (KH - 1) * dil + 1 or W + 2 * pad < (KW - 1) * dil + 1:
+        return
+    rng = np.random.default_rng(seed)
+    x = rng.standard_normal((N, H, W, 64)).astype(np.float16)
+    w = (rng.standard_normal((KH, KW, 64, CO)) / np.sqrt(KH * KW * 64)).astype(np.float16)
+    od = np.float16 if half_out else np.float32
+    got = k_conv(K, x, w, 1, pad, dil, out_dtype=od, knobs=dict(conv_algo=2))
+    check(got, co.conv2d_nhwc_f16(x, w, 1, pad, dil, od), "strip %s" % ((N, H, W, CO, KH, KW, pad, dil),))
