@@ -76,11 +76,12 @@ class HbKnobs(ctypes.Structure):
         ("l2_prefetch", ctypes.c_int),
         ("conv_algo", ctypes.c_int),
         ("tail_split", ctypes.c_int),
+        ("split_k", ctypes.c_int),
         ("reserved", ctypes.c_int),
     ]
 
     FIELDS = ("tile_n", "stages", "swizzle_bytes", "acc_stages", "raster", "epilogue", "max_ctas",
-              "cta_group", "l2_prefetch", "conv_algo", "tail_split", "reserved")
+              "cta_group", "l2_prefetch", "conv_algo", "tail_split", "split_k", "reserved")
 
     @classmethod
     def from_dict(cls, d):

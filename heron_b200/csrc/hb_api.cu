@@ -250,6 +250,11 @@ int check_knobs(const Problem& pr, const hb_knobs& k, int* smem_bytes, int* tmem
   if (k.cta_group != 1 && k.cta_group != 2) return HB_ERR_KNOB;
   if (k.l2_prefetch < -1 || k.l2_prefetch > 64) return HB_ERR_KNOB;
   if (k.tail_split != 0 && k.tail_split != 1 && k.tail_split != 2 && k.tail_split != 4) return HB_ERR_KNOB;
+  if (k.split_k < 0 || k.split_k > 4) return HB_ERR_KNOB;
+  if (k.split_k > 1) {
+    // slices add into the output: 4-byte elements only; fp32 sums stay order-independent with two
+    if (eo != 4 || (pr.out == HB_F32 && k.split_k != 2) || k.tail_split > 1) return HB_ERR_KNOB;
+  }
   if (pr.conv) {
     if ((pr.CI * es) % k.swizzle_bytes != 0) return HB_ERR_KNOB;
     // whole MN-major chunks in every CTA of the group
@@ -451,8 +456,36 @@ int build_plan(Driver& d, const Problem& pr, const hb_knobs& k, const ConvGeom* 
   };
   const int tiles = p.num_tiles;
   const int tail = tiles % units;
-  int split = 1;
-  if (k.tail_split > 1) {
+  int split = 1, ksplit = 1;
+  // Split-K first: a slice of the reduction keeps the full-width MMA shape, so its cost falls in
+  // proportion, but the output tiles must be zeroed by a launch of its own and every slice then
+  // adds its partial sums through the L2 atomic units.  Measured on B200: about 3 us for the extra
+  // launch and 0.7 adds per ns; a K block of a full-width tile takes about 0.3 us in the GEMMs and
+  // 0.58 us in the im2col conv.  A partly filled wave also runs faster than a full one where the
+  // kernel is load-bound, so the library takes split-K only when the saving is clearly more than
+  // that cost and at least a quarter of the whole launch; a tuner may force it either way.
+  auto waves_of = [&](int s) {
+    return static_cast<double>((static_cast<long long>(s) * tail + units - 1) / units) / s;
+  };
+  if (k.split_k > 1) {
+    if (p.num_kb < k.split_k) return HB_ERR_KNOB;
+    ksplit = tail > 0 ? k.split_k : 1;
+  } else if (k.split_k == 0 && k.tail_split == 0 && eo == 4 && tail > 0) {
+    const int max_ks = pr.out == HB_F32 ? 2 : 4;
+    const double kb_us = pr.conv ? 0.58 : 0.30;
+    const double tile_elems = static_cast<double>(hb::kTileM) * cgrp * k.tile_n;
+    double best_gain = 0.0;
+    for (int s2 = 2; s2 <= max_ks; ++s2) {
+      if (p.num_kb < 4 * s2) continue;
+      const double saving = (1.0 - waves_of(s2)) * p.num_kb * kb_us;
+      const double cost = 3.0 + tail * tile_elems * s2 / 700e3;
+      const double launch_waves = static_cast<double>((tiles + units - 1) / units);
+      if ((1.0 - waves_of(s2)) < 0.25 * launch_waves) continue;
+      if (saving > 1.25 * cost && saving - cost > best_gain) { best_gain = saving - cost; ksplit = s2; }
+    }
+  }
+  if (ksplit > 1) {
+  } else if (k.tail_split > 1) {
     if (!slice_ok(k.tail_split)) return HB_ERR_KNOB;
     split = tail > 0 ? k.tail_split : 1;
   } else if (k.tail_split == 0 && tail > 0 && p.num_kb >= 8) {
@@ -460,13 +493,14 @@ int build_plan(Driver& d, const Problem& pr, const hb_knobs& k, const ConvGeom* 
     double best = 1.0;
     for (int s2 = 2; s2 <= 4; s2 *= 2) {
       if (!slice_ok(s2)) continue;
-      const double t = static_cast<double>((static_cast<long long>(s2) * tail + units - 1) / units) / s2;
+      const double t = waves_of(s2);
       if (t < best - 1e-9) { best = t; split = s2; }
     }
   }
   p.split = split;
-  p.whole_tiles = split > 1 ? tiles - tail : tiles;
-  p.num_tiles = p.whole_tiles + (tiles - p.whole_tiles) * split;
+  p.ksplit = ksplit;
+  p.whole_tiles = (split > 1 || ksplit > 1) ? tiles - tail : tiles;
+  p.num_tiles = p.whole_tiles + (tiles - p.whole_tiles) * split * ksplit;
   p.idesc_split = make_idesc(kind, pr.in_a, pr.in_b, hb::kTileM * cgrp, k.tile_n / split, pr.conv);
   plan->tmB2 = plan->tmB;
   if (split > 1 && !pr.conv) {
@@ -476,6 +510,7 @@ int build_plan(Driver& d, const Problem& pr, const hb_knobs& k, const ConvGeom* 
     if (rc != HB_OK) return rc;
   }
   plan->knobs.tail_split = split;
+  plan->knobs.split_k = ksplit;
   plan->grid = (p.num_tiles < units ? p.num_tiles : units) * cgrp;
   return HB_OK;
 }
@@ -529,6 +564,13 @@ int run_main(const hb_plan* plan, cudaStream_t stream) {
   }
   const bool half_out = plan->p.esize_out == 2;
   const bool i8 = plan->p.kind == 1;
+  if (plan->p.ksplit > 1) {
+    const int row_groups = 8;
+    const int sliced_tiles = (plan->p.num_tiles - plan->p.whole_tiles) / plan->p.ksplit;
+    hb::hb_zero_tiles_kernel<<<sliced_tiles * row_groups, 256, 0, stream>>>(
+        plan->p, hb::kTileM * plan->knobs.cta_group, row_groups);
+    if (cudaGetLastError() != cudaSuccess) return HB_ERR_LAUNCH;
+  }
   if (plan->knobs.cta_group == 2) {
     if (half_out) return launch_kernel<2, 2, 0>(plan, stream);
     return i8 ? launch_kernel<4, 2, 1>(plan, stream) : launch_kernel<4, 2, 0>(plan, stream);

@@ -60,6 +60,9 @@ struct KParams {
   // `split` column slices of BN/split, so that the last, partly filled wave of the persistent
   // grid is made of shorter work items.  num_tiles counts work items (whole tiles + slices).
   int whole_tiles, split;
+  // Alternatively (ksplit > 1, split == 1) each remaining tile is cut into `ksplit` slices of the
+  // reduction: full-width work items whose epilogue adds into an output that was zeroed first.
+  int ksplit;
   uint32_t idesc_split;
   long long wait_limit_cycles;  // 0: the default bound on every mbarrier wait
   uint32_t idesc;
@@ -148,14 +151,23 @@ hb_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   const int tile_step = gridDim.x / CG;
   const int tile_rows = kTileM * CG;
   // work item -> (batch, first row of the pair tile, first column, width)
-  auto decode = [&](int t, int& b, int& m_pair, int& n_first, int& bn) {
+  auto decode = [&](int t, int& b, int& m_pair, int& n_first, int& bn, int& kb0, int& kb1) {
     int slice = 0;
     bn = p.BN;
+    kb0 = 0;
+    kb1 = p.num_kb;
     if (t >= p.whole_tiles) {
       const int h = t - p.whole_tiles;
-      slice = h % p.split;
-      t = p.whole_tiles + h / p.split;
-      bn = p.BN / p.split;
+      if (p.ksplit > 1) {
+        const int ks = h % p.ksplit;
+        t = p.whole_tiles + h / p.ksplit;
+        kb0 = ks * p.num_kb / p.ksplit;
+        kb1 = (ks + 1) * p.num_kb / p.ksplit;
+      } else {
+        slice = h % p.split;
+        t = p.whole_tiles + h / p.split;
+        bn = p.BN / p.split;
+      }
     }
     b = t / tiles_per_batch;
     const int r = t - b * tiles_per_batch;
@@ -175,8 +187,8 @@ hb_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     // diagnostic 12: the producer stays silent, so the consumers' bounded waits run out and the
     // abort path (drain, TMEM release, status word) is what the launch exercises
     for (int t = first_tile; ok && t < p.num_tiles && p.probe != 12; t += tile_step) {
-      int b, m_pair, n_first, bn;
-      decode(t, b, m_pair, n_first, bn);
+      int b, m_pair, n_first, bn, kb0, kb1;
+      decode(t, b, m_pair, n_first, bn, kb0, kb1);
       const int bn_mine = bn / CG;  // B rows this CTA stages for this work item
       const int n_chunks = p.b_mn_major ? bn_mine / chunk_cols : 1;
       const uint32_t tx_bytes = static_cast<uint32_t>(a_bytes + bn_mine * p.SW) * CG;
@@ -193,7 +205,7 @@ hb_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         pix_w = x * p.stride_w - p.pad;
         pix_h = y * p.stride_h - p.pad;
       }
-      for (int kb = 0; kb < p.num_kb; ++kb) {
+      for (int kb = kb0; kb < kb1; ++kb) {
         const uint32_t full_local = smem_u32(&bars->full[stage]);
         const uint32_t full = (CG == 2) ? mapa(full_local, 0) : full_local;  // the leader's barrier
         if (!mbar_wait(smem_u32(&bars->empty[stage]), phase ^ 1u, wctx)) {
@@ -226,7 +238,7 @@ hb_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         } else {
           if (part & 1) tma_load_3d_cg<CG>(dA, &tmA, full, kb * BK, m0, b);
           krow = kb * BK;
-          if (p.l2_prefetch > 0 && kb + p.l2_prefetch < p.num_kb) {
+          if (p.l2_prefetch > 0 && kb + p.l2_prefetch < kb1) {
             tma_prefetch_3d(&tmA, (kb + p.l2_prefetch) * BK, m0, b);
             tma_prefetch_3d(tmBk, (kb + p.l2_prefetch) * BK, n0, b);
           }
@@ -306,7 +318,12 @@ hb_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * p.BN);
         const uint32_t idesc_t = (t >= p.whole_tiles) ? p.idesc_split : idesc;
         uint32_t accum = 0u;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        int n_kb = num_kb;  // K blocks of this work item
+        if (t >= p.whole_tiles && p.ksplit > 1) {
+          const int ks = (t - p.whole_tiles) % p.ksplit;
+          n_kb = (ks + 1) * num_kb / p.ksplit - ks * num_kb / p.ksplit;
+        }
+        for (int kb = 0; kb < n_kb; ++kb) {
           if (!mbar_wait(full0 + 8u * stage, phase, wctx)) {
             ok = false;
             break;
@@ -368,8 +385,9 @@ hb_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     constexpr int kColsPerStore = 128 / OUT_BYTES;  // 32 (4-byte) or 64 (fp16) columns
     const uint32_t my_buf = sEpi + ew * 2 * kEpiBufBytes;
     for (int t = first_tile; ok && t < p.num_tiles; t += tile_step) {
-      int b, m_pair, n0, bn;
-      decode(t, b, m_pair, n0, bn);
+      int b, m_pair, n0, bn, kb0, kb1;
+      decode(t, b, m_pair, n0, bn, kb0, kb1);
+      const bool reduce = OUT_BYTES == 4 && p.ksplit > 1 && t >= p.whole_tiles;
       const int row0 = m_pair + static_cast<int>(cta_rank) * kTileM + q * 32;
       if (!(p.probe == 8 ? mbar_wait(smem_u32(&bars->tmem_full[acc]), acc_phase, wctx)
                          : mbar_wait_relaxed(smem_u32(&bars->tmem_full[acc]), acc_phase, wctx))) {
@@ -439,7 +457,10 @@ hb_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             fence_proxy_async_smem();
             __syncwarp();
             if (issuer) {
-              tma_store_3d(&tmC, buf, col, row0, b);
+              if (reduce)
+                tma_reduce_add_3d(&tmC, buf, col, row0, b);
+              else
+                tma_store_3d(&tmC, buf, col, row0, b);
               bulk_commit();
             }
           }
@@ -452,7 +473,18 @@ hb_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                                 OUT_BYTES;
             const bool vec_ok = ((reinterpret_cast<uintptr_t>(base) & 15u) == 0) &&
                                 (col + kColsPerStore <= p.N);
-            if (vec_ok) {
+            if (reduce) {
+              const int ncols = min(kColsPerStore, p.N - col);
+#pragma unroll
+              for (int i = 0; i < 32; ++i) {
+                if (i < ncols) {
+                  if (KIND == 1)
+                    atomicAdd(reinterpret_cast<int*>(base) + i, static_cast<int>(packed[i]));
+                  else
+                    atomicAdd(reinterpret_cast<float*>(base) + i, __uint_as_float(packed[i]));
+                }
+              }
+            } else if (vec_ok) {
 #pragma unroll
               for (int j = 0; j < 8; ++j) {
                 *reinterpret_cast<uint4*>(base + 16 * j) =
@@ -495,6 +527,33 @@ hb_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     tmem_dealloc_cg<CG>(tmem_base, static_cast<uint32_t>(p.tmem_cols));
   }
   if (threadIdx.x == 0 && *abort_flag) atomicExch(&g_hb_status, kErrTimeout);
+}
+
+// Zeroes the output tiles that the split-K work items of hb_umma_kernel add into (4-byte
+// elements).  blockIdx.x walks (tile, row group) pairs; a warp writes 128 consecutive bytes of a row.
+__global__ void hb_zero_tiles_kernel(const KParams p, int tile_rows, int row_groups) {
+  const int tiles = (p.num_tiles - p.whole_tiles) / p.ksplit;
+  const int tiles_per_batch = p.tiles_m * p.tiles_n;
+  const int rows_per_group = tile_rows / row_groups;
+  for (int item = blockIdx.x; item < tiles * row_groups; item += gridDim.x) {
+    const int t = p.whole_tiles + item / row_groups;
+    const int g = item - (item / row_groups) * row_groups;
+    const int b = t / tiles_per_batch;
+    const int r = t - b * tiles_per_batch;
+    const int mb = p.raster ? (r % p.tiles_m) : (r / p.tiles_n);
+    const int nb = p.raster ? (r / p.tiles_m) : (r % p.tiles_n);
+    const int m0 = mb * tile_rows + g * rows_per_group;
+    const int n0 = nb * p.BN;
+    const int rows = min(rows_per_group, p.M - m0);
+    const int cols = min(p.BN, p.N - n0);
+    if (rows <= 0 || cols <= 0) continue;
+    uint32_t* base = static_cast<uint32_t*>(p.C) + static_cast<long long>(b) * p.batch_stride_c +
+                     static_cast<long long>(m0) * p.ldc + n0;
+    for (int i = threadIdx.x; i < rows * cols; i += blockDim.x) {
+      const int rr = i / cols;
+      base[static_cast<long long>(rr) * p.ldc + (i - rr * cols)] = 0u;
+    }
+  }
 }
 
 // Unpacks the x86 operator's int8 filter (CO/sco, KH, KW, CI/4, sco, 4) to HWIO (KH,KW,CI,CO).

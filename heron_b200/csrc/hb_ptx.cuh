@@ -140,6 +140,14 @@ __device__ __forceinline__ void tma_store_3d(const CUtensorMap* m, uint32_t src,
       "r"(src), "r"(x), "r"(y), "r"(z)
       : "memory");
 }
+// The same box added element-wise (s32 or f32, per the tensor map's type) into global memory.
+__device__ __forceinline__ void tma_reduce_add_3d(const CUtensorMap* m, uint32_t src, int x, int y, int z) {
+  asm volatile(
+      "cp.reduce.async.bulk.tensor.3d.global.shared::cta.add.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(
+          reinterpret_cast<uint64_t>(m)),
+      "r"(src), "r"(x), "r"(y), "r"(z)
+      : "memory");
+}
 __device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void bulk_wait_read() {

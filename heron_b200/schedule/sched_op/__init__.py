@@ -213,12 +213,35 @@ class rasterOp(SchedOp):
         ctx.addSchedDesc("## raster %s\n" % ctx.kernel_knobs["raster"])
 
 
+class splitKOp(SchedOp):
+    """Whether the work items of a partly filled wave are cut along the reduction (their partial
+    sums are added into a zeroed output).  0 leaves the choice to the library, 1 turns it off.
+    Only 4-byte outputs can be added into; fp32 sums stay order-independent with two slices."""
+
+    def perform(self, s, stage_name, ctx):
+        km = ctx.knob_manager
+        out = _problem(s, stage_name)
+        p = out.op.params
+        es, eo = ELEM_BYTES[p["in_dtype"]], ELEM_BYTES[p["out_dtype"]]
+        _, M, N, K, _ = _gemm_view(out)
+        split_k = genKey("P", stage_name, "k", param_name="split_k")
+        if km.is_building:
+            most = 1
+            if eo == 4:
+                most = 2 if p["out_dtype"] == "float32" else 4
+                most = max(1, min(most, (K * es) // 128))  # every slice keeps at least one K block
+            km.define_value(split_k, 0, most, 0, True)
+        ctx.kernel_knobs["split_k"] = km.get_val(split_k)
+        ctx.addSchedDesc("## split-K %s\n" % ctx.kernel_knobs["split_k"])
+
+
 _METHODS = {
     "tileOp": tileOp,
     "pipelineOp": pipelineOp,
     "epilogueOp": epilogueOp,
     "rasterOp": rasterOp,
     "convAlgoOp": convAlgoOp,
+    "splitKOp": splitKOp,
 }
 
 
@@ -235,5 +258,5 @@ def sched_via_rule(_type, ctx, s):
     that ``Task.instantiate`` can replay them (schedule/sched_op/__init__.py:23-30)."""
     get_op_methods(_type)
     for out in s.outputs:
-        for rule in ("tileOp", "pipelineOp", "epilogueOp", "rasterOp", "convAlgoOp"):
+        for rule in ("tileOp", "pipelineOp", "epilogueOp", "rasterOp", "convAlgoOp", "splitKOp"):
             ctx.addSched(rule, out.op.name, s)

@@ -141,6 +141,63 @@ def test_gemm_every_knob_gives_the_same_bits(K, co, knobs):
     check(k_gemm(K, a, b, knobs=knobs), co.gemm_int(a, b), str(knobs))
 
 
+# ---- split-K: slices of the reduction added into a zeroed output ---------------------------
+@pytest.mark.parametrize("knobs", [
+    dict(split_k=2), dict(split_k=3), dict(split_k=4), dict(split_k=2, epilogue=2), dict(split_k=4, epilogue=2),
+    dict(split_k=3, cta_group=1, tile_n=128), dict(split_k=2, cta_group=2, tile_n=64, swizzle_bytes=64),
+    dict(split_k=4, max_ctas=6), dict(split_k=2, raster=1, max_ctas=10),
+])
+@pytest.mark.parametrize("M,N,Kd", [(300, 200, 1040), (1024, 520, 512)])
+def test_split_k_int8_exact(K, co, knobs, M, N, Kd):
+    rng = np.random.default_rng(M + Kd)
+    a, b = rand_i8(rng, (M, Kd), False), rand_i8(rng, (N, Kd), True)
+    plan = K.plan_gemm(dev(a), dev(b), out=poison((M, N), torch.int32), knobs=knobs)
+    tiles = -(-M // (128 * plan.knobs()["cta_group"])) * -(-N // plan.knobs()["tile_n"])
+    units = plan.knobs()["grid"] // plan.knobs()["cta_group"]
+    if tiles % max(units, 1) or tiles < units:
+        assert plan.knobs()["split_k"] == knobs["split_k"]  # the path under test is the one that runs
+    check(k_gemm(K, a, b, knobs=knobs), co.gemm_int(a, b), "split-K %s" % (knobs,))
+
+
+def test_split_k_fp16_is_deterministic_and_close(K, co):
+    rng = np.random.default_rng(77)
+    M, N, Kd = 300, 264, 2048
+    a = (rng.standard_normal((M, Kd)) / np.sqrt(Kd)).astype(np.float16)
+    b = rng.standard_normal((N, Kd)).astype(np.float16)
+    want = co.gemm_f16(a, b)
+    first = None
+    for _ in range(3):
+        for knobs in (dict(split_k=2), dict(split_k=2, epilogue=2)):
+            got = k_gemm(K, a, b, knobs=knobs)
+            check(got, want, "split-K fp16")
+            if first is None:
+                first = got.clone()
+            assert torch.equal(got, first)  # two partial sums: the order of arrival cannot matter
+
+
+def test_split_k_conv_and_bmm(K, co):
+    rng = np.random.default_rng(5)
+    x = rand_i8(rng, (6, 7, 7, 128), False)
+    w = rand_i8(rng, (3, 3, 128, 128), True)
+    want = co.conv2d_nhwc_int(x, w, 1, 1, 1)
+    for knobs in (dict(split_k=2, conv_algo=1), dict(split_k=3, conv_algo=1, cta_group=1), dict(split_k=4, conv_algo=1, epilogue=2)):
+        check(k_conv(K, x, w, 1, 1, 1, knobs=knobs), want, "conv split-K %s" % (knobs,))
+    a, b = rand_i8(rng, (5, 200, 512), True), rand_i8(rng, (5, 72, 512), True)
+    for knobs in (dict(split_k=2), dict(split_k=4, max_ctas=4)):
+        check(k_bmm(K, a, b, knobs=knobs), co.bmm_int(a, b), "bmm split-K %s" % (knobs,))
+
+
+def test_split_k_rejected_where_it_cannot_add(K):
+    from heron_b200._lib import HB_ERR_KNOB, HeronB200Error
+    a = torch.zeros(128, 512, dtype=torch.float16, device="cuda")
+    b = torch.zeros(128, 512, dtype=torch.float16, device="cuda")
+    for knobs, out in ((dict(split_k=2), torch.float16), (dict(split_k=3), torch.float32), (dict(split_k=5), torch.float32),
+                       (dict(split_k=2, tail_split=2), torch.float32)):
+        with pytest.raises(HeronB200Error) as e:
+            K.gemm(a, b, out=torch.empty(128, 128, dtype=out, device="cuda"), knobs=knobs)
+        assert e.value.status == HB_ERR_KNOB
+
+
 def test_gemm_rejects_bad_arguments(K):
     from heron_b200._lib import HB_ERR_KNOB, HB_ERR_SHAPE, HeronB200Error
     a, b = torch.zeros(64, 24, dtype=torch.uint8, device="cuda"), torch.zeros(64, 24, dtype=torch.int8, device="cuda")
