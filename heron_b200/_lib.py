@@ -47,6 +47,13 @@ EXPORTED_SYMBOLS = (
     "hb_conv2d_nchw_scratch_bytes",
     "hb_conv2d_nchw",
     "hb_plan_conv2d_nchw",
+    "hb_gemv",
+    "hb_conv1d_ncw_scratch_bytes",
+    "hb_conv1d_ncw",
+    "hb_conv1d_nwc_packed",
+    "hb_plan_gemv",
+    "hb_plan_conv1d_ncw",
+    "hb_plan_conv1d_nwc_packed",
     "hb_conv2d_packed_noalloc_max_bytes",
     "hb_conv2d_nhwc_packed_noalloc",
     "hb_plan_gemm",
@@ -167,6 +174,20 @@ def load():
     pp = ctypes.POINTER(c_void_p)
     lib.hb_plan_conv2d_nchw.restype = c_int
     lib.hb_plan_conv2d_nchw.argtypes = [pp] + lib.hb_conv2d_nchw.argtypes[:-1]
+    lib.hb_gemv.restype = c_int
+    lib.hb_gemv.argtypes = [c_void_p] * 3 + [c_int] * 2 + [c_int] * 3 + [kp, c_void_p]
+    lib.hb_conv1d_ncw_scratch_bytes.restype = c_size_t
+    lib.hb_conv1d_ncw_scratch_bytes.argtypes = [c_int] * 7 + [c_int, c_int]
+    lib.hb_conv1d_ncw.restype = c_int
+    lib.hb_conv1d_ncw.argtypes = [c_void_p] * 3 + [c_int] * 7 + [c_int] * 3 + [c_void_p, c_size_t, kp, c_void_p]
+    lib.hb_conv1d_nwc_packed.restype = c_int
+    lib.hb_conv1d_nwc_packed.argtypes = [c_void_p] * 3 + [c_int] * 8 + [c_int, c_void_p, c_size_t, kp, c_void_p]
+    lib.hb_plan_gemv.restype = c_int
+    lib.hb_plan_gemv.argtypes = [pp] + lib.hb_gemv.argtypes[:-1]
+    lib.hb_plan_conv1d_ncw.restype = c_int
+    lib.hb_plan_conv1d_ncw.argtypes = [pp] + lib.hb_conv1d_ncw.argtypes[:-1]
+    lib.hb_plan_conv1d_nwc_packed.restype = c_int
+    lib.hb_plan_conv1d_nwc_packed.argtypes = [pp] + lib.hb_conv1d_nwc_packed.argtypes[:-1]
     lib.hb_plan_gemm.restype = c_int
     lib.hb_plan_gemm.argtypes = [pp] + lib.hb_gemm.argtypes[:-1]
     lib.hb_plan_bmm.restype = c_int

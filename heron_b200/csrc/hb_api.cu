@@ -165,7 +165,8 @@ struct Problem {
   int batch, M, N, K;
   hb_dtype in_a, in_b, out;
   bool conv;
-  int CI;  // conv only
+  int CI;      // conv only
+  int b_rows;  // gemm only: rows B really has when fewer than N (the rest read as zeros); 0 = N
 };
 
 // Ring-stage bytes of one CTA: 128 rows of A plus this CTA's share of B's tile_n rows.
@@ -284,7 +285,7 @@ int encode_tiled3(Driver& d, CUtensorMap* m, hb_dtype t, const void* ptr, uint64
 }
 
 struct ConvGeom {
-  int N, H, W, CI, CO, KH, KW, stride_h, stride_w, pad, dil_h, dil_w, HO, WO;
+  int N, H, W, CI, CO, KH, KW, stride_h, stride_w, pad_h, pad_w, dil_h, dil_w, HO, WO;
 };
 
 }  // namespace
@@ -381,7 +382,8 @@ int build_plan(Driver& d, const Problem& pr, const hb_knobs& k, const ConvGeom* 
     rc = encode_tiled3(d, &tmA, pr.in_a, A, pr.K, pr.M, pr.batch, rowA, rowA * pr.M, BK, hb::kTileM,
                        k.swizzle_bytes);
     if (rc != HB_OK) return rc;
-    rc = encode_tiled3(d, &tmB, pr.in_b, B, pr.K, pr.N, pr.batch, rowA, rowA * pr.N, BK,
+    const int b_rows = pr.b_rows > 0 ? pr.b_rows : pr.N;  // rows past the end are zero-filled by TMA
+    rc = encode_tiled3(d, &tmB, pr.in_b, B, pr.K, b_rows, pr.batch, rowA, rowA * b_rows, BK,
                        k.tile_n / cgrp, k.swizzle_bytes);
     if (rc != HB_OK) return rc;
   } else {
@@ -389,7 +391,7 @@ int build_plan(Driver& d, const Problem& pr, const hb_knobs& k, const ConvGeom* 
     p.kb_per_tap = cg->CI / BK;
     p.num_kb = cg->KH * cg->KW * p.kb_per_tap;
     p.stride_h = cg->stride_h; p.stride_w = cg->stride_w; p.dil_h = cg->dil_h; p.dil_w = cg->dil_w;
-    p.pad = cg->pad;
+    p.pad_h = cg->pad_h; p.pad_w = cg->pad_w;
     // Activations as a (C, W, H, N) tensor read in im2col mode.  The bounding box spans the
     // positions the top-left filter tap visits: from -pad to (extent - 1 + pad - (K-1)*dil).
     cuuint64_t dims[4] = {static_cast<cuuint64_t>(cg->CI), static_cast<cuuint64_t>(cg->W),
@@ -397,8 +399,8 @@ int build_plan(Driver& d, const Problem& pr, const hb_knobs& k, const ConvGeom* 
     cuuint64_t strides[3] = {static_cast<cuuint64_t>(cg->CI) * es,
                              static_cast<cuuint64_t>(cg->W) * cg->CI * es,
                              static_cast<cuuint64_t>(cg->H) * cg->W * cg->CI * es};
-    int lower[2] = {-cg->pad, -cg->pad};
-    int upper[2] = {cg->pad - (cg->KW - 1) * cg->dil_w, cg->pad - (cg->KH - 1) * cg->dil_h};
+    int lower[2] = {-cg->pad_w, -cg->pad_h};
+    int upper[2] = {cg->pad_w - (cg->KW - 1) * cg->dil_w, cg->pad_h - (cg->KH - 1) * cg->dil_h};
     cuuint32_t estr[4] = {1, static_cast<cuuint32_t>(cg->stride_w),
                           static_cast<cuuint32_t>(cg->stride_h), 1};
     CUresult r = d.im2col(&tmA, tmap_dtype(pr.in_a), 4, const_cast<void*>(A), dims, strides, lower,
@@ -505,7 +507,8 @@ int build_plan(Driver& d, const Problem& pr, const hb_knobs& k, const ConvGeom* 
   plan->tmB2 = plan->tmB;
   if (split > 1 && !pr.conv) {
     const uint64_t rowA = static_cast<uint64_t>(pr.K) * es;
-    rc = encode_tiled3(d, &plan->tmB2, pr.in_b, B, pr.K, pr.N, pr.batch, rowA, rowA * pr.N, BK,
+    const int b_rows = pr.b_rows > 0 ? pr.b_rows : pr.N;
+    rc = encode_tiled3(d, &plan->tmB2, pr.in_b, B, pr.K, b_rows, pr.batch, rowA, rowA * b_rows, BK,
                        k.tile_n / split / cgrp, k.swizzle_bytes);
     if (rc != HB_OK) return rc;
   }
@@ -599,7 +602,7 @@ int launch_kernel(const hb_plan* plan, cudaStream_t stream) {
 
 int plan_gemm_like(int op, const void* A, const void* B, void* C, int batch, int M, int K, int N,
                    hb_dtype in_a, hb_dtype in_b, hb_dtype out, const hb_knobs* knobs,
-                   hb_plan* plan) {
+                   hb_plan* plan, int b_rows = 0) {
   if (batch <= 0 || M <= 0 || K <= 0 || N <= 0) return HB_ERR_SHAPE;
   if (mma_kind(in_a, in_b, out) < 0) return HB_ERR_DTYPE;
   if ((static_cast<long long>(K) * esize(in_a)) % 16 != 0) return HB_ERR_SHAPE;
@@ -607,7 +610,7 @@ int plan_gemm_like(int op, const void* A, const void* B, void* C, int batch, int
   if (!aligned16(A) || !aligned16(B) || !aligned16(C)) return HB_ERR_ALIGN;
   Driver& d = driver();
   if (d.status != HB_OK) return d.status;
-  Problem pr{op, batch, M, N, K, in_a, in_b, out, false, 0};
+  Problem pr{op, batch, M, N, K, in_a, in_b, out, false, 0, b_rows};
   hb_knobs k;
   resolve_knobs(pr, knobs, d.sm_count, &k);
   return build_plan(d, pr, k, nullptr, A, B, C, plan);
@@ -640,7 +643,7 @@ int strip_smem_bytes(const ConvGeom& g, int es, int eo, hb::StripParams* sp) {
   if (g.stride_h != 1 || g.stride_w != 1) return 0;
   if ((g.CI * es) % 128 != 0 || (g.CO * es) % 128 != 0) return 0;
   if (g.CO > 256 || g.CO % (128 / eo) != 0 || g.CO % 16 != 0) return 0;
-  const int Wp = g.W + 2 * g.pad;
+  const int Wp = g.W + 2 * g.pad_w;
   if (Wp > 128 || Wp < 1) return 0;
   const int R = 128 / Wp;
   const int strip_rows = R + (g.KH - 1) * g.dil_h;
@@ -676,7 +679,7 @@ int build_strip_plan(Driver& d, const ConvGeom& g, hb_dtype in_a, hb_dtype in_w,
   const long long tiles = static_cast<long long>(g.N) * sp.groups;
   if (tiles > 0x7fffffffLL) return HB_ERR_SHAPE;
   sp.N = g.N; sp.H = g.H; sp.W = g.W; sp.CI = g.CI; sp.CO = g.CO; sp.KH = g.KH; sp.KW = g.KW;
-  sp.pad = g.pad; sp.dil_h = g.dil_h; sp.dil_w = g.dil_w; sp.HO = g.HO; sp.WO = g.WO;
+  sp.pad_h = g.pad_h; sp.pad_w = g.pad_w; sp.dil_h = g.dil_h; sp.dil_w = g.dil_w; sp.HO = g.HO; sp.WO = g.WO;
   sp.num_tiles = static_cast<int>(tiles);
   sp.esize_in = es; sp.esize_out = eo;
   sp.tmem_cols = next_pow2_cols(2 * g.CO);
@@ -716,21 +719,24 @@ int build_strip_plan(Driver& d, const ConvGeom& g, hb_dtype in_a, hb_dtype in_w,
   return HB_OK;
 }
 
+// pad_h / pad_w: rows / columns of zeros on each side of the height / width axis.  The 2-D
+// operators of the reference pad both axes alike; its 1-D convolutions are the H = KH = 1 case
+// with pad_h = 0.
 int plan_conv(const void* in, const void* w, void* out, int N, int H, int W, int CI, int CO, int KH,
-              int KW, int stride_h, int stride_w, int pad, int dil_h, int dil_w, hb_dtype in_a,
-              hb_dtype in_w, hb_dtype out_t, const hb_knobs* knobs, hb_plan* plan) {
+              int KW, int stride_h, int stride_w, int pad_h, int pad_w, int dil_h, int dil_w,
+              hb_dtype in_a, hb_dtype in_w, hb_dtype out_t, const hb_knobs* knobs, hb_plan* plan) {
   if (N <= 0 || H <= 0 || W <= 0 || CI <= 0 || CO <= 0 || KH <= 0 || KW <= 0) return HB_ERR_SHAPE;
-  if (stride_h <= 0 || stride_w <= 0 || dil_h <= 0 || dil_w <= 0 || pad < 0) return HB_ERR_SHAPE;
+  if (stride_h <= 0 || stride_w <= 0 || dil_h <= 0 || dil_w <= 0 || pad_h < 0 || pad_w < 0) return HB_ERR_SHAPE;
   if (mma_kind(in_a, in_w, out_t) < 0) return HB_ERR_DTYPE;
   const int es = esize(in_a);
   if ((CI * es) % 32 != 0) return HB_ERR_SHAPE;
   if ((static_cast<long long>(CO) * es) % 16 != 0) return HB_ERR_SHAPE;
   // im2col-mode TMA limits: 8-bit signed corners, 8-bit tap offsets, traversal stride <= 8.
-  if (pad > 127 || (KW - 1) * dil_w > 255 || (KH - 1) * dil_h > 255) return HB_ERR_SHAPE;
-  if (pad - (KW - 1) * dil_w < -128 || pad - (KH - 1) * dil_h < -128) return HB_ERR_SHAPE;
+  if (pad_h > 127 || pad_w > 127 || (KW - 1) * dil_w > 255 || (KH - 1) * dil_h > 255) return HB_ERR_SHAPE;
+  if (pad_w - (KW - 1) * dil_w < -128 || pad_h - (KH - 1) * dil_h < -128) return HB_ERR_SHAPE;
   if (stride_h > 8 || stride_w > 8) return HB_ERR_SHAPE;
-  const int HO = conv_out_extent(H, KH, stride_h, pad, dil_h);
-  const int WO = conv_out_extent(W, KW, stride_w, pad, dil_w);
+  const int HO = conv_out_extent(H, KH, stride_h, pad_h, dil_h);
+  const int WO = conv_out_extent(W, KW, stride_w, pad_w, dil_w);
   if (HO <= 0 || WO <= 0) return HB_ERR_SHAPE;
   const long long M = static_cast<long long>(N) * HO * WO;
   const long long K = static_cast<long long>(KH) * KW * CI;
@@ -740,7 +746,7 @@ int plan_conv(const void* in, const void* w, void* out, int N, int H, int W, int
   Driver& d = driver();
   if (d.status != HB_OK) return d.status;
   Problem pr{2, 1, static_cast<int>(M), CO, static_cast<int>(K), in_a, in_w, out_t, true, CI};
-  ConvGeom cg{N, H, W, CI, CO, KH, KW, stride_h, stride_w, pad, dil_h, dil_w, HO, WO};
+  ConvGeom cg{N, H, W, CI, CO, KH, KW, stride_h, stride_w, pad_h, pad_w, dil_h, dil_w, HO, WO};
   const int algo = knobs ? knobs->conv_algo : 0;
   if (algo < 0 || algo > 2) return HB_ERR_KNOB;
   if (algo != 1) {
@@ -750,7 +756,8 @@ int plan_conv(const void* in, const void* w, void* out, int N, int H, int W, int
     // Picked by default when the filter has more than one tap (so pixels would otherwise be
     // re-fetched per tap), tiles fill at least three quarters of the 128 MMA rows, and the whole
     // reduction is short enough that operand traffic, not tensor time, bounds the kernel.
-    const bool wanted = algo == 2 || (KH * KW > 1 && probe.R * probe.Wp >= 96 && K * es <= 2048);
+    const bool rows_used = fits && static_cast<long long>(HO) * probe.Wp * 4 >= static_cast<long long>(probe.groups) * 128 * 3;
+    const bool wanted = algo == 2 || (KH * KW > 1 && rows_used && K * es <= 2048);
     if (algo == 2 && !fits) return HB_ERR_KNOB;
     if (fits && wanted) {
       hb_knobs k0;
@@ -765,17 +772,17 @@ int plan_conv(const void* in, const void* w, void* out, int N, int H, int W, int
 }
 
 int plan_conv_packed(const void* in, const void* w_packed, void* out, int N, int H, int W, int CI,
-                     int CO, int KH, int KW, int stride_h, int stride_w, int pad, int dil_h,
-                     int dil_w, int sco, void* scratch, size_t scratch_bytes, const hb_knobs* knobs,
-                     hb_plan* plan) {
+                     int CO, int KH, int KW, int stride_h, int stride_w, int pad_h, int pad_w,
+                     int dil_h, int dil_w, int sco, void* scratch, size_t scratch_bytes,
+                     const hb_knobs* knobs, hb_plan* plan) {
   if (sco != 64 && sco != 48 && sco != 32) return HB_ERR_SHAPE;
   if (CI <= 0 || CO <= 0 || KH <= 0 || KW <= 0) return HB_ERR_SHAPE;
   if (CI % 4 != 0 || CO % sco != 0) return HB_ERR_SHAPE;
   if (!scratch || scratch_bytes < hb_conv2d_packed_scratch_bytes(CI, CO, KH, KW))
     return HB_ERR_SCRATCH;
   if (!w_packed || !aligned16(w_packed) || !aligned16(scratch)) return HB_ERR_ALIGN;
-  const int rc = plan_conv(in, scratch, out, N, H, W, CI, CO, KH, KW, stride_h, stride_w, pad, dil_h,
-                           dil_w, HB_U8, HB_S8, HB_S32, knobs, plan);
+  const int rc = plan_conv(in, scratch, out, N, H, W, CI, CO, KH, KW, stride_h, stride_w, pad_h, pad_w,
+                           dil_h, dil_w, HB_U8, HB_S8, HB_S32, knobs, plan);
   if (rc != HB_OK) return rc;
   const long long groups = static_cast<long long>(KH) * KW * (CI / 4) * CO;
   int blocks = static_cast<int>((groups + 255) / 256);
@@ -796,16 +803,16 @@ struct NchwLayout {
   size_t in_bytes, w_bytes, out_bytes, total;
 };
 
-bool nchw_layout(int N, int H, int W, int CI, int CO, int KH, int KW, int sh, int sw, int pad,
-                 hb_dtype in_a, hb_dtype out_t, NchwLayout* L) {
+bool nchw_layout(int N, int H, int W, int CI, int CO, int KH, int KW, int sh, int sw, int pad_h,
+                 int pad_w, hb_dtype in_a, hb_dtype out_t, NchwLayout* L) {
   const int es = esize(in_a), eo = esize(out_t);
   if (es == 0 || eo == 0 || N <= 0 || H <= 0 || W <= 0 || CI <= 0 || CO <= 0 || KH <= 0 || KW <= 0 ||
-      sh <= 0 || sw <= 0 || pad < 0)
+      sh <= 0 || sw <= 0 || pad_h < 0 || pad_w < 0)
     return false;
   const int gran = 32 / es;  // the NHWC kernels want whole 32-byte channel groups
   L->CIp = (CI + gran - 1) / gran * gran;
-  L->HO = conv_out_extent(H, KH, sh, pad, 1);
-  L->WO = conv_out_extent(W, KW, sw, pad, 1);
+  L->HO = conv_out_extent(H, KH, sh, pad_h, 1);
+  L->WO = conv_out_extent(W, KW, sw, pad_w, 1);
   if (L->HO <= 0 || L->WO <= 0) return false;
   L->in_bytes = align256(static_cast<size_t>(N) * H * W * L->CIp * es);
   L->w_bytes = align256(static_cast<size_t>(KH) * KW * L->CIp * CO * es);
@@ -815,11 +822,11 @@ bool nchw_layout(int N, int H, int W, int CI, int CO, int KH, int KW, int sh, in
 }
 
 int plan_conv_nchw(const void* in, const void* w, void* out, int N, int H, int W, int CI, int CO,
-                   int KH, int KW, int sh, int sw, int pad, hb_dtype in_a, hb_dtype in_w,
+                   int KH, int KW, int sh, int sw, int pad_h, int pad_w, hb_dtype in_a, hb_dtype in_w,
                    hb_dtype out_t, void* scratch, size_t scratch_bytes, const hb_knobs* knobs,
                    hb_plan* plan) {
   NchwLayout L;
-  if (!nchw_layout(N, H, W, CI, CO, KH, KW, sh, sw, pad, in_a, out_t, &L)) return HB_ERR_SHAPE;
+  if (!nchw_layout(N, H, W, CI, CO, KH, KW, sh, sw, pad_h, pad_w, in_a, out_t, &L)) return HB_ERR_SHAPE;
   if (esize(in_w) != esize(in_a)) return HB_ERR_DTYPE;
   if (!scratch || scratch_bytes < L.total) return HB_ERR_SCRATCH;
   if (!in || !w || !out) return HB_ERR_ALIGN;
@@ -827,7 +834,7 @@ int plan_conv_nchw(const void* in, const void* w, void* out, int N, int H, int W
   uint8_t* s_in = static_cast<uint8_t*>(scratch);
   uint8_t* s_w = s_in + L.in_bytes;
   uint8_t* s_out = s_w + L.w_bytes;
-  const int rc = plan_conv(s_in, s_w, s_out, N, H, W, L.CIp, CO, KH, KW, sh, sw, pad, 1, 1, in_a, in_w,
+  const int rc = plan_conv(s_in, s_w, s_out, N, H, W, L.CIp, CO, KH, KW, sh, sw, pad_h, pad_w, 1, 1, in_a, in_w,
                            out_t, knobs, plan);
   if (rc != HB_OK) return rc;
   const int es = esize(in_a), eo = esize(out_t);
@@ -853,7 +860,7 @@ size_t hb_conv2d_nchw_scratch_bytes(int N, int H, int W, int CI, int CO, int KH,
                                     int stride_h, int stride_w, int pad, hb_dtype in_a,
                                     hb_dtype out_t) {
   NchwLayout L;
-  return nchw_layout(N, H, W, CI, CO, KH, KW, stride_h, stride_w, pad, in_a, out_t, &L) ? L.total : 0;
+  return nchw_layout(N, H, W, CI, CO, KH, KW, stride_h, stride_w, pad, pad, in_a, out_t, &L) ? L.total : 0;
 }
 
 int hb_conv2d_nchw(const void* in, const void* w, void* out, int N, int H, int W, int CI, int CO,
@@ -861,7 +868,7 @@ int hb_conv2d_nchw(const void* in, const void* w, void* out, int N, int H, int W
                    hb_dtype in_w, hb_dtype out_t, void* scratch, size_t scratch_bytes,
                    const hb_knobs* knobs, void* stream) {
   hb_plan plan;
-  const int rc = plan_conv_nchw(in, w, out, N, H, W, CI, CO, KH, KW, stride_h, stride_w, pad, in_a,
+  const int rc = plan_conv_nchw(in, w, out, N, H, W, CI, CO, KH, KW, stride_h, stride_w, pad, pad, in_a,
                                 in_w, out_t, scratch, scratch_bytes, knobs, &plan);
   return rc != HB_OK ? rc : run_plan(&plan, static_cast<cudaStream_t>(stream));
 }
@@ -871,7 +878,7 @@ int hb_plan_conv2d_nchw(hb_plan** plan, const void* in, const void* w, void* out
                         hb_dtype in_a, hb_dtype in_w, hb_dtype out_t, void* scratch,
                         size_t scratch_bytes, const hb_knobs* knobs) {
   return new_plan(plan, [&](hb_plan* p) {
-    return plan_conv_nchw(in, w, out, N, H, W, CI, CO, KH, KW, stride_h, stride_w, pad, in_a, in_w,
+    return plan_conv_nchw(in, w, out, N, H, W, CI, CO, KH, KW, stride_h, stride_w, pad, pad, in_a, in_w,
                           out_t, scratch, scratch_bytes, knobs, p);
   });
 }
@@ -929,12 +936,72 @@ int hb_bmm(const void* A, const void* B, void* C, int batch, int M, int K, int N
   return rc != HB_OK ? rc : run_plan(&plan, static_cast<cudaStream_t>(stream));
 }
 
+// Matrix-vector product in the reference's tensor-core form: the vector is row 0 of an 8-row
+// B whose other rows are zero, the result is column 0 of an (M, 8) output.  B's tensor map covers
+// the one real row; TMA's out-of-bounds fill supplies the zero rows, so no padded copy is made.
+int hb_gemv(const void* A, const void* x, void* out, int M, int K, hb_dtype in_a, hb_dtype in_x,
+            hb_dtype out_t, const hb_knobs* knobs, void* stream) {
+  hb_plan plan;
+  const int rc = plan_gemm_like(0, A, x, out, 1, M, K, 8, in_a, in_x, out_t, knobs, &plan, 1);
+  return rc != HB_OK ? rc : run_plan(&plan, static_cast<cudaStream_t>(stream));
+}
+
+int hb_plan_gemv(hb_plan** plan, const void* A, const void* x, void* out, int M, int K,
+                 hb_dtype in_a, hb_dtype in_x, hb_dtype out_t, const hb_knobs* knobs) {
+  return new_plan(plan, [&](hb_plan* p) {
+    return plan_gemm_like(0, A, x, out, 1, M, K, 8, in_a, in_x, out_t, knobs, p, 1);
+  });
+}
+
+// 1-D convolutions: the 2-D kernels with H = KH = 1 and no padding along the height.
+size_t hb_conv1d_ncw_scratch_bytes(int N, int W, int CI, int CO, int KW, int stride, int pad,
+                                   hb_dtype in_a, hb_dtype out_t) {
+  NchwLayout L;
+  return nchw_layout(N, 1, W, CI, CO, 1, KW, 1, stride, 0, pad, in_a, out_t, &L) ? L.total : 0;
+}
+
+int hb_conv1d_ncw(const void* in, const void* w, void* out, int N, int W, int CI, int CO, int KW,
+                  int stride, int pad, hb_dtype in_a, hb_dtype in_w, hb_dtype out_t, void* scratch,
+                  size_t scratch_bytes, const hb_knobs* knobs, void* stream) {
+  hb_plan plan;
+  const int rc = plan_conv_nchw(in, w, out, N, 1, W, CI, CO, 1, KW, 1, stride, 0, pad, in_a, in_w,
+                                out_t, scratch, scratch_bytes, knobs, &plan);
+  return rc != HB_OK ? rc : run_plan(&plan, static_cast<cudaStream_t>(stream));
+}
+
+int hb_plan_conv1d_ncw(hb_plan** plan, const void* in, const void* w, void* out, int N, int W,
+                       int CI, int CO, int KW, int stride, int pad, hb_dtype in_a, hb_dtype in_w,
+                       hb_dtype out_t, void* scratch, size_t scratch_bytes, const hb_knobs* knobs) {
+  return new_plan(plan, [&](hb_plan* p) {
+    return plan_conv_nchw(in, w, out, N, 1, W, CI, CO, 1, KW, 1, stride, 0, pad, in_a, in_w, out_t,
+                          scratch, scratch_bytes, knobs, p);
+  });
+}
+
+int hb_conv1d_nwc_packed(const void* in, const void* w_packed, void* out, int N, int W, int CI,
+                         int CO, int KW, int stride, int pad, int dil, int sco, void* scratch,
+                         size_t scratch_bytes, const hb_knobs* knobs, void* stream) {
+  hb_plan plan;
+  const int rc = plan_conv_packed(in, w_packed, out, N, 1, W, CI, CO, 1, KW, 1, stride, 0, pad, 1, dil,
+                                  sco, scratch, scratch_bytes, knobs, &plan);
+  return rc != HB_OK ? rc : run_plan(&plan, static_cast<cudaStream_t>(stream));
+}
+
+int hb_plan_conv1d_nwc_packed(hb_plan** plan, const void* in, const void* w_packed, void* out, int N,
+                              int W, int CI, int CO, int KW, int stride, int pad, int dil, int sco,
+                              void* scratch, size_t scratch_bytes, const hb_knobs* knobs) {
+  return new_plan(plan, [&](hb_plan* p) {
+    return plan_conv_packed(in, w_packed, out, N, 1, W, CI, CO, 1, KW, 1, stride, 0, pad, 1, dil, sco,
+                            scratch, scratch_bytes, knobs, p);
+  });
+}
+
 int hb_conv2d_nhwc(const void* in, const void* w, void* out, int N, int H, int W, int CI, int CO,
                    int KH, int KW, int stride_h, int stride_w, int pad, int dil_h, int dil_w,
                    hb_dtype in_a, hb_dtype in_w, hb_dtype out_t, const hb_knobs* knobs,
                    void* stream) {
   hb_plan plan;
-  const int rc = plan_conv(in, w, out, N, H, W, CI, CO, KH, KW, stride_h, stride_w, pad, dil_h,
+  const int rc = plan_conv(in, w, out, N, H, W, CI, CO, KH, KW, stride_h, stride_w, pad, pad, dil_h,
                            dil_w, in_a, in_w, out_t, knobs, &plan);
   return rc != HB_OK ? rc : run_plan(&plan, static_cast<cudaStream_t>(stream));
 }
@@ -951,7 +1018,7 @@ int hb_conv2d_nhwc_packed(const void* in, const void* w_packed, void* out, int N
                           const hb_knobs* knobs, void* stream) {
   hb_plan plan;
   const int rc = plan_conv_packed(in, w_packed, out, N, H, W, CI, CO, KH, KW, stride_h, stride_w,
-                                  pad, dil_h, dil_w, sco, scratch, scratch_bytes, knobs, &plan);
+                                  pad, pad, dil_h, dil_w, sco, scratch, scratch_bytes, knobs, &plan);
   return rc != HB_OK ? rc : run_plan(&plan, static_cast<cudaStream_t>(stream));
 }
 
@@ -972,7 +1039,7 @@ int hb_conv2d_nhwc_packed_noalloc(const void* in, const void* w_packed, void* ou
   // The unpack kernel rewrites every byte of the scratch the conv kernel will read (the whole
   // KH*KW*CI*CO filter), so nothing left over from an earlier call can leak into this one.
   hb_plan plan;
-  rc = plan_conv_packed(in, w_packed, out, N, H, W, CI, CO, KH, KW, stride_h, stride_w, pad, dil_h,
+  rc = plan_conv_packed(in, w_packed, out, N, H, W, CI, CO, KH, KW, stride_h, stride_w, pad, pad, dil_h,
                         dil_w, sco, scratch, HB_STATIC_SCRATCH_BYTES, knobs, &plan);
   return rc != HB_OK ? rc : run_plan(&plan, static_cast<cudaStream_t>(stream));
 }
@@ -996,7 +1063,7 @@ int hb_plan_conv2d_nhwc(hb_plan** plan, const void* in, const void* w, void* out
                         int dil_h, int dil_w, hb_dtype in_a, hb_dtype in_w, hb_dtype out_t,
                         const hb_knobs* knobs) {
   return new_plan(plan, [&](hb_plan* p) {
-    return plan_conv(in, w, out, N, H, W, CI, CO, KH, KW, stride_h, stride_w, pad, dil_h, dil_w,
+    return plan_conv(in, w, out, N, H, W, CI, CO, KH, KW, stride_h, stride_w, pad, pad, dil_h, dil_w,
                      in_a, in_w, out_t, knobs, p);
   });
 }
@@ -1006,7 +1073,7 @@ int hb_plan_conv2d_nhwc_packed(hb_plan** plan, const void* in, const void* w_pac
                                int stride_w, int pad, int dil_h, int dil_w, int sco, void* scratch,
                                size_t scratch_bytes, const hb_knobs* knobs) {
   return new_plan(plan, [&](hb_plan* p) {
-    return plan_conv_packed(in, w_packed, out, N, H, W, CI, CO, KH, KW, stride_h, stride_w, pad,
+    return plan_conv_packed(in, w_packed, out, N, H, W, CI, CO, KH, KW, stride_h, stride_w, pad, pad,
                             dil_h, dil_w, sco, scratch, scratch_bytes, knobs, p);
   });
 }

@@ -6,8 +6,8 @@
 //   * keeps the whole HWIO filter in shared memory for the life of the kernel (it is loaded once
 //     per CTA: KH*KW*CI*CO elements, 72 KiB for 3x3x64x64 fp16), and
 //   * loads, per tile, one zero-padded strip of the input — (R + (KH-1)*dil) rows of the padded
-//     width Wp = W + 2*pad — with a single tiled TMA box per 128-byte channel chunk; padding comes
-//     from TMA's out-of-bounds zero fill (the box starts at w = -pad, h = y0 - pad).
+//     width Wp = W + 2*pad_w — with a single tiled TMA box per 128-byte channel chunk; padding comes
+//     from TMA's out-of-bounds zero fill (the box starts at w = -pad_w, h = y0 - pad_h).
 // Output positions are numbered in padded-linear order i = y*Wp + x (x < Wp, so each row carries
 // Wp - WO junk positions).  For filter tap (ry, rx) the A operand of the MMA is the same strip
 // read from pixel (ry*dil*Wp + rx*dil) on: its shared-memory descriptor simply starts that many
@@ -25,7 +25,7 @@
 namespace hb {
 
 struct StripParams {
-  int N, H, W, CI, CO, KH, KW, pad, dil_h, dil_w, HO, WO;
+  int N, H, W, CI, CO, KH, KW, pad_h, pad_w, dil_h, dil_w, HO, WO;
   int Wp;             // padded width
   int R;              // output rows per tile
   int strip_rows;     // input rows per strip = R + (KH-1)*dil_h
@@ -145,8 +145,8 @@ hb_conv_strip_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_cons
         }
         mbar_arrive_expect_tx(full, tx);
         for (int cc = 0; cc < p.n_cchunks; ++cc)
-          tma_load_4d(sStrip + buf * strip_total + cc * p.strip_bytes, &tmIn, full, cc * BK, -p.pad,
-                      y0 - p.pad, n);
+          tma_load_4d(sStrip + buf * strip_total + cc * p.strip_bytes, &tmIn, full, cc * BK, -p.pad_w,
+                      y0 - p.pad_h, n);
         ++issued;
         if (++buf == p.ring) {
           buf = 0;

@@ -67,7 +67,7 @@ struct KParams {
   long long wait_limit_cycles;  // 0: the default bound on every mbarrier wait
   uint32_t idesc;
   // conv geometry (a_im2col only)
-  int HO, WO, KW, CI, kb_per_tap, stride_h, stride_w, dil_h, dil_w, pad;
+  int HO, WO, KW, CI, kb_per_tap, stride_h, stride_w, dil_h, dil_w, pad_h, pad_w;
   // direct-store epilogue
   void* C;
   long long ldc;             // elements between consecutive rows of C
@@ -202,8 +202,8 @@ hb_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         const int rem = m0 - pix_n * hw;
         const int y = rem / p.WO;
         const int x = rem - y * p.WO;
-        pix_w = x * p.stride_w - p.pad;
-        pix_h = y * p.stride_h - p.pad;
+        pix_w = x * p.stride_w - p.pad_w;
+        pix_h = y * p.stride_h - p.pad_h;
       }
       for (int kb = kb0; kb < kb1; ++kb) {
         const uint32_t full_local = smem_u32(&bars->full[stage]);
@@ -214,7 +214,7 @@ hb_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         }
         if (p.probe == 1 && issued >= p.stages) {
           // diagnostic: operands stay as first loaded; only the barrier protocol runs
-          if (leader) mbar_arrive(full_local);
+          if (leader && (part & 1)) mbar_arrive(full_local);  // one arrival per stage: the A producer's
           ++issued;
           if (++stage == p.stages) {
             stage = 0;

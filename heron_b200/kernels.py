@@ -290,3 +290,110 @@ def plan_conv2d_nhwc_packed(x, w_packed, CO, KH, KW, stride=1, padding=0, dilati
                                         scratch.numel(), _knobs(knobs))
     _lib.check(rc, "hb_plan_conv2d_nhwc_packed")
     return Plan(h, (x, w_packed, scratch), out)
+
+
+# ---- operators next to the hot path that run on the same kernels ---------------------------
+def _gemv_args(a, x, out, out_dtype):
+    M, K = a.shape
+    if tuple(x.shape) != (1, K):
+        raise ValueError("a is (M,K), x is (1,K)")
+    if out is None:
+        out = torch.empty((M, 8), dtype=out_dtype or default_out_dtype(a.dtype), device=a.device)
+    if tuple(out.shape) != (M, 8):
+        raise ValueError("out is (M, 8): column 0 holds the product (ops/cuda/gemv.py:7)")
+    return M, K, out
+
+
+def gemv(a, x, out=None, out_dtype=None, knobs=None):
+    """out[i,0] = sum_k a[i,k] * x[0,k]; out[i,1..7] = 0 (the reference's 8-row padded form)."""
+    M, K, out = _gemv_args(a, x, out, out_dtype)
+    rc = _lib.load().hb_gemv(_dev(a, "a"), _dev(x, "x"), _dev(out, "out"), M, K, _code(a), _code(x),
+                             _code(out), _knobs(knobs), _stream(a))
+    _lib.check(rc, "hb_gemv")
+    return out
+
+
+def plan_gemv(a, x, out=None, out_dtype=None, knobs=None):
+    M, K, out = _gemv_args(a, x, out, out_dtype)
+    h = ctypes.c_void_p()
+    rc = _lib.load().hb_plan_gemv(ctypes.byref(h), _dev(a, "a"), _dev(x, "x"), _dev(out, "out"), M, K,
+                                  _code(a), _code(x), _code(out), _knobs(knobs))
+    _lib.check(rc, "hb_plan_gemv")
+    return Plan(h, (a, x), out)
+
+
+def conv1d_out_w(W, KW, stride, padding, dilation=1):
+    """(W - dilated_KW + 2*pad) // stride + 1 (ops/cuda/conv1d.py:24-25, ops/x86/conv1d_int8.py:53-55)."""
+    WO = (W - ((KW - 1) * dilation + 1) + 2 * padding) // stride + 1
+    if WO <= 0:
+        raise _lib.HeronB200Error(_lib.HB_ERR_SHAPE, "conv1d output extent %d" % WO)
+    return WO
+
+
+def _c1d_ncw_args(x, w, stride, padding, out, out_dtype, scratch):
+    N, CI, W = x.shape
+    CO, CI2, KW = w.shape
+    if CI != CI2:
+        raise ValueError("input channels of x and w differ")
+    WO = conv1d_out_w(W, KW, int(stride), int(padding))
+    if out is None:
+        out = torch.empty((N, CO, WO), dtype=out_dtype or default_out_dtype(x.dtype), device=x.device)
+    need = _lib.load().hb_conv1d_ncw_scratch_bytes(N, W, CI, CO, KW, int(stride), int(padding), _code(x),
+                                                  _code(out))
+    if scratch is None:
+        scratch = torch.empty(need, dtype=torch.uint8, device=x.device)
+    return (N, W, CI, CO, KW, int(stride), int(padding)), out, scratch
+
+
+def conv1d_ncw(x, w, stride=1, padding=0, out=None, out_dtype=None, scratch=None, knobs=None):
+    """out[n,c,q] = sum pad(x)[n,ci,q*s+kw] * w[c,ci,kw]; x (N,CI,W), w (CO,CI,KW), dilation 1."""
+    dims, out, scratch = _c1d_ncw_args(x, w, stride, padding, out, out_dtype, scratch)
+    rc = _lib.load().hb_conv1d_ncw(_dev(x, "x"), _dev(w, "w"), _dev(out, "out"), *dims, _code(x), _code(w),
+                                   _code(out), _dev(scratch, "scratch"), scratch.numel(), _knobs(knobs),
+                                   _stream(x))
+    _lib.check(rc, "hb_conv1d_ncw")
+    return out
+
+
+def plan_conv1d_ncw(x, w, stride=1, padding=0, out=None, out_dtype=None, scratch=None, knobs=None):
+    dims, out, scratch = _c1d_ncw_args(x, w, stride, padding, out, out_dtype, scratch)
+    h = ctypes.c_void_p()
+    rc = _lib.load().hb_plan_conv1d_ncw(ctypes.byref(h), _dev(x, "x"), _dev(w, "w"), _dev(out, "out"), *dims,
+                                        _code(x), _code(w), _code(out), _dev(scratch, "scratch"),
+                                        scratch.numel(), _knobs(knobs))
+    _lib.check(rc, "hb_plan_conv1d_ncw")
+    return Plan(h, (x, w, scratch), out)
+
+
+def _c1d_packed_args(x, CO, KW, stride, padding, dilation, sco, out, scratch):
+    N, W, CI = x.shape
+    WO = conv1d_out_w(W, KW, int(stride), int(padding), int(dilation))
+    lib = _lib.load()
+    if scratch is None:
+        scratch = torch.empty(lib.hb_conv2d_packed_scratch_bytes(CI, CO, 1, KW), dtype=torch.int8,
+                              device=x.device)
+    if out is None:
+        out = torch.empty((N, WO, CO // sco, sco), dtype=torch.int32, device=x.device)
+    return (N, W, CI, CO, KW, int(stride), int(padding), int(dilation), int(sco)), out, scratch
+
+
+def conv1d_nwc_packed(x, w_packed, CO, KW, stride=1, padding=0, dilation=1, sco=64, out=None,
+                      scratch=None, knobs=None):
+    """The x86 1-D conv: uint8 (N,W,CI) input, int8 filter packed (CO/sco, KW, CI/4, sco, 4)."""
+    dims, out, scratch = _c1d_packed_args(x, CO, KW, stride, padding, dilation, sco, out, scratch)
+    rc = _lib.load().hb_conv1d_nwc_packed(_dev(x, "x"), _dev(w_packed, "w_packed"), _dev(out, "out"), *dims,
+                                          _dev(scratch, "scratch"), scratch.numel(), _knobs(knobs),
+                                          _stream(x))
+    _lib.check(rc, "hb_conv1d_nwc_packed")
+    return out
+
+
+def plan_conv1d_nwc_packed(x, w_packed, CO, KW, stride=1, padding=0, dilation=1, sco=64, out=None,
+                           scratch=None, knobs=None):
+    dims, out, scratch = _c1d_packed_args(x, CO, KW, stride, padding, dilation, sco, out, scratch)
+    h = ctypes.c_void_p()
+    rc = _lib.load().hb_plan_conv1d_nwc_packed(ctypes.byref(h), _dev(x, "x"), _dev(w_packed, "w_packed"),
+                                               _dev(out, "out"), *dims, _dev(scratch, "scratch"),
+                                               scratch.numel(), _knobs(knobs))
+    _lib.check(rc, "hb_plan_conv1d_nwc_packed")
+    return Plan(h, (x, w_packed, scratch), out)

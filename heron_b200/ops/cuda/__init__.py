@@ -1,20 +1,27 @@
-"""The tensor-core operator registry (ops/cuda/__init__.py:15-32), limited to the hot path."""
+"""The tensor-core operator registry (ops/cuda/__init__.py:15-32): the hot path (gemm, bmm, c2d_nhwc)
+and the operators next to it that run on the same kernels (c2d, dil, c1d, gemv)."""
 from .batch_matmul import heron_batch_matmul
+from .conv1d import heron_conv1d_ncw_tensorcore
 from .conv2d import heron_conv2d_nchw_tensorcore, heron_conv2d_nhwc_tensorcore
 from .dense import heron_dense
+from .dil import heron_dil_tensorcore
+from .gemv import heron_gemv
 
 _OPMAP = {
+    "gemv": heron_gemv,
     "gemm": heron_dense,
+    "c1d": heron_conv1d_ncw_tensorcore,
     "bmm": heron_batch_matmul,
     "c2d": heron_conv2d_nchw_tensorcore,
     "c2d_nhwc": heron_conv2d_nhwc_tensorcore,
+    "dil": heron_dil_tensorcore,
 }
 
 # Names the reference registers that have no B200 kernel here.
-_NOT_BUILT = ("gemv", "c1d", "c3d", "t2d", "mean", "var", "scan", "dil", "dep")
+_NOT_BUILT = ("c3d", "t2d", "mean", "var", "scan", "dep")
 
 
 def getOpFromName(name):
     if name in _NOT_BUILT:
-        raise NotImplementedError("operator %r is outside the GEMM / BMM / NHWC-conv hot path" % name)
+        raise NotImplementedError("operator %r is outside the GEMM / BMM / conv hot path and its neighbours" % name)
     return _OPMAP[name]

@@ -35,6 +35,15 @@ def _gemm_view(out):
         return 1, p["M"], p["N"], p["K"], p["K"]
     if out.op.kind == "bmm":
         return p["batch"], p["M"], p["N"], p["K"], p["K"]
+    if out.op.kind == "gemv":
+        return 1, p["M"], 8, p["K"], p["K"]
+    if out.op.kind == "conv1d_ncw":
+        N, WO = out.shape[0], out.shape[2]
+        gran = 32 // ELEM_BYTES[p["in_dtype"]]
+        ci = (p["CI"] + gran - 1) // gran * gran
+        return 1, N * WO, p["CO"], p["KW"] * ci, ci
+    if out.op.kind == "conv1d_nwc_packed":
+        return 1, out.shape[0] * out.shape[1], p["CO"], p["KW"] * p["CI"], p["CI"]
     if out.op.kind == "conv2d_nchw":
         N, HO, WO = out.shape[0], out.shape[2], out.shape[3]
         gran = 32 // ELEM_BYTES[p["in_dtype"]]
@@ -66,6 +75,9 @@ class tileOp(SchedOp):
             # Swizzle spans the kernel accepts for this shape: conv blocks must not straddle
             # two filter taps, so the span has to divide the channel bytes.
             spans = [sw for sw in (32, 64, 128) if not conv or (k_inner * es) % sw == 0]
+            if not spans:
+                raise ValueError("conv channels of %d bytes are not a multiple of 32: outside the kernels' "
+                                 "documented limits" % (k_inner * es))
             if not conv and K * es < 128:
                 spans = [sw for sw in spans if sw <= max(32, 1 << ((K * es - 1).bit_length()))] or [32]
             gran = step

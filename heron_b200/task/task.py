@@ -53,6 +53,19 @@ class KernelHandle:
             fn = K.plan_conv2d_nhwc_packed if planned else K.conv2d_nhwc_packed
             return fn(x, w, p["CO"], p["KH"], p["KW"], stride=p["stride"], padding=p["padding"],
                       dilation=p["dilation"], sco=p["sco"], out=out, knobs=knobs)
+        if kind == "gemv":
+            a, x, out = tensors
+            fn = K.plan_gemv if planned else K.gemv
+            return fn(a, x, out=out, knobs=knobs)
+        if kind == "conv1d_ncw":
+            x, w, out = tensors
+            fn = K.plan_conv1d_ncw if planned else K.conv1d_ncw
+            return fn(x, w, stride=p["stride"], padding=p["padding"], out=out, knobs=knobs)
+        if kind == "conv1d_nwc_packed":
+            x, w, out = tensors
+            fn = K.plan_conv1d_nwc_packed if planned else K.conv1d_nwc_packed
+            return fn(x, w, p["CO"], p["KW"], stride=p["stride"], padding=p["padding"],
+                      dilation=p["dilation"], sco=p["sco"], out=out, knobs=knobs)
         raise NotImplementedError(kind)
 
     def __call__(self, *tensors):

@@ -177,6 +177,36 @@ int hb_conv2d_nchw(const void* in, const void* w, void* out, int N, int H, int W
                    const hb_knobs* knobs, void* stream);
 
 /*
+ * Operators next to the hot path that run on the same kernels.
+ *
+ * hb_gemv: the tensor-core matrix-vector product of ops/cuda/gemv.py:4-30.  `A` (M,K), `x` (1,K),
+ * `out` (M,8): out[i,0] = sum_k A[i,k] * x[0,k], out[i,1..7] = 0 (the reference pads the vector to
+ * an 8-row matrix of zeros so that a wmma fragment fits; the zeros are written here too, so the
+ * buffer holds what the reference's would).  The x86 form (ops/x86/gemv.py:6-19: A (1,K), B (M,K),
+ * out (1,M)) is hb_gemm with M = 1.
+ *
+ * hb_conv1d_ncw: ops/cuda/conv1d.py:11-110.  `in` (N,CI,W), `w` (CO,CI,KW), `out` (N,CO,WO),
+ * WO = (W - KW + 2*pad) / stride + 1, dilation 1 (asserted there).  Runs as hb_conv2d_nchw with
+ * H = KH = 1 and no padding along the height; `scratch` as for hb_conv2d_nchw, sized by
+ * hb_conv1d_ncw_scratch_bytes.
+ *
+ * hb_conv1d_nwc_packed: ops/x86/conv1d_int8.py:31-101.  `in` uint8 (N,W,CI), `w_packed` int8
+ * (CO/sco, KW, CI/4, sco, 4), `out` int32 (N, WO, CO/sco, sco), WO from the dilated kernel size.
+ * Runs as hb_conv2d_nhwc_packed with H = KH = 1; scratch of hb_conv2d_packed_scratch_bytes(CI, CO,
+ * 1, KW) bytes.
+ */
+int hb_gemv(const void* A, const void* x, void* out, int M, int K, hb_dtype in_a, hb_dtype in_x,
+            hb_dtype out_t, const hb_knobs* knobs, void* stream);
+size_t hb_conv1d_ncw_scratch_bytes(int N, int W, int CI, int CO, int KW, int stride, int pad,
+                                   hb_dtype in_a, hb_dtype out_t);
+int hb_conv1d_ncw(const void* in, const void* w, void* out, int N, int W, int CI, int CO, int KW,
+                  int stride, int pad, hb_dtype in_a, hb_dtype in_w, hb_dtype out_t, void* scratch,
+                  size_t scratch_bytes, const hb_knobs* knobs, void* stream);
+int hb_conv1d_nwc_packed(const void* in, const void* w_packed, void* out, int N, int W, int CI,
+                         int CO, int KW, int stride, int pad, int dil, int sco, void* scratch,
+                         size_t scratch_bytes, const hb_knobs* knobs, void* stream);
+
+/*
  * hb_conv2d_nhwc_packed without a scratch argument and without any allocation.  It has no
  * counterpart in the reference: it exists because the reference's calling convention has no room
  * for a workspace.  A built operator there receives exactly its tensors (input, filter, output;
@@ -229,6 +259,14 @@ int hb_plan_conv2d_nchw(hb_plan** plan, const void* in, const void* w, void* out
                         int W, int CI, int CO, int KH, int KW, int stride_h, int stride_w, int pad,
                         hb_dtype in_a, hb_dtype in_w, hb_dtype out_t, void* scratch,
                         size_t scratch_bytes, const hb_knobs* knobs);
+int hb_plan_gemv(hb_plan** plan, const void* A, const void* x, void* out, int M, int K,
+                 hb_dtype in_a, hb_dtype in_x, hb_dtype out_t, const hb_knobs* knobs);
+int hb_plan_conv1d_ncw(hb_plan** plan, const void* in, const void* w, void* out, int N, int W,
+                       int CI, int CO, int KW, int stride, int pad, hb_dtype in_a, hb_dtype in_w,
+                       hb_dtype out_t, void* scratch, size_t scratch_bytes, const hb_knobs* knobs);
+int hb_plan_conv1d_nwc_packed(hb_plan** plan, const void* in, const void* w_packed, void* out, int N,
+                              int W, int CI, int CO, int KW, int stride, int pad, int dil, int sco,
+                              void* scratch, size_t scratch_bytes, const hb_knobs* knobs);
 int hb_plan_launch(const hb_plan* plan, void* stream);
 /* The knobs after defaults were resolved, the persistent grid and the dynamic shared memory. */
 int hb_plan_knobs(const hb_plan* plan, hb_knobs* knobs, int* grid, int* smem_bytes);

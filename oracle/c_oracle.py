@@ -1,6 +1,5 @@
 """ctypes front end of heron_oracle.c (numpy arrays in, numpy arrays out).  TEST INFRASTRUCTURE ONLY."""
 import ctypes
-import os
 
 import numpy as np
 
@@ -12,8 +11,7 @@ _lib = None
 def lib():
     global _lib
     if _lib is None:
-        if not os.path.exists(_build.ORACLE_SO):
-            _build.build()
+        _build.build()  # no-op unless the source is newer than the library
         _lib = ctypes.CDLL(_build.ORACLE_SO)
         _lib.oracle_half_to_float.restype = ctypes.c_float
         _lib.oracle_half_to_float.argtypes = [ctypes.c_uint16]
@@ -144,4 +142,47 @@ def conv2d_nchw(x, w, stride=1, pad=0, out_dtype=None):
         out = np.empty((N, CO, HO, WO), dtype=np.int32)
         lib().oracle_conv2d_nchw(_p(x), _p(w), _p(out), N, H, W, CI, CO, KH, KW, sh, sw, pad, 0, _signed(x),
                                  _signed(w))
+    return out
+
+
+def gemv(a, x, out_dtype=None):
+    """The tensor-core gemv: a (M,K), x (1,K) -> (M,8) with the product in column 0."""
+    a, x = _c(a), _c(x)
+    M, K = a.shape
+    assert x.shape == (1, K)
+    if a.dtype == np.float16:
+        half = out_dtype is not None and np.dtype(out_dtype) == np.float16
+        out = np.empty((M, 8), dtype=np.float16 if half else np.float32)
+        lib().oracle_gemv(_p(a), _p(x), _p(out), M, K, 2 if half else 1, 0, 0)
+    else:
+        out = np.empty((M, 8), dtype=np.int32)
+        lib().oracle_gemv(_p(a), _p(x), _p(out), M, K, 0, _signed(a), _signed(x))
+    return out
+
+
+def conv1d_ncw(x, w, stride=1, pad=0, out_dtype=None):
+    x, w = _c(x), _c(w)
+    N, CI, W = x.shape
+    CO, _, KW = w.shape
+    WO = (W - KW + 2 * pad) // stride + 1
+    if x.dtype == np.float16:
+        half = out_dtype is not None and np.dtype(out_dtype) == np.float16
+        out = np.empty((N, CO, WO), dtype=np.float16 if half else np.float32)
+        lib().oracle_conv1d_ncw(_p(x), _p(w), _p(out), N, W, CI, CO, KW, stride, pad, 2 if half else 1, 0, 0)
+    else:
+        out = np.empty((N, CO, WO), dtype=np.int32)
+        lib().oracle_conv1d_ncw(_p(x), _p(w), _p(out), N, W, CI, CO, KW, stride, pad, 0, _signed(x), _signed(w))
+    return out
+
+
+def conv1d_nwc_packed(x, w_packed, stride=1, pad=0, dilation=1):
+    x, w_packed = _c(x), _c(w_packed)
+    assert x.dtype == np.uint8 and w_packed.dtype == np.int8
+    N, W, CI = x.shape
+    OC, KW, IC, sco, sci = w_packed.shape
+    assert sci == 4 and IC * 4 == CI
+    WO = (W - ((KW - 1) * dilation + 1) + 2 * pad) // stride + 1
+    out = np.empty((N, WO, OC, sco), dtype=np.int32)
+    lib().oracle_conv1d_nwc_packed(_p(x), _p(w_packed), _p(out), N, W, CI, OC * sco, KW, stride, pad,
+                                   dilation, sco)
     return out

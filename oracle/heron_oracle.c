@@ -283,3 +283,90 @@ void oracle_conv2d_nchw(const void* in, const void* w, void* out, int N, int H, 
           else ((uint16_t*)out)[oi] = float_to_half_rn((float)facc);
         }
 }
+
+/*
+ * Tensor-core matrix-vector product, ops/cuda/gemv.py:12-30: the vector B (1,K) becomes an
+ * (8,K) matrix whose rows 1..7 are zero; out[i,j] = sum_k A[i,k] * BPad[j,k], out (M,8).
+ * `mode` 0: integer operands, int32 output; 1: binary16 operands, float output; 2: binary16 output.
+ */
+void oracle_gemv(const void* A, const void* x, void* out, int M, int K, int mode, int a_signed,
+                 int x_signed) {
+  for (int i = 0; i < M; ++i) {
+    for (int j = 0; j < 8; ++j) {
+      if (mode == 0) {
+        int32_t acc = 0;
+        for (int k = 0; k < K; ++k) {
+          const int32_t b = (j == 0) ? load_i8(x, (size_t)k, x_signed) : 0;
+          acc += load_i8(A, (size_t)i * K + k, a_signed) * b;
+        }
+        ((int32_t*)out)[(size_t)i * 8 + j] = acc;
+      } else {
+        double acc = 0.0;
+        for (int k = 0; k < K; ++k) {
+          const double b = (j == 0) ? (double)half_to_float(((const uint16_t*)x)[k]) : 0.0;
+          acc += (double)half_to_float(((const uint16_t*)A)[(size_t)i * K + k]) * b;
+        }
+        if (mode == 1) ((float*)out)[(size_t)i * 8 + j] = (float)acc;
+        else ((uint16_t*)out)[(size_t)i * 8 + j] = float_to_half_rn((float)acc);
+      }
+    }
+  }
+}
+
+/*
+ * NCW conv1d, ops/cuda/conv1d.py:23-69 written as the direct sum its im2col GEMM computes:
+ *   out[n,c,q] = sum_{ci,kw} pad(in)[n, ci, q*stride + kw] * w[c,ci,kw],  W_O = (W - KW + 2*pad)/stride + 1
+ * `pad` zeros on both ends of the width (get_pad_tuple1d of an int).  Modes as oracle_gemv.
+ */
+void oracle_conv1d_ncw(const void* in, const void* w, void* out, int N, int W, int CI, int CO, int KW,
+                       int stride, int pad, int mode, int in_signed, int w_signed) {
+  const int WO = (W - KW + 2 * pad) / stride + 1;
+  for (int n = 0; n < N; ++n)
+    for (int c = 0; c < CO; ++c)
+      for (int q = 0; q < WO; ++q) {
+        int32_t iacc = 0;
+        double dacc = 0.0;
+        for (int ci = 0; ci < CI; ++ci)
+          for (int kw = 0; kw < KW; ++kw) {
+            const int xw = q * stride + kw - pad;
+            if (xw < 0 || xw >= W) continue;
+            const size_t ii = ((size_t)n * CI + ci) * W + xw;
+            const size_t wi = ((size_t)c * CI + ci) * KW + kw;
+            if (mode == 0) iacc += load_i8(in, ii, in_signed) * load_i8(w, wi, w_signed);
+            else dacc += (double)half_to_float(((const uint16_t*)in)[ii]) *
+                         (double)half_to_float(((const uint16_t*)w)[wi]);
+          }
+        const size_t oi = ((size_t)n * CO + c) * WO + q;
+        if (mode == 0) ((int32_t*)out)[oi] = iacc;
+        else if (mode == 1) ((float*)out)[oi] = (float)dacc;
+        else ((uint16_t*)out)[oi] = float_to_half_rn((float)dacc);
+      }
+}
+
+/*
+ * The DL Boost NWC conv1d, ops/x86/conv1d_int8.py:53-84: input uint8 (N,W,CI), filter int8
+ * (CO/sco, KW, CI/4, sco, 4), output int32 (N, W_O, CO/sco, sco);
+ *   out[n,x,oc,ob] = sum_{rx,icc,icb} pad(in)[n, x*stride + rx*dil, icc*4+icb] * w[oc,rx,icc,ob,icb]
+ */
+void oracle_conv1d_nwc_packed(const uint8_t* in, const int8_t* wp, int32_t* out, int N, int W, int CI,
+                              int CO, int KW, int stride, int pad, int dil, int sco) {
+  const int WO = (W - ((KW - 1) * dil + 1) + 2 * pad) / stride + 1;
+  const int OC = CO / sco, IC = CI / 4;
+  for (int n = 0; n < N; ++n)
+    for (int x = 0; x < WO; ++x)
+      for (int oc = 0; oc < OC; ++oc)
+        for (int ob = 0; ob < sco; ++ob) {
+          int32_t acc = 0;
+          for (int rx = 0; rx < KW; ++rx) {
+            const int xw = x * stride + rx * dil - pad;
+            if (xw < 0 || xw >= W) continue;
+            for (int icc = 0; icc < IC; ++icc)
+              for (int icb = 0; icb < 4; ++icb) {
+                const int32_t a = in[((size_t)n * W + xw) * CI + icc * 4 + icb];
+                const int32_t b = wp[((((size_t)oc * KW + rx) * IC + icc) * sco + ob) * 4 + icb];
+                acc += a * b;
+              }
+          }
+          out[(((size_t)n * WO + x) * OC + oc) * sco + ob] = acc;
+        }
+}

@@ -147,3 +147,54 @@ def conv2d_nchw_f16(x, w, stride=1, pad=0, out_dtype=np.float32):
     C = (B.astype(np.float64) @ A.astype(np.float64).T).astype(np.float32)
     out = np.ascontiguousarray(C.reshape(CO, N, HO, WO).transpose(1, 0, 2, 3))
     return out.astype(np.float16) if np.dtype(out_dtype) == np.float16 else out
+
+
+def gemv(a, x, out_dtype=None):
+    """The tensor-core gemv exactly as the reference builds it (ops/cuda/gemv.py:12-30): pad the
+    vector to an (8, K) matrix of zeros, multiply; out (M, 8)."""
+    M, K = a.shape
+    bpad = np.zeros((8, K), dtype=x.dtype)
+    bpad[0] = x[0]
+    if a.dtype == np.float16:
+        out = (a.astype(np.float64) @ bpad.astype(np.float64).T).astype(np.float32)
+        return out.astype(np.float16) if out_dtype is not None and np.dtype(out_dtype) == np.float16 else out
+    return _to_i32(_as_i64(a) @ _as_i64(bpad).T)
+
+
+def _ncw_im2col(x, w, stride, pad):
+    """The reference's lowering (ops/cuda/conv1d.py:27-69): A[N*W_O, CI*KW] with columns ordered
+    (ci, kw), B[CO, CI*KW]; C = B . A^T; output[n, c, q] = C[c, n*W_O + q]."""
+    N, CI, W = x.shape
+    CO, _, KW = w.shape
+    WO = (W - KW + 2 * pad) // stride + 1
+    xp = np.zeros((N, CI, W + 2 * pad), dtype=x.dtype)
+    xp[:, :, pad:pad + W] = x
+    A = np.empty((N, WO, CI, KW), dtype=x.dtype)
+    for kw in range(KW):
+        A[:, :, :, kw] = xp[:, :, kw: kw + (WO - 1) * stride + 1: stride].transpose(0, 2, 1)
+    return A.reshape(N * WO, CI * KW), w.reshape(CO, CI * KW), (N, CO, WO)
+
+
+def conv1d_ncw(x, w, stride=1, pad=0, out_dtype=None):
+    A, B, (N, CO, WO) = _ncw_im2col(x, w, stride, pad)
+    if x.dtype == np.float16:
+        C = (B.astype(np.float64) @ A.astype(np.float64).T).astype(np.float32)
+    else:
+        C = _to_i32(_as_i64(B) @ _as_i64(A).T)
+    out = np.ascontiguousarray(C.reshape(CO, N, WO).transpose(1, 0, 2))
+    return out.astype(np.float16) if out_dtype is not None and np.dtype(out_dtype) == np.float16 else out
+
+
+def pack_filter_x86_1d(w_wio, sco=64, sci=4):
+    """(KW, CI, CO) int8 filter -> (CO/sco, KW, CI/sci, sco, sci) (ops/x86/conv1d_int8.py:48)."""
+    return pack_filter_x86(w_wio[None], sco, sci)[:, 0]
+
+
+def conv1d_nwc_packed(x, w_packed, stride=1, pad=0, dilation=1):
+    """ops/x86/conv1d_int8.py:53-84 through the 2-D oracle with a height of one: the input is
+    padded along the width here, so the 2-D call runs unpadded."""
+    N, W, CI = x.shape
+    xp = np.zeros((N, 1, W + 2 * pad, CI), dtype=x.dtype)
+    xp[:, 0, pad:pad + W] = x
+    out = conv2d_nhwc_packed(xp, w_packed[:, None], (1, stride), 0, (1, dilation))
+    return out[:, 0]

@@ -80,14 +80,56 @@ def build_cases():
     return cases
 
 
-def main():
+def build_neighbour_cases():
+    """kat_neighbours.npz: gemv (ops/cuda/gemv.py:12-30) and the 1-D convolutions
+    (ops/cuda/conv1d.py:23-69, ops/x86/conv1d_int8.py:53-84), same two kinds of case."""
+    cases = {}
+    rng = np.random.Generator(np.random.PCG64(778))
+    # gemv, one-hot rows of A: out[i,0] = x[i], columns 1..7 zero
+    a = np.eye(16, 32, dtype=np.uint8)
+    x = rng.integers(-128, 128, size=(1, 32)).astype(np.int8)
+    out = np.zeros((16, 8), dtype=np.int32)
+    out[:, 0] = x[0, :16]
+    cases["gemv_u8s8_onehot"] = dict(a=a, x=x, out=out)
+    a = (rng.standard_normal((40, 48)) / 7.0).astype(np.float16)
+    x = rng.standard_normal((1, 48)).astype(np.float16)
+    cases["gemv_f16_40x48"] = dict(a=a, x=x, out=npo.gemv(a, x))
+    # conv1d NCW, all ones, KW = 3, pad 4 (wider than the filter, as in the reference's own cases):
+    # output position q sees the taps q-4 .. q-2 of a width-6 input
+    xi = np.ones((1, 16, 6), dtype=np.uint8)
+    wi = np.ones((32, 16, 3), dtype=np.int8)
+    taps = np.array([0, 0, 1, 2, 3, 3, 3, 3, 2, 1, 0, 0], dtype=np.int32) * 16
+    cases["c1d_ncw_ones_wide_padding"] = dict(x=xi, w=wi, stride=1, pad=4,
+                                              out=np.broadcast_to(taps[None, None, :], (1, 32, 12)).copy())
+    xf = rng.standard_normal((2, 16, 21)).astype(np.float16)
+    wf = (rng.standard_normal((24, 16, 3)) / 7.0).astype(np.float16)
+    cases["c1d_ncw_f16_s2"] = dict(x=xf, w=wf, stride=2, pad=1, out=npo.conv1d_ncw(xf, wf, 2, 1))
+    # conv1d NWC packed, one tap of identity channels: out == in
+    xi = rng.integers(0, 256, size=(2, 9, 32), dtype=np.uint8)
+    w = np.eye(32, dtype=np.int8)[None]
+    cases["c1d_nwc_packed_identity"] = dict(x=xi, w=npo.pack_filter_x86_1d(w, 32), stride=1, pad=0, dil=1,
+                                            out=xi.astype(np.int32).reshape(2, 9, 1, 32))
+    xi = rng.integers(0, 256, size=(2, 23, 32), dtype=np.uint8)
+    w = rng.integers(-128, 128, size=(3, 32, 64)).astype(np.int8)
+    wp = npo.pack_filter_x86_1d(w, 64)
+    cases["c1d_nwc_packed_d2"] = dict(x=xi, w=wp, stride=1, pad=4, dil=2,
+                                      out=npo.conv1d_nwc_packed(xi, wp, 1, 4, 2))
+    return cases
+
+
+def _write(name, cases):
     flat = {}
-    for name, case in build_cases().items():
+    for cname, case in cases.items():
         for key, val in case.items():
-            flat["%s/%s" % (name, key)] = np.asarray(val)
-    path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "kat.npz")
+            flat["%s/%s" % (cname, key)] = np.asarray(val)
+    path = os.path.join(os.path.dirname(os.path.abspath(__file__)), name)
     np.savez_compressed(path, **flat)
-    print("wrote", path, os.path.getsize(path), "bytes,", len(build_cases()), "cases")
+    print("wrote", path, os.path.getsize(path), "bytes,", len(cases), "cases")
+
+
+def main():
+    _write("kat.npz", build_cases())
+    _write("kat_neighbours.npz", build_neighbour_cases())
 
 
 if __name__ == "__main__":

@@ -6,8 +6,8 @@ import numpy as np
 _PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "kat.npz")
 
 
-def load_cases():
-    data = np.load(_PATH)
+def load_cases(name="kat.npz"):
+    data = np.load(os.path.join(os.path.dirname(_PATH), name))
     cases = {}
     for key in data.files:
         name, field = key.split("/")
@@ -45,3 +45,12 @@ def assert_matches(name, got, want):
         scale = max(float(np.abs(want.astype(np.float64)).max()), 1e-30)
         err = float(np.abs(got.astype(np.float64) - want.astype(np.float64)).max()) / scale
         assert err <= 1e-2, (name, err)
+
+
+def run_neighbour_case(name, case, gemv, conv1d_ncw, conv1d_nwc_packed):
+    """The same for tests/golden/kat_neighbours.npz (gemv and the 1-D convolutions)."""
+    if name.startswith("gemv"):
+        return gemv(case["a"], case["x"])
+    if name.startswith("c1d_ncw"):
+        return conv1d_ncw(case["x"], case["w"], case["stride"], case["pad"])
+    return conv1d_nwc_packed(case["x"], case["w"], case["stride"], case["pad"], case["dil"])

@@ -109,6 +109,19 @@ def test_golden_cases(K):
         assert_matches(name, got.cpu().numpy(), case["out"])
 
 
+def test_golden_neighbour_cases(K):
+    from golden_util import run_neighbour_case
+
+    def c1d_packed(x, wp, s, p, d):
+        OC, KW, IC, sco, _ = wp.shape
+        return K.conv1d_nwc_packed(dev(x), dev(wp), OC * sco, KW, stride=s, padding=p, dilation=d, sco=sco)
+
+    for name, case in load_cases("kat_neighbours.npz").items():
+        got = run_neighbour_case(name, case, lambda a, x: K.gemv(dev(a), dev(x)),
+                                 lambda x, w, s, p: K.conv1d_ncw(dev(x), dev(w), s, p), c1d_packed)
+        assert_matches(name, got.cpu().numpy(), case["out"])
+
+
 # ---- GEMM ---------------------------------------------------------------------------------
 @pytest.mark.parametrize("M,N,Kd", [(64, 64, 64), (1, 16, 16), (128, 256, 128), (129, 257, 144), (300, 200, 80),
                                     (512, 512, 512), (1000, 136, 1040), (128, 36, 64)])
@@ -317,6 +330,107 @@ def test_task_random_knob_points_agree(K, co):
         out = poison(args[-1].shape, torch.int32)
         handle(ta, tb, out)
         check(out, want, str(handle.knobs))
+
+
+@pytest.mark.parametrize("case", [(16, 28, 28, 128, 128, 3, 3, 1, 1, 2), (16, 14, 14, 256, 512, 1, 1, 2, 0, 2),
+                                  (16, 20, 20, 64, 64, 3, 3, 1, 2, 2), (8, 17, 17, 32, 64, 3, 3, 2, 3, 3)])
+def test_dilated_conv_through_both_registries(K, co, case):
+    """The "dil" operator (the reference's dilated-conv benchmark cases, shapes shortened): the
+    tensor-core form in fp16 and the DL Boost form with the packed int8 filter."""
+    from heron_b200.ops import cuda as heron_cuda, x86 as heron_cpu
+    N, H, W, CI, CO, KH, KW, s, p, d = case
+    rng = np.random.default_rng(sum(case))
+    t = _task(heron_cuda, "dil", list(case) + ["float16", "float16"], "GPU_TENSOR_CORE")
+    t.knob_manager.randSample()
+    handle, args = t.instantiate(t.knob_manager)
+    x = rng.standard_normal((N, H, W, CI)).astype(np.float16)
+    w = (rng.standard_normal((KH, KW, CI, CO)) / np.sqrt(KH * KW * CI)).astype(np.float16)
+    out = poison(args[-1].shape, torch.float16)
+    handle(dev(x), dev(w), out)
+    check(out, co.conv2d_nhwc_f16(x, w, s, p, d, out_dtype=np.float16), "dil fp16 %s" % (case,))
+    if CO % 64 == 0 and CI % 4 == 0:
+        t = _task(heron_cpu, "dil", list(case) + ["OhwI64o4i", "uint8", "int32"], "CPU")
+        t.knob_manager.randSample()
+        handle, args = t.instantiate(t.knob_manager)
+        xi, wi = rand_i8(rng, (N, H, W, CI), False), rand_i8(rng, (KH, KW, CI, CO), True)
+        wp = npo.pack_filter_x86(wi, 64)
+        out = poison(args[-1].shape, torch.int32)
+        handle(dev(xi), dev(wp), out)
+        check(out, co.conv2d_nhwc_packed(xi, wp, s, p, d), "dil x86 %s" % (case,))
+
+
+# ---- gemv and the 1-D convolutions: operators next to the hot path on the same kernels --------
+@pytest.mark.parametrize("M,Kd", [(512, 16), (1024, 256), (256, 1024), (130, 80)])
+def test_gemv_both_forms(K, co, M, Kd):
+    """The reference's gemv cases (plus a ragged one): tensor-core form (M,8) in fp16 and int8, and
+    the DL Boost form (1,M) through its registry."""
+    from heron_b200.ops import cuda as heron_cuda, x86 as heron_cpu
+    rng = np.random.default_rng(M + Kd)
+    a = (rng.standard_normal((M, Kd)) / np.sqrt(Kd)).astype(np.float16)
+    x = rng.standard_normal((1, Kd)).astype(np.float16)
+    for od in (np.float32, np.float16):
+        t = _task(heron_cuda, "gemv", [M, Kd, "float16", np.dtype(od).name], "GPU_TENSOR_CORE")
+        t.knob_manager.randSample()
+        handle, args = t.instantiate(t.knob_manager)
+        out = poison((M, 8), _T[np.dtype(od)])
+        handle(dev(a), dev(x), out)
+        check(out, co.gemv(a, x, od), "gemv fp16 -> %s %s" % (np.dtype(od).name, handle.knobs))
+        assert not out[:, 1:].any()
+    ai, xi = rand_i8(rng, (M, Kd), False), rand_i8(rng, (1, Kd), True)
+    out = poison((M, 8), torch.int32)
+    K.gemv(dev(ai), dev(xi), out=out)
+    check(out, co.gemv(ai, xi), "gemv int8")
+    plan = K.plan_gemv(dev(ai), dev(xi), out=poison((M, 8), torch.int32))
+    check(plan.launch(), co.gemv(ai, xi), "gemv int8 plan")
+    t = _task(heron_cpu, "gemv", [M, Kd, "uint8", "int32"], "CPU")
+    t.knob_manager.randSample()
+    handle, args = t.instantiate(t.knob_manager)
+    a1, b1 = rand_i8(rng, (1, Kd), False), rand_i8(rng, (M, Kd), True)
+    out = poison((1, M), torch.int32)
+    handle(dev(a1), dev(b1), out)
+    check(out, co.gemm_int(a1, b1), "x86 gemv")
+
+
+@pytest.mark.parametrize("case", [(16, 892, 64, 128, 3, 1, 4), (4, 100, 512, 512, 3, 1, 32), (8, 77, 48, 64, 1, 1, 0),
+                                  (2, 200, 3, 32, 7, 2, 3), (16, 223, 128, 256, 1, 2, 0)])
+def test_conv1d_ncw(K, co, case):
+    """(N, W, CI, CO, KW, stride, pad): the reference's c1d cases shortened, a 3-channel input and
+    strided ones; padding wider than the filter is part of the reference's own cases."""
+    from heron_b200.ops import cuda as heron_cuda
+    N, W, CI, CO, KW, s, p = case
+    rng = np.random.default_rng(sum(case))
+    x = rng.standard_normal((N, CI, W)).astype(np.float16)
+    w = (rng.standard_normal((CO, CI, KW)) / np.sqrt(CI * KW)).astype(np.float16)
+    if CI % 16 == 0:
+        t = _task(heron_cuda, "c1d", [N, W, CI, CO, KW, s, p, 1, "float16", "float16"], "GPU_TENSOR_CORE")
+        t.knob_manager.randSample()
+        handle, args = t.instantiate(t.knob_manager)
+        out = poison(args[-1].shape, torch.float16)
+        handle(dev(x), dev(w), out)
+        check(out, co.conv1d_ncw(x, w, s, p, np.float16), "c1d fp16 %s %s" % (case, handle.knobs))
+    check(K.conv1d_ncw(dev(x), dev(w), s, p), co.conv1d_ncw(x, w, s, p), "c1d fp32 out %s" % (case,))
+    xi, wi = rand_i8(rng, (N, CI, W), False), rand_i8(rng, (CO, CI, KW), True)
+    plan = K.plan_conv1d_ncw(dev(xi), dev(wi), s, p)
+    check(plan.launch(), co.conv1d_ncw(xi, wi, s, p), "c1d int8 %s" % (case,))
+
+
+@pytest.mark.parametrize("case", [(1, 892, 512, 1024, 1, 1, 0, 1, 64), (1, 892, 512, 512, 3, 1, 4, 2, 64),
+                                  (2, 300, 96, 64, 3, 1, 16, 8, 48), (3, 57, 32, 64, 5, 2, 3, 1, 32)])
+def test_conv1d_nwc_packed_through_the_x86_registry(K, co, case):
+    """(batch, W, co, ci, kernel, stride, pad, dilation, sco) in the reference's argument order."""
+    from heron_b200.ops import x86 as heron_cpu
+    N, W, CO, CI, KW, s, p, d, sco = case
+    rng = np.random.default_rng(sum(case))
+    x = rand_i8(rng, (N, W, CI), False)
+    w = rand_i8(rng, (KW, CI, CO), True)
+    wp = npo.pack_filter_x86_1d(w, sco)
+    t = _task(heron_cpu, "c1d", [N, W, CO, CI, KW, s, p, d, "OwI%do4i" % sco, "uint8", "int32"], "CPU")
+    t.knob_manager.randSample()
+    handle, args = t.instantiate(t.knob_manager)
+    assert tuple(args[1].shape) == wp.shape
+    out = poison(args[-1].shape, torch.int32)
+    handle(dev(x), dev(wp), out)
+    check(out, co.conv1d_nwc_packed(x, wp, s, p, d), "x86 c1d %s %s" % (case, handle.knobs))
 
 
 def test_quick_start_config_through_x86_interface(K, co):

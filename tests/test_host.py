@@ -33,8 +33,14 @@ def test_registry_names_and_signatures():
     assert heron_cuda.getOpFromName("c2d_nhwc").__name__ == "heron_conv2d_nhwc_tensorcore"
     assert heron_cpu.getOpFromName("c2d").__name__ == "heron_conv2d_nhwc"
     assert heron_cuda.getOpFromName("c2d").__name__ == "heron_conv2d_nchw_tensorcore"
+    assert heron_cuda.getOpFromName("dil").__name__ == "heron_dil_tensorcore"
+    assert heron_cpu.getOpFromName("dil").__name__ == "heron_dil_nhwc"
+    assert heron_cuda.getOpFromName("gemv").__name__ == "heron_gemv"
+    assert heron_cpu.getOpFromName("gemv").__name__ == "heron_gemv"
+    assert heron_cuda.getOpFromName("c1d").__name__ == "heron_conv1d_ncw_tensorcore"
+    assert heron_cpu.getOpFromName("c1d").__name__ == "heron_conv1d_nwc"
     with pytest.raises(NotImplementedError):
-        heron_cuda.getOpFromName("gemv")
+        heron_cuda.getOpFromName("t2d")
     with pytest.raises(KeyError):
         heron_cuda.getOpFromName("nonsense")
 

@@ -34,6 +34,14 @@ def test_golden_c(co):
         assert_matches(name, got, case["out"])
 
 
+def test_golden_neighbour_cases_both_oracles(co):
+    from golden_util import run_neighbour_case
+    for name, case in load_cases("kat_neighbours.npz").items():
+        for impl in (npo, co):
+            got = run_neighbour_case(name, case, impl.gemv, impl.conv1d_ncw, impl.conv1d_nwc_packed)
+            assert_matches(name, got, case["out"])
+
+
 def test_golden_fp16_cases_bit_exact_between_oracles(co):
     """Both restatements accumulate in double, so even the floating-point cases agree to the bit."""
     for name, case in load_cases().items():
@@ -169,3 +177,43 @@ def test_nchw_operator_three_ways(co):
         wf = rng.standard_normal((CO, CI, KH, KW)).astype(np.float16)
         for od in (np.float32, np.float16):
             assert np.array_equal(npo.conv2d_nchw_f16(xf, wf, s, p, od), co.conv2d_nchw(xf, wf, s, p, od))
+
+
+def test_neighbour_operators_c_vs_numpy(co):
+    """gemv and the two 1-D convolutions: the scalar C loops against the numpy restatement of the
+    reference's own lowering (padded vector, explicit im2col, packed filter)."""
+    rng = np.random.default_rng(404)
+    a = rng.integers(0, 256, (37, 48), dtype=np.uint8)
+    x = rng.integers(-128, 128, (1, 48)).astype(np.int8)
+    got = co.gemv(a, x)
+    assert np.array_equal(got, npo.gemv(a, x)) and not got[:, 1:].any()
+    assert np.array_equal(got[:, 0], a.astype(np.int64) @ x[0].astype(np.int64))
+    ah = rng.standard_normal((20, 32)).astype(np.float16)
+    xh = rng.standard_normal((1, 32)).astype(np.float16)
+    assert np.array_equal(co.gemv(ah, xh), npo.gemv(ah, xh))
+    assert np.array_equal(co.gemv(ah, xh, np.float16), npo.gemv(ah, xh, np.float16))
+    for (N, W, CI, CO, KW, s, p) in [(2, 19, 16, 24, 3, 1, 4), (3, 30, 8, 16, 1, 2, 0), (1, 12, 4, 8, 5, 3, 2)]:
+        xi = rng.integers(-128, 128, (N, CI, W)).astype(np.int8)
+        wi = rng.integers(-128, 128, (CO, CI, KW)).astype(np.int8)
+        assert np.array_equal(co.conv1d_ncw(xi, wi, s, p), npo.conv1d_ncw(xi, wi, s, p))
+        xf = rng.standard_normal((N, CI, W)).astype(np.float16)
+        wf = rng.standard_normal((CO, CI, KW)).astype(np.float16)
+        assert np.array_equal(co.conv1d_ncw(xf, wf, s, p), npo.conv1d_ncw(xf, wf, s, p))
+        assert co.conv1d_ncw(xf, wf, s, p).shape == (N, CO, (W - KW + 2 * p) // s + 1)
+    for (N, W, CI, CO, KW, s, p, d, sco) in [(2, 21, 8, 64, 3, 1, 4, 2, 64), (1, 17, 12, 96, 3, 2, 1, 1, 48), (2, 9, 4, 32, 1, 1, 0, 1, 32)]:
+        xi = rng.integers(0, 256, (N, W, CI), dtype=np.uint8)
+        w = rng.integers(-128, 128, (KW, CI, CO)).astype(np.int8)
+        wp = npo.pack_filter_x86_1d(w, sco)
+        assert wp.shape == (CO // sco, KW, CI // 4, sco, 4)
+        got = co.conv1d_nwc_packed(xi, wp, s, p, d)
+        assert np.array_equal(got, npo.conv1d_nwc_packed(xi, wp, s, p, d))
+        WO = (W - ((KW - 1) * d + 1) + 2 * p) // s + 1
+        assert got.shape == (N, WO, CO // sco, sco)
+        # one element by hand
+        n, q, f = N - 1, WO // 2, CO - 1
+        want = 0
+        for rx in range(KW):
+            xw = q * s + rx * d - p
+            if 0 <= xw < W:
+                want += int(xi[n, xw].astype(np.int64) @ w[rx, :, f].astype(np.int64))
+        assert int(got[n, q, f // sco, f % sco]) == want
