@@ -286,6 +286,7 @@ int encode_tiled3(Driver& d, CUtensorMap* m, hb_dtype t, const void* ptr, uint64
 
 struct ConvGeom {
   int N, H, W, CI, CO, KH, KW, stride_h, stride_w, pad_h, pad_w, dil_h, dil_w, HO, WO;
+  bool out_nchw;  // the conv kernel writes (N, CO, HO, WO)
 };
 
 }  // namespace
@@ -301,13 +302,11 @@ struct hb_plan {
   // strip conv (conv_algo 2): its own parameter block; tmA = tiled input map, tmB = filter map
   bool strip;
   hb::StripParams sp;
-  // NCHW conv only: layout transposes before (input, filter) and after (output) the conv kernel
-  struct Glue {
-    const void* src; void* dst;
-    int esize, R, C, Rp, Cp, batch;
-    long long rs, cs, bs;
-  } glue_pre[2], glue_post;
-  int n_glue_pre; bool has_glue_post;
+  // NCHW operators only: one launch that brings input and filter to NHWC / HWIO first (the conv
+  // kernel's epilogue writes NCHW itself)
+  bool has_pre;
+  hb::NchwPre pre;
+  int pre_esize, pre_grid;
   // packed-filter conv only: the unpack kernel that runs first on the same stream
   const void* packed_w;
   void* scratch;
@@ -392,6 +391,7 @@ int build_plan(Driver& d, const Problem& pr, const hb_knobs& k, const ConvGeom* 
     p.num_kb = cg->KH * cg->KW * p.kb_per_tap;
     p.stride_h = cg->stride_h; p.stride_w = cg->stride_w; p.dil_h = cg->dil_h; p.dil_w = cg->dil_w;
     p.pad_h = cg->pad_h; p.pad_w = cg->pad_w;
+    p.out_nchw = cg->out_nchw ? 1 : 0;
     // Activations as a (C, W, H, N) tensor read in im2col mode.  The bounding box spans the
     // positions the top-left filter tap visits: from -pad to (extent - 1 + pad - (K-1)*dil).
     cuuint64_t dims[4] = {static_cast<cuuint64_t>(cg->CI), static_cast<cuuint64_t>(cg->W),
@@ -521,31 +521,24 @@ int build_plan(Driver& d, const Problem& pr, const hb_knobs& k, const ConvGeom* 
 template <int OUT_BYTES, int CG, int KIND>
 int launch_kernel(const hb_plan* plan, cudaStream_t stream);
 
-int run_glue(const hb_plan::Glue& g, cudaStream_t stream) {
-  dim3 grid((g.Cp + 31) / 32, (g.Rp + 31) / 32, g.batch), block(32, 8);
-  if (grid.y > 65535 || grid.z > 65535) return HB_ERR_SHAPE;
-  if (g.esize == 1)
-    hb::hb_transpose_pad_kernel<uint8_t><<<grid, block, 0, stream>>>(
-        static_cast<const uint8_t*>(g.src), static_cast<uint8_t*>(g.dst), g.R, g.C, g.Rp, g.Cp, g.rs, g.cs, g.bs);
-  else if (g.esize == 2)
-    hb::hb_transpose_pad_kernel<uint16_t><<<grid, block, 0, stream>>>(
-        static_cast<const uint16_t*>(g.src), static_cast<uint16_t*>(g.dst), g.R, g.C, g.Rp, g.Cp, g.rs, g.cs, g.bs);
+int run_pre(const hb_plan* plan, cudaStream_t stream) {
+  if (plan->pre_esize == 1)
+    hb::hb_nchw_pre_kernel<uint8_t><<<plan->pre_grid, 256, 0, stream>>>(plan->pre);
+  else if (plan->pre_esize == 2)
+    hb::hb_nchw_pre_kernel<uint16_t><<<plan->pre_grid, 256, 0, stream>>>(plan->pre);
   else
-    hb::hb_transpose_pad_kernel<uint32_t><<<grid, block, 0, stream>>>(
-        static_cast<const uint32_t*>(g.src), static_cast<uint32_t*>(g.dst), g.R, g.C, g.Rp, g.Cp, g.rs, g.cs, g.bs);
+    hb::hb_nchw_pre_kernel<uint32_t><<<plan->pre_grid, 256, 0, stream>>>(plan->pre);
   return cudaGetLastError() == cudaSuccess ? HB_OK : HB_ERR_LAUNCH;
 }
 
 int run_main(const hb_plan* plan, cudaStream_t stream);
 
 int run_plan(const hb_plan* plan, cudaStream_t stream) {
-  for (int i = 0; i < plan->n_glue_pre; ++i) {
-    const int rc = run_glue(plan->glue_pre[i], stream);
+  if (plan->has_pre) {
+    const int rc = run_pre(plan, stream);
     if (rc != HB_OK) return rc;
   }
-  int rc = run_main(plan, stream);
-  if (rc != HB_OK) return rc;
-  return plan->has_glue_post ? run_glue(plan->glue_post, stream) : HB_OK;
+  return run_main(plan, stream);
 }
 
 int run_main(const hb_plan* plan, cudaStream_t stream) {
@@ -686,6 +679,7 @@ int build_strip_plan(Driver& d, const ConvGeom& g, hb_dtype in_a, hb_dtype in_w,
   const int kind = mma_kind(in_a, in_w, out_t);
   sp.idesc = make_idesc(kind, in_a, in_w, hb::kTileM, g.CO, true);
   sp.out = out;
+  sp.out_nchw = g.out_nchw ? 1 : 0;
   sp.probe = k.reserved;
   // input as a tiled (C, W, H, N) tensor: one box = 128 bytes of channels x padded width x strip rows
   cuuint64_t dims[4] = {static_cast<cuuint64_t>(g.CI), static_cast<cuuint64_t>(g.W),
@@ -724,7 +718,8 @@ int build_strip_plan(Driver& d, const ConvGeom& g, hb_dtype in_a, hb_dtype in_w,
 // with pad_h = 0.
 int plan_conv(const void* in, const void* w, void* out, int N, int H, int W, int CI, int CO, int KH,
               int KW, int stride_h, int stride_w, int pad_h, int pad_w, int dil_h, int dil_w,
-              hb_dtype in_a, hb_dtype in_w, hb_dtype out_t, const hb_knobs* knobs, hb_plan* plan) {
+              hb_dtype in_a, hb_dtype in_w, hb_dtype out_t, const hb_knobs* knobs, hb_plan* plan,
+              bool out_nchw = false) {
   if (N <= 0 || H <= 0 || W <= 0 || CI <= 0 || CO <= 0 || KH <= 0 || KW <= 0) return HB_ERR_SHAPE;
   if (stride_h <= 0 || stride_w <= 0 || dil_h <= 0 || dil_w <= 0 || pad_h < 0 || pad_w < 0) return HB_ERR_SHAPE;
   if (mma_kind(in_a, in_w, out_t) < 0) return HB_ERR_DTYPE;
@@ -746,7 +741,7 @@ int plan_conv(const void* in, const void* w, void* out, int N, int H, int W, int
   Driver& d = driver();
   if (d.status != HB_OK) return d.status;
   Problem pr{2, 1, static_cast<int>(M), CO, static_cast<int>(K), in_a, in_w, out_t, true, CI};
-  ConvGeom cg{N, H, W, CI, CO, KH, KW, stride_h, stride_w, pad_h, pad_w, dil_h, dil_w, HO, WO};
+  ConvGeom cg{N, H, W, CI, CO, KH, KW, stride_h, stride_w, pad_h, pad_w, dil_h, dil_w, HO, WO, out_nchw};
   const int algo = knobs ? knobs->conv_algo : 0;
   if (algo < 0 || algo > 2) return HB_ERR_KNOB;
   if (algo != 1) {
@@ -766,7 +761,17 @@ int plan_conv(const void* in, const void* w, void* out, int N, int H, int W, int
     }
   }
   hb_knobs k;
-  resolve_knobs(pr, knobs, d.sm_count, &k);
+  if (out_nchw) {
+    // channel-major output goes through the direct-store epilogue; split-K's zeroing pass knows
+    // only the row-major tile layout
+    hb_knobs k0;
+    if (knobs) k0 = *knobs; else std::memset(&k0, 0, sizeof(k0));
+    k0.epilogue = 2;
+    k0.split_k = 1;
+    resolve_knobs(pr, &k0, d.sm_count, &k);
+  } else {
+    resolve_knobs(pr, knobs, d.sm_count, &k);
+  }
   k.conv_algo = 1;
   return build_plan(d, pr, k, &cg, in, w, out, plan);
 }
@@ -800,7 +805,7 @@ size_t align256(size_t v) { return (v + 255) & ~static_cast<size_t>(255); }
 
 struct NchwLayout {
   int CIp, HO, WO;
-  size_t in_bytes, w_bytes, out_bytes, total;
+  size_t in_bytes, w_bytes, total;
 };
 
 bool nchw_layout(int N, int H, int W, int CI, int CO, int KH, int KW, int sh, int sw, int pad_h,
@@ -816,8 +821,7 @@ bool nchw_layout(int N, int H, int W, int CI, int CO, int KH, int KW, int sh, in
   if (L->HO <= 0 || L->WO <= 0) return false;
   L->in_bytes = align256(static_cast<size_t>(N) * H * W * L->CIp * es);
   L->w_bytes = align256(static_cast<size_t>(KH) * KW * L->CIp * CO * es);
-  L->out_bytes = align256(static_cast<size_t>(N) * L->HO * L->WO * CO * eo);
-  L->total = L->in_bytes + L->w_bytes + L->out_bytes;
+  L->total = L->in_bytes + L->w_bytes;
   return true;
 }
 
@@ -833,23 +837,39 @@ int plan_conv_nchw(const void* in, const void* w, void* out, int N, int H, int W
   if ((reinterpret_cast<uintptr_t>(scratch) & 255u) != 0) return HB_ERR_ALIGN;
   uint8_t* s_in = static_cast<uint8_t*>(scratch);
   uint8_t* s_w = s_in + L.in_bytes;
-  uint8_t* s_out = s_w + L.w_bytes;
-  const int rc = plan_conv(s_in, s_w, s_out, N, H, W, L.CIp, CO, KH, KW, sh, sw, pad_h, pad_w, 1, 1, in_a, in_w,
-                           out_t, knobs, plan);
+  if (!aligned16(out)) return HB_ERR_ALIGN;
+  const int rc = plan_conv(s_in, s_w, out, N, H, W, L.CIp, CO, KH, KW, sh, sw, pad_h, pad_w, 1, 1, in_a, in_w,
+                           out_t, knobs, plan, /*out_nchw=*/true);
   if (rc != HB_OK) return rc;
-  const int es = esize(in_a), eo = esize(out_t);
-  const int T = KH * KW;
-  // input (N, CI, H*W) -> (N, H*W, CIp)
-  plan->glue_pre[0] = hb_plan::Glue{in, s_in, es, CI, H * W, L.CIp, H * W, N,
-                                    static_cast<long long>(H) * W, 1, static_cast<long long>(CI) * H * W};
-  // filter (CO, CI, T) -> (T, CIp, CO)
-  plan->glue_pre[1] = hb_plan::Glue{w, s_w, es, CO, CI, CO, L.CIp, T,
-                                    static_cast<long long>(CI) * T, T, 1};
-  plan->n_glue_pre = 2;
-  // output (N, HO*WO, CO) -> (N, CO, HO*WO)
-  const int P = L.HO * L.WO;
-  plan->glue_post = hb_plan::Glue{s_out, out, eo, P, CO, P, CO, N, CO, 1, static_cast<long long>(P) * CO};
-  plan->has_glue_post = true;
+  const int es = esize(in_a);
+  const int T = KH * KW, P = H * W;
+  const int vec = 8 / es, tile = 16 * vec;
+  hb::NchwPre& g = plan->pre;
+  g.in = in; g.in_t = s_in; g.w = w; g.w_t = s_w;
+  g.N = N; g.CI = CI; g.CIp = L.CIp; g.P = P; g.CO = CO; g.T = T;
+  // 8-byte accesses need every image and channel row of the source to start on 8 bytes
+  g.vec = (P % vec == 0 && (reinterpret_cast<uintptr_t>(in) & 7u) == 0) ? 1 : 0;
+  g.in_bx = (P + tile - 1) / tile;
+  g.in_by = (L.CIp + tile - 1) / tile;
+  const long long in_blocks = static_cast<long long>(g.in_bx) * g.in_by * N;
+  g.f_tchunk = T < hb::kFilterRun ? T : hb::kFilterRun;
+  g.f_ci_tile = hb::kFilterRun / g.f_tchunk;
+  if (g.f_ci_tile > 32) g.f_ci_tile = 32;
+  g.f_bco = (CO + 31) / 32;
+  g.f_bci = (L.CIp + g.f_ci_tile - 1) / g.f_ci_tile;
+  g.f_bt = (T + g.f_tchunk - 1) / g.f_tchunk;
+  if (T == 1) {
+    // a plain (CO x CI) -> (CIp x CO) transpose: the tile transposer, vectorised when it may be
+    g.f_bco = (CO + tile - 1) / tile;
+    g.f_bci = (L.CIp + tile - 1) / tile;
+    g.f_vec = (CI % vec == 0 && CO % vec == 0 && (reinterpret_cast<uintptr_t>(w) & 7u) == 0) ? 1 : 0;
+  }
+  const long long f_blocks = static_cast<long long>(g.f_bco) * g.f_bci * g.f_bt;
+  if (in_blocks + f_blocks > 0x7fffffffLL) return HB_ERR_SHAPE;
+  g.in_blocks = static_cast<int>(in_blocks);
+  plan->pre_grid = static_cast<int>(in_blocks + f_blocks);
+  plan->pre_esize = es;
+  plan->has_pre = true;
   return HB_OK;
 }
 }  // namespace

@@ -40,6 +40,7 @@ struct StripParams {
   int probe;  // diagnostic: 2 = no MMAs, 3 = epilogue only hands the accumulator back, 4 = strips loaded once
   uint32_t idesc;
   void* out;
+  int out_nchw;  // output is (N, CO, HO, WO) instead of (N, HO, WO, CO)
 };
 
 struct StripBars {
@@ -286,7 +287,20 @@ hb_conv_strip_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_cons
           __syncwarp();
           if (lane == 0) mbar_arrive(smem_u32(&bars->tmem_empty[acc]));
         }
-        if (valid) {
+        if (valid && p.out_nchw) {
+          // channel-major output: consecutive lanes are consecutive pixels of one image row
+          const long long plane = static_cast<long long>(p.HO) * p.WO;
+          uint8_t* o = static_cast<uint8_t*>(p.out) +
+                       ((static_cast<long long>(n) * p.CO + c0) * plane + static_cast<long long>(y) * p.WO + px) * OUT_BYTES;
+#pragma unroll
+          for (int i = 0; i < kColsPerStep; ++i) {
+            if (OUT_BYTES == 4)
+              *reinterpret_cast<uint32_t*>(o + i * plane * OUT_BYTES) = packed[i % 32];
+            else
+              *reinterpret_cast<uint16_t*>(o + i * plane * OUT_BYTES) =
+                  static_cast<uint16_t>(packed[(i >> 1) % 32] >> (16 * (i & 1)));
+          }
+        } else if (valid) {
 #pragma unroll
           for (int j = 0; j < 8; ++j)
             *reinterpret_cast<uint4*>(orow + c0 * OUT_BYTES + 16 * j) =

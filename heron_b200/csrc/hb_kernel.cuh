@@ -69,6 +69,7 @@ struct KParams {
   // conv geometry (a_im2col only)
   int HO, WO, KW, CI, kb_per_tap, stride_h, stride_w, dil_h, dil_w, pad_h, pad_w;
   // direct-store epilogue
+  int out_nchw;  // conv only: C is (N, CO, HO, WO) instead of (N*HO*WO, CO)
   void* C;
   long long ldc;             // elements between consecutive rows of C
   long long batch_stride_c;  // elements between consecutive batches of C
@@ -473,7 +474,28 @@ hb_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                                 OUT_BYTES;
             const bool vec_ok = ((reinterpret_cast<uintptr_t>(base) & 15u) == 0) &&
                                 (col + kColsPerStore <= p.N);
-            if (reduce) {
+            if (p.out_nchw) {
+              // channel-major output: for one channel the 32 lanes of the warp hold 32 consecutive
+              // pixels, so each store instruction writes one contiguous run (two where the warp
+              // straddles two images)
+              const int P = p.HO * p.WO;
+              const int n = row / P;
+              const int pix = row - n * P;
+              uint8_t* o = static_cast<uint8_t*>(p.C) +
+                           ((static_cast<long long>(n) * p.N + col) * P + pix) * OUT_BYTES;
+              const long long cstep = static_cast<long long>(P) * OUT_BYTES;
+              const int ncols = min(kColsPerStore, p.N - col);
+#pragma unroll
+              for (int i = 0; i < kColsPerStore; ++i) {
+                if (i < ncols) {
+                  if (OUT_BYTES == 4)
+                    *reinterpret_cast<uint32_t*>(o + i * cstep) = packed[i % 32];
+                  else
+                    *reinterpret_cast<uint16_t*>(o + i * cstep) =
+                        static_cast<uint16_t>(packed[(i >> 1) % 32] >> (16 * (i & 1)));
+                }
+              }
+            } else if (reduce) {
               const int ncols = min(kColsPerStore, p.N - col);
 #pragma unroll
               for (int i = 0; i < 32; ++i) {
@@ -581,27 +603,146 @@ __global__ void hb_unpack_filter_kernel(const int8_t* __restrict__ packed, int8_
   }
 }
 
-// Batched transpose with zero padding, the layout glue of the NCHW operator:
-//   dst[b][j][i] = (i < R && j < C) ? src[b*src_bs + i*src_rs + j*src_cs] : 0,   j < Cp, i < Rp
-// with dst dense ([Cp][Rp] per batch).  32 x 32 tiles through shared memory so that both the
-// reads (along j when src_cs == 1) and the writes (along i) are coalesced.
+// Layout glue of the NCHW operators in one launch: blocks [0, in_blocks) transpose the input
+// (N, CI, P) to (N, P, CIp) with channels zero-padded to CIp, the rest bring the filter
+// (CO, CI, T) to (T, CIp, CO).
+constexpr int kFilterRun = 128;  // filter elements staged per output channel and block
+
+struct NchwPre {
+  const void* in; void* in_t;
+  const void* w; void* w_t;
+  int N, CI, CIp, P, CO, T;
+  int vec, f_vec;                   // 8-byte accesses are possible (input; 1-tap filter)
+  int in_bx, in_by, in_blocks;      // input tiles per image along P and along CIp; total
+  int f_ci_tile, f_tchunk, f_bco, f_bci, f_bt;  // filter tiling (f_bco x f_bci tiles when T == 1)
+};
+
+// One (16*VEC)^2 tile of  dst[j*Rp + i] = (i < R && j < C) ? src[i*pitch + j] : 0,  i < Rp, j < Cp.
+// 256 threads.  With `vec`, global accesses are 8 bytes wide: a warp reads 256 contiguous bytes of
+// a source row and writes 128 contiguous bytes of a destination row per instruction.
+template <typename T, int PITCH>
+__device__ __forceinline__ void transpose_tile(T (*tile)[PITCH], const T* __restrict__ s, T* __restrict__ d,
+                                               int R, int C, int Rp, int Cp, long long pitch, int i0,
+                                               int j0, bool vec) {
+  constexpr int VEC = 8 / sizeof(T);
+  constexpr int TILE = 16 * VEC;
+  const int tid = threadIdx.x;
+  if (vec) {
+    const int lane16 = tid & 15, grp = tid >> 4;
+    uint2 v[VEC];  // TILE / 16 = VEC passes; all loads are issued before the first shared-memory store
+#pragma unroll
+    for (int u = 0; u < VEC; ++u) {
+      const int i = i0 + grp + 16 * u, j = j0 + lane16 * VEC;
+      v[u] = make_uint2(0u, 0u);
+      if (i < R && j < C) v[u] = *reinterpret_cast<const uint2*>(s + i * pitch + j);
+    }
+#pragma unroll
+    for (int u = 0; u < VEC; ++u) {
+      uint32_t* t32 = reinterpret_cast<uint32_t*>(&tile[grp + 16 * u][lane16 * VEC]);
+      t32[0] = v[u].x;
+      t32[1] = v[u].y;
+    }
+    __syncthreads();
+    for (int jj = grp; jj < TILE; jj += 16) {
+      const int j = j0 + jj, i = i0 + lane16 * VEC;
+      if (j >= Cp || i >= Rp) continue;
+      __align__(8) T e[VEC];
+#pragma unroll
+      for (int r = 0; r < VEC; ++r) e[r] = tile[lane16 * VEC + r][jj];
+      *reinterpret_cast<uint2*>(d + static_cast<long long>(j) * Rp + i) = *reinterpret_cast<const uint2*>(e);
+    }
+  } else {
+    for (int base = tid; base < TILE * TILE; base += 4 * 256) {  // TILE * TILE is a multiple of 1024
+      T v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int idx = base + u * 256;
+        const int ii = idx / TILE, jj = idx - ii * TILE;
+        const int i = i0 + ii, j = j0 + jj;
+        v[u] = (i < R && j < C) ? s[i * pitch + j] : T(0);
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int idx = base + u * 256;
+        tile[idx / TILE][idx % TILE] = v[u];
+      }
+    }
+    __syncthreads();
+    for (int idx = tid; idx < TILE * TILE; idx += 256) {
+      const int jj = idx / TILE, ii = idx - jj * TILE;
+      const int i = i0 + ii, j = j0 + jj;
+      if (j < Cp && i < Rp) d[static_cast<long long>(j) * Rp + i] = tile[ii][jj];
+    }
+  }
+}
+
 template <typename T>
-__global__ void hb_transpose_pad_kernel(const T* __restrict__ src, T* __restrict__ dst, int R, int C,
-                                        int Rp, int Cp, long long src_rs, long long src_cs,
-                                        long long src_bs) {
-  __shared__ T tile[32][33];
-  const int b = blockIdx.z;
-  const int i0 = blockIdx.y * 32, j0 = blockIdx.x * 32;
-  const T* s = src + static_cast<long long>(b) * src_bs;
-  T* d = dst + static_cast<long long>(b) * Cp * Rp;
-  for (int ii = threadIdx.y; ii < 32; ii += blockDim.y) {
-    const int i = i0 + ii, j = j0 + threadIdx.x;
-    tile[ii][threadIdx.x] = (i < R && j < C) ? s[i * src_rs + j * src_cs] : T(0);
+__global__ void __launch_bounds__(256) hb_nchw_pre_kernel(const NchwPre g) {
+  constexpr int VEC = 8 / sizeof(T);
+  constexpr int TILE = 16 * VEC;
+  constexpr int PITCH = TILE + 4 / sizeof(T);   // row pitch of 33 words: conflict-free column reads
+  constexpr int FPITCH = kFilterRun + 4 / sizeof(T);
+  constexpr size_t kTileBytes = sizeof(T) * TILE * PITCH;
+  constexpr size_t kFiltBytes = sizeof(T) * 32 * FPITCH;
+  __shared__ __align__(8) uint8_t raw[kTileBytes > kFiltBytes ? kTileBytes : kFiltBytes];
+  T (*tile)[PITCH] = reinterpret_cast<T (*)[PITCH]>(raw);
+  if (static_cast<int>(blockIdx.x) < g.in_blocks) {
+    // ---- input: per image a (CI x P) matrix, transposed to (P x CIp) ----
+    int b = blockIdx.x;
+    const int bx = b % g.in_bx; b /= g.in_bx;   // along P
+    const int by = b % g.in_by;                 // along CI
+    const int n = b / g.in_by;
+    transpose_tile<T, PITCH>(tile, static_cast<const T*>(g.in) + static_cast<long long>(n) * g.CI * g.P,
+                             static_cast<T*>(g.in_t) + static_cast<long long>(n) * g.P * g.CIp, g.CI, g.P,
+                             g.CIp, g.P, g.P, by * TILE, bx * TILE, g.vec != 0);
+    return;
+  }
+  int b = blockIdx.x - g.in_blocks;
+  if (g.T == 1) {
+    // ---- one-tap filter: a (CO x CI) matrix, transposed to (CIp x CO) ----
+    const int bci = b % g.f_bci, bco = b / g.f_bci;
+    transpose_tile<T, PITCH>(tile, static_cast<const T*>(g.w), static_cast<T*>(g.w_t), g.CO, g.CI, g.CO,
+                             g.CIp, g.CI, bco * TILE, bci * TILE, g.f_vec != 0);
+    return;
+  }
+  // ---- filter with taps: 32 output channels x f_ci_tile input channels x f_tchunk taps per block.
+  // For one output channel those source elements are one contiguous run (f_tchunk == T), or a run
+  // of taps of a single input channel (T > kFilterRun).
+  T (*fbuf)[FPITCH] = reinterpret_cast<T (*)[FPITCH]>(raw);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int bt = b % g.f_bt; b /= g.f_bt;
+  const int bci = b % g.f_bci;
+  const int bco = b / g.f_bci;
+  const int co0 = bco * 32, ci0 = bci * g.f_ci_tile, t0 = bt * g.f_tchunk;
+  const int nt = min(g.f_tchunk, g.T - t0);
+  const int run = g.f_ci_tile * nt;
+  const int run_valid = min(run, max(0, g.CI - ci0) * nt);  // beyond it: zero-padded channels
+  const T* w = static_cast<const T*>(g.w);
+  T* wt = static_cast<T*>(g.w_t);
+  {
+    T v[4][4];  // 16 independent loads per thread: the loop is bound by load latency otherwise
+#pragma unroll
+    for (int cc = 0; cc < 4; ++cc) {
+      const int co = co0 + warp + 8 * cc;
+      const T* srow = w + (static_cast<long long>(co) * g.CI + ci0) * g.T + t0;
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int r = lane + 32 * u;
+        v[cc][u] = (co < g.CO && r < run_valid) ? srow[r] : T(0);
+      }
+    }
+#pragma unroll
+    for (int cc = 0; cc < 4; ++cc)
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        if (lane + 32 * u < run) fbuf[warp + 8 * cc][lane + 32 * u] = v[cc][u];
   }
   __syncthreads();
-  for (int jj = threadIdx.y; jj < 32; jj += blockDim.y) {
-    const int j = j0 + jj, i = i0 + threadIdx.x;
-    if (j < Cp && i < Rp) d[static_cast<long long>(j) * Rp + i] = tile[threadIdx.x][jj];
+  const int co = co0 + lane;
+  for (int r = warp; r < run; r += 8) {
+    const int cil = r / nt;
+    const int ci = ci0 + cil, t = t0 + (r - cil * nt);
+    if (co < g.CO && ci < g.CIp) wt[(static_cast<long long>(t) * g.CIp + ci) * g.CO + co] = fbuf[lane][r];
   }
 }
 

@@ -162,11 +162,12 @@ int hb_conv2d_nhwc_packed(const void* in, const void* w_packed, void* out, int N
  * (ops/cuda/conv2d.py:9-135; tests/figure10/configs/resnet50.json):
  *   out[n,c,p,q] = sum_{ci,kh,kw} pad(in)[n, ci, p*sh+kh, q*sw+kw] * w[c,ci,kh,kw]
  * `in` (N,CI,H,W), `w` (CO,CI,KH,KW), `out` (N,CO,HO,WO), dilation 1 (the reference asserts it).
- * The reference lowers it to an explicit im2col GEMM; here two small transposes bring input and
- * filter to NHWC / HWIO in `scratch` (channels zero-padded to a 32-byte multiple, which also
- * covers the reference's CI == 3 special case: its zero-padded filter taps add nothing), the
- * NHWC kernel runs, and a third transpose writes NCHW.  `scratch` is caller-owned device memory,
- * 256-byte aligned, of at least hb_conv2d_nchw_scratch_bytes(...) bytes.
+ * The reference lowers it to an explicit im2col GEMM; here one launch brings input and filter
+ * to NHWC / HWIO in `scratch` (channels zero-padded to a 32-byte multiple, which also covers the
+ * reference's CI == 3 special case: its zero-padded filter taps add nothing) and the conv
+ * kernel's epilogue writes NCHW directly (for one channel a warp's 32 accumulator rows are 32
+ * consecutive pixels).  `scratch` is caller-owned device memory, 256-byte aligned, of at least
+ * hb_conv2d_nchw_scratch_bytes(...) bytes (the transposed input and filter).
  */
 size_t hb_conv2d_nchw_scratch_bytes(int N, int H, int W, int CI, int CO, int KH, int KW,
                                     int stride_h, int stride_w, int pad, hb_dtype in_a,
