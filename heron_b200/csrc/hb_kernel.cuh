@@ -746,4 +746,52 @@ __global__ void __launch_bounds__(256) hb_nchw_pre_kernel(const NchwPre g) {
   }
 }
 
+// Layout glue of an NCHW conv with very few input channels (the first layer of an image
+// network).  The input becomes a zero-bordered (N, Hs, Ws, cis) tensor with cis = 16 bytes of
+// channels per pixel; the conv kernel then reads, as one "pixel" of KWp * cis channels, KWp
+// horizontally adjacent pixels at once (a tensor map whose W stride is one real pixel), so a
+// whole filter row is one K block.  The filter (CO, CI, KH, KW) becomes (KH, KWp, cis, CO) with
+// zeros for the padded taps and channels.
+struct StemPre {
+  const void* in; void* in_t;
+  const void* w; void* w_t;
+  int N, CI, H, W, CO, KH, KW, KWp, cis, Hs, Ws, pad_h, pad_w;
+  long long in_px, w_elems;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(256) hb_nchw_stem_pre_kernel(const StemPre g) {
+  constexpr int CIS = 16 / sizeof(T);
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  const long long first = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+  const T* in = static_cast<const T*>(g.in);
+  for (long long idx = first; idx < g.in_px; idx += stride) {
+    const int ws = static_cast<int>(idx % g.Ws);
+    const long long rest = idx / g.Ws;
+    const int hs = static_cast<int>(rest % g.Hs);
+    const int n = static_cast<int>(rest / g.Hs);
+    const int y = hs - g.pad_h, x = ws - g.pad_w;
+    __align__(16) T v[CIS];
+#pragma unroll
+    for (int c = 0; c < CIS; ++c) v[c] = T(0);
+    if (y >= 0 && y < g.H && x >= 0 && x < g.W) {
+#pragma unroll
+      for (int c = 0; c < CIS; ++c)
+        if (c < g.CI) v[c] = in[((static_cast<long long>(n) * g.CI + c) * g.H + y) * g.W + x];
+    }
+    reinterpret_cast<uint4*>(g.in_t)[idx] = *reinterpret_cast<const uint4*>(v);
+  }
+  const T* w = static_cast<const T*>(g.w);
+  T* wt = static_cast<T*>(g.w_t);
+  for (long long idx = first; idx < g.w_elems; idx += stride) {
+    const int co = static_cast<int>(idx % g.CO);
+    long long r = idx / g.CO;
+    const int ci = static_cast<int>(r % CIS); r /= CIS;
+    const int kw = static_cast<int>(r % g.KWp);
+    const int kh = static_cast<int>(r / g.KWp);
+    wt[idx] = (ci < g.CI && kw < g.KW)
+                  ? w[((static_cast<long long>(co) * g.CI + ci) * g.KH + kh) * g.KW + kw] : T(0);
+  }
+}
+
 }  // namespace hb

@@ -672,6 +672,12 @@ NCHW_CASES = [
     (2, 64, 14, 14, 256, 1, 1, 1, 0),
     (2, 256, 14, 14, 128, 1, 1, 2, 0),
     (3, 16, 9, 11, 40, 3, 3, (2, 1), 1),
+    # few input channels: the form where a whole filter row is one K block
+    (2, 3, 30, 41, 32, 3, 3, 1, 1),
+    (1, 1, 20, 20, 16, 5, 5, (1, 2), 2),
+    (2, 4, 18, 18, 64, 3, 8, (2, 3), 0),
+    (2, 8, 12, 23, 24, 2, 2, 1, 1),
+    (3, 3, 16, 9, 64, 7, 7, 2, 3),        # narrower than the filter is wide plus padding
 ]
 
 
@@ -699,6 +705,15 @@ def test_conv_nchw_int8_and_plan(K, co):
     out.view(torch.uint8).fill_(0xCD)
     plan.launch()
     check(out, want, "nchw int8 relaunch")
+
+
+@pytest.mark.parametrize("case", [(2, 3, 20, 20, 32, 7, 7, 2, 3), (2, 16, 9, 13, 32, 3, 3, 1, 1), (1, 5, 11, 11, 16, 3, 4, 1, 2)])
+def test_conv_nchw_int8_few_channels(K, co, case):
+    N, CI, H, W, CO, KH, KW, s, p = case
+    rng = np.random.default_rng(sum(case))
+    x, w = rand_i8(rng, (N, CI, H, W), False), rand_i8(rng, (CO, CI, KH, KW), True)
+    out = K.conv2d_nchw(dev(x), dev(w), stride=s, padding=p)
+    check(out, co.conv2d_nchw(x, w, s, p), "nchw int8 stem %s" % (case,))
 
 
 def test_conv_nchw_through_the_registry(K, co):
