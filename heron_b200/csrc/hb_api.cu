@@ -289,6 +289,7 @@ struct ConvGeom {
   bool out_nchw;  // the conv kernel writes (N, CO, HO, WO)
   // byte strides of the input's W, H and N axes when it is not a dense NHWC tensor (0: dense)
   long long w_stride, h_stride, n_stride;
+  int kslab;  // > 1: split-K into that many workspace slabs (see KParams::kslab)
 };
 
 }  // namespace
@@ -310,6 +311,11 @@ struct hb_plan {
   hb::NchwPre pre;
   hb::StemPre stem;
   int pre_esize, pre_grid;
+  // split-K NCHW plans: the kernel that sums the workspace slabs into the NCHW output
+  bool has_post;
+  const void* post_ws; void* post_out;
+  int post_slabs, post_P, post_CO, post_N, post_kind;  // kind 0: float -> half, 1: float -> float, 2: int32
+  long long post_slab_elems;
   // packed-filter conv only: the unpack kernel that runs first on the same stream
   const void* packed_w;
   void* scratch;
@@ -427,9 +433,12 @@ int build_plan(Driver& d, const Problem& pr, const hb_knobs& k, const ConvGeom* 
                        k.swizzle_bytes / es, BK, k.swizzle_bytes);
     if (rc != HB_OK) return rc;
   }
+  const int kslab = (cg && cg->kslab > 1) ? cg->kslab : 0;
+  if (kslab && (eo != 4 || p.num_kb < kslab)) return HB_ERR_KNOB;
   if (p.epilogue) {
     const uint64_t rowC = static_cast<uint64_t>(pr.N) * eo;
-    rc = encode_tiled3(d, &tmC, pr.out, C, pr.N, pr.M, pr.batch, rowC, rowC * pr.M, 128 / eo, 32, 128);
+    rc = encode_tiled3(d, &tmC, pr.out, C, pr.N, pr.M, kslab ? kslab : pr.batch, rowC, rowC * pr.M,
+                       128 / eo, 32, 128);
     if (rc != HB_OK) return rc;
   }
 
@@ -476,7 +485,9 @@ int build_plan(Driver& d, const Problem& pr, const hb_knobs& k, const ConvGeom* 
   auto waves_of = [&](int s) {
     return static_cast<double>((static_cast<long long>(s) * tail + units - 1) / units) / s;
   };
-  if (k.split_k > 1) {
+  if (kslab) {
+    ksplit = kslab;
+  } else if (k.split_k > 1) {
     if (p.num_kb < k.split_k) return HB_ERR_KNOB;
     ksplit = tail > 0 ? k.split_k : 1;
   } else if (k.split_k == 0 && k.tail_split == 0 && eo == 4 && tail > 0) {
@@ -508,7 +519,8 @@ int build_plan(Driver& d, const Problem& pr, const hb_knobs& k, const ConvGeom* 
   }
   p.split = split;
   p.ksplit = ksplit;
-  p.whole_tiles = (split > 1 || ksplit > 1) ? tiles - tail : tiles;
+  p.kslab = kslab ? 1 : 0;
+  p.whole_tiles = kslab ? 0 : ((split > 1 || ksplit > 1) ? tiles - tail : tiles);
   p.num_tiles = p.whole_tiles + (tiles - p.whole_tiles) * split * ksplit;
   p.idesc_split = make_idesc(kind, pr.in_a, pr.in_b, hb::kTileM * cgrp, k.tile_n / split, pr.conv);
   plan->tmB2 = plan->tmB;
@@ -552,7 +564,23 @@ int run_plan(const hb_plan* plan, cudaStream_t stream) {
     const int rc = run_pre(plan, stream);
     if (rc != HB_OK) return rc;
   }
-  return run_main(plan, stream);
+  const int rc = run_main(plan, stream);
+  if (rc != HB_OK || !plan->has_post) return rc;
+  dim3 grid((plan->post_P + 31) / 32, (plan->post_CO + 31) / 32, plan->post_N), block(32, 8);
+  if (grid.y > 65535 || grid.z > 65535) return HB_ERR_SHAPE;
+  if (plan->post_kind == 0)
+    hb::hb_nchw_post_kernel<float, __half><<<grid, block, 0, stream>>>(
+        static_cast<const float*>(plan->post_ws), static_cast<__half*>(plan->post_out), plan->post_slabs,
+        plan->post_slab_elems, plan->post_P, plan->post_CO);
+  else if (plan->post_kind == 1)
+    hb::hb_nchw_post_kernel<float, float><<<grid, block, 0, stream>>>(
+        static_cast<const float*>(plan->post_ws), static_cast<float*>(plan->post_out), plan->post_slabs,
+        plan->post_slab_elems, plan->post_P, plan->post_CO);
+  else
+    hb::hb_nchw_post_kernel<int, int><<<grid, block, 0, stream>>>(
+        static_cast<const int*>(plan->post_ws), static_cast<int*>(plan->post_out), plan->post_slabs,
+        plan->post_slab_elems, plan->post_P, plan->post_CO);
+  return cudaGetLastError() == cudaSuccess ? HB_OK : HB_ERR_LAUNCH;
 }
 
 int run_main(const hb_plan* plan, cudaStream_t stream) {
@@ -574,7 +602,7 @@ int run_main(const hb_plan* plan, cudaStream_t stream) {
   }
   const bool half_out = plan->p.esize_out == 2;
   const bool i8 = plan->p.kind == 1;
-  if (plan->p.ksplit > 1) {
+  if (plan->p.ksplit > 1 && !plan->p.kslab) {
     const int row_groups = 8;
     const int sliced_tiles = (plan->p.num_tiles - plan->p.whole_tiles) / plan->p.ksplit;
     hb::hb_zero_tiles_kernel<<<sliced_tiles * row_groups, 256, 0, stream>>>(
@@ -732,6 +760,7 @@ int build_strip_plan(Driver& d, const ConvGeom& g, hb_dtype in_a, hb_dtype in_w,
 struct ConvExtra {
   bool out_nchw;
   long long w_stride, h_stride, n_stride;
+  int kslab;  // > 1: every tile is cut into this many K slices, each stored to its own slab of `out`
 };
 
 // pad_h / pad_w: rows / columns of zeros on each side of the height / width axis.  The 2-D
@@ -764,7 +793,7 @@ int plan_conv(const void* in, const void* w, void* out, int N, int H, int W, int
   if (d.status != HB_OK) return d.status;
   Problem pr{2, 1, static_cast<int>(M), CO, static_cast<int>(K), in_a, in_w, out_t, true, CI};
   ConvGeom cg{N, H, W, CI, CO, KH, KW, stride_h, stride_w, pad_h, pad_w, dil_h, dil_w, HO, WO, out_nchw,
-              ex ? ex->w_stride : 0, ex ? ex->h_stride : 0, ex ? ex->n_stride : 0};
+              ex ? ex->w_stride : 0, ex ? ex->h_stride : 0, ex ? ex->n_stride : 0, ex ? ex->kslab : 0};
   const bool strided_view = cg.w_stride > 0;  // only the im2col kernel reads through custom strides
   const int algo = knobs ? knobs->conv_algo : 0;
   if (algo < 0 || algo > 2 || (algo == 2 && strided_view)) return HB_ERR_KNOB;
@@ -832,8 +861,13 @@ struct NchwLayout {
   // few-channel ("stem") form: KWp horizontally adjacent pixels of `cis` channels make one K block
   bool stem;
   int cis, KWp, Hs, Ws, Wv;
-  size_t in_bytes, w_bytes, total;
+  size_t in_bytes, w_bytes, ws_bytes, total;
 };
+
+// Most slabs a split-K plan of the NCHW operators takes, and the largest output (elements) it is
+// considered for: small outputs are the ones that leave most of the GPU idle.
+constexpr int kMaxSlabs = 8;
+constexpr long long kSlabMaxOutElems = 1ll << 21;
 
 bool nchw_layout(int N, int H, int W, int CI, int CO, int KH, int KW, int sh, int sw, int pad_h,
                  int pad_w, hb_dtype in_a, hb_dtype out_t, NchwLayout* L) {
@@ -860,7 +894,10 @@ bool nchw_layout(int N, int H, int W, int CI, int CO, int KH, int KW, int sh, in
     L->in_bytes = align256(static_cast<size_t>(N) * L->Hs * L->Ws * 16);
     L->w_bytes = align256(static_cast<size_t>(KH) * L->KWp * 16 * CO);
   }
-  L->total = L->in_bytes + L->w_bytes;
+  // room for the partial sums of a split-K plan (4-byte accumulators, row-major (M, CO) slabs)
+  const long long out_elems = static_cast<long long>(N) * L->HO * L->WO * CO;
+  L->ws_bytes = out_elems <= kSlabMaxOutElems ? align256(static_cast<size_t>(out_elems) * 4 * kMaxSlabs) : 0;
+  L->total = L->in_bytes + L->w_bytes + L->ws_bytes;
   return true;
 }
 
@@ -878,12 +915,54 @@ int plan_conv_nchw(const void* in, const void* w, void* out, int N, int H, int W
   uint8_t* s_w = s_in + L.in_bytes;
   if (!aligned16(out)) return HB_ERR_ALIGN;
   const int es = esize(in_a);
+  uint8_t* s_ws = s_w + L.w_bytes;
+  // The conv the kernel runs: the NHWC form of the problem, or its few-channel form.
+  ConvExtra ex{true, 0, 0, 0, 0};
+  int cH = H, cW = W, cCI = L.CIp, cKW = KW, cpad_h = pad_h, cpad_w = pad_w;
   if (L.stem) {
     const long long px = 16;  // bytes per stored pixel
-    const ConvExtra ex{true, px, px * L.Ws, px * L.Ws * L.Hs};
-    const int rc = plan_conv(s_in, s_w, out, N, L.Hs, L.Wv, L.KWp * L.cis, CO, KH, 1, sh, sw, 0, 0, 1, 1,
-                             in_a, in_w, out_t, knobs, plan, &ex);
+    ex.w_stride = px; ex.h_stride = px * L.Ws; ex.n_stride = px * L.Ws * L.Hs;
+    cH = L.Hs; cW = L.Wv; cCI = L.KWp * L.cis; cKW = 1; cpad_h = 0; cpad_w = 0;
+  }
+  int rc = plan_conv(s_in, s_w, out, N, cH, cW, cCI, CO, KH, cKW, sh, sw, cpad_h, cpad_w, 1, 1, in_a, in_w,
+                     out_t, knobs, plan, &ex);
+  if (rc != HB_OK) return rc;
+  // A problem with far fewer tiles than SMs and a long reduction runs as split-K: every tile's K
+  // range is cut into slabs stored side by side in the workspace, and a small kernel adds them in
+  // slab order while it writes NCHW (deterministic, no atomics, any output type).
+  bool post = false;
+  int slabs = 0;
+  if (!plan->strip && L.ws_bytes > 0 && (!knobs || knobs->split_k != 1)) {
+    const int units = driver().sm_count / plan->knobs.cta_group;
+    const int tiles = plan->p.num_tiles;
+    slabs = tiles > 0 ? units / tiles : 0;
+    if (knobs && knobs->split_k > 1) slabs = knobs->split_k;
+    if (slabs > kMaxSlabs) slabs = kMaxSlabs;
+    while (slabs > 1 && plan->p.num_kb / slabs < 4) --slabs;
+    // the extra launch and the workspace round trip cost about 4 us; a K block takes about 0.4 us
+    post = slabs >= 2 && ((knobs && knobs->split_k > 1) ||
+                          static_cast<long long>(plan->p.num_kb) * (slabs - 1) >= 24ll * slabs);
+  }
+  if (post) {
+    const hb_dtype acc_t = (in_a == HB_F16) ? HB_F32 : HB_S32;
+    ex.out_nchw = false;
+    ex.kslab = slabs;
+    hb_knobs k0;
+    if (knobs) k0 = *knobs; else std::memset(&k0, 0, sizeof(k0));
+    k0.epilogue = 0;
+    k0.split_k = 0;
+    k0.tail_split = 1;
+    if (k0.tile_n != 0 && out_t == HB_F16 && k0.tile_n % 64 != 0) k0.tile_n = 0;
+    rc = plan_conv(s_in, s_w, s_ws, N, cH, cW, cCI, CO, KH, cKW, sh, sw, cpad_h, cpad_w, 1, 1, in_a, in_w,
+                   acc_t, &k0, plan, &ex);
     if (rc != HB_OK) return rc;
+    plan->has_post = true;
+    plan->post_ws = s_ws; plan->post_out = out;
+    plan->post_slabs = slabs; plan->post_P = L.HO * L.WO; plan->post_CO = CO; plan->post_N = N;
+    plan->post_slab_elems = static_cast<long long>(N) * L.HO * L.WO * CO;
+    plan->post_kind = out_t == HB_F16 ? 0 : (out_t == HB_F32 ? 1 : 2);
+  }
+  if (L.stem) {
     hb::StemPre& g = plan->stem;
     g.in = in; g.in_t = s_in; g.w = w; g.w_t = s_w;
     g.N = N; g.CI = CI; g.H = H; g.W = W; g.CO = CO; g.KH = KH; g.KW = KW; g.KWp = L.KWp; g.cis = L.cis;
@@ -899,10 +978,6 @@ int plan_conv_nchw(const void* in, const void* w, void* out, int N, int H, int W
     plan->has_pre = true;
     return HB_OK;
   }
-  const ConvExtra ex{true, 0, 0, 0};
-  const int rc = plan_conv(s_in, s_w, out, N, H, W, L.CIp, CO, KH, KW, sh, sw, pad_h, pad_w, 1, 1, in_a, in_w,
-                           out_t, knobs, plan, &ex);
-  if (rc != HB_OK) return rc;
   const int T = KH * KW, P = H * W;
   const int vec = 8 / es, tile = 16 * vec;
   hb::NchwPre& g = plan->pre;

@@ -63,6 +63,9 @@ struct KParams {
   // Alternatively (ksplit > 1, split == 1) each remaining tile is cut into `ksplit` slices of the
   // reduction: full-width work items whose epilogue adds into an output that was zeroed first.
   int ksplit;
+  // kslab = 1 (with ksplit > 1 and whole_tiles == 0): slice s of every tile is stored, not added,
+  // into slab s of a (ksplit, M, N) workspace; a later kernel sums the slabs in a fixed order.
+  int kslab;
   uint32_t idesc_split;
   long long wait_limit_cycles;  // 0: the default bound on every mbarrier wait
   uint32_t idesc;
@@ -152,15 +155,17 @@ hb_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   const int tile_step = gridDim.x / CG;
   const int tile_rows = kTileM * CG;
   // work item -> (batch, first row of the pair tile, first column, width)
-  auto decode = [&](int t, int& b, int& m_pair, int& n_first, int& bn, int& kb0, int& kb1) {
+  auto decode = [&](int t, int& b, int& m_pair, int& n_first, int& bn, int& kb0, int& kb1, int& kslice) {
     int slice = 0;
     bn = p.BN;
     kb0 = 0;
     kb1 = p.num_kb;
+    kslice = 0;
     if (t >= p.whole_tiles) {
       const int h = t - p.whole_tiles;
       if (p.ksplit > 1) {
         const int ks = h % p.ksplit;
+        kslice = ks;
         t = p.whole_tiles + h / p.ksplit;
         kb0 = ks * p.num_kb / p.ksplit;
         kb1 = (ks + 1) * p.num_kb / p.ksplit;
@@ -188,8 +193,8 @@ hb_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     // diagnostic 12: the producer stays silent, so the consumers' bounded waits run out and the
     // abort path (drain, TMEM release, status word) is what the launch exercises
     for (int t = first_tile; ok && t < p.num_tiles && p.probe != 12; t += tile_step) {
-      int b, m_pair, n_first, bn, kb0, kb1;
-      decode(t, b, m_pair, n_first, bn, kb0, kb1);
+      int b, m_pair, n_first, bn, kb0, kb1, kslice;
+      decode(t, b, m_pair, n_first, bn, kb0, kb1, kslice);
       const int bn_mine = bn / CG;  // B rows this CTA stages for this work item
       const int n_chunks = p.b_mn_major ? bn_mine / chunk_cols : 1;
       const uint32_t tx_bytes = static_cast<uint32_t>(a_bytes + bn_mine * p.SW) * CG;
@@ -386,9 +391,10 @@ hb_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     constexpr int kColsPerStore = 128 / OUT_BYTES;  // 32 (4-byte) or 64 (fp16) columns
     const uint32_t my_buf = sEpi + ew * 2 * kEpiBufBytes;
     for (int t = first_tile; ok && t < p.num_tiles; t += tile_step) {
-      int b, m_pair, n0, bn, kb0, kb1;
-      decode(t, b, m_pair, n0, bn, kb0, kb1);
-      const bool reduce = OUT_BYTES == 4 && p.ksplit > 1 && t >= p.whole_tiles;
+      int b, m_pair, n0, bn, kb0, kb1, kslice;
+      decode(t, b, m_pair, n0, bn, kb0, kb1, kslice);
+      const bool reduce = OUT_BYTES == 4 && p.ksplit > 1 && t >= p.whole_tiles && !p.kslab;
+      const int zc = p.kslab ? kslice : b;  // third coordinate of the output: batch, or workspace slab
       const int row0 = m_pair + static_cast<int>(cta_rank) * kTileM + q * 32;
       if (!(p.probe == 8 ? mbar_wait(smem_u32(&bars->tmem_full[acc]), acc_phase, wctx)
                          : mbar_wait_relaxed(smem_u32(&bars->tmem_full[acc]), acc_phase, wctx))) {
@@ -459,9 +465,9 @@ hb_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             __syncwarp();
             if (issuer) {
               if (reduce)
-                tma_reduce_add_3d(&tmC, buf, col, row0, b);
+                tma_reduce_add_3d(&tmC, buf, col, row0, zc);
               else
-                tma_store_3d(&tmC, buf, col, row0, b);
+                tma_store_3d(&tmC, buf, col, row0, zc);
               bulk_commit();
             }
           }
@@ -469,7 +475,7 @@ hb_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           const int row = row0 + lane;
           if (row < p.M && col < p.N) {
             uint8_t* base = static_cast<uint8_t*>(p.C) +
-                            (static_cast<long long>(b) * p.batch_stride_c +
+                            (static_cast<long long>(zc) * p.batch_stride_c +
                              static_cast<long long>(row) * p.ldc + col) *
                                 OUT_BYTES;
             const bool vec_ok = ((reinterpret_cast<uintptr_t>(base) & 15u) == 0) &&
@@ -743,6 +749,30 @@ __global__ void __launch_bounds__(256) hb_nchw_pre_kernel(const NchwPre g) {
     const int cil = r / nt;
     const int ci = ci0 + cil, t = t0 + (r - cil * nt);
     if (co < g.CO && ci < g.CIp) wt[(static_cast<long long>(t) * g.CIp + ci) * g.CO + co] = fbuf[lane][r];
+  }
+}
+
+// Last step of a split-K NCHW conv: sums the `slabs` partial results ws[s][n*P + pix][co] in slab
+// order and writes out[n][co][pix].  32 x 32 tiles through shared memory: reads coalesced along
+// co, writes along pix.
+template <typename ACC, typename OUT>
+__global__ void hb_nchw_post_kernel(const ACC* __restrict__ ws, OUT* __restrict__ out, int slabs,
+                                    long long slab_elems, int P, int CO) {
+  __shared__ ACC tile[32][33];
+  const int n = blockIdx.z, p0 = blockIdx.x * 32, c0 = blockIdx.y * 32;
+  for (int pp = threadIdx.y; pp < 32; pp += blockDim.y) {
+    const int pix = p0 + pp, co = c0 + threadIdx.x;
+    ACC acc = ACC(0);
+    if (pix < P && co < CO) {
+      const ACC* src = ws + (static_cast<long long>(n) * P + pix) * CO + co;
+      for (int s = 0; s < slabs; ++s) acc += src[s * slab_elems];
+    }
+    tile[pp][threadIdx.x] = acc;
+  }
+  __syncthreads();
+  for (int cc = threadIdx.y; cc < 32; cc += blockDim.y) {
+    const int co = c0 + cc, pix = p0 + threadIdx.x;
+    if (co < CO && pix < P) out[(static_cast<long long>(n) * CO + co) * P + pix] = static_cast<OUT>(tile[threadIdx.x][cc]);
   }
 }
 

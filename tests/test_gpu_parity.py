@@ -716,6 +716,36 @@ def test_conv_nchw_int8_few_channels(K, co, case):
     check(out, co.conv2d_nchw(x, w, s, p), "nchw int8 stem %s" % (case,))
 
 
+@pytest.mark.parametrize("case", [(4, 512, 7, 7, 512, 3, 3, 1, 1), (2, 2048, 7, 7, 256, 1, 1, 1, 0), (8, 256, 14, 14, 64, 3, 3, 2, 1)])
+def test_conv_nchw_small_output_long_reduction_splits_k(K, co, case):
+    """Late-network shapes: few output tiles, thousands of reduction steps.  The plan cuts K into
+    workspace slabs and a last kernel adds them in slab order: same bits on every launch, int8 exact."""
+    N, CI, H, W, CO, KH, KW, s, p = case
+    rng = np.random.default_rng(sum(case))
+    x = rng.standard_normal((N, CI, H, W)).astype(np.float16)
+    w = (rng.standard_normal((CO, CI, KH, KW)) / np.sqrt(CI * KH * KW)).astype(np.float16)
+    for od, tdt in ((np.float16, torch.float16), (np.float32, torch.float32)):
+        want = co.conv2d_nchw(x, w, s, p, od)
+        out = poison(want.shape, tdt)
+        plan = K.plan_conv2d_nchw(dev(x), dev(w), stride=s, padding=p, out=out)
+        assert plan.knobs()["split_k"] > 1, plan.knobs()
+        plan.launch()
+        check(out, want, "nchw split-K %s" % (case,))
+        first = out.clone()
+        out.view(torch.uint8).fill_(0xCD)
+        plan.launch()
+        assert torch.equal(out, first)
+        off = poison(want.shape, tdt)
+        K.conv2d_nchw(dev(x), dev(w), stride=s, padding=p, out=off, knobs=dict(split_k=1))
+        check(off, want, "nchw, split-K off %s" % (case,))
+    xi, wi = rand_i8(rng, (N, CI, H, W), False), rand_i8(rng, (CO, CI, KH, KW), True)
+    plan = K.plan_conv2d_nchw(dev(xi), dev(wi), stride=s, padding=p)
+    assert (plan.knobs()["split_k"] > 1) == (CI * KH * KW >= 4096), plan.knobs()  # half the K blocks in int8
+    check(plan.launch(), co.conv2d_nchw(xi, wi, s, p), "nchw int8 split-K %s" % (case,))
+    check(K.conv2d_nchw(dev(xi), dev(wi), stride=s, padding=p, knobs=dict(split_k=3)), co.conv2d_nchw(xi, wi, s, p),
+          "nchw int8 split-K 3 %s" % (case,))
+
+
 def test_conv_nchw_through_the_registry(K, co):
     """`c2d` of the tensor-core registry, with a ResNet-50 table row scaled down in batch."""
     from heron_b200.ops import cuda as heron_cuda
