@@ -167,7 +167,14 @@ struct Problem {
   bool conv;
   int CI;      // conv only
   int b_rows;  // gemm only: rows B really has when fewer than N (the rest read as zeros); 0 = N
+  // bmm only: A (M, K) is shared by all batches and B is stored (batch, K, N) with N contiguous.
+  // A 1x1 stride-1 NCHW conv is exactly this product on the tensors as they are:
+  // out[n] (CO x P) = filter (CO x CI) . in[n] (CI x P).
+  bool shared_a_b_mn;
 };
+
+// B is read as (K, N) tiles with N contiguous: the conv filter (HWIO) and the form above.
+bool b_mn_major(const Problem& pr) { return pr.conv || pr.shared_a_b_mn; }
 
 // Ring-stage bytes of one CTA: 128 rows of A plus this CTA's share of B's tile_n rows.
 int stage_bytes(int tile_n, int sw, int cg) { return (hb::kTileM + tile_n / cg) * sw; }
@@ -195,7 +202,7 @@ void resolve_knobs(const Problem& pr, const hb_knobs* in, int sm_count, hb_knobs
     // tile and when each CTA of the pair still gets a whole B chunk of a tile no wider than N.
     const int sw = k.swizzle_bytes ? k.swizzle_bytes : 128;
     const long long kblocks = (static_cast<long long>(pr.K) * es + sw - 1) / sw;
-    const int min_pair_n = pr.conv ? 2 * sw / es : 64;
+    const int min_pair_n = b_mn_major(pr) ? 2 * sw / es : 64;
     k.cta_group = (pr.M > hb::kTileM && kblocks >= 8 && pr.N >= min_pair_n) ? 2 : 1;
   }
   if (k.epilogue == 0) {
@@ -205,7 +212,7 @@ void resolve_knobs(const Problem& pr, const hb_knobs* in, int sm_count, hb_knobs
   if (k.tile_n == 0) {
     const int step = (eo == 2) ? 64 : 32;
     // MN-major B needs whole swizzle-span chunks of columns in every CTA of the group
-    const int chunk = pr.conv ? k.cta_group * k.swizzle_bytes / es : step;
+    const int chunk = b_mn_major(pr) ? k.cta_group * k.swizzle_bytes / es : step;
     const int gran = chunk > step ? chunk : step;
     const int rows = hb::kTileM * k.cta_group;
     const long long tiles_m = (pr.M + rows - 1) / rows;
@@ -256,11 +263,9 @@ int check_knobs(const Problem& pr, const hb_knobs& k, int* smem_bytes, int* tmem
     // slices add into the output: 4-byte elements only; fp32 sums stay order-independent with two
     if (eo != 4 || (pr.out == HB_F32 && k.split_k != 2) || k.tail_split > 1) return HB_ERR_KNOB;
   }
-  if (pr.conv) {
-    if ((pr.CI * es) % k.swizzle_bytes != 0) return HB_ERR_KNOB;
-    // whole MN-major chunks in every CTA of the group
-    if ((k.tile_n / k.cta_group * es) % k.swizzle_bytes != 0) return HB_ERR_KNOB;
-  }
+  if (pr.conv && (pr.CI * es) % k.swizzle_bytes != 0) return HB_ERR_KNOB;
+  // whole MN-major chunks in every CTA of the group
+  if (b_mn_major(pr) && (k.tile_n / k.cta_group * es) % k.swizzle_bytes != 0) return HB_ERR_KNOB;
   const int epi = k.epilogue == 1 ? hb::kEpiWarps * 2 * hb::kEpiBufBytes : 0;
   const int smem = k.stages * stage_bytes(k.tile_n, k.swizzle_bytes, k.cta_group) + epi + kSmemSlack;
   if (smem > kSmemLimit) return HB_ERR_KNOB;
@@ -373,12 +378,13 @@ int build_plan(Driver& d, const Problem& pr, const hb_knobs& k, const ConvGeom* 
   if (ntiles > 0x7fffffffLL) return HB_ERR_SHAPE;
   p.num_tiles = static_cast<int>(ntiles);
   const int BK = k.swizzle_bytes / es;
-  p.raster = k.raster; p.kind = kind; p.b_mn_major = pr.conv ? 1 : 0; p.a_im2col = pr.conv ? 1 : 0;
+  p.raster = k.raster; p.kind = kind; p.b_mn_major = b_mn_major(pr) ? 1 : 0; p.a_im2col = pr.conv ? 1 : 0;
+  p.a_shared = pr.shared_a_b_mn ? 1 : 0;
   p.epilogue = k.epilogue == 1 ? 1 : 0;
   p.l2_prefetch = (!pr.conv && k.l2_prefetch > 0) ? k.l2_prefetch : 0;
   p.probe = k.reserved;  // diagnostic modes
   if (k.reserved == 12) p.wait_limit_cycles = 200000000LL;  // ~0.1 s: the timeout test should be quick: 1 = no reloads, 2 = no MMAs (results undefined)
-  p.idesc = make_idesc(kind, pr.in_a, pr.in_b, hb::kTileM * cgrp, k.tile_n, pr.conv);
+  p.idesc = make_idesc(kind, pr.in_a, pr.in_b, hb::kTileM * cgrp, k.tile_n, b_mn_major(pr));
   p.C = C; p.ldc = pr.N; p.batch_stride_c = static_cast<long long>(pr.M) * pr.N;
 
   CUtensorMap& tmA = plan->tmA;
@@ -390,9 +396,20 @@ int build_plan(Driver& d, const Problem& pr, const hb_knobs& k, const ConvGeom* 
     rc = encode_tiled3(d, &tmA, pr.in_a, A, pr.K, pr.M, pr.batch, rowA, rowA * pr.M, BK, hb::kTileM,
                        k.swizzle_bytes);
     if (rc != HB_OK) return rc;
-    const int b_rows = pr.b_rows > 0 ? pr.b_rows : pr.N;  // rows past the end are zero-filled by TMA
-    rc = encode_tiled3(d, &tmB, pr.in_b, B, pr.K, b_rows, pr.batch, rowA, rowA * b_rows, BK,
-                       k.tile_n / cgrp, k.swizzle_bytes);
+    if (pr.shared_a_b_mn) {
+      // A once for all batches; B as a (N, K, batch) tensor with N contiguous: one box = BK rows of
+      // K x one swizzle span of N
+      rc = encode_tiled3(d, &tmA, pr.in_a, A, pr.K, pr.M, 1, rowA, rowA * pr.M, BK, hb::kTileM,
+                         k.swizzle_bytes);
+      if (rc != HB_OK) return rc;
+      const uint64_t rowB = static_cast<uint64_t>(pr.N) * es;
+      rc = encode_tiled3(d, &tmB, pr.in_b, B, pr.N, pr.K, pr.batch, rowB, rowB * pr.K,
+                         k.swizzle_bytes / es, BK, k.swizzle_bytes);
+    } else {
+      const int b_rows = pr.b_rows > 0 ? pr.b_rows : pr.N;  // rows past the end are zero-filled by TMA
+      rc = encode_tiled3(d, &tmB, pr.in_b, B, pr.K, b_rows, pr.batch, rowA, rowA * b_rows, BK,
+                         k.tile_n / cgrp, k.swizzle_bytes);
+    }
     if (rc != HB_OK) return rc;
   } else {
     p.HO = cg->HO; p.WO = cg->WO; p.KW = cg->KW; p.CI = cg->CI;
@@ -469,7 +486,7 @@ int build_plan(Driver& d, const Problem& pr, const hb_knobs& k, const ConvGeom* 
   auto slice_ok = [&](int s) {
     const int bn = k.tile_n / s;
     if (bn * s != k.tile_n || bn % ((eo == 2) ? 64 : 32) != 0 || (bn / cgrp) % 8 != 0 || bn % 16 != 0) return false;
-    if (pr.conv && ((bn / cgrp) * es) % k.swizzle_bytes != 0) return false;
+    if (b_mn_major(pr) && ((bn / cgrp) * es) % k.swizzle_bytes != 0) return false;
     return true;
   };
   const int tiles = p.num_tiles;
@@ -522,9 +539,9 @@ int build_plan(Driver& d, const Problem& pr, const hb_knobs& k, const ConvGeom* 
   p.kslab = kslab ? 1 : 0;
   p.whole_tiles = kslab ? 0 : ((split > 1 || ksplit > 1) ? tiles - tail : tiles);
   p.num_tiles = p.whole_tiles + (tiles - p.whole_tiles) * split * ksplit;
-  p.idesc_split = make_idesc(kind, pr.in_a, pr.in_b, hb::kTileM * cgrp, k.tile_n / split, pr.conv);
+  p.idesc_split = make_idesc(kind, pr.in_a, pr.in_b, hb::kTileM * cgrp, k.tile_n / split, b_mn_major(pr));
   plan->tmB2 = plan->tmB;
-  if (split > 1 && !pr.conv) {
+  if (split > 1 && !b_mn_major(pr)) {
     const uint64_t rowA = static_cast<uint64_t>(pr.K) * es;
     const int b_rows = pr.b_rows > 0 ? pr.b_rows : pr.N;
     rc = encode_tiled3(d, &plan->tmB2, pr.in_b, B, pr.K, b_rows, pr.batch, rowA, rowA * b_rows, BK,
@@ -911,6 +928,26 @@ int plan_conv_nchw(const void* in, const void* w, void* out, int N, int H, int W
   if (!scratch || scratch_bytes < L.total) return HB_ERR_SCRATCH;
   if (!in || !w || !out) return HB_ERR_ALIGN;
   if ((reinterpret_cast<uintptr_t>(scratch) & 255u) != 0) return HB_ERR_ALIGN;
+  // A 1x1, stride-1, unpadded conv is, per image, out (CO x P) = filter (CO x CI) . in (CI x P): a
+  // batched GEMM on the NCHW tensors as they are (filter as the shared K-major A, each image as an
+  // N-contiguous B, row-major C = NCHW), with no layout pass.  Needs 16-byte rows for the tensor maps.
+  const long long P1 = static_cast<long long>(H) * W;
+  const int es1 = esize(in_a), eo1 = esize(out_t);
+  if (KH == 1 && KW == 1 && sh == 1 && sw == 1 && pad_h == 0 && pad_w == 0 && (P1 * es1) % 16 == 0 &&
+      (static_cast<long long>(CI) * es1) % 16 == 0 && P1 <= 0x7fffffffLL && P1 >= 32 &&
+      aligned16(in) && aligned16(w) && aligned16(out) && (!knobs || knobs->conv_algo == 0)) {
+    if (mma_kind(in_w, in_a, out_t) < 0) return HB_ERR_DTYPE;
+    Driver& d = driver();
+    if (d.status != HB_OK) return d.status;
+    Problem pr{1, N, CO, static_cast<int>(P1), CI, in_w, in_a, out_t, false, 0, 0, true};
+    hb_knobs k0, k;
+    if (knobs) k0 = *knobs; else std::memset(&k0, 0, sizeof(k0));
+    if (k0.epilogue == 0 && (P1 * eo1) % 16 != 0) k0.epilogue = 2;
+    if (k0.epilogue == 1 && (P1 * eo1) % 16 != 0) return HB_ERR_KNOB;
+    k0.l2_prefetch = -1;
+    resolve_knobs(pr, &k0, d.sm_count, &k);
+    return build_plan(d, pr, k, nullptr, w, in, out, plan);
+  }
   uint8_t* s_in = static_cast<uint8_t*>(scratch);
   uint8_t* s_w = s_in + L.in_bytes;
   if (!aligned16(out)) return HB_ERR_ALIGN;

@@ -73,6 +73,7 @@ struct KParams {
   int HO, WO, KW, CI, kb_per_tap, stride_h, stride_w, dil_h, dil_w, pad_h, pad_w;
   // direct-store epilogue
   int out_nchw;  // conv only: C is (N, CO, HO, WO) instead of (N*HO*WO, CO)
+  int a_shared;  // batched: A has no batch dimension (every batch multiplies the same matrix)
   void* C;
   long long ldc;             // elements between consecutive rows of C
   long long batch_stride_c;  // elements between consecutive batches of C
@@ -242,7 +243,7 @@ hb_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                                       static_cast<uint16_t>(rx * p.dil_w), static_cast<uint16_t>(ry * p.dil_h));
           krow = tap * p.CI + cc * BK;
         } else {
-          if (part & 1) tma_load_3d_cg<CG>(dA, &tmA, full, kb * BK, m0, b);
+          if (part & 1) tma_load_3d_cg<CG>(dA, &tmA, full, kb * BK, m0, p.a_shared ? 0 : b);
           krow = kb * BK;
           if (p.l2_prefetch > 0 && kb + p.l2_prefetch < kb1) {
             tma_prefetch_3d(&tmA, (kb + p.l2_prefetch) * BK, m0, b);

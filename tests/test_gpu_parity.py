@@ -678,6 +678,12 @@ NCHW_CASES = [
     (2, 4, 18, 18, 64, 3, 8, (2, 3), 0),
     (2, 8, 12, 23, 24, 2, 2, 1, 1),
     (3, 3, 16, 9, 64, 7, 7, 2, 3),        # narrower than the filter is wide plus padding
+    # 1x1, stride 1, 16-byte image rows: a batched GEMM on the NCHW tensors as they are, no layout pass
+    (2, 64, 16, 16, 256, 1, 1, 1, 0),
+    (3, 128, 12, 20, 72, 1, 1, 1, 0),
+    (2, 72, 28, 28, 40, 1, 1, 1, 0),
+    (5, 512, 8, 12, 320, 1, 1, 1, 0),
+    (1, 1024, 56, 56, 64, 1, 1, 1, 0),
 ]
 
 
@@ -705,6 +711,13 @@ def test_conv_nchw_int8_and_plan(K, co):
     out.view(torch.uint8).fill_(0xCD)
     plan.launch()
     check(out, want, "nchw int8 relaunch")
+
+
+def test_conv_nchw_int8_pointwise_in_place(K, co):
+    rng = np.random.default_rng(31)
+    for (N, CI, H, W, CO) in [(3, 64, 8, 8, 96), (2, 272, 4, 12, 40), (1, 128, 16, 16, 256)]:
+        x, w = rand_i8(rng, (N, CI, H, W), False), rand_i8(rng, (CO, CI, 1, 1), True)
+        check(K.conv2d_nchw(dev(x), dev(w)), co.conv2d_nchw(x, w, 1, 0), "nchw int8 1x1 %s" % ((N, CI, H, W, CO),))
 
 
 @pytest.mark.parametrize("case", [(2, 3, 20, 20, 32, 7, 7, 2, 3), (2, 16, 9, 13, 32, 3, 3, 1, 1), (1, 5, 11, 11, 16, 3, 4, 1, 2)])
