@@ -976,9 +976,10 @@ int plan_conv_nchw(const void* in, const void* w, void* out, int N, int H, int W
     if (knobs && knobs->split_k > 1) slabs = knobs->split_k;
     if (slabs > kMaxSlabs) slabs = kMaxSlabs;
     while (slabs > 1 && plan->p.num_kb / slabs < 4) --slabs;
-    // the extra launch and the workspace round trip cost about 4 us; a K block takes about 0.4 us
+    // the extra launch and the workspace round trip cost about 4 us; a K block of the im2col conv
+    // takes about 0.5 us
     post = slabs >= 2 && ((knobs && knobs->split_k > 1) ||
-                          static_cast<long long>(plan->p.num_kb) * (slabs - 1) >= 24ll * slabs);
+                          static_cast<long long>(plan->p.num_kb) * (slabs - 1) >= 16ll * slabs);
   }
   if (post) {
     const hb_dtype acc_t = (in_a == HB_F16) ? HB_F32 : HB_S32;
