@@ -340,7 +340,7 @@ def run_ours(args):
                         "%.1f MB gathered per step" % (gather_bytes / 1e6)}
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline(name, budget_s=args.cpu_seconds)
-        print(json.dumps(line), flush=True)
+        emit(line)
     sampler.stop()
     if world > 1:
         dist.destroy_process_group()
@@ -444,7 +444,28 @@ def run_reference(args):
         "e2e": {"value": value, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
-    print(json.dumps(line), flush=True)
+    emit(line)
+
+
+_RESULT_FD = None
+
+
+def keep_stdout_for_the_result():
+    """Whatever libraries print (NCCL's version banner is a C-level write to stdout) goes to stderr;
+    the descriptor stdout had is kept for the one JSON line."""
+    global _RESULT_FD
+    sys.stdout.flush()
+    _RESULT_FD = os.dup(1)
+    os.dup2(2, 1)
+
+
+def emit(line):
+    data = (json.dumps(line) + "\n").encode()
+    if _RESULT_FD is None:
+        sys.stdout.write(data.decode())
+        sys.stdout.flush()
+    else:
+        os.write(_RESULT_FD, data)
 
 
 def main():
@@ -457,6 +478,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-seconds", type=float, default=8.0)
     args = ap.parse_args()
+    keep_stdout_for_the_result()
     if args.impl == "reference":
         args.steps = args.steps if args.steps is not None else 10
         args.warmup = args.warmup if args.warmup is not None else 3
