@@ -167,6 +167,24 @@ def test_conv_knob_space_respects_channel_bytes(hb_lib):
         assert hb_lib.hb_check_knobs(2, 1, 16 * 81, 64, 144, 16, _lib.HB_F16, _lib.HB_F32, ctypes.byref(k), None, None) == 0
 
 
+def test_nchw_first_layer_knob_space_is_the_row_packed_form(hb_lib):
+    """3 input channels, 7x7 filter: the library reads a whole filter row (8 taps of 16 bytes) as one
+    128-byte K block, and the tuner's space must offer that block size, not the 32 bytes of the
+    channel-padded form."""
+    t = _task("c2d", [16, 224, 224, 3, 64, 7, 7, 2, 3, 1, "float16", "float16"])
+    spans = set()
+    random.seed(6)
+    for _ in range(30):
+        t.knob_manager.randSample()
+        handle, _ = t.instantiate(t.knob_manager)
+        spans.add(handle.knobs["swizzle_bytes"])
+    assert 128 in spans
+    t = _task("c2d", [16, 56, 56, 3, 64, 3, 3, 1, 1, 1, "float16", "float16"])
+    t.knob_manager.randSample()
+    handle, _ = t.instantiate(t.knob_manager)
+    assert handle.knobs["swizzle_bytes"] in (32, 64)  # 4 taps of 16 bytes
+
+
 def test_cga_crossover_keeps_parent_values():
     import copy
     t = _task("bmm", [192, 512, 64, 512, "int8", "int32"])
