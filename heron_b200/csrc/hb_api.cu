@@ -878,6 +878,8 @@ struct NchwLayout {
   // few-channel ("stem") form: KWp horizontally adjacent pixels of `cis` channels make one K block
   bool stem;
   int cis, KWp, Hs, Ws, Wv;
+  // strided 1x1 conv: the glue keeps only the pixels the conv reads, and the conv runs unstrided
+  bool subsample;
   size_t in_bytes, w_bytes, ws_bytes, total;
 };
 
@@ -897,7 +899,9 @@ bool nchw_layout(int N, int H, int W, int CI, int CO, int KH, int KW, int sh, in
   L->HO = conv_out_extent(H, KH, sh, pad_h, 1);
   L->WO = conv_out_extent(W, KW, sw, pad_w, 1);
   if (L->HO <= 0 || L->WO <= 0) return false;
-  L->in_bytes = align256(static_cast<size_t>(N) * H * W * L->CIp * es);
+  L->subsample = KH == 1 && KW == 1 && pad_h == 0 && pad_w == 0 && (sh > 1 || sw > 1);
+  const size_t kept_px = L->subsample ? static_cast<size_t>(L->HO) * L->WO : static_cast<size_t>(H) * W;
+  L->in_bytes = align256(static_cast<size_t>(N) * kept_px * L->CIp * es);
   L->w_bytes = align256(static_cast<size_t>(KH) * KW * L->CIp * CO * es);
   // With at most 16 bytes of channels per pixel and a filter row of 2..8 taps, a whole filter
   // row fits one 64- or 128-byte K block: far fewer, fuller pipeline stages than one tap each.
@@ -955,13 +959,14 @@ int plan_conv_nchw(const void* in, const void* w, void* out, int N, int H, int W
   uint8_t* s_ws = s_w + L.w_bytes;
   // The conv the kernel runs: the NHWC form of the problem, or its few-channel form.
   ConvExtra ex{true, 0, 0, 0, 0};
-  int cH = H, cW = W, cCI = L.CIp, cKW = KW, cpad_h = pad_h, cpad_w = pad_w;
+  int cH = H, cW = W, cCI = L.CIp, cKW = KW, cpad_h = pad_h, cpad_w = pad_w, csh = sh, csw = sw;
+  if (L.subsample) { cH = L.HO; cW = L.WO; csh = 1; csw = 1; }
   if (L.stem) {
     const long long px = 16;  // bytes per stored pixel
     ex.w_stride = px; ex.h_stride = px * L.Ws; ex.n_stride = px * L.Ws * L.Hs;
     cH = L.Hs; cW = L.Wv; cCI = L.KWp * L.cis; cKW = 1; cpad_h = 0; cpad_w = 0;
   }
-  int rc = plan_conv(s_in, s_w, out, N, cH, cW, cCI, CO, KH, cKW, sh, sw, cpad_h, cpad_w, 1, 1, in_a, in_w,
+  int rc = plan_conv(s_in, s_w, out, N, cH, cW, cCI, CO, KH, cKW, csh, csw, cpad_h, cpad_w, 1, 1, in_a, in_w,
                      out_t, knobs, plan, &ex);
   if (rc != HB_OK) return rc;
   // A problem with far fewer tiles than SMs and a long reduction runs as split-K: every tile's K
@@ -991,7 +996,7 @@ int plan_conv_nchw(const void* in, const void* w, void* out, int N, int H, int W
     k0.split_k = 0;
     k0.tail_split = 1;
     if (k0.tile_n != 0 && out_t == HB_F16 && k0.tile_n % 64 != 0) k0.tile_n = 0;
-    rc = plan_conv(s_in, s_w, s_ws, N, cH, cW, cCI, CO, KH, cKW, sh, sw, cpad_h, cpad_w, 1, 1, in_a, in_w,
+    rc = plan_conv(s_in, s_w, s_ws, N, cH, cW, cCI, CO, KH, cKW, csh, csw, cpad_h, cpad_w, 1, 1, in_a, in_w,
                    acc_t, &k0, plan, &ex);
     if (rc != HB_OK) return rc;
     plan->has_post = true;
@@ -1016,13 +1021,15 @@ int plan_conv_nchw(const void* in, const void* w, void* out, int N, int H, int W
     plan->has_pre = true;
     return HB_OK;
   }
-  const int T = KH * KW, P = H * W;
+  const int T = KH * KW, P = L.subsample ? L.HO * L.WO : H * W;
   const int vec = 8 / es, tile = 16 * vec;
   hb::NchwPre& g = plan->pre;
   g.in = in; g.in_t = s_in; g.w = w; g.w_t = s_w;
   g.N = N; g.CI = CI; g.CIp = L.CIp; g.P = P; g.CO = CO; g.T = T;
+  g.sub_wo = 0; g.sub_col = 1; g.sub_row = 0; g.src_P = H * W;
+  if (L.subsample) { g.sub_wo = L.WO; g.sub_col = sw; g.sub_row = sh * W; }
   // 8-byte accesses need every image and channel row of the source to start on 8 bytes
-  g.vec = (P % vec == 0 && (reinterpret_cast<uintptr_t>(in) & 7u) == 0) ? 1 : 0;
+  g.vec = (!L.subsample && P % vec == 0 && (reinterpret_cast<uintptr_t>(in) & 7u) == 0) ? 1 : 0;
   g.in_bx = (P + tile - 1) / tile;
   g.in_by = (L.CIp + tile - 1) / tile;
   const long long in_blocks = static_cast<long long>(g.in_bx) * g.in_by * N;

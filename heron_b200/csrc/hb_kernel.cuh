@@ -620,6 +620,9 @@ struct NchwPre {
   const void* w; void* w_t;
   int N, CI, CIp, P, CO, T;
   int vec, f_vec;                   // 8-byte accesses are possible (input; 1-tap filter)
+  // strided 1x1 conv: only the pixels the conv reads are kept.  P counts kept pixels (HO*WO); kept
+  // pixel j sits at source pixel (j / sub_wo) * sub_row + (j % sub_wo) * sub_col.  sub_wo = 0: all.
+  int sub_wo, sub_col, sub_row, src_P;
   int in_bx, in_by, in_blocks;      // input tiles per image along P and along CIp; total
   int f_ci_tile, f_tchunk, f_bco, f_bci, f_bt;  // filter tiling (f_bco x f_bci tiles when T == 1)
 };
@@ -630,7 +633,8 @@ struct NchwPre {
 template <typename T, int PITCH>
 __device__ __forceinline__ void transpose_tile(T (*tile)[PITCH], const T* __restrict__ s, T* __restrict__ d,
                                                int R, int C, int Rp, int Cp, long long pitch, int i0,
-                                               int j0, bool vec) {
+                                               int j0, bool vec, int sub_wo = 0, int sub_col = 1,
+                                               int sub_row = 0) {
   constexpr int VEC = 8 / sizeof(T);
   constexpr int TILE = 16 * VEC;
   const int tid = threadIdx.x;
@@ -666,7 +670,12 @@ __device__ __forceinline__ void transpose_tile(T (*tile)[PITCH], const T* __rest
         const int idx = base + u * 256;
         const int ii = idx / TILE, jj = idx - ii * TILE;
         const int i = i0 + ii, j = j0 + jj;
-        v[u] = (i < R && j < C) ? s[i * pitch + j] : T(0);
+        long long col = j;
+        if (sub_wo > 0) {
+          const int jy = j / sub_wo;
+          col = static_cast<long long>(jy) * sub_row + (j - jy * sub_wo) * sub_col;
+        }
+        v[u] = (i < R && j < C) ? s[i * pitch + col] : T(0);
       }
 #pragma unroll
       for (int u = 0; u < 4; ++u) {
@@ -699,9 +708,11 @@ __global__ void __launch_bounds__(256) hb_nchw_pre_kernel(const NchwPre g) {
     const int bx = b % g.in_bx; b /= g.in_bx;   // along P
     const int by = b % g.in_by;                 // along CI
     const int n = b / g.in_by;
-    transpose_tile<T, PITCH>(tile, static_cast<const T*>(g.in) + static_cast<long long>(n) * g.CI * g.P,
+    const int src_P = g.sub_wo > 0 ? g.src_P : g.P;
+    transpose_tile<T, PITCH>(tile, static_cast<const T*>(g.in) + static_cast<long long>(n) * g.CI * src_P,
                              static_cast<T*>(g.in_t) + static_cast<long long>(n) * g.P * g.CIp, g.CI, g.P,
-                             g.CIp, g.P, g.P, by * TILE, bx * TILE, g.vec != 0);
+                             g.CIp, g.P, src_P, by * TILE, bx * TILE, g.vec != 0, g.sub_wo, g.sub_col,
+                             g.sub_row);
     return;
   }
   int b = blockIdx.x - g.in_blocks;

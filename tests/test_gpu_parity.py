@@ -672,6 +672,8 @@ NCHW_CASES = [
     (2, 64, 14, 14, 256, 1, 1, 1, 0),
     (2, 256, 14, 14, 128, 1, 1, 2, 0),
     (3, 16, 9, 11, 40, 3, 3, (2, 1), 1),
+    (2, 32, 9, 13, 48, 1, 1, (2, 3), 0),   # strided 1x1: the glue keeps only the pixels the conv reads
+    (1, 64, 28, 28, 32, 1, 1, 2, 0),
     # few input channels: the form where a whole filter row is one K block
     (2, 3, 30, 41, 32, 3, 3, 1, 1),
     (1, 1, 20, 20, 16, 5, 5, (1, 2), 2),
