@@ -12,8 +12,13 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 TARGET = os.path.join(HERE, "libheron_b200.so")
 SOURCES = [os.path.join(CSRC, "hb_api.cu")]
-DEPS = SOURCES + [os.path.join(CSRC, "hb_kernel.cuh"), os.path.join(CSRC, "hb_ptx.cuh"),
-                  os.path.join(HERE, os.pardir, "include", "heron_b200.h")]
+HEADER = os.path.join(HERE, os.pardir, "include", "heron_b200.h")
+
+
+def deps():
+    """Everything the one translation unit includes: all of csrc/ and the public header."""
+    return [os.path.join(CSRC, f) for f in sorted(os.listdir(CSRC)) if f.endswith((".cu", ".cuh"))] + [HEADER]
+
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
@@ -32,7 +37,7 @@ def is_stale():
     if not os.path.exists(TARGET):
         return True
     t = os.path.getmtime(TARGET)
-    return any(os.path.exists(d) and os.path.getmtime(d) > t for d in DEPS)
+    return any(os.path.exists(d) and os.path.getmtime(d) > t for d in deps())
 
 
 def build(force=False, verbose=False, extra_flags=()):
