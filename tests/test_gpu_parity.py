@@ -871,3 +871,29 @@ def test_conv_strip_random_geometry(K, co, N, H, W, CO, KH, KW, pad, dil, half_o
     od = np.float16 if half_out else np.float32
     got = k_conv(K, x, w, 1, pad, dil, out_dtype=od, knobs=dict(conv_algo=2))
     check(got, co.conv2d_nhwc_f16(x, w, 1, pad, dil, od), "strip %s" % ((N, H, W, CO, KH, KW, pad, dil),))
+
+
+@settings(max_examples=80, deadline=None, suppress_health_check=[HealthCheck.function_scoped_fixture])
+@given(N=st.integers(1, 4), CI=st.sampled_from([1, 3, 4, 8, 16, 24, 64, 72, 136]), H=st.integers(1, 24),
+       W=st.integers(1, 24), CO8=st.integers(1, 12), KH=st.integers(1, 7), KW=st.integers(1, 8),
+       sh=st.integers(1, 3), sw=st.integers(1, 3), pad=st.integers(0, 3), int8=st.booleans(),
+       half_out=st.booleans(), split_k=st.sampled_from([0, 0, 1, 3]), seed=st.integers(0, 2 ** 20))
+def test_conv_nchw_random_geometry(K, co, N, CI, H, W, CO8, KH, KW, sh, sw, pad, int8, half_out, split_k, seed):
+    """The NCHW operator over random geometries, so that every route it can take is hit: tensors
+    in place (1x1, 16-byte rows), the few-channel form, kept-pixel glue for strided 1x1, the tile
+    transposes with and without 8-byte accesses, the strip kernel, workspace split-K."""
+    if H + 2 * pad < KH or W + 2 * pad < KW:
+        return
+    rng = np.random.default_rng(seed)
+    CO = 8 * CO8 * (2 if int8 else 1)  # output rows of the filter matrix are 16-byte multiples
+    if int8:
+        x, w = rand_i8(rng, (N, CI, H, W), False), rand_i8(rng, (CO, CI, KH, KW), True)
+        od = None
+    else:
+        x = rng.standard_normal((N, CI, H, W)).astype(np.float16)
+        w = (rng.standard_normal((CO, CI, KH, KW)) / np.sqrt(CI * KH * KW)).astype(np.float16)
+        od = np.float16 if half_out else np.float32
+    want = co.conv2d_nchw(x, w, (sh, sw), pad, od)
+    out = poison(want.shape, _T[want.dtype])
+    K.conv2d_nchw(dev(x), dev(w), stride=(sh, sw), padding=pad, out=out, knobs=dict(split_k=split_k))
+    check(out, want, "nchw %s" % ((N, CI, H, W, CO, KH, KW, sh, sw, pad, int8, half_out, split_k),))
