@@ -544,7 +544,8 @@ hb_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       }
     }
     // every lane may have been the elected issuer of some store: each drains its own groups
-    if (p.epilogue) bulk_wait<0>();
+    // shared memory must outlive the stores' reads of it; their writes complete with the grid
+    if (p.epilogue) bulk_wait_read<0>();
     __syncwarp();
   }
 
