@@ -48,6 +48,9 @@ EXPORTED_SYMBOLS = (
     "hb_conv2d_nchw",
     "hb_plan_conv2d_nchw",
     "hb_gemv",
+    "hb_scan_scratch_bytes",
+    "hb_scan",
+    "hb_plan_scan",
     "hb_conv1d_ncw_scratch_bytes",
     "hb_conv1d_ncw",
     "hb_conv1d_nwc_packed",
@@ -182,6 +185,12 @@ def load():
     lib.hb_conv1d_ncw.argtypes = [c_void_p] * 3 + [c_int] * 7 + [c_int] * 3 + [c_void_p, c_size_t, kp, c_void_p]
     lib.hb_conv1d_nwc_packed.restype = c_int
     lib.hb_conv1d_nwc_packed.argtypes = [c_void_p] * 3 + [c_int] * 8 + [c_int, c_void_p, c_size_t, kp, c_void_p]
+    lib.hb_scan_scratch_bytes.restype = c_size_t
+    lib.hb_scan_scratch_bytes.argtypes = [c_int, c_int, c_int]
+    lib.hb_scan.restype = c_int
+    lib.hb_scan.argtypes = [c_void_p] * 2 + [c_int] * 3 + [c_int] * 2 + [c_void_p, c_size_t, kp, c_void_p]
+    lib.hb_plan_scan.restype = c_int
+    lib.hb_plan_scan.argtypes = [pp] + lib.hb_scan.argtypes[:-1]
     lib.hb_plan_gemv.restype = c_int
     lib.hb_plan_gemv.argtypes = [pp] + lib.hb_gemv.argtypes[:-1]
     lib.hb_plan_conv1d_ncw.restype = c_int

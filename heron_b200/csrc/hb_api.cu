@@ -101,6 +101,25 @@ int hb_plan_gemv(hb_plan** plan, const void* A, const void* x, void* out, int M,
   });
 }
 
+size_t hb_scan_scratch_bytes(int N, int K, hb_dtype in_a) {
+  if (N <= 0 || K <= 0) return 0;
+  return static_cast<size_t>(N) * K * (in_a == HB_F16 ? 2 : 1);
+}
+
+int hb_scan(const void* A, void* out, int M, int N, int K, hb_dtype in_a, hb_dtype out_t, void* scratch,
+            size_t scratch_bytes, const hb_knobs* knobs, void* stream) {
+  hb_plan plan;
+  const int rc = plan_scan(A, out, M, N, K, in_a, out_t, scratch, scratch_bytes, knobs, &plan);
+  return rc != HB_OK ? rc : run_plan(&plan, static_cast<cudaStream_t>(stream));
+}
+
+int hb_plan_scan(hb_plan** plan, const void* A, void* out, int M, int N, int K, hb_dtype in_a,
+                 hb_dtype out_t, void* scratch, size_t scratch_bytes, const hb_knobs* knobs) {
+  return new_plan(plan, [&](hb_plan* p) {
+    return plan_scan(A, out, M, N, K, in_a, out_t, scratch, scratch_bytes, knobs, p);
+  });
+}
+
 // 1-D convolutions: the 2-D kernels with H = KH = 1 and no padding along the height.
 size_t hb_conv1d_ncw_scratch_bytes(int N, int W, int CI, int CO, int KW, int stride, int pad,
                                    hb_dtype in_a, hb_dtype out_t) {

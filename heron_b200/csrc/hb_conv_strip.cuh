@@ -15,7 +15,7 @@
 // address, so a descriptor may start at any 128-byte row.  One tile = R = floor(128 / Wp) output
 // rows of one image = one 128-row MMA per (tap, 32 bytes of channels).
 //
-// Roles as in hb_umma_kernel: warp 0 loads (filter once, then strips into a ring of two to four buffers),
+// Roles as in hb_umma_kernel: warp 0 loads (filter once, then strips into a ring of two to six buffers),
 // warp 1 issues MMAs into one of two TMEM accumulators, warps 2..5 read the accumulator and store
 // the valid positions straight to global memory (each thread owns one output pixel: CO
 // contiguous elements).  All waits are bounded, with the same abort protocol.
@@ -23,6 +23,8 @@
 #include "hb_kernel.cuh"
 
 namespace hb {
+
+constexpr int kMaxStripRing = 6;
 
 struct StripParams {
   int N, H, W, CI, CO, KH, KW, pad_h, pad_w, dil_h, dil_w, HO, WO;
@@ -35,7 +37,7 @@ struct StripParams {
   int num_tiles;
   int esize_in, esize_out;
   int tmem_cols;
-  int ring;   // strip buffers in flight (2..4)
+  int ring;   // strip buffers in flight (2..kMaxStripRing)
   long long wait_limit_cycles;
   int probe;  // diagnostic: 2 = no MMAs, 3 = epilogue only hands the accumulator back, 4 = strips loaded once
   uint32_t idesc;
@@ -45,8 +47,8 @@ struct StripParams {
 
 struct StripBars {
   uint64_t filt_full;
-  uint64_t strip_full[4];
-  uint64_t strip_empty[4];
+  uint64_t strip_full[kMaxStripRing];
+  uint64_t strip_empty[kMaxStripRing];
   uint64_t tmem_full[2];
   uint64_t tmem_empty[2];
   uint64_t drain;

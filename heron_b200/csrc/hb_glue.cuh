@@ -33,6 +33,18 @@ __global__ void hb_zero_tiles_kernel(const KParams p, int tile_rows, int row_gro
   }
 }
 
+// The constant operand of the reference's scan operator: B[i][j] = (i <= j) ? 0 : 1, an (N, K)
+// matrix whose product with A gives out[m][n] = sum of A[m][k] over k < n.
+template <typename T>
+__global__ void hb_scan_mask_kernel(T* __restrict__ b, int N, int K, T one) {
+  const long long total = static_cast<long long>(N) * K;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int row = static_cast<int>(i / K), col = static_cast<int>(i - static_cast<long long>(row) * K);
+    b[i] = row <= col ? T(0) : one;
+  }
+}
+
 // Unpacks the x86 operator's int8 filter (CO/sco, KH, KW, CI/4, sco, 4) to HWIO (KH,KW,CI,CO).
 // One thread per 4-byte group of input channels; consecutive threads walk output channels so
 // that the HWIO writes of a warp land in consecutive bytes of four rows.

@@ -323,6 +323,9 @@ struct hb_plan {
   const void* post_ws; void* post_out;
   int post_slabs, post_P, post_CO, post_N, post_kind;  // kind 0: float -> half, 1: float -> float, 2: int32
   long long post_slab_elems;
+  // scan only: the kernel that writes the constant triangular operand first
+  void* scan_b;
+  int scan_N, scan_K, scan_es, scan_blocks;
   // packed-filter conv only: the unpack kernel that runs first on the same stream
   const void* packed_w;
   void* scratch;

@@ -247,6 +247,15 @@ int run_plan(const hb_plan* plan, cudaStream_t stream) {
 }
 
 int run_main(const hb_plan* plan, cudaStream_t stream) {
+  if (plan->scan_b) {
+    if (plan->scan_es == 2)
+      hb::hb_scan_mask_kernel<uint16_t><<<plan->scan_blocks, 256, 0, stream>>>(
+          static_cast<uint16_t*>(plan->scan_b), plan->scan_N, plan->scan_K, static_cast<uint16_t>(0x3C00));
+    else
+      hb::hb_scan_mask_kernel<int8_t><<<plan->scan_blocks, 256, 0, stream>>>(
+          static_cast<int8_t*>(plan->scan_b), plan->scan_N, plan->scan_K, static_cast<int8_t>(1));
+    if (cudaGetLastError() != cudaSuccess) return HB_ERR_LAUNCH;
+  }
   if (plan->packed_w) {
     hb::hb_unpack_filter_kernel<<<plan->unpack_blocks, 256, 0, stream>>>(
         static_cast<const int8_t*>(plan->packed_w), static_cast<int8_t*>(plan->scratch), plan->p.N,
@@ -312,6 +321,26 @@ int plan_gemm_like(int op, const void* A, const void* B, void* C, int batch, int
   hb_knobs k;
   resolve_knobs(pr, knobs, d.sm_count, &k);
   return build_plan(d, pr, k, nullptr, A, B, C, plan);
+}
+
+// scan (ops/cuda/scan.py:4-23, ops/x86/scan.py:6-27): a GEMM of A (M, K) with the constant (N, K)
+// matrix B[i][j] = (i <= j) ? 0 : 1, written into the caller's scratch by a kernel of the plan.
+// The tensor-core form takes fp16, the x86 form uint8 A with an int8 B.
+int plan_scan(const void* A, void* out, int M, int N, int K, hb_dtype in_a, hb_dtype out_t, void* scratch,
+              size_t scratch_bytes, const hb_knobs* knobs, hb_plan* plan) {
+  if (M <= 0 || N <= 0 || K <= 0) return HB_ERR_SHAPE;
+  const hb_dtype in_b = in_a == HB_F16 ? HB_F16 : HB_S8;
+  const int es = esize(in_b);
+  const size_t need = static_cast<size_t>(N) * K * es;
+  if (!scratch || scratch_bytes < need) return HB_ERR_SCRATCH;
+  const int rc = plan_gemm_like(0, A, scratch, out, 1, M, K, N, in_a, in_b, out_t, knobs, plan);
+  if (rc != HB_OK) return rc;
+  plan->scan_b = scratch;
+  plan->scan_N = N; plan->scan_K = K; plan->scan_es = es;
+  long long blocks = (static_cast<long long>(N) * K + 255) / 256;
+  const long long cap = static_cast<long long>(driver().sm_count) * 8;
+  plan->scan_blocks = static_cast<int>(blocks < cap ? blocks : cap);
+  return HB_OK;
 }
 
 template <class BuildFn>

@@ -31,7 +31,7 @@ int strip_smem_bytes(const ConvGeom& g, int es, int eo, hb::StripParams* sp) {
   long long smem = ((filt + 1023) & ~1023LL) + 2LL * n_cchunks * strip_bytes + 1024 + 256;
   if (smem > kSmemLimit) return 0;
   int ring = 2;  // deeper when shared memory allows: more strips in flight hide HBM latency
-  while (ring < 4 && smem + static_cast<long long>(n_cchunks) * strip_bytes <= kSmemLimit) {
+  while (ring < hb::kMaxStripRing && smem + static_cast<long long>(n_cchunks) * strip_bytes <= kSmemLimit) {
     smem += static_cast<long long>(n_cchunks) * strip_bytes;
     ++ring;
   }

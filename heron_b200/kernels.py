@@ -397,3 +397,31 @@ def plan_conv1d_nwc_packed(x, w_packed, CO, KW, stride=1, padding=0, dilation=1,
                                                scratch.numel(), _knobs(knobs))
     _lib.check(rc, "hb_plan_conv1d_nwc_packed")
     return Plan(h, (x, w_packed, scratch), out)
+
+
+def _scan_args(a, N, out, out_dtype, scratch):
+    M, K = a.shape
+    if out is None:
+        out = torch.empty((M, N), dtype=out_dtype or default_out_dtype(a.dtype), device=a.device)
+    if scratch is None:
+        scratch = torch.empty(_lib.load().hb_scan_scratch_bytes(N, K, _code(a)), dtype=torch.uint8, device=a.device)
+    return M, K, out, scratch
+
+
+def scan(a, N, out=None, out_dtype=None, scratch=None, knobs=None):
+    """out[m,n] = sum of a[m,k] over k < min(n, K): the reference's scan operator, a GEMM with the
+    constant matrix B[n,k] = (n <= k) ? 0 : 1 (ops/cuda/scan.py:6-23)."""
+    M, K, out, scratch = _scan_args(a, N, out, out_dtype, scratch)
+    rc = _lib.load().hb_scan(_dev(a, "a"), _dev(out, "out"), M, N, K, _code(a), _code(out),
+                             _dev(scratch, "scratch"), scratch.numel(), _knobs(knobs), _stream(a))
+    _lib.check(rc, "hb_scan")
+    return out
+
+
+def plan_scan(a, N, out=None, out_dtype=None, scratch=None, knobs=None):
+    M, K, out, scratch = _scan_args(a, N, out, out_dtype, scratch)
+    h = ctypes.c_void_p()
+    rc = _lib.load().hb_plan_scan(ctypes.byref(h), _dev(a, "a"), _dev(out, "out"), M, N, K, _code(a),
+                                  _code(out), _dev(scratch, "scratch"), scratch.numel(), _knobs(knobs))
+    _lib.check(rc, "hb_plan_scan")
+    return Plan(h, (a, scratch), out)

@@ -5,6 +5,7 @@ from .conv2d_int8 import heron_conv2d_nhwc
 from .dense import heron_dense
 from .dil import heron_dil_nhwc
 from .gemv import heron_gemv
+from .scan import heron_scan
 
 _OPMAP = {
     "gemm": heron_dense,
@@ -13,9 +14,10 @@ _OPMAP = {
     "bmm": heron_batch_matmul,
     "c2d": heron_conv2d_nhwc,
     "dil": heron_dil_nhwc,
+    "scan": heron_scan,
 }
 
-_NOT_BUILT = ("c3d", "t2d", "scan")
+_NOT_BUILT = ("c3d", "t2d")
 
 
 def getOpFromName(name):

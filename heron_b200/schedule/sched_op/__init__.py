@@ -31,7 +31,7 @@ def _problem(s, stage_name):
 def _gemm_view(out):
     """(batch, M, N, K, k_inner) of the operator's implicit GEMM."""
     p = out.op.params
-    if out.op.kind == "gemm":
+    if out.op.kind in ("gemm", "scan"):
         return 1, p["M"], p["N"], p["K"], p["K"]
     if out.op.kind == "bmm":
         return p["batch"], p["M"], p["N"], p["K"], p["K"]

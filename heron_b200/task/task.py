@@ -53,6 +53,10 @@ class KernelHandle:
             fn = K.plan_conv2d_nhwc_packed if planned else K.conv2d_nhwc_packed
             return fn(x, w, p["CO"], p["KH"], p["KW"], stride=p["stride"], padding=p["padding"],
                       dilation=p["dilation"], sco=p["sco"], out=out, knobs=knobs)
+        if kind == "scan":
+            a, out = tensors
+            fn = K.plan_scan if planned else K.scan
+            return fn(a, p["N"], out=out, knobs=knobs)
         if kind == "gemv":
             a, x, out = tensors
             fn = K.plan_gemv if planned else K.gemv

@@ -195,9 +195,18 @@ int hb_conv2d_nchw(const void* in, const void* w, void* out, int N, int H, int W
  * (CO/sco, KW, CI/4, sco, 4), `out` int32 (N, WO, CO/sco, sco), WO from the dilated kernel size.
  * Runs as hb_conv2d_nhwc_packed with H = KH = 1; scratch of hb_conv2d_packed_scratch_bytes(CI, CO,
  * 1, KW) bytes.
+ *
+ * hb_scan: ops/cuda/scan.py:4-23 and ops/x86/scan.py:6-27.  out[m,n] = sum_k A[m,k] * B[n,k] with
+ * the constant B[n,k] = (n <= k) ? 0 : 1, i.e. out[m,n] = sum of A[m,k] over k < min(n, K): an
+ * exclusive running sum written as a GEMM.  `A` (M,K) fp16, or uint8 for the x86 form (B is then
+ * int8); `out` (M,N).  A kernel of the plan writes B into `scratch`
+ * (hb_scan_scratch_bytes(N, K, in_a) bytes, 16-byte aligned) before the GEMM kernel reads it.
  */
 int hb_gemv(const void* A, const void* x, void* out, int M, int K, hb_dtype in_a, hb_dtype in_x,
             hb_dtype out_t, const hb_knobs* knobs, void* stream);
+size_t hb_scan_scratch_bytes(int N, int K, hb_dtype in_a);
+int hb_scan(const void* A, void* out, int M, int N, int K, hb_dtype in_a, hb_dtype out_t, void* scratch,
+            size_t scratch_bytes, const hb_knobs* knobs, void* stream);
 size_t hb_conv1d_ncw_scratch_bytes(int N, int W, int CI, int CO, int KW, int stride, int pad,
                                    hb_dtype in_a, hb_dtype out_t);
 int hb_conv1d_ncw(const void* in, const void* w, void* out, int N, int W, int CI, int CO, int KW,
@@ -260,6 +269,8 @@ int hb_plan_conv2d_nchw(hb_plan** plan, const void* in, const void* w, void* out
                         int W, int CI, int CO, int KH, int KW, int stride_h, int stride_w, int pad,
                         hb_dtype in_a, hb_dtype in_w, hb_dtype out_t, void* scratch,
                         size_t scratch_bytes, const hb_knobs* knobs);
+int hb_plan_scan(hb_plan** plan, const void* A, void* out, int M, int N, int K, hb_dtype in_a,
+                 hb_dtype out_t, void* scratch, size_t scratch_bytes, const hb_knobs* knobs);
 int hb_plan_gemv(hb_plan** plan, const void* A, const void* x, void* out, int M, int K,
                  hb_dtype in_a, hb_dtype in_x, hb_dtype out_t, const hb_knobs* knobs);
 int hb_plan_conv1d_ncw(hb_plan** plan, const void* in, const void* w, void* out, int N, int W,

@@ -186,3 +186,16 @@ def conv1d_nwc_packed(x, w_packed, stride=1, pad=0, dilation=1):
     lib().oracle_conv1d_nwc_packed(_p(x), _p(w_packed), _p(out), N, W, CI, OC * sco, KW, stride, pad,
                                    dilation, sco)
     return out
+
+
+def scan(a, N, out_dtype=None):
+    a = _c(a)
+    M, K = a.shape
+    if a.dtype == np.float16:
+        half = out_dtype is not None and np.dtype(out_dtype) == np.float16
+        out = np.empty((M, N), dtype=np.float16 if half else np.float32)
+        lib().oracle_scan(_p(a), _p(out), M, N, K, 2 if half else 1, 0)
+    else:
+        out = np.empty((M, N), dtype=np.int32)
+        lib().oracle_scan(_p(a), _p(out), M, N, K, 0, _signed(a))
+    return out

@@ -370,3 +370,25 @@ void oracle_conv1d_nwc_packed(const uint8_t* in, const int8_t* wp, int32_t* out,
           out[(((size_t)n * WO + x) * OC + oc) * sco + ob] = acc;
         }
 }
+
+/*
+ * scan, ops/cuda/scan.py:6-23 and ops/x86/scan.py:11-27: out[i,j] = sum_k A[i,k] * B[j,k] with the
+ * constant B[j,k] = (j <= k) ? 0 : 1.  `mode` 0: uint8/int8 A, int32 output; 1: binary16 A, float
+ * output; 2: binary16 output.
+ */
+void oracle_scan(const void* A, void* out, int M, int N, int K, int mode, int a_signed) {
+  for (int i = 0; i < M; ++i)
+    for (int j = 0; j < N; ++j) {
+      int32_t iacc = 0;
+      double dacc = 0.0;
+      for (int k = 0; k < K; ++k) {
+        const int b = (j <= k) ? 0 : 1;
+        if (mode == 0) iacc += load_i8(A, (size_t)i * K + k, a_signed) * b;
+        else dacc += (double)half_to_float(((const uint16_t*)A)[(size_t)i * K + k]) * (double)b;
+      }
+      const size_t o = (size_t)i * N + j;
+      if (mode == 0) ((int32_t*)out)[o] = iacc;
+      else if (mode == 1) ((float*)out)[o] = (float)dacc;
+      else ((uint16_t*)out)[o] = float_to_half_rn((float)dacc);
+    }
+}

@@ -198,3 +198,14 @@ def conv1d_nwc_packed(x, w_packed, stride=1, pad=0, dilation=1):
     xp[:, 0, pad:pad + W] = x
     out = conv2d_nhwc_packed(xp, w_packed[:, None], (1, stride), 0, (1, dilation))
     return out[:, 0]
+
+
+def scan(a, N, out_dtype=None):
+    """The reference's scan as it is written there: a product with the constant (N, K) matrix
+    B[i, j] = 0 if i <= j else 1 (ops/cuda/scan.py:6-23)."""
+    M, K = a.shape
+    b = (np.arange(N)[:, None] > np.arange(K)[None, :])
+    if a.dtype == np.float16:
+        out = (a.astype(np.float64) @ b.astype(np.float64).T).astype(np.float32)
+        return out.astype(np.float16) if out_dtype is not None and np.dtype(out_dtype) == np.float16 else out
+    return _to_i32(_as_i64(a) @ b.astype(np.int64).T)

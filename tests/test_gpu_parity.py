@@ -391,6 +391,30 @@ def test_gemv_both_forms(K, co, M, Kd):
     check(out, co.gemm_int(a1, b1), "x86 gemv")
 
 
+@pytest.mark.parametrize("M,N,Kd", [(16, 512, 128), (1024, 16, 256), (256, 1024, 256), (512, 256, 16), (100, 72, 48)])
+def test_scan_both_forms(K, co, M, N, Kd):
+    """The reference's scan cases (S5 shortened to a ragged one): the constant triangular operand is
+    written by a kernel of the plan, then the GEMM kernel runs."""
+    from heron_b200.ops import cuda as heron_cuda, x86 as heron_cpu
+    rng = np.random.default_rng(M + N + Kd)
+    a = (rng.standard_normal((M, Kd)) / np.sqrt(Kd)).astype(np.float16)
+    for od in (np.float32, np.float16):
+        t = _task(heron_cuda, "scan", [M, N, Kd, "float16", np.dtype(od).name], "GPU_TENSOR_CORE")
+        t.knob_manager.randSample()
+        handle, args = t.instantiate(t.knob_manager)
+        assert [tuple(x.shape) for x in args] == [(M, Kd), (M, N)]
+        out = poison((M, N), _T[np.dtype(od)])
+        handle(dev(a), out)
+        check(out, co.scan(a, N, od), "scan fp16 -> %s %s" % (np.dtype(od).name, handle.knobs))
+    t = _task(heron_cpu, "scan", [M, N, Kd, "int8", "int32"], "CPU")
+    t.knob_manager.randSample()
+    handle, args = t.instantiate(t.knob_manager)
+    ai = rand_i8(rng, (M, Kd), False)
+    out = poison((M, N), torch.int32)
+    plan = handle.plan(dev(ai), out)
+    check(plan.launch(), co.scan(ai, N), "x86 scan %s" % (handle.knobs,))
+
+
 @pytest.mark.parametrize("case", [(16, 892, 64, 128, 3, 1, 4), (4, 100, 512, 512, 3, 1, 32), (8, 77, 48, 64, 1, 1, 0),
                                   (2, 200, 3, 32, 7, 2, 3), (16, 223, 128, 256, 1, 2, 0)])
 def test_conv1d_ncw(K, co, case):

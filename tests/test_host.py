@@ -38,6 +38,8 @@ def test_registry_names_and_signatures():
     assert heron_cuda.getOpFromName("gemv").__name__ == "heron_gemv"
     assert heron_cpu.getOpFromName("gemv").__name__ == "heron_gemv"
     assert heron_cuda.getOpFromName("c1d").__name__ == "heron_conv1d_ncw_tensorcore"
+    assert heron_cuda.getOpFromName("scan").__name__ == "heron_scan"
+    assert heron_cpu.getOpFromName("scan").__name__ == "heron_scan"
     assert heron_cpu.getOpFromName("c1d").__name__ == "heron_conv1d_nwc"
     with pytest.raises(NotImplementedError):
         heron_cuda.getOpFromName("t2d")

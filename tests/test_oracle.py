@@ -192,6 +192,17 @@ def test_neighbour_operators_c_vs_numpy(co):
     xh = rng.standard_normal((1, 32)).astype(np.float16)
     assert np.array_equal(co.gemv(ah, xh), npo.gemv(ah, xh))
     assert np.array_equal(co.gemv(ah, xh, np.float16), npo.gemv(ah, xh, np.float16))
+    # scan: the product with the constant triangle is an exclusive running sum
+    a = rng.integers(0, 256, (9, 40), dtype=np.uint8)
+    for N in (1, 17, 40, 55):
+        got = co.scan(a, N)
+        assert np.array_equal(got, npo.scan(a, N))
+        run = np.concatenate([np.zeros((9, 1), np.int64), np.cumsum(a.astype(np.int64), axis=1)], axis=1)
+        want = run[:, np.minimum(np.arange(N), 40)]
+        assert np.array_equal(got, want)
+    ah = rng.standard_normal((6, 24)).astype(np.float16)
+    assert np.array_equal(co.scan(ah, 30), npo.scan(ah, 30))
+    assert np.array_equal(co.scan(ah, 30, np.float16), npo.scan(ah, 30, np.float16))
     for (N, W, CI, CO, KW, s, p) in [(2, 19, 16, 24, 3, 1, 4), (3, 30, 8, 16, 1, 2, 0), (1, 12, 4, 8, 5, 3, 2)]:
         xi = rng.integers(-128, 128, (N, CI, W)).astype(np.int8)
         wi = rng.integers(-128, 128, (CO, CI, KW)).astype(np.int8)
