@@ -1,7 +1,8 @@
 """The tensor-core operator registry (ops/cuda/__init__.py:15-32): the hot path (gemm, bmm, c2d_nhwc)
-and the operators next to it that run on the same kernels (c2d, dil, c1d, gemv, scan)."""
+and the operators next to it that run on the same kernels (c2d, dil, c1d, gemv, scan, t2d at stride 1)."""
 from .batch_matmul import heron_batch_matmul
 from .conv1d import heron_conv1d_ncw_tensorcore
+from .conv2d_transposed import heron_conv2d_nchw_transposed_tensorcore
 from .conv2d import heron_conv2d_nchw_tensorcore, heron_conv2d_nhwc_tensorcore
 from .dense import heron_dense
 from .dil import heron_dil_tensorcore
@@ -17,10 +18,11 @@ _OPMAP = {
     "c2d_nhwc": heron_conv2d_nhwc_tensorcore,
     "dil": heron_dil_tensorcore,
     "scan": heron_scan,
+    "t2d": heron_conv2d_nchw_transposed_tensorcore,
 }
 
 # Names the reference registers that have no B200 kernel here.
-_NOT_BUILT = ("c3d", "t2d", "mean", "var", "dep")
+_NOT_BUILT = ("c3d", "mean", "var", "dep")
 
 
 def getOpFromName(name):

@@ -6,6 +6,7 @@ from .dense import heron_dense
 from .dil import heron_dil_nhwc
 from .gemv import heron_gemv
 from .scan import heron_scan
+from .t2d import heron_conv2d_transposed_nhwc
 
 _OPMAP = {
     "gemm": heron_dense,
@@ -15,9 +16,10 @@ _OPMAP = {
     "c2d": heron_conv2d_nhwc,
     "dil": heron_dil_nhwc,
     "scan": heron_scan,
+    "t2d": heron_conv2d_transposed_nhwc,
 }
 
-_NOT_BUILT = ("c3d", "t2d")
+_NOT_BUILT = ("c3d",)
 
 
 def getOpFromName(name):

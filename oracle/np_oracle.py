@@ -209,3 +209,28 @@ def scan(a, N, out_dtype=None):
         out = (a.astype(np.float64) @ b.astype(np.float64).T).astype(np.float32)
         return out.astype(np.float16) if out_dtype is not None and np.dtype(out_dtype) == np.float16 else out
     return _to_i32(_as_i64(a) @ b.astype(np.int64).T)
+
+
+def t2d_nchw_stride1(x, w, padding, out_dtype=None):
+    """The reference's "transposed" NCHW conv for stride 1, staged as it stages it
+    (ops/cuda/conv2d_transposed.py:82-135): pad the input by K-1-padding zeros on every side, build
+    A[N*H_O*W_O, CI*KH*KW] with A[i, (ci,kh,kw)] = Padded[n, ci, p+kh, q+kw], B[CO, CI*KH*KW] from
+    the filter as stored, C = B . A^T, output[n, c, p, q] = C[c, n*H_O*W_O + p*W_O + q]."""
+    N, CI, H, W = x.shape
+    CO, _, KH, KW = w.shape
+    ph, pw = KH - 1 - padding, KW - 1 - padding
+    HO, WO = H - 2 * padding + KH - 1, W - 2 * padding + KW - 1
+    xp = np.zeros((N, CI, H + 2 * ph, W + 2 * pw), dtype=x.dtype)
+    xp[:, :, ph:ph + H, pw:pw + W] = x
+    A = np.empty((N, HO, WO, CI, KH, KW), dtype=x.dtype)
+    for kh in range(KH):
+        for kw in range(KW):
+            A[:, :, :, :, kh, kw] = xp[:, :, kh:kh + HO, kw:kw + WO].transpose(0, 2, 3, 1)
+    A = A.reshape(N * HO * WO, CI * KH * KW)
+    B = w.reshape(CO, CI * KH * KW)
+    if x.dtype == np.float16:
+        C = (B.astype(np.float64) @ A.astype(np.float64).T).astype(np.float32)
+    else:
+        C = _to_i32(_as_i64(B) @ _as_i64(A).T)
+    out = np.ascontiguousarray(C.reshape(CO, N, HO, WO).transpose(1, 0, 2, 3))
+    return out.astype(np.float16) if out_dtype is not None and np.dtype(out_dtype) == np.float16 else out

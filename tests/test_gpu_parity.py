@@ -785,6 +785,25 @@ def test_conv_nchw_small_output_long_reduction_splits_k(K, co, case):
           "nchw int8 split-K 3 %s" % (case,))
 
 
+@pytest.mark.parametrize("case", [(4, 28, 28, 64, 64, 3, 3, 1, 1, 1, 0), (2, 14, 14, 256, 128, 3, 3, 1, 0, 1, 0),
+                                  (3, 16, 16, 32, 48, 1, 1, 1, 0, 1, 0)])
+def test_t2d_stride1_through_the_registry(K, co, case):
+    """The reference's "transposed" conv at stride 1 against its own staging restated in numpy."""
+    from heron_b200.ops import cuda as heron_cuda
+    N, H, W, CI, CO, KH, KW, s, p, d, op_ = case
+    t = _task(heron_cuda, "t2d", list(case) + ["float16", "float16"], "GPU_TENSOR_CORE")
+    t.knob_manager.randSample()
+    handle, args = t.instantiate(t.knob_manager)
+    rng = np.random.default_rng(sum(case))
+    x = rng.standard_normal((N, CI, H, W)).astype(np.float16)
+    w = (rng.standard_normal((CO, CI, KH, KW)) / np.sqrt(CI * KH * KW)).astype(np.float16)
+    want = npo.t2d_nchw_stride1(x, w, p, np.float16)
+    assert tuple(args[-1].shape) == want.shape
+    out = poison(want.shape, torch.float16)
+    handle(dev(x), dev(w), out)
+    check(out, want, "t2d %s" % (case,))
+
+
 def test_conv_nchw_through_the_registry(K, co):
     """`c2d` of the tensor-core registry, with a ResNet-50 table row scaled down in batch."""
     from heron_b200.ops import cuda as heron_cuda

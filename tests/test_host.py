@@ -41,10 +41,26 @@ def test_registry_names_and_signatures():
     assert heron_cuda.getOpFromName("scan").__name__ == "heron_scan"
     assert heron_cpu.getOpFromName("scan").__name__ == "heron_scan"
     assert heron_cpu.getOpFromName("c1d").__name__ == "heron_conv1d_nwc"
+    assert heron_cuda.getOpFromName("t2d").__name__ == "heron_conv2d_nchw_transposed_tensorcore"
+    assert heron_cpu.getOpFromName("t2d").__name__ == "heron_conv2d_transposed_nhwc"
     with pytest.raises(NotImplementedError):
-        heron_cuda.getOpFromName("t2d")
+        heron_cuda.getOpFromName("c3d")
     with pytest.raises(KeyError):
         heron_cuda.getOpFromName("nonsense")
+
+
+def test_t2d_refuses_the_strides_the_reference_leaves_undefined():
+    ctx = _Ctx()
+    (out,) = heron_cuda.getOpFromName("t2d")(ctx, 16, 56, 56, 64, 64, 3, 3, 1, 1, 1, 0, "float16", "float16")
+    assert out.shape == (16, 64, 56, 56) and out.op.params["padding"] == 1
+    (out,) = heron_cuda.getOpFromName("t2d")(ctx, 16, 14, 14, 256, 512, 3, 3, 1, 0, 1, 0, "float16", "float16")
+    assert out.shape == (16, 512, 16, 16) and out.op.params["padding"] == 2
+    with pytest.raises(NotImplementedError):
+        heron_cuda.getOpFromName("t2d")(ctx, 16, 56, 56, 64, 128, 1, 1, 2, 0, 1, 0, "float16", "float16")
+    with pytest.raises(NotImplementedError):
+        heron_cpu.getOpFromName("t2d")(ctx, 1, 56, 56, 64, 128, 1, 1, 2, 0, 1, 0, "OhwI64o4i", "uint8", "int32")
+    (out,) = heron_cpu.getOpFromName("t2d")(ctx, 1, 14, 14, 64, 64, 3, 3, 1, 1, 2, 0, "OhwI64o4i", "uint8", "int32")
+    assert out.op.params["padding"] == 3 and out.shape == (1, 16, 16, 1, 64)
 
 
 def test_gemm_op_layout_and_hints():

@@ -179,6 +179,18 @@ def test_nchw_operator_three_ways(co):
             assert np.array_equal(npo.conv2d_nchw_f16(xf, wf, s, p, od), co.conv2d_nchw(xf, wf, s, p, od))
 
 
+def test_t2d_stride1_is_the_padded_conv(co):
+    """The reference's transposed-conv expression at stride 1, staged as it stages it, against the
+    C conv loops with padding K-1-p."""
+    rng = np.random.default_rng(77)
+    for (N, CI, H, W, CO, K, p) in [(2, 8, 6, 7, 16, 3, 1), (1, 4, 5, 5, 8, 3, 0), (2, 16, 9, 4, 8, 1, 0), (1, 8, 6, 6, 8, 5, 2)]:
+        x = rng.integers(-128, 128, (N, CI, H, W)).astype(np.int8)
+        w = rng.integers(-128, 128, (CO, CI, K, K)).astype(np.int8)
+        want = npo.t2d_nchw_stride1(x, w, p)
+        assert want.shape == (N, CO, H - 2 * p + K - 1, W - 2 * p + K - 1)
+        assert np.array_equal(co.conv2d_nchw(x, w, 1, K - 1 - p), want)
+
+
 def test_neighbour_operators_c_vs_numpy(co):
     """gemv and the two 1-D convolutions: the scalar C loops against the numpy restatement of the
     reference's own lowering (padded vector, explicit im2col, packed filter)."""
