@@ -49,6 +49,9 @@ EXPORTED_SYMBOLS = (
     "hb_plan_conv2d_nchw",
     "hb_gemv",
     "hb_scan_scratch_bytes",
+    "hb_conv3d_ncdhw_scratch_bytes",
+    "hb_conv3d_ncdhw",
+    "hb_plan_conv3d_ncdhw",
     "hb_scan",
     "hb_plan_scan",
     "hb_conv1d_ncw_scratch_bytes",
@@ -185,6 +188,12 @@ def load():
     lib.hb_conv1d_ncw.argtypes = [c_void_p] * 3 + [c_int] * 7 + [c_int] * 3 + [c_void_p, c_size_t, kp, c_void_p]
     lib.hb_conv1d_nwc_packed.restype = c_int
     lib.hb_conv1d_nwc_packed.argtypes = [c_void_p] * 3 + [c_int] * 8 + [c_int, c_void_p, c_size_t, kp, c_void_p]
+    lib.hb_conv3d_ncdhw_scratch_bytes.restype = c_size_t
+    lib.hb_conv3d_ncdhw_scratch_bytes.argtypes = [c_int] * 13 + [c_int, c_int]
+    lib.hb_conv3d_ncdhw.restype = c_int
+    lib.hb_conv3d_ncdhw.argtypes = [c_void_p] * 3 + [c_int] * 13 + [c_int] * 3 + [c_void_p, c_size_t, kp, c_void_p]
+    lib.hb_plan_conv3d_ncdhw.restype = c_int
+    lib.hb_plan_conv3d_ncdhw.argtypes = [pp] + lib.hb_conv3d_ncdhw.argtypes[:-1]
     lib.hb_scan_scratch_bytes.restype = c_size_t
     lib.hb_scan_scratch_bytes.argtypes = [c_int, c_int, c_int]
     lib.hb_scan.restype = c_int

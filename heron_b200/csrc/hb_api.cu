@@ -101,6 +101,35 @@ int hb_plan_gemv(hb_plan** plan, const void* A, const void* x, void* out, int M,
   });
 }
 
+// 3-D convolution, NCDHW: the NCHW machinery with a depth axis (5-D im2col loads in the kernel).
+size_t hb_conv3d_ncdhw_scratch_bytes(int N, int D, int H, int W, int CI, int CO, int KD, int KH, int KW,
+                                     int stride_d, int stride_h, int stride_w, int pad, hb_dtype in_a,
+                                     hb_dtype out_t) {
+  NchwLayout L;
+  return nchw_layout(N, H, W, CI, CO, KH, KW, stride_h, stride_w, pad, pad, in_a, out_t, &L,
+                     Depth{D, KD, stride_d, pad}) ? L.total : 0;
+}
+
+int hb_conv3d_ncdhw(const void* in, const void* w, void* out, int N, int D, int H, int W, int CI, int CO,
+                    int KD, int KH, int KW, int stride_d, int stride_h, int stride_w, int pad,
+                    hb_dtype in_a, hb_dtype in_w, hb_dtype out_t, void* scratch, size_t scratch_bytes,
+                    const hb_knobs* knobs, void* stream) {
+  hb_plan plan;
+  const int rc = plan_conv_nchw(in, w, out, N, H, W, CI, CO, KH, KW, stride_h, stride_w, pad, pad, in_a, in_w,
+                                out_t, scratch, scratch_bytes, knobs, &plan, Depth{D, KD, stride_d, pad});
+  return rc != HB_OK ? rc : run_plan(&plan, static_cast<cudaStream_t>(stream));
+}
+
+int hb_plan_conv3d_ncdhw(hb_plan** plan, const void* in, const void* w, void* out, int N, int D, int H,
+                         int W, int CI, int CO, int KD, int KH, int KW, int stride_d, int stride_h,
+                         int stride_w, int pad, hb_dtype in_a, hb_dtype in_w, hb_dtype out_t,
+                         void* scratch, size_t scratch_bytes, const hb_knobs* knobs) {
+  return new_plan(plan, [&](hb_plan* p) {
+    return plan_conv_nchw(in, w, out, N, H, W, CI, CO, KH, KW, stride_h, stride_w, pad, pad, in_a, in_w, out_t,
+                          scratch, scratch_bytes, knobs, p, Depth{D, KD, stride_d, pad});
+  });
+}
+
 size_t hb_scan_scratch_bytes(int N, int K, hb_dtype in_a) {
   if (N <= 0 || K <= 0) return 0;
   return static_cast<size_t>(N) * K * (in_a == HB_F16 ? 2 : 1);

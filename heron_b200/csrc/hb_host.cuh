@@ -297,7 +297,12 @@ struct ConvGeom {
   // byte strides of the input's W, H and N axes when it is not a dense NHWC tensor (0: dense)
   long long w_stride, h_stride, n_stride;
   int kslab;  // > 1: split-K into that many workspace slabs (see KParams::kslab)
+  // 3-D convolution (see is_3d): depth extent, taps, stride, padding and output extent
+  int D, KD, stride_d, pad_d, DO;
 };
+
+// (a padded depth axis of extent one still has more than one output plane)
+bool is_3d(const ConvGeom& g) { return g.D > 1 || g.KD > 1 || g.pad_d > 0; }
 
 }  // namespace
 

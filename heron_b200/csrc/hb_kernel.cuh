@@ -71,6 +71,8 @@ struct KParams {
   uint32_t idesc;
   // conv geometry (a_im2col only)
   int HO, WO, KW, CI, kb_per_tap, stride_h, stride_w, dil_h, dil_w, pad_h, pad_w;
+  // a_im2col == 2: 3-D convolution over an NDHWC tensor (5-D im2col loads); taps ordered (kd, kh, kw)
+  int DO, KH, stride_d, pad_d;
   // direct-store epilogue
   int out_nchw;  // conv only: C is (N, CO, HO, WO) instead of (N*HO*WO, CO)
   int a_shared;  // batched: A has no batch dimension (every batch multiplies the same matrix)
@@ -202,11 +204,21 @@ hb_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       const CUtensorMap* tmBk = (bn == p.BN) ? &tmB : &tmB2;  // K-major B: box rows = bn / CG
       const int m0 = m_pair + static_cast<int>(cta_rank) * kTileM;
       const int n0 = n_first + static_cast<int>(cta_rank) * bn_mine;
-      int pix_w = 0, pix_h = 0, pix_n = 0;
+      int pix_w = 0, pix_h = 0, pix_d = 0, pix_n = 0;
       if (p.a_im2col) {
         const int hw = p.HO * p.WO;
-        pix_n = m0 / hw;
-        const int rem = m0 - pix_n * hw;
+        int rem;
+        if (p.a_im2col == 2) {
+          const int dhw = p.DO * hw;
+          pix_n = m0 / dhw;
+          rem = m0 - pix_n * dhw;
+          const int z = rem / hw;
+          rem -= z * hw;
+          pix_d = z * p.stride_d - p.pad_d;
+        } else {
+          pix_n = m0 / hw;
+          rem = m0 - pix_n * hw;
+        }
         const int y = rem / p.WO;
         const int x = rem - y * p.WO;
         pix_w = x * p.stride_w - p.pad_w;
@@ -236,11 +248,18 @@ hb_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         if (p.a_im2col) {
           const int tap = kb / p.kb_per_tap;
           const int cc = kb - tap * p.kb_per_tap;
-          const int ry = tap / p.KW;
-          const int rx = tap - ry * p.KW;
-          if (part & 1)
+          int ryz = tap / p.KW;
+          const int rx = tap - ryz * p.KW;
+          if ((part & 1) && p.a_im2col == 2) {
+            const int rz = ryz / p.KH;
+            const int ry = ryz - rz * p.KH;
+            tma_load_im2col_5d_cg<CG>(dA, &tmA, full, cc * BK, pix_w, pix_h, pix_d, pix_n,
+                                      static_cast<uint16_t>(rx), static_cast<uint16_t>(ry),
+                                      static_cast<uint16_t>(rz));
+          } else if (part & 1) {
             tma_load_im2col_4d_cg<CG>(dA, &tmA, full, cc * BK, pix_w, pix_h, pix_n,
-                                      static_cast<uint16_t>(rx * p.dil_w), static_cast<uint16_t>(ry * p.dil_h));
+                                      static_cast<uint16_t>(rx * p.dil_w), static_cast<uint16_t>(ryz * p.dil_h));
+          }
           krow = tap * p.CI + cc * BK;
         } else {
           if (part & 1) tma_load_3d_cg<CG>(dA, &tmA, full, kb * BK, m0, p.a_shared ? 0 : b);
@@ -485,7 +504,7 @@ hb_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
               // channel-major output: for one channel the 32 lanes of the warp hold 32 consecutive
               // pixels, so each store instruction writes one contiguous run (two where the warp
               // straddles two images)
-              const int P = p.HO * p.WO;
+              const int P = p.HO * p.WO * (p.a_im2col == 2 ? p.DO : 1);
               const int n = row / P;
               const int pix = row - n * P;
               uint8_t* o = static_cast<uint8_t*>(p.C) +

@@ -100,6 +100,8 @@ struct ConvExtra {
   bool out_nchw;
   long long w_stride, h_stride, n_stride;
   int kslab;  // > 1: every tile is cut into this many K slices, each stored to its own slab of `out`
+  // 3-D convolution: depth extent, taps, stride and padding (D = KD = 1, stride 1, pad 0 otherwise)
+  int D, KD, stride_d, pad_d;
 };
 
 // pad_h / pad_w: rows / columns of zeros on each side of the height / width axis.  The 2-D
@@ -123,8 +125,13 @@ int plan_conv(const void* in, const void* w, void* out, int N, int H, int W, int
   const int HO = conv_out_extent(H, KH, stride_h, pad_h, dil_h);
   const int WO = conv_out_extent(W, KW, stride_w, pad_w, dil_w);
   if (HO <= 0 || WO <= 0) return HB_ERR_SHAPE;
-  const long long M = static_cast<long long>(N) * HO * WO;
-  const long long K = static_cast<long long>(KH) * KW * CI;
+  const int D3 = (ex && ex->D > 0) ? ex->D : 1, KD = (ex && ex->KD > 0) ? ex->KD : 1;
+  const int stride_d = (ex && ex->stride_d > 0) ? ex->stride_d : 1, pad_d = ex ? ex->pad_d : 0;
+  if (pad_d < 0 || pad_d > 127 || KD - 1 > 255 || pad_d - (KD - 1) < -128 || stride_d > 8) return HB_ERR_SHAPE;
+  const int DO = conv_out_extent(D3, KD, stride_d, pad_d, 1);
+  if (DO <= 0) return HB_ERR_SHAPE;
+  const long long M = static_cast<long long>(N) * DO * HO * WO;
+  const long long K = static_cast<long long>(KD) * KH * KW * CI;
   if (M > 0x7fffffffLL || K > 0x7fffffffLL) return HB_ERR_SHAPE;
   if (!in || !w || !out) return HB_ERR_ALIGN;
   if (!aligned16(in) || !aligned16(w) || !aligned16(out)) return HB_ERR_ALIGN;
@@ -132,8 +139,10 @@ int plan_conv(const void* in, const void* w, void* out, int N, int H, int W, int
   if (d.status != HB_OK) return d.status;
   Problem pr{2, 1, static_cast<int>(M), CO, static_cast<int>(K), in_a, in_w, out_t, true, CI};
   ConvGeom cg{N, H, W, CI, CO, KH, KW, stride_h, stride_w, pad_h, pad_w, dil_h, dil_w, HO, WO, out_nchw,
-              ex ? ex->w_stride : 0, ex ? ex->h_stride : 0, ex ? ex->n_stride : 0, ex ? ex->kslab : 0};
-  const bool strided_view = cg.w_stride > 0;  // only the im2col kernel reads through custom strides
+              ex ? ex->w_stride : 0, ex ? ex->h_stride : 0, ex ? ex->n_stride : 0, ex ? ex->kslab : 0,
+              D3, KD, stride_d, pad_d, DO};
+  // only the im2col kernel reads through custom strides or walks a third spatial axis
+  const bool strided_view = cg.w_stride > 0 || is_3d(cg);
   const int algo = knobs ? knobs->conv_algo : 0;
   if (algo < 0 || algo > 2 || (algo == 2 && strided_view)) return HB_ERR_KNOB;
   if (algo != 1 && !strided_view) {
@@ -196,7 +205,7 @@ int plan_conv_packed(const void* in, const void* w_packed, void* out, int N, int
 size_t align256(size_t v) { return (v + 255) & ~static_cast<size_t>(255); }
 
 struct NchwLayout {
-  int CIp, HO, WO;
+  int CIp, HO, WO, DO;
   // few-channel ("stem") form: KWp horizontally adjacent pixels of `cis` channels make one K block
   bool stem;
   int cis, KWp, Hs, Ws, Wv;
@@ -210,25 +219,35 @@ struct NchwLayout {
 constexpr int kMaxSlabs = 8;
 constexpr long long kSlabMaxOutElems = 1ll << 21;
 
+// Depth axis of the NCDHW operator; {1, 1, 1, 0} for the 2-D and 1-D ones.
+struct Depth {
+  int D, KD, stride, pad;
+};
+constexpr Depth kNoDepth{1, 1, 1, 0};
+
 bool nchw_layout(int N, int H, int W, int CI, int CO, int KH, int KW, int sh, int sw, int pad_h,
-                 int pad_w, hb_dtype in_a, hb_dtype out_t, NchwLayout* L) {
+                 int pad_w, hb_dtype in_a, hb_dtype out_t, NchwLayout* L, const Depth& dz = kNoDepth) {
   const int es = esize(in_a), eo = esize(out_t);
   if (es == 0 || eo == 0 || N <= 0 || H <= 0 || W <= 0 || CI <= 0 || CO <= 0 || KH <= 0 || KW <= 0 ||
-      sh <= 0 || sw <= 0 || pad_h < 0 || pad_w < 0)
+      sh <= 0 || sw <= 0 || pad_h < 0 || pad_w < 0 || dz.D <= 0 || dz.KD <= 0 || dz.stride <= 0 || dz.pad < 0)
     return false;
+  const bool three_d = dz.D > 1 || dz.KD > 1 || dz.pad > 0;
+  L->DO = conv_out_extent(dz.D, dz.KD, dz.stride, dz.pad, 1);
+  if (L->DO <= 0) return false;
   const int gran = 32 / es;  // the NHWC kernels want whole 32-byte channel groups
   L->CIp = (CI + gran - 1) / gran * gran;
   L->HO = conv_out_extent(H, KH, sh, pad_h, 1);
   L->WO = conv_out_extent(W, KW, sw, pad_w, 1);
   if (L->HO <= 0 || L->WO <= 0) return false;
-  L->subsample = KH == 1 && KW == 1 && pad_h == 0 && pad_w == 0 && (sh > 1 || sw > 1);
-  const size_t kept_px = L->subsample ? static_cast<size_t>(L->HO) * L->WO : static_cast<size_t>(H) * W;
+  L->subsample = !three_d && KH == 1 && KW == 1 && pad_h == 0 && pad_w == 0 && (sh > 1 || sw > 1);
+  const size_t kept_px =
+      L->subsample ? static_cast<size_t>(L->HO) * L->WO : static_cast<size_t>(dz.D) * H * W;
   L->in_bytes = align256(static_cast<size_t>(N) * kept_px * L->CIp * es);
-  L->w_bytes = align256(static_cast<size_t>(KH) * KW * L->CIp * CO * es);
+  L->w_bytes = align256(static_cast<size_t>(dz.KD) * KH * KW * L->CIp * CO * es);
   // With at most 16 bytes of channels per pixel and a filter row of 2..8 taps, a whole filter
   // row fits one 64- or 128-byte K block: far fewer, fuller pipeline stages than one tap each.
   L->cis = 16 / es;
-  L->stem = CI <= L->cis && KW >= 2 && KW <= 8;
+  L->stem = !three_d && CI <= L->cis && KW >= 2 && KW <= 8;
   if (L->stem) {
     L->KWp = KW <= 4 ? 4 : 8;
     L->Hs = (L->HO - 1) * sh + KH;           // rows the windows touch, borders included
@@ -238,7 +257,7 @@ bool nchw_layout(int N, int H, int W, int CI, int CO, int KH, int KW, int sh, in
     L->w_bytes = align256(static_cast<size_t>(KH) * L->KWp * 16 * CO);
   }
   // room for the partial sums of a split-K plan (4-byte accumulators, row-major (M, CO) slabs)
-  const long long out_elems = static_cast<long long>(N) * L->HO * L->WO * CO;
+  const long long out_elems = static_cast<long long>(N) * L->DO * L->HO * L->WO * CO;
   L->ws_bytes = out_elems <= kSlabMaxOutElems ? align256(static_cast<size_t>(out_elems) * 4 * kMaxSlabs) : 0;
   L->total = L->in_bytes + L->w_bytes + L->ws_bytes;
   return true;
@@ -247,9 +266,9 @@ bool nchw_layout(int N, int H, int W, int CI, int CO, int KH, int KW, int sh, in
 int plan_conv_nchw(const void* in, const void* w, void* out, int N, int H, int W, int CI, int CO,
                    int KH, int KW, int sh, int sw, int pad_h, int pad_w, hb_dtype in_a, hb_dtype in_w,
                    hb_dtype out_t, void* scratch, size_t scratch_bytes, const hb_knobs* knobs,
-                   hb_plan* plan) {
+                   hb_plan* plan, const Depth& dz = kNoDepth) {
   NchwLayout L;
-  if (!nchw_layout(N, H, W, CI, CO, KH, KW, sh, sw, pad_h, pad_w, in_a, out_t, &L)) return HB_ERR_SHAPE;
+  if (!nchw_layout(N, H, W, CI, CO, KH, KW, sh, sw, pad_h, pad_w, in_a, out_t, &L, dz)) return HB_ERR_SHAPE;
   if (esize(in_w) != esize(in_a)) return HB_ERR_DTYPE;
   if (!scratch || scratch_bytes < L.total) return HB_ERR_SCRATCH;
   if (!in || !w || !out) return HB_ERR_ALIGN;
@@ -257,9 +276,10 @@ int plan_conv_nchw(const void* in, const void* w, void* out, int N, int H, int W
   // A 1x1, stride-1, unpadded conv is, per image, out (CO x P) = filter (CO x CI) . in (CI x P): a
   // batched GEMM on the NCHW tensors as they are (filter as the shared K-major A, each image as an
   // N-contiguous B, row-major C = NCHW), with no layout pass.  Needs 16-byte rows for the tensor maps.
-  const long long P1 = static_cast<long long>(H) * W;
+  const long long P1 = static_cast<long long>(dz.D) * H * W;
   const int es1 = esize(in_a), eo1 = esize(out_t);
-  if (KH == 1 && KW == 1 && sh == 1 && sw == 1 && pad_h == 0 && pad_w == 0 && (P1 * es1) % 16 == 0 &&
+  if (KH == 1 && KW == 1 && sh == 1 && sw == 1 && pad_h == 0 && pad_w == 0 && dz.KD == 1 && dz.stride == 1 &&
+      dz.pad == 0 && (P1 * es1) % 16 == 0 &&
       (static_cast<long long>(CI) * es1) % 16 == 0 && P1 <= 0x7fffffffLL && P1 >= 32 &&
       aligned16(in) && aligned16(w) && aligned16(out) && (!knobs || knobs->conv_algo == 0)) {
     if (mma_kind(in_w, in_a, out_t) < 0) return HB_ERR_DTYPE;
@@ -280,7 +300,7 @@ int plan_conv_nchw(const void* in, const void* w, void* out, int N, int H, int W
   const int es = esize(in_a);
   uint8_t* s_ws = s_w + L.w_bytes;
   // The conv the kernel runs: the NHWC form of the problem, or its few-channel form.
-  ConvExtra ex{true, 0, 0, 0, 0};
+  ConvExtra ex{true, 0, 0, 0, 0, dz.D, dz.KD, dz.stride, dz.pad};
   int cH = H, cW = W, cCI = L.CIp, cKW = KW, cpad_h = pad_h, cpad_w = pad_w, csh = sh, csw = sw;
   if (L.subsample) { cH = L.HO; cW = L.WO; csh = 1; csw = 1; }
   if (L.stem) {
@@ -323,8 +343,8 @@ int plan_conv_nchw(const void* in, const void* w, void* out, int N, int H, int W
     if (rc != HB_OK) return rc;
     plan->has_post = true;
     plan->post_ws = s_ws; plan->post_out = out;
-    plan->post_slabs = slabs; plan->post_P = L.HO * L.WO; plan->post_CO = CO; plan->post_N = N;
-    plan->post_slab_elems = static_cast<long long>(N) * L.HO * L.WO * CO;
+    plan->post_slabs = slabs; plan->post_P = L.DO * L.HO * L.WO; plan->post_CO = CO; plan->post_N = N;
+    plan->post_slab_elems = static_cast<long long>(N) * L.DO * L.HO * L.WO * CO;
     plan->post_kind = out_t == HB_F16 ? 0 : (out_t == HB_F32 ? 1 : 2);
   }
   if (L.stem) {
@@ -343,7 +363,7 @@ int plan_conv_nchw(const void* in, const void* w, void* out, int N, int H, int W
     plan->has_pre = true;
     return HB_OK;
   }
-  const int T = KH * KW, P = L.subsample ? L.HO * L.WO : H * W;
+  const int T = dz.KD * KH * KW, P = L.subsample ? L.HO * L.WO : dz.D * H * W;
   const int vec = 8 / es, tile = 16 * vec;
   hb::NchwPre& g = plan->pre;
   g.in = in; g.in_t = s_in; g.w = w; g.w_t = s_w;

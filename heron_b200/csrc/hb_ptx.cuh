@@ -276,6 +276,27 @@ __device__ __forceinline__ void tma_load_im2col_4d_cg(uint32_t dst, const CUtens
         : "memory");
   }
 }
+// im2col-mode 5-D load over an NDHWC tensor (3-D convolution): three tap offsets.
+template <int CG>
+__device__ __forceinline__ void tma_load_im2col_5d_cg(uint32_t dst, const CUtensorMap* m, uint32_t bar,
+                                                      int c, int w, int h, int d, int n, uint16_t off_w,
+                                                      uint16_t off_h, uint16_t off_d) {
+  if constexpr (CG == 1) {
+    asm volatile(
+        "cp.async.bulk.tensor.5d.shared::cluster.global.im2col.mbarrier::complete_tx::bytes"
+        " [%0], [%1, {%3, %4, %5, %6, %7}], [%2], {%8, %9, %10};" ::"r"(dst),
+        "l"(reinterpret_cast<uint64_t>(m)), "r"(bar), "r"(c), "r"(w), "r"(h), "r"(d), "r"(n), "h"(off_w),
+        "h"(off_h), "h"(off_d)
+        : "memory");
+  } else {
+    asm volatile(
+        "cp.async.bulk.tensor.5d.im2col.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+        " [%0], [%1, {%3, %4, %5, %6, %7}], [%2], {%8, %9, %10};" ::"r"(dst),
+        "l"(reinterpret_cast<uint64_t>(m)), "r"(bar), "r"(c), "r"(w), "r"(h), "r"(d), "r"(n), "h"(off_w),
+        "h"(off_h), "h"(off_d)
+        : "memory");
+  }
+}
 // L2 prefetch of a tile a few ring stages ahead (no shared memory, no completion to wait for).
 __device__ __forceinline__ void tma_prefetch_3d(const CUtensorMap* m, int x, int y, int z) {
   asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global.tile [%0, {%1, %2, %3}];" ::"l"(

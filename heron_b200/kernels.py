@@ -425,3 +425,50 @@ def plan_scan(a, N, out=None, out_dtype=None, scratch=None, knobs=None):
                                   _code(out), _dev(scratch, "scratch"), scratch.numel(), _knobs(knobs))
     _lib.check(rc, "hb_plan_scan")
     return Plan(h, (a, scratch), out)
+
+
+def _triple(v):
+    if isinstance(v, int):
+        return v, v, v
+    a, b, c = v
+    return int(a), int(b), int(c)
+
+
+def _c3d_args(x, w, stride, padding, out, out_dtype, scratch):
+    N, CI, D, H, W = x.shape
+    CO, CI2, KD, KH, KW = w.shape
+    if CI != CI2:
+        raise ValueError("input channels of x and w differ")
+    sd, sh, sw = _triple(stride)
+    p = int(padding)
+    DO, HO, WO = (D - KD + 2 * p) // sd + 1, (H - KH + 2 * p) // sh + 1, (W - KW + 2 * p) // sw + 1
+    if DO <= 0 or HO <= 0 or WO <= 0:
+        raise _lib.HeronB200Error(_lib.HB_ERR_SHAPE, "conv3d output extent %d x %d x %d" % (DO, HO, WO))
+    if out is None:
+        out = torch.empty((N, CO, DO, HO, WO), dtype=out_dtype or default_out_dtype(x.dtype), device=x.device)
+    dims = (N, D, H, W, CI, CO, KD, KH, KW, sd, sh, sw, p)
+    need = _lib.load().hb_conv3d_ncdhw_scratch_bytes(*dims, _code(x), _code(out))
+    if scratch is None:
+        scratch = torch.empty(need, dtype=torch.uint8, device=x.device)
+    return dims, out, scratch
+
+
+def conv3d_ncdhw(x, w, stride=1, padding=0, out=None, out_dtype=None, scratch=None, knobs=None):
+    """out[n,c,d,p,q] = sum pad(x)[n,ci,d*sd+kd,p*sh+kh,q*sw+kw] * w[c,ci,kd,kh,kw]; x NCDHW, w OIDHW,
+    dilation 1 (ops/cuda/conv3d.py:9-85)."""
+    dims, out, scratch = _c3d_args(x, w, stride, padding, out, out_dtype, scratch)
+    rc = _lib.load().hb_conv3d_ncdhw(_dev(x, "x"), _dev(w, "w"), _dev(out, "out"), *dims, _code(x), _code(w),
+                                     _code(out), _dev(scratch, "scratch"), scratch.numel(), _knobs(knobs),
+                                     _stream(x))
+    _lib.check(rc, "hb_conv3d_ncdhw")
+    return out
+
+
+def plan_conv3d_ncdhw(x, w, stride=1, padding=0, out=None, out_dtype=None, scratch=None, knobs=None):
+    dims, out, scratch = _c3d_args(x, w, stride, padding, out, out_dtype, scratch)
+    h = ctypes.c_void_p()
+    rc = _lib.load().hb_plan_conv3d_ncdhw(ctypes.byref(h), _dev(x, "x"), _dev(w, "w"), _dev(out, "out"), *dims,
+                                          _code(x), _code(w), _code(out), _dev(scratch, "scratch"),
+                                          scratch.numel(), _knobs(knobs))
+    _lib.check(rc, "hb_plan_conv3d_ncdhw")
+    return Plan(h, (x, w, scratch), out)

@@ -62,7 +62,8 @@ def kill_child_processes(parent_pid, sig=signal.SIGTERM):
 
 # Position of the sharded leading dimension in each operator's case arguments
 # (gemm [M,K,N] does not shard; bmm [batch,M,K,N]; conv [N,H,W,CI,CO,KH,KW,stride,pad,dil,...]).
-SHARD_ARG = {"bmm": 0, "c2d_nhwc": 0, "c2d": 0}
+# The image-parallel operators next to them (dil, c1d, c3d, t2d) lead with N as well.
+SHARD_ARG = {"bmm": 0, "c2d_nhwc": 0, "c2d": 0, "dil": 0, "c1d": 0, "c3d": 0, "t2d": 0}
 
 
 def partition(extent, world):

@@ -41,6 +41,11 @@ def _gemm_view(out):
         N, WO = out.shape[0], out.shape[2]
         ci, taps = _nchw_k_block(p["CI"], 1, p["KW"], ELEM_BYTES[p["in_dtype"]])
         return 1, N * WO, p["CO"], taps * ci, ci
+    if out.op.kind == "conv3d_ncdhw":
+        gran = 32 // ELEM_BYTES[p["in_dtype"]]
+        ci = (p["CI"] + gran - 1) // gran * gran
+        return (1, out.shape[0] * out.shape[2] * out.shape[3] * out.shape[4], p["CO"],
+                p["KD"] * p["KH"] * p["KW"] * ci, ci)
     if out.op.kind == "conv1d_nwc_packed":
         return 1, out.shape[0] * out.shape[1], p["CO"], p["KW"] * p["CI"], p["CI"]
     if out.op.kind == "conv2d_nchw":

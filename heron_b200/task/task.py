@@ -53,6 +53,10 @@ class KernelHandle:
             fn = K.plan_conv2d_nhwc_packed if planned else K.conv2d_nhwc_packed
             return fn(x, w, p["CO"], p["KH"], p["KW"], stride=p["stride"], padding=p["padding"],
                       dilation=p["dilation"], sco=p["sco"], out=out, knobs=knobs)
+        if kind == "conv3d_ncdhw":
+            x, w, out = tensors
+            fn = K.plan_conv3d_ncdhw if planned else K.conv3d_ncdhw
+            return fn(x, w, stride=p["stride"], padding=p["padding"], out=out, knobs=knobs)
         if kind == "scan":
             a, out = tensors
             fn = K.plan_scan if planned else K.scan

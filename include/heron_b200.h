@@ -205,6 +205,22 @@ int hb_conv2d_nchw(const void* in, const void* w, void* out, int N, int H, int W
 int hb_gemv(const void* A, const void* x, void* out, int M, int K, hb_dtype in_a, hb_dtype in_x,
             hb_dtype out_t, const hb_knobs* knobs, void* stream);
 size_t hb_scan_scratch_bytes(int N, int K, hb_dtype in_a);
+
+/*
+ * hb_conv3d_ncdhw: ops/cuda/conv3d.py:9-110.  `in` (N,CI,D,H,W), `w` (CO,CI,KD,KH,KW), `out`
+ * (N,CO,DO,HO,WO); `pad` zeros on every side of the three spatial axes (an int padding in
+ * get_pad_tuple3d), dilation 1 (asserted there):
+ *   out[n,c,d,p,q] = sum_{ci,kd,kh,kw} pad(in)[n, ci, d*sd+kd, p*sh+kh, q*sw+kw] * w[c,ci,kd,kh,kw]
+ * The glue of hb_conv2d_nchw brings input and filter to NDHWC / (KD,KH,KW,CI,CO); the conv kernel
+ * reads the activations with 5-D im2col TMA loads (three tap offsets) and writes NCDHW.
+ */
+size_t hb_conv3d_ncdhw_scratch_bytes(int N, int D, int H, int W, int CI, int CO, int KD, int KH, int KW,
+                                     int stride_d, int stride_h, int stride_w, int pad, hb_dtype in_a,
+                                     hb_dtype out_t);
+int hb_conv3d_ncdhw(const void* in, const void* w, void* out, int N, int D, int H, int W, int CI, int CO,
+                    int KD, int KH, int KW, int stride_d, int stride_h, int stride_w, int pad,
+                    hb_dtype in_a, hb_dtype in_w, hb_dtype out_t, void* scratch, size_t scratch_bytes,
+                    const hb_knobs* knobs, void* stream);
 int hb_scan(const void* A, void* out, int M, int N, int K, hb_dtype in_a, hb_dtype out_t, void* scratch,
             size_t scratch_bytes, const hb_knobs* knobs, void* stream);
 size_t hb_conv1d_ncw_scratch_bytes(int N, int W, int CI, int CO, int KW, int stride, int pad,
@@ -269,6 +285,10 @@ int hb_plan_conv2d_nchw(hb_plan** plan, const void* in, const void* w, void* out
                         int W, int CI, int CO, int KH, int KW, int stride_h, int stride_w, int pad,
                         hb_dtype in_a, hb_dtype in_w, hb_dtype out_t, void* scratch,
                         size_t scratch_bytes, const hb_knobs* knobs);
+int hb_plan_conv3d_ncdhw(hb_plan** plan, const void* in, const void* w, void* out, int N, int D, int H,
+                         int W, int CI, int CO, int KD, int KH, int KW, int stride_d, int stride_h,
+                         int stride_w, int pad, hb_dtype in_a, hb_dtype in_w, hb_dtype out_t,
+                         void* scratch, size_t scratch_bytes, const hb_knobs* knobs);
 int hb_plan_scan(hb_plan** plan, const void* A, void* out, int M, int N, int K, hb_dtype in_a,
                  hb_dtype out_t, void* scratch, size_t scratch_bytes, const hb_knobs* knobs);
 int hb_plan_gemv(hb_plan** plan, const void* A, const void* x, void* out, int M, int K,

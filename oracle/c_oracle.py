@@ -199,3 +199,21 @@ def scan(a, N, out_dtype=None):
         out = np.empty((M, N), dtype=np.int32)
         lib().oracle_scan(_p(a), _p(out), M, N, K, 0, _signed(a))
     return out
+
+
+def conv3d_ncdhw(x, w, stride=1, pad=0, out_dtype=None):
+    x, w = _c(x), _c(w)
+    N, CI, D, H, W = x.shape
+    CO, _, KD, KH, KW = w.shape
+    sd, sh, sw = (stride, stride, stride) if isinstance(stride, int) else tuple(int(v) for v in stride)
+    shape = (N, CO, (D - KD + 2 * pad) // sd + 1, (H - KH + 2 * pad) // sh + 1, (W - KW + 2 * pad) // sw + 1)
+    if x.dtype == np.float16:
+        half = out_dtype is not None and np.dtype(out_dtype) == np.float16
+        out = np.empty(shape, dtype=np.float16 if half else np.float32)
+        lib().oracle_conv3d_ncdhw(_p(x), _p(w), _p(out), N, D, H, W, CI, CO, KD, KH, KW, sd, sh, sw, pad,
+                                  2 if half else 1, 0, 0)
+    else:
+        out = np.empty(shape, dtype=np.int32)
+        lib().oracle_conv3d_ncdhw(_p(x), _p(w), _p(out), N, D, H, W, CI, CO, KD, KH, KW, sd, sh, sw, pad, 0,
+                                  _signed(x), _signed(w))
+    return out

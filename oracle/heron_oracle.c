@@ -392,3 +392,44 @@ void oracle_scan(const void* A, void* out, int M, int N, int K, int mode, int a_
       else ((uint16_t*)out)[o] = float_to_half_rn((float)dacc);
     }
 }
+
+/*
+ * NCDHW conv3d, ops/cuda/conv3d.py:23-85 as the direct sum its im2col GEMM computes:
+ *   out[n,c,d,p,q] = sum_{ci,kd,kh,kw} pad(in)[n,ci,d*sd+kd,p*sh+kh,q*sw+kw] * w[c,ci,kd,kh,kw]
+ * `pad` zeros on every side of the three spatial axes.  Modes as oracle_conv1d_ncw.
+ */
+void oracle_conv3d_ncdhw(const void* in, const void* w, void* out, int N, int D, int H, int W, int CI,
+                         int CO, int KD, int KH, int KW, int sd, int sh, int sw, int pad, int mode,
+                         int in_signed, int w_signed) {
+  const int DO = (D - KD + 2 * pad) / sd + 1, HO = (H - KH + 2 * pad) / sh + 1, WO = (W - KW + 2 * pad) / sw + 1;
+  for (int n = 0; n < N; ++n)
+    for (int c = 0; c < CO; ++c)
+      for (int d = 0; d < DO; ++d)
+        for (int p = 0; p < HO; ++p)
+          for (int q = 0; q < WO; ++q) {
+            int32_t iacc = 0;
+            double dacc = 0.0;
+            for (int ci = 0; ci < CI; ++ci)
+              for (int kd = 0; kd < KD; ++kd) {
+                const int z = d * sd + kd - pad;
+                if (z < 0 || z >= D) continue;
+                for (int kh = 0; kh < KH; ++kh) {
+                  const int y = p * sh + kh - pad;
+                  if (y < 0 || y >= H) continue;
+                  for (int kw = 0; kw < KW; ++kw) {
+                    const int x = q * sw + kw - pad;
+                    if (x < 0 || x >= W) continue;
+                    const size_t ii = ((((size_t)n * CI + ci) * D + z) * H + y) * W + x;
+                    const size_t wi = ((((size_t)c * CI + ci) * KD + kd) * KH + kh) * KW + kw;
+                    if (mode == 0) iacc += load_i8(in, ii, in_signed) * load_i8(w, wi, w_signed);
+                    else dacc += (double)half_to_float(((const uint16_t*)in)[ii]) *
+                                 (double)half_to_float(((const uint16_t*)w)[wi]);
+                  }
+                }
+              }
+            const size_t oi = ((((size_t)n * CO + c) * DO + d) * HO + p) * WO + q;
+            if (mode == 0) ((int32_t*)out)[oi] = iacc;
+            else if (mode == 1) ((float*)out)[oi] = (float)dacc;
+            else ((uint16_t*)out)[oi] = float_to_half_rn((float)dacc);
+          }
+}

@@ -234,3 +234,29 @@ def t2d_nchw_stride1(x, w, padding, out_dtype=None):
         C = _to_i32(_as_i64(B) @ _as_i64(A).T)
     out = np.ascontiguousarray(C.reshape(CO, N, HO, WO).transpose(1, 0, 2, 3))
     return out.astype(np.float16) if out_dtype is not None and np.dtype(out_dtype) == np.float16 else out
+
+
+def conv3d_ncdhw(x, w, stride=1, pad=0, out_dtype=None):
+    """The reference's lowering of the NCDHW operator (ops/cuda/conv3d.py:33-85): pad, build
+    A[N*D_O*H_O*W_O, CI*KD*KH*KW] with columns ordered (ci, kd, kh, kw), B[CO, CI*KD*KH*KW];
+    C = B . A^T; output[n, c, d, p, q] = C[c, ((n*D_O + d)*H_O + p)*W_O + q]."""
+    sd, sh, sw = (stride, stride, stride) if isinstance(stride, int) else tuple(int(v) for v in stride)
+    N, CI, D, H, W = x.shape
+    CO, _, KD, KH, KW = w.shape
+    DO, HO, WO = (D - KD + 2 * pad) // sd + 1, (H - KH + 2 * pad) // sh + 1, (W - KW + 2 * pad) // sw + 1
+    xp = np.zeros((N, CI, D + 2 * pad, H + 2 * pad, W + 2 * pad), dtype=x.dtype)
+    xp[:, :, pad:pad + D, pad:pad + H, pad:pad + W] = x
+    A = np.empty((N, DO, HO, WO, CI, KD, KH, KW), dtype=x.dtype)
+    for kd in range(KD):
+        for kh in range(KH):
+            for kw in range(KW):
+                A[..., kd, kh, kw] = xp[:, :, kd:kd + (DO - 1) * sd + 1:sd, kh:kh + (HO - 1) * sh + 1:sh,
+                                        kw:kw + (WO - 1) * sw + 1:sw].transpose(0, 2, 3, 4, 1)
+    A = A.reshape(N * DO * HO * WO, CI * KD * KH * KW)
+    B = w.reshape(CO, CI * KD * KH * KW)
+    if x.dtype == np.float16:
+        C = (B.astype(np.float64) @ A.astype(np.float64).T).astype(np.float32)
+    else:
+        C = _to_i32(_as_i64(B) @ _as_i64(A).T)
+    out = np.ascontiguousarray(C.reshape(CO, N, DO, HO, WO).transpose(1, 0, 2, 3, 4))
+    return out.astype(np.float16) if out_dtype is not None and np.dtype(out_dtype) == np.float16 else out

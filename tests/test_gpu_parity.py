@@ -804,6 +804,31 @@ def test_t2d_stride1_through_the_registry(K, co, case):
     check(out, want, "t2d %s" % (case,))
 
 
+@pytest.mark.parametrize("case", [(2, 4, 14, 14, 64, 64, 3, 3, 3, 1, 1, 1), (2, 4, 12, 12, 32, 48, 1, 1, 1, 2, 0, 1),
+                                  (1, 3, 9, 11, 16, 32, 2, 3, 1, (1, 2, 1), 1, 1), (2, 2, 8, 8, 64, 128, 1, 1, 1, 1, 0, 1),
+                                  (1, 5, 6, 7, 3, 16, 3, 3, 3, 1, 1, 1)])
+def test_conv3d_ncdhw(K, co, case):
+    """(N, D, H, W, CI, CO, KD, KH, KW, stride, pad, dilation): the reference's c3d cases scaled
+    down, unequal taps and strides, the 1x1x1 form that runs on the tensors in place, 3 channels."""
+    from heron_b200.ops import cuda as heron_cuda
+    N, D, H, W, CI, CO, KD, KH, KW, s, p, d = case
+    rng = np.random.default_rng(sum(v if isinstance(v, int) else 5 for v in case))
+    x = rng.standard_normal((N, CI, D, H, W)).astype(np.float16)
+    w = (rng.standard_normal((CO, CI, KD, KH, KW)) / np.sqrt(CI * KD * KH * KW)).astype(np.float16)
+    t = _task(heron_cuda, "c3d", list(case) + ["float16", "float16"], "GPU_TENSOR_CORE")
+    t.knob_manager.randSample()
+    handle, args = t.instantiate(t.knob_manager)
+    want = co.conv3d_ncdhw(x, w, s, p, np.float16)
+    assert tuple(args[-1].shape) == want.shape
+    out = poison(want.shape, torch.float16)
+    handle(dev(x), dev(w), out)
+    check(out, want, "c3d fp16 %s %s" % (case, handle.knobs))
+    check(K.conv3d_ncdhw(dev(x), dev(w), s, p), co.conv3d_ncdhw(x, w, s, p), "c3d fp32 out %s" % (case,))
+    xi, wi = rand_i8(rng, (N, CI, D, H, W), False), rand_i8(rng, (CO, CI, KD, KH, KW), True)
+    plan = K.plan_conv3d_ncdhw(dev(xi), dev(wi), s, p)
+    check(plan.launch(), co.conv3d_ncdhw(xi, wi, s, p), "c3d int8 %s" % (case,))
+
+
 def test_conv_nchw_through_the_registry(K, co):
     """`c2d` of the tensor-core registry, with a ResNet-50 table row scaled down in batch."""
     from heron_b200.ops import cuda as heron_cuda
@@ -940,3 +965,23 @@ def test_conv_nchw_random_geometry(K, co, N, CI, H, W, CO8, KH, KW, sh, sw, pad,
     out = poison(want.shape, _T[want.dtype])
     K.conv2d_nchw(dev(x), dev(w), stride=(sh, sw), padding=pad, out=out, knobs=dict(split_k=split_k))
     check(out, want, "nchw %s" % ((N, CI, H, W, CO, KH, KW, sh, sw, pad, int8, half_out, split_k),))
+
+
+@_prop
+@given(N=st.integers(1, 2), CI=st.sampled_from([3, 16, 40]), D=st.integers(1, 6), H=st.integers(1, 10),
+       W=st.integers(1, 10), CO8=st.integers(1, 6), KD=st.integers(1, 3), KH=st.integers(1, 3), KW=st.integers(1, 3),
+       sd=st.integers(1, 2), sh=st.integers(1, 2), sw=st.integers(1, 3), pad=st.integers(0, 2), int8=st.booleans(),
+       seed=st.integers(0, 2 ** 20))
+def test_conv3d_random_geometry(K, co, N, CI, D, H, W, CO8, KD, KH, KW, sd, sh, sw, pad, int8, seed):
+    if D + 2 * pad < KD or H + 2 * pad < KH or W + 2 * pad < KW:
+        return
+    rng = np.random.default_rng(seed)
+    CO = 8 * CO8 * (2 if int8 else 1)
+    if int8:
+        x, w = rand_i8(rng, (N, CI, D, H, W), False), rand_i8(rng, (CO, CI, KD, KH, KW), True)
+    else:
+        x = rng.standard_normal((N, CI, D, H, W)).astype(np.float16)
+        w = (rng.standard_normal((CO, CI, KD, KH, KW)) / np.sqrt(CI * KD * KH * KW)).astype(np.float16)
+    want = co.conv3d_ncdhw(x, w, (sd, sh, sw), pad)
+    got = K.conv3d_ncdhw(dev(x), dev(w), (sd, sh, sw), pad)
+    check(got, want, "c3d %s" % ((N, CI, D, H, W, CO, KD, KH, KW, sd, sh, sw, pad, int8),))

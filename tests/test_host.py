@@ -43,8 +43,11 @@ def test_registry_names_and_signatures():
     assert heron_cpu.getOpFromName("c1d").__name__ == "heron_conv1d_nwc"
     assert heron_cuda.getOpFromName("t2d").__name__ == "heron_conv2d_nchw_transposed_tensorcore"
     assert heron_cpu.getOpFromName("t2d").__name__ == "heron_conv2d_transposed_nhwc"
+    assert heron_cuda.getOpFromName("c3d").__name__ == "heron_conv3d_ncdhw_tensorcore"
     with pytest.raises(NotImplementedError):
-        heron_cuda.getOpFromName("c3d")
+        heron_cuda.getOpFromName("dep")
+    with pytest.raises(NotImplementedError):
+        heron_cpu.getOpFromName("c3d")
     with pytest.raises(KeyError):
         heron_cuda.getOpFromName("nonsense")
 
@@ -267,6 +270,8 @@ def test_partition_and_shard_case():
     assert args[0] == 128 and (start, count) == (384, 128)
     with pytest.raises(ValueError):
         shard_case("gemm", [64, 64, 64], 0, 2)
+    args, (start, count) = shard_case("c3d", [8, 8, 56, 56, 64, 64, 3, 3, 3, 1, 1, 1], 1, 4)
+    assert args[0] == 2 and (start, count) == (2, 2) and args[1:] == [8, 56, 56, 64, 64, 3, 3, 3, 1, 1, 1]
 
 
 def _square(x):

@@ -179,6 +179,22 @@ def test_nchw_operator_three_ways(co):
             assert np.array_equal(npo.conv2d_nchw_f16(xf, wf, s, p, od), co.conv2d_nchw(xf, wf, s, p, od))
 
 
+def test_conv3d_c_vs_numpy(co):
+    rng = np.random.default_rng(303)
+    for (N, CI, D, H, W, CO, KD, KH, KW, s, p) in [(2, 4, 3, 5, 6, 8, 3, 3, 3, 1, 1), (1, 8, 4, 6, 5, 8, 1, 1, 1, 2, 0),
+                                                  (2, 3, 5, 4, 7, 8, 2, 3, 1, (2, 1, 2), 1), (1, 4, 2, 3, 3, 8, 3, 3, 3, 1, 1)]:
+        x = rng.integers(-128, 128, (N, CI, D, H, W)).astype(np.int8)
+        w = rng.integers(-128, 128, (CO, CI, KD, KH, KW)).astype(np.int8)
+        assert np.array_equal(co.conv3d_ncdhw(x, w, s, p), npo.conv3d_ncdhw(x, w, s, p))
+        xf = rng.standard_normal((N, CI, D, H, W)).astype(np.float16)
+        wf = rng.standard_normal((CO, CI, KD, KH, KW)).astype(np.float16)
+        assert np.array_equal(co.conv3d_ncdhw(xf, wf, s, p), npo.conv3d_ncdhw(xf, wf, s, p))
+    # depth 1, one depth tap: the 2-D operator
+    x = rng.integers(0, 256, (2, 4, 1, 6, 6), dtype=np.uint8)
+    w = rng.integers(-128, 128, (8, 4, 1, 3, 3)).astype(np.int8)
+    assert np.array_equal(co.conv3d_ncdhw(x, w, 1, 0)[:, :, 0], co.conv2d_nchw(x[:, :, 0], w[:, :, 0], 1, 0))
+
+
 def test_t2d_stride1_is_the_padded_conv(co):
     """The reference's transposed-conv expression at stride 1, staged as it stages it, against the
     C conv loops with padding K-1-p."""
