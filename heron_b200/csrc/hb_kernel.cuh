@@ -33,6 +33,13 @@
 // For conv the A tile is fetched with im2col-mode TMA: 128 consecutive output pixels of one
 // filter tap and one channel chunk, zero-filled where the tap falls into the padding.
 //
+// Work items are whole tiles, or — for the tiles that would leave a wave of the persistent grid
+// partly empty — column slices of a tile or slices of its K range.  K slices either add into a
+// zeroed output (TMA reduce-add / red.global) or are stored side by side into workspace slabs that
+// a later kernel sums in a fixed order.  Other variants of the same body: A shared by all batches
+// with B read as (K, N) tiles (a 1x1 NCHW conv on the tensors in place), a third spatial axis
+// (5-D im2col loads), channel-major (NCHW) stores from the direct epilogue.
+//
 // Every wait on an mbarrier is bounded.  When one runs out, the CTA raises a shared abort flag,
 // every role leaves its loop, in-flight TMA loads and MMAs are waited for (bounded again), TMEM
 // is freed and HB_ERR_TIMEOUT is left in the device status word.
