@@ -205,7 +205,10 @@ void resolve_knobs(const Problem& pr, const hb_knobs* in, int sm_count, hb_knobs
     const int sw = k.swizzle_bytes ? k.swizzle_bytes : 128;
     const long long kblocks = (static_cast<long long>(pr.K) * es + sw - 1) / sw;
     const int min_pair_n = b_mn_major(pr) ? 2 * sw / es : 64;
-    k.cta_group = (pr.M > hb::kTileM && kblocks >= 8 && pr.N >= min_pair_n) ? 2 : 1;
+    // (on-device tuning of the ResNet-50 and BERT tables picked single CTAs up to 16 K blocks and
+    // pairs from 32 on, except for wide outputs, where halving each CTA's share of B pays at once)
+    const bool long_k = kblocks >= 24 || (kblocks >= 8 && pr.N >= 1024);
+    k.cta_group = (pr.M > hb::kTileM && long_k && pr.N >= min_pair_n) ? 2 : 1;
   }
   if (k.epilogue == 0) {
     // Default: TMA store whenever the output rows are 16-byte multiples.
