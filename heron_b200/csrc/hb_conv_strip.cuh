@@ -109,6 +109,7 @@ hb_conv_strip_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_cons
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = bars->tmem_base;
+  griddep_wait();  // input and filter may come from a layout kernel this one was launched behind
 
   if (warp == 0) {
     // ------------------------------ producer ----------------------------------------------

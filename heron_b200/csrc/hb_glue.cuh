@@ -9,6 +9,7 @@ namespace hb {
 // Zeroes the output tiles that the split-K work items of hb_umma_kernel add into (4-byte
 // elements).  blockIdx.x walks (tile, row group) pairs; a warp writes 128 consecutive bytes of a row.
 __global__ void hb_zero_tiles_kernel(const KParams p, int tile_rows, int row_groups) {
+  griddep_launch_dependents();
   const int tiles = (p.num_tiles - p.whole_tiles) / p.ksplit;
   const int tiles_per_batch = p.tiles_m * p.tiles_n;
   const int rows_per_group = tile_rows / row_groups;
@@ -37,6 +38,7 @@ __global__ void hb_zero_tiles_kernel(const KParams p, int tile_rows, int row_gro
 // matrix whose product with A gives out[m][n] = sum of A[m][k] over k < n.
 template <typename T>
 __global__ void hb_scan_mask_kernel(T* __restrict__ b, int N, int K, T one) {
+  griddep_launch_dependents();
   const long long total = static_cast<long long>(N) * K;
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
        i += static_cast<long long>(gridDim.x) * blockDim.x) {
@@ -50,6 +52,7 @@ __global__ void hb_scan_mask_kernel(T* __restrict__ b, int N, int K, T one) {
 // that the HWIO writes of a warp land in consecutive bytes of four rows.
 __global__ void hb_unpack_filter_kernel(const int8_t* __restrict__ packed, int8_t* __restrict__ hwio,
                                         int CO, int KH, int KW, int CI, int sco) {
+  griddep_launch_dependents();
   const long long total = static_cast<long long>(KH) * KW * (CI / 4) * CO;
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
        i += static_cast<long long>(gridDim.x) * blockDim.x) {
@@ -162,6 +165,7 @@ __global__ void __launch_bounds__(256) hb_nchw_pre_kernel(const NchwPre g) {
   constexpr size_t kFiltBytes = sizeof(T) * 32 * FPITCH;
   __shared__ __align__(8) uint8_t raw[kTileBytes > kFiltBytes ? kTileBytes : kFiltBytes];
   T (*tile)[PITCH] = reinterpret_cast<T (*)[PITCH]>(raw);
+  griddep_launch_dependents();  // the conv kernel behind this one may set itself up meanwhile
   if (static_cast<int>(blockIdx.x) < g.in_blocks) {
     // ---- input: per image a (CI x P) matrix, transposed to (P x CIp) ----
     int b = blockIdx.x;
@@ -264,6 +268,7 @@ struct StemPre {
 template <typename T>
 __global__ void __launch_bounds__(256) hb_nchw_stem_pre_kernel(const StemPre g) {
   constexpr int CIS = 16 / sizeof(T);
+  griddep_launch_dependents();  // the conv kernel behind this one may set itself up meanwhile
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
   const long long first = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
   const T* in = static_cast<const T*>(g.in);

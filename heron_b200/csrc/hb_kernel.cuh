@@ -159,6 +159,9 @@ hb_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   if (CG == 2) cluster_sync();  // the peer's barriers exist before anything arrives on them
   tc_fence_after();
   const uint32_t tmem_base = bars->tmem_base;
+  // Everything above touched only this CTA's own resources; the operands may still be being
+  // written by the layout kernel this one was launched behind.
+  griddep_wait();
 
   const int tiles_per_batch = p.tiles_m * p.tiles_n;
   const int first_tile = blockIdx.x / CG;  // a pair of CTAs walks the tile list together

@@ -244,6 +244,14 @@ int run_pre(const hb_plan* plan, cudaStream_t stream) {
 
 int run_main(const hb_plan* plan, cudaStream_t stream);
 
+// The conv / GEMM kernel of this plan runs right behind another kernel of the same plan (layout
+// glue, filter unpack, the scan operand, split-K zeroing): it is launched with programmatic
+// serialization, sets itself up while that kernel drains and waits for it in griddep_wait().
+bool follows_own_kernel(const hb_plan* plan) {
+  return plan->has_pre || plan->packed_w != nullptr || plan->scan_b != nullptr ||
+         (!plan->strip && plan->p.ksplit > 1 && !plan->p.kslab);
+}
+
 int run_plan(const hb_plan* plan, cudaStream_t stream) {
   if (plan->has_pre) {
     const int rc = run_pre(plan, stream);
@@ -286,13 +294,25 @@ int run_main(const hb_plan* plan, cudaStream_t stream) {
   }
   if (plan->strip) {
     const hb::StripParams& sp = plan->sp;
+    cudaLaunchConfig_t cfg;
+    std::memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = dim3(plan->grid);
+    cfg.blockDim = dim3(hb::kThreads);
+    cfg.dynamicSmemBytes = plan->smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = follows_own_kernel(plan) ? 1 : 0;
+    cudaError_t e;
     if (sp.esize_out == 2)
-      hb::hb_conv_strip_kernel<2, 0><<<plan->grid, hb::kThreads, plan->smem, stream>>>(plan->tmA, plan->tmB, sp);
+      e = cudaLaunchKernelEx(&cfg, hb::hb_conv_strip_kernel<2, 0>, plan->tmA, plan->tmB, sp);
     else if (sp.esize_in == 2)
-      hb::hb_conv_strip_kernel<4, 0><<<plan->grid, hb::kThreads, plan->smem, stream>>>(plan->tmA, plan->tmB, sp);
+      e = cudaLaunchKernelEx(&cfg, hb::hb_conv_strip_kernel<4, 0>, plan->tmA, plan->tmB, sp);
     else
-      hb::hb_conv_strip_kernel<4, 1><<<plan->grid, hb::kThreads, plan->smem, stream>>>(plan->tmA, plan->tmB, sp);
-    return cudaGetLastError() == cudaSuccess ? HB_OK : HB_ERR_LAUNCH;
+      e = cudaLaunchKernelEx(&cfg, hb::hb_conv_strip_kernel<4, 1>, plan->tmA, plan->tmB, sp);
+    return e == cudaSuccess ? HB_OK : HB_ERR_LAUNCH;
   }
   const bool half_out = plan->p.esize_out == 2;
   const bool i8 = plan->p.kind == 1;
@@ -319,11 +339,14 @@ int launch_kernel(const hb_plan* plan, cudaStream_t stream) {
   cfg.blockDim = dim3(hb::kUmmaThreads);
   cfg.dynamicSmemBytes = plan->smem;
   cfg.stream = stream;
-  cudaLaunchAttribute attr;
-  attr.id = cudaLaunchAttributeClusterDimension;
-  attr.val.clusterDim.x = CG; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
-  cfg.attrs = &attr;
-  cfg.numAttrs = 1;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = CG; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+  // behind a layout kernel of the same plan: start early, wait in the kernel (griddep_wait)
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = follows_own_kernel(plan) ? 2 : 1;
   const cudaError_t e = cudaLaunchKernelEx(&cfg, hb::hb_umma_kernel<OUT_BYTES, CG, KIND>, plan->tmA,
                                            plan->tmB, plan->tmC, plan->tmB2, plan->p);
   return e == cudaSuccess ? HB_OK : HB_ERR_LAUNCH;

@@ -297,6 +297,13 @@ __device__ __forceinline__ void tma_load_im2col_5d_cg(uint32_t dst, const CUtens
         : "memory");
   }
 }
+// Programmatic dependent launch: a kernel launched with the programmatic-serialization attribute
+// may start while its predecessor in the stream is still running; griddep_wait() returns once
+// that predecessor has completed and its writes are visible (at once when there is none).
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void griddep_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
 // L2 prefetch of a tile a few ring stages ahead (no shared memory, no completion to wait for).
 __device__ __forceinline__ void tma_prefetch_3d(const CUtensorMap* m, int x, int y, int z) {
   asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global.tile [%0, {%1, %2, %3}];" ::"l"(
