@@ -330,8 +330,7 @@ def run_ours(args):
                     "ms_per_step": round(e2e_ms, 4), "steps": e2e_steps,
                     "how": "pinned host inputs -> device -> kernel -> pinned host output every step, "
                            "3-stream pipeline of depth 2"},
-            # one kernel per step, plus the zeroing launch when the plan splits the reduction
-            "gpu_launches": args.steps * (2 if sets[0].knobs().get("split_k", 1) > 1 else 1),
+            "gpu_launches": args.steps,  # one kernel per step
         }
         if shards:
             line["config"]["with_all_gather"] = {

@@ -300,6 +300,10 @@ int hb_last_status(int* status) {
   if (v != 0) {
     const int zero = 0;
     if (cudaMemcpyToSymbol(hb::g_hb_status, &zero, sizeof(int)) != cudaSuccess) return HB_ERR_LAUNCH;
+    // a kernel that gave up may have left turn-taking flags of its split-K tiles half way
+    void* flags = nullptr;
+    if (cudaGetSymbolAddress(&flags, g_hb_split_flags) == cudaSuccess && flags)
+      cudaMemset(flags, 0, sizeof(int) * HB_FLAG_SLOTS);
   }
   return HB_OK;
 }

@@ -1,38 +1,10 @@
-// Small kernels around the MMA kernels: zeroing for split-K, the x86 filter unpack, the layout
+// Small kernels around the MMA kernels: the scan operand, the x86 filter unpack, the layout
 // glue of the NCHW operators (input / filter transposes, the few-channel form, the split-K
 // reduction that writes NCHW).
 #pragma once
 #include "hb_kernel.cuh"
 
 namespace hb {
-
-// Zeroes the output tiles that the split-K work items of hb_umma_kernel add into (4-byte
-// elements).  blockIdx.x walks (tile, row group) pairs; a warp writes 128 consecutive bytes of a row.
-__global__ void hb_zero_tiles_kernel(const KParams p, int tile_rows, int row_groups) {
-  griddep_launch_dependents();
-  const int tiles = (p.num_tiles - p.whole_tiles) / p.ksplit;
-  const int tiles_per_batch = p.tiles_m * p.tiles_n;
-  const int rows_per_group = tile_rows / row_groups;
-  for (int item = blockIdx.x; item < tiles * row_groups; item += gridDim.x) {
-    const int t = p.whole_tiles + item / row_groups;
-    const int g = item - (item / row_groups) * row_groups;
-    const int b = t / tiles_per_batch;
-    const int r = t - b * tiles_per_batch;
-    const int mb = p.raster ? (r % p.tiles_m) : (r / p.tiles_n);
-    const int nb = p.raster ? (r / p.tiles_m) : (r % p.tiles_n);
-    const int m0 = mb * tile_rows + g * rows_per_group;
-    const int n0 = nb * p.BN;
-    const int rows = min(rows_per_group, p.M - m0);
-    const int cols = min(p.BN, p.N - n0);
-    if (rows <= 0 || cols <= 0) continue;
-    uint32_t* base = static_cast<uint32_t*>(p.C) + static_cast<long long>(b) * p.batch_stride_c +
-                     static_cast<long long>(m0) * p.ldc + n0;
-    for (int i = threadIdx.x; i < rows * cols; i += blockDim.x) {
-      const int rr = i / cols;
-      base[static_cast<long long>(rr) * p.ldc + (i - rr * cols)] = 0u;
-    }
-  }
-}
 
 // The constant operand of the reference's scan operator: B[i][j] = (i <= j) ? 0 : 1, an (N, K)
 // matrix whose product with A gives out[m][n] = sum of A[m][k] over k < n.

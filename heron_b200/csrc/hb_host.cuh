@@ -265,8 +265,8 @@ int check_knobs(const Problem& pr, const hb_knobs& k, int* smem_bytes, int* tmem
   if (k.tail_split != 0 && k.tail_split != 1 && k.tail_split != 2 && k.tail_split != 4) return HB_ERR_KNOB;
   if (k.split_k < 0 || k.split_k > 4) return HB_ERR_KNOB;
   if (k.split_k > 1) {
-    // slices add into the output: 4-byte elements only; fp32 sums stay order-independent with two
-    if (eo != 4 || (pr.out == HB_F32 && k.split_k != 2) || k.tail_split > 1) return HB_ERR_KNOB;
+    // slices add into the output, one after the other: 4-byte elements only
+    if (eo != 4 || k.tail_split > 1) return HB_ERR_KNOB;
   }
   if (pr.conv && (pr.CI * es) % k.swizzle_bytes != 0) return HB_ERR_KNOB;
   // whole MN-major chunks in every CTA of the group
@@ -348,11 +348,39 @@ struct hb_plan {
 #define HB_STATIC_SCRATCH_BYTES (4u << 20)
 static __device__ __align__(256) int8_t g_hb_static_scratch[HB_STATIC_SCRATCH_BYTES];
 
+// Turn-taking flags of split-K tiles (KParams::flags): one int per sliced tile, zero between
+// launches.  A plan takes a run of slots from a rotating cursor, so launches that overlap on the
+// GPU use different flags unless more than kFlagSlots / 148 of them are in flight at once.
+#define HB_FLAG_SLOTS 16384
+static __device__ int g_hb_split_flags[HB_FLAG_SLOTS];
+
 namespace {
 
 constexpr int kMaxDevices = 64;
+int* g_split_flags_addr[kMaxDevices] = {nullptr};
+unsigned g_split_flags_cursor = 0;
 void* g_static_scratch_addr[kMaxDevices] = {nullptr};
 std::mutex g_static_scratch_mutex;
+
+// `count` consecutive flags of the current device's flag array (see g_hb_split_flags).
+int split_flags(int count, int** out) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return HB_ERR_DEVICE;
+  if (count <= 0 || count > HB_FLAG_SLOTS) return HB_ERR_SHAPE;
+  std::lock_guard<std::mutex> lock(g_static_scratch_mutex);
+  if (g_split_flags_addr[dev] == nullptr) {
+    void* ptr = nullptr;
+    if (cudaGetSymbolAddress(&ptr, g_hb_split_flags) != cudaSuccess || ptr == nullptr) {
+      cudaGetLastError();
+      return HB_ERR_LAUNCH;
+    }
+    g_split_flags_addr[dev] = static_cast<int*>(ptr);
+  }
+  if (g_split_flags_cursor + count > HB_FLAG_SLOTS) g_split_flags_cursor = 0;
+  *out = g_split_flags_addr[dev] + g_split_flags_cursor;
+  g_split_flags_cursor += count;
+  return HB_OK;
+}
 
 // Device address of g_hb_static_scratch on the current device (looked up on first use there).
 int static_scratch_address(void** out) {

@@ -73,6 +73,11 @@ struct KParams {
   // kslab = 1 (with ksplit > 1 and whole_tiles == 0): slice s of every tile is stored, not added,
   // into slab s of a (ksplit, M, N) workspace; a later kernel sums the slabs in a fixed order.
   int kslab;
+  // flags != nullptr (with ksplit > 1, no slabs): the K slices of a tile take turns instead of adding
+  // into a zeroed output.  Slice 0 stores its partial sums, slice s > 0 waits until flags[tile] shows
+  // that every epilogue warp of slice s-1 has finished, then adds its own.  No zeroing pass, and the
+  // order of the additions is fixed.  The last arrival resets the flag for the next launch.
+  int* flags;
   uint32_t idesc_split;
   long long wait_limit_cycles;  // 0: the default bound on every mbarrier wait
   uint32_t idesc;
@@ -423,7 +428,11 @@ hb_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     for (int t = first_tile; ok && t < p.num_tiles; t += tile_step) {
       int b, m_pair, n0, bn, kb0, kb1, kslice;
       decode(t, b, m_pair, n0, bn, kb0, kb1, kslice);
-      const bool reduce = OUT_BYTES == 4 && p.ksplit > 1 && t >= p.whole_tiles && !p.kslab;
+      const bool ksliced = OUT_BYTES == 4 && p.ksplit > 1 && t >= p.whole_tiles && !p.kslab;
+      const bool chain = ksliced && p.flags != nullptr;
+      const bool reduce = ksliced && (!chain || kslice > 0);
+      int* const flag = chain ? p.flags + (t - p.whole_tiles) / p.ksplit : nullptr;
+      constexpr int kArrivals = kEpiWarps * CG;  // epilogue warps that work on one tile
       const int zc = p.kslab ? kslice : b;  // third coordinate of the output: batch, or workspace slab
       const int row0 = m_pair + static_cast<int>(cta_rank) * kTileM + q * 32;
       if (!(p.probe == 8 ? mbar_wait(smem_u32(&bars->tmem_full[acc]), acc_phase, wctx)
@@ -432,6 +441,27 @@ hb_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         break;
       }
       tc_fence_after();
+      if (chain && kslice > 0) {
+        // wait (bounded) for the slice before this one to have written the tile
+        int got = 1;
+        if (lane == 0) {
+          const long long t0 = clock64();
+          while (ld_acquire_gpu(flag) < kslice * kArrivals) {
+            if (*abort_flag || clock64() - t0 > wctx.limit_cycles) {
+              *abort_flag = 1;
+              got = 0;
+              break;
+            }
+            __nanosleep(64);
+          }
+        }
+        got = __shfl_sync(0xffffffffu, got, 0);
+        if (!got) {
+          ok = false;
+          break;
+        }
+        fence_proxy_async_all();
+      }
       const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) +
                               static_cast<uint32_t>(acc * p.BN);
       // Software pipeline over 128-byte column chunks: the TMEM load of chunk i+1 is in flight
@@ -565,6 +595,16 @@ hb_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
               }
             }
           }
+        }
+      }
+      if (chain) {
+        // this warp's part of the tile is in memory: tell the next slice, or, as the very last
+        // arrival of the tile, put the flag back to zero
+        if (p.epilogue) bulk_wait<0>();
+        __syncwarp();
+        if (lane == 0) {
+          __threadfence();
+          if (atomicAdd(flag, 1) + 1 == p.ksplit * kArrivals) atomicExch(flag, 0);
         }
       }
       if (++acc == p.acc_stages) {

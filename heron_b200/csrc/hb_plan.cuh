@@ -161,12 +161,12 @@ int build_plan(Driver& d, const Problem& pr, const hb_knobs& k, const ConvGeom* 
   const int tail = tiles % units;
   int split = 1, ksplit = 1;
   // Split-K first: a slice of the reduction keeps the full-width MMA shape, so its cost falls in
-  // proportion, but the output tiles must be zeroed by a launch of its own and every slice then
-  // adds its partial sums through the L2 atomic units.  Measured on B200: about 3 us for the extra
-  // launch and 0.7 adds per ns; a K block of a full-width tile takes about 0.3 us in the GEMMs and
-  // 0.58 us in the im2col conv.  A partly filled wave also runs faster than a full one where the
-  // kernel is load-bound, so the library takes split-K only when the saving is clearly more than
-  // that cost and at least a quarter of the whole launch; a tuner may force it either way.
+  // proportion.  The slices of a tile take turns (KParams::flags): the first stores, the others add
+  // through the L2 atomic units (about 0.7 adds per ns on B200) once the one before has finished,
+  // which costs about 2 us of hand-over.  A K block of a full-width tile takes about 0.3 us in the
+  // GEMMs and 0.58 us in the im2col conv.  A partly filled wave also runs faster than a full one
+  // where the kernel is load-bound (the convs), so there the saving has to be a quarter of the
+  // whole launch as well; a tuner may force it either way.
   auto waves_of = [&](int s) {
     return static_cast<double>((static_cast<long long>(s) * tail + units - 1) / units) / s;
   };
@@ -176,16 +176,16 @@ int build_plan(Driver& d, const Problem& pr, const hb_knobs& k, const ConvGeom* 
     if (p.num_kb < k.split_k) return HB_ERR_KNOB;
     ksplit = tail > 0 ? k.split_k : 1;
   } else if (k.split_k == 0 && k.tail_split == 0 && eo == 4 && tail > 0) {
-    const int max_ks = pr.out == HB_F32 ? 2 : 4;
+    const int max_ks = 2;  // more slices wait on one another's epilogues: left to an explicit knob
     const double kb_us = pr.conv ? 0.58 : 0.30;
     const double tile_elems = static_cast<double>(hb::kTileM) * cgrp * k.tile_n;
     double best_gain = 0.0;
     for (int s2 = 2; s2 <= max_ks; ++s2) {
       if (p.num_kb < 4 * s2) continue;
       const double saving = (1.0 - waves_of(s2)) * p.num_kb * kb_us;
-      const double cost = 3.0 + tail * tile_elems * s2 / 700e3;
+      const double cost = 2.0 + tail * tile_elems * (s2 - 1) / 700e3;
       const double launch_waves = static_cast<double>((tiles + units - 1) / units);
-      if ((1.0 - waves_of(s2)) < 0.25 * launch_waves) continue;
+      if (pr.conv && (1.0 - waves_of(s2)) < 0.25 * launch_waves) continue;
       if (saving > 1.25 * cost && saving - cost > best_gain) { best_gain = saving - cost; ksplit = s2; }
     }
   }
@@ -205,6 +205,10 @@ int build_plan(Driver& d, const Problem& pr, const hb_knobs& k, const ConvGeom* 
   p.split = split;
   p.ksplit = ksplit;
   p.kslab = kslab ? 1 : 0;
+  if (ksplit > 1 && !kslab) {
+    rc = split_flags(tail, &p.flags);
+    if (rc != HB_OK) return rc;
+  }
   p.whole_tiles = kslab ? 0 : ((split > 1 || ksplit > 1) ? tiles - tail : tiles);
   p.num_tiles = p.whole_tiles + (tiles - p.whole_tiles) * split * ksplit;
   p.idesc_split = make_idesc(kind, pr.in_a, pr.in_b, hb::kTileM * cgrp, k.tile_n / split, b_mn_major(pr));
@@ -248,8 +252,7 @@ int run_main(const hb_plan* plan, cudaStream_t stream);
 // glue, filter unpack, the scan operand, split-K zeroing): it is launched with programmatic
 // serialization, sets itself up while that kernel drains and waits for it in griddep_wait().
 bool follows_own_kernel(const hb_plan* plan) {
-  return plan->has_pre || plan->packed_w != nullptr || plan->scan_b != nullptr ||
-         (!plan->strip && plan->p.ksplit > 1 && !plan->p.kslab);
+  return plan->has_pre || plan->packed_w != nullptr || plan->scan_b != nullptr;
 }
 
 int run_plan(const hb_plan* plan, cudaStream_t stream) {
@@ -316,13 +319,6 @@ int run_main(const hb_plan* plan, cudaStream_t stream) {
   }
   const bool half_out = plan->p.esize_out == 2;
   const bool i8 = plan->p.kind == 1;
-  if (plan->p.ksplit > 1 && !plan->p.kslab) {
-    const int row_groups = 8;
-    const int sliced_tiles = (plan->p.num_tiles - plan->p.whole_tiles) / plan->p.ksplit;
-    hb::hb_zero_tiles_kernel<<<sliced_tiles * row_groups, 256, 0, stream>>>(
-        plan->p, hb::kTileM * plan->knobs.cta_group, row_groups);
-    if (cudaGetLastError() != cudaSuccess) return HB_ERR_LAUNCH;
-  }
   if (plan->knobs.cta_group == 2) {
     if (half_out) return launch_kernel<2, 2, 0>(plan, stream);
     return i8 ? launch_kernel<4, 2, 1>(plan, stream) : launch_kernel<4, 2, 0>(plan, stream);

@@ -297,6 +297,15 @@ __device__ __forceinline__ void tma_load_im2col_5d_cg(uint32_t dst, const CUtens
         : "memory");
   }
 }
+__device__ __forceinline__ int ld_acquire_gpu(const int* p) {
+  int v;
+  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+// Orders later async-proxy accesses (TMA stores / reductions) of this thread after what it has
+// observed through ordinary loads.
+__device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
+
 // Programmatic dependent launch: a kernel launched with the programmatic-serialization attribute
 // may start while its predecessor in the stream is still running; griddep_wait() returns once
 // that predecessor has completed and its writes are visible (at once when there is none).

@@ -240,9 +240,9 @@ class rasterOp(SchedOp):
 
 
 class splitKOp(SchedOp):
-    """Whether the work items of a partly filled wave are cut along the reduction (their partial
-    sums are added into a zeroed output).  0 leaves the choice to the library, 1 turns it off.
-    Only 4-byte outputs can be added into; fp32 sums stay order-independent with two slices."""
+    """Whether the work items of a partly filled wave are cut along the reduction (the slices of a
+    tile add their partial sums one after the other).  0 leaves the choice to the library, 1 turns
+    it off.  Only 4-byte outputs can be added into."""
 
     def perform(self, s, stage_name, ctx):
         km = ctx.knob_manager
@@ -254,8 +254,7 @@ class splitKOp(SchedOp):
         if km.is_building:
             most = 1
             if eo == 4:
-                most = 2 if p["out_dtype"] == "float32" else 4
-                most = max(1, min(most, (K * es) // 128))  # every slice keeps at least one K block
+                most = max(1, min(4, (K * es) // 128))  # every slice keeps at least one K block
             km.define_value(split_k, 0, most, 0, True)
         ctx.kernel_knobs["split_k"] = km.get_val(split_k)
         ctx.addSchedDesc("## split-K %s\n" % ctx.kernel_knobs["split_k"])

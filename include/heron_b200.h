@@ -73,9 +73,10 @@ typedef struct {
                         this many column slices (1, 2 or 4); 0 = library picks                      */
   int split_k;       /* work items that do not fill a wave of the persistent grid (the tiles of the
                         last wave, or all tiles of a small problem) are cut into this many slices of
-                        the reduction instead; the slices add into a zeroed output (TMA reduce-add
-                        or red.global).  1 = off, 2..4 (fp32 output: 2 only, so that the sum does
-                        not depend on arrival order), 0 = library picks.  4-byte outputs only       */
+                        the reduction instead; the slices of a tile take turns: the first stores,
+                        the next ones add (TMA reduce-add or red.global) once the one before has
+                        finished, so the order of the additions is fixed.  1 = off, 2..4,
+                        0 = library picks.  4-byte outputs only                                   */
   int reserved;      /* diagnostic probe modes; leave 0                                            */
 } hb_knobs;
 

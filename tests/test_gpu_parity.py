@@ -180,12 +180,12 @@ def test_split_k_fp16_is_deterministic_and_close(K, co):
     want = co.gemm_f16(a, b)
     first = None
     for _ in range(3):
-        for knobs in (dict(split_k=2), dict(split_k=2, epilogue=2)):
+        for knobs in (dict(split_k=4), dict(split_k=4, epilogue=2)):
             got = k_gemm(K, a, b, knobs=knobs)
             check(got, want, "split-K fp16")
             if first is None:
                 first = got.clone()
-            assert torch.equal(got, first)  # two partial sums: the order of arrival cannot matter
+            assert torch.equal(got, first)  # the slices of a tile add in slice order, whoever finishes first
 
 
 def test_split_k_conv_and_bmm(K, co):
@@ -204,7 +204,7 @@ def test_split_k_rejected_where_it_cannot_add(K):
     from heron_b200._lib import HB_ERR_KNOB, HeronB200Error
     a = torch.zeros(128, 512, dtype=torch.float16, device="cuda")
     b = torch.zeros(128, 512, dtype=torch.float16, device="cuda")
-    for knobs, out in ((dict(split_k=2), torch.float16), (dict(split_k=3), torch.float32), (dict(split_k=5), torch.float32),
+    for knobs, out in ((dict(split_k=2), torch.float16), (dict(split_k=5), torch.float32),
                        (dict(split_k=2, tail_split=2), torch.float32)):
         with pytest.raises(HeronB200Error) as e:
             K.gemm(a, b, out=torch.empty(128, 128, dtype=out, device="cuda"), knobs=knobs)
