@@ -100,6 +100,42 @@ def test_argument_errors_come_before_the_device(hb_lib):
     assert hb_lib.hb_conv2d_packed_scratch_bytes(64, 64, 3, 3) == 3 * 3 * 64 * 64
 
 
+def test_argument_errors_of_the_neighbour_operators(hb_lib):
+    """gemv, scan, the 1-D / 3-D / NCHW convolutions: bad shapes, missing or small scratch and
+    misaligned scratch are answered on the host."""
+    from heron_b200 import _lib
+    buf = np.zeros(1 << 16, dtype=np.uint8)
+    base = (buf.ctypes.data + 255) & ~255
+    p = ctypes.c_void_p(base)
+    F16, F32, U8, S8, S32 = _lib.HB_F16, _lib.HB_F32, _lib.HB_U8, _lib.HB_S8, _lib.HB_S32
+    assert hb_lib.hb_gemv(p, p, p, 0, 64, F16, F16, F32, None, None) == _lib.HB_ERR_SHAPE
+    assert hb_lib.hb_gemv(p, p, p, 64, 12, U8, S8, S32, None, None) == _lib.HB_ERR_SHAPE  # K bytes % 16
+    assert hb_lib.hb_gemv(p, p, p, 64, 64, F16, S8, F32, None, None) == _lib.HB_ERR_DTYPE
+    assert hb_lib.hb_scan_scratch_bytes(100, 48, F16) == 100 * 48 * 2
+    assert hb_lib.hb_scan_scratch_bytes(100, 48, U8) == 100 * 48
+    assert hb_lib.hb_scan(p, p, 16, 100, 48, F16, F32, None, 0, None, None) == _lib.HB_ERR_SCRATCH
+    assert hb_lib.hb_scan(p, p, 16, 100, 48, F16, F32, p, 100, None, None) == _lib.HB_ERR_SCRATCH
+    assert hb_lib.hb_scan(p, p, 0, 100, 48, F16, F32, p, 1 << 15, None, None) == _lib.HB_ERR_SHAPE
+    # NCHW family: window larger than the padded image, no scratch, scratch not 256-byte aligned
+    assert hb_lib.hb_conv2d_nchw_scratch_bytes(2, 4, 4, 16, 16, 7, 7, 1, 1, 0, F16, F16) == 0
+    need = hb_lib.hb_conv2d_nchw_scratch_bytes(2, 8, 8, 16, 16, 3, 3, 1, 1, 1, F16, F16)
+    assert need > 0 and need % 256 == 0
+    args = [p, p, p, 2, 8, 8, 16, 16, 3, 3, 1, 1, 1, F16, F16, F16]
+    assert hb_lib.hb_conv2d_nchw(*args, None, 0, None, None) == _lib.HB_ERR_SCRATCH
+    assert hb_lib.hb_conv2d_nchw(*args, p, need - 1, None, None) == _lib.HB_ERR_SCRATCH
+    assert hb_lib.hb_conv2d_nchw(*args, ctypes.c_void_p(base + 16), need, None, None) == _lib.HB_ERR_ALIGN
+    assert hb_lib.hb_conv1d_ncw_scratch_bytes(2, 5, 16, 16, 9, 1, 0, F16, F16) == 0
+    assert hb_lib.hb_conv1d_ncw(p, p, p, 2, 50, 16, 16, 3, 1, 1, F16, F16, F16, None, 0, None, None) == _lib.HB_ERR_SCRATCH
+    assert hb_lib.hb_conv3d_ncdhw_scratch_bytes(1, 2, 4, 4, 16, 16, 3, 3, 3, 1, 1, 1, 0, F16, F16) == 0  # depth 2 < 3 taps
+    assert hb_lib.hb_conv3d_ncdhw_scratch_bytes(1, 2, 4, 4, 16, 16, 3, 3, 3, 1, 1, 1, 1, F16, F16) > 0
+    rc = hb_lib.hb_conv3d_ncdhw(p, p, p, 1, 2, 4, 4, 16, 16, 3, 3, 3, 1, 1, 1, 1, F16, F16, F16, None, 0, None, None)
+    assert rc == _lib.HB_ERR_SCRATCH
+    rc = hb_lib.hb_conv1d_nwc_packed(p, p, p, 1, 50, 30, 64, 3, 1, 1, 1, 64, p, 1 << 15, None, None)
+    assert rc == _lib.HB_ERR_SHAPE  # CI % 4
+    rc = hb_lib.hb_conv1d_nwc_packed(p, p, p, 1, 50, 32, 64, 3, 1, 1, 1, 40, p, 1 << 15, None, None)
+    assert rc == _lib.HB_ERR_SHAPE  # sco
+
+
 def test_no_cpu_fallback(hb_lib):
     """Without a usable sm_100 device a well-formed call reports HB_ERR_DEVICE instead of
     computing anywhere else."""
