@@ -4,6 +4,7 @@ Bit-exact for the integer paths; for fp16 inputs with fp32 accumulation the boun
 error of 1e-2 relative to the largest magnitude of the oracle's output (the benchmark's stated
 tolerance) — observed errors are around 1e-6 (fp32 output) and 5e-4 (fp16 output).
 """
+import os
 import random
 
 import numpy as np
@@ -879,7 +880,19 @@ def test_bounded_wait_runs_out_cleanly(K, co):
 # ---- property tests over random small shapes ------------------------------------------------------
 from hypothesis import HealthCheck, given, settings, strategies as st  # noqa: E402
 
-_prop = settings(max_examples=40, deadline=None, suppress_health_check=[HealthCheck.function_scoped_fixture])
+
+
+def _props(examples):
+    """Settings of the property tests. The examples are drawn from a fixed seed, so that a run of
+    the suite is repeatable; HB_PROP_RANDOM=1 draws fresh ones and HB_PROP_SCALE=n draws n times as
+    many, for a deeper search by hand."""
+    scale = int(os.environ.get("HB_PROP_SCALE", "1"))
+    return settings(max_examples=examples * scale, deadline=None, database=None,
+                    derandomize=os.environ.get("HB_PROP_RANDOM", "0") != "1",
+                    suppress_health_check=[HealthCheck.function_scoped_fixture])
+
+
+_prop = _props(40)
 
 
 @_prop
@@ -941,7 +954,7 @@ def test_conv_strip_random_geometry(K, co, N, H, W, CO, KH, KW, pad, dil, half_o
     check(got, co.conv2d_nhwc_f16(x, w, 1, pad, dil, od), "strip %s" % ((N, H, W, CO, KH, KW, pad, dil),))
 
 
-@settings(max_examples=80, deadline=None, suppress_health_check=[HealthCheck.function_scoped_fixture])
+@_props(80)
 @given(N=st.integers(1, 4), CI=st.sampled_from([1, 3, 4, 8, 16, 24, 64, 72, 136]), H=st.integers(1, 24),
        W=st.integers(1, 24), CO8=st.integers(1, 12), KH=st.integers(1, 7), KW=st.integers(1, 8),
        sh=st.integers(1, 3), sw=st.integers(1, 3), pad=st.integers(0, 3), int8=st.booleans(),
