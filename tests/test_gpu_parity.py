@@ -727,6 +727,42 @@ def test_conv_nchw_fp16(K, co, case):
         check(out, want, "nchw %s" % (case,))
 
 
+# Layers of the other two published networks (VGG-16, Inception-v3; the table files under
+# heron_b200/configs/), at a batch the oracle finishes in seconds: odd image sizes (299, 149, 73,
+# 35, 17), 1x7 and 7x1 windows with the operator's single padding number applied to both axes,
+# channel counts that are not powers of two, stride 2 without padding.
+NETWORK_LAYER_CASES = [
+    (1, 3, 299, 299, 32, 3, 3, 2, 0),
+    (1, 32, 149, 149, 32, 3, 3, 1, 0),
+    (1, 64, 73, 73, 80, 1, 1, 1, 0),
+    (1, 80, 73, 73, 192, 3, 3, 1, 0),
+    (2, 48, 35, 35, 64, 5, 5, 1, 2),
+    (2, 192, 35, 35, 48, 1, 1, 1, 0),
+    (1, 288, 35, 35, 384, 3, 3, 2, 0),
+    (2, 128, 17, 17, 128, 1, 7, 1, 0),
+    (2, 160, 17, 17, 192, 7, 1, 1, 3),
+    (2, 768, 17, 17, 160, 1, 1, 1, 0),
+    (2, 192, 17, 17, 320, 3, 3, 2, 0),
+    (2, 384, 8, 8, 384, 1, 3, 1, 0),
+    (2, 384, 8, 8, 384, 3, 1, 1, 1),
+    (2, 2048, 8, 8, 448, 1, 1, 1, 0),
+    (1, 3, 224, 224, 64, 3, 3, 1, 1),
+    (1, 512, 14, 14, 512, 3, 3, 1, 1),
+]
+
+
+@pytest.mark.parametrize("case", NETWORK_LAYER_CASES)
+def test_conv_nchw_network_layers(K, co, case):
+    N, CI, H, W, CO, KH, KW, s, p = case
+    rng = np.random.default_rng(sum(case))
+    x = rng.standard_normal((N, CI, H, W)).astype(np.float16)
+    w = (rng.standard_normal((CO, CI, KH, KW)) / np.sqrt(CI * KH * KW)).astype(np.float16)
+    want = co.conv2d_nchw(x, w, s, p, np.float16)
+    out = poison(want.shape, torch.float16)
+    K.conv2d_nchw(dev(x), dev(w), stride=s, padding=p, out=out)
+    check(out, want, "network layer %s" % (case,))
+
+
 def test_conv_nchw_int8_and_plan(K, co):
     rng = np.random.default_rng(12)
     x, w = rand_i8(rng, (2, 32, 10, 10), False), rand_i8(rng, (48, 32, 3, 3), True)
