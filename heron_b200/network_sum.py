@@ -1,5 +1,6 @@
 """Whole-network operator sums: the reference's figure-10 experiment
-(tests/figure10/run.py, tests/figure10/configs/{resnet50,bert}.json) on the B200 kernels.
+(tests/figure10/run.py, tests/figure10/configs/{resnet50,vgg16,inceptionv3,bert}.json) on the B200
+kernels.
 
     python -m heron_b200.network_sum -c heron_b200/configs/resnet50_nchw_fp16.json [--tune N]
 
@@ -7,7 +8,8 @@ Every case of the JSON file is ``[op, shape arguments, count]``: the operator is
 (library default knobs, or the best of an ``N``-trial CGA run with ``--tune N``), timed on the
 device with CUDA events, and the network figure is sum(latency * count) — the quantity the
 reference's PyTorch baselines log (tests/figure10/pytorch/logs/*.log).  The layer tables are the
-published ResNet-50 / BERT-base operator shapes at batch 16, in the reference's case format.
+published ResNet-50 / VGG-16 / Inception-v3 / BERT-base operator shapes at batch 16, in the
+reference's case format.
 """
 import argparse
 import json
