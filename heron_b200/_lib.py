@@ -90,11 +90,12 @@ class HbKnobs(ctypes.Structure):
         ("conv_algo", ctypes.c_int),
         ("tail_split", ctypes.c_int),
         ("split_k", ctypes.c_int),
+        ("k_slices", ctypes.c_int),
         ("reserved", ctypes.c_int),
     ]
 
     FIELDS = ("tile_n", "stages", "swizzle_bytes", "acc_stages", "raster", "epilogue", "max_ctas",
-              "cta_group", "l2_prefetch", "conv_algo", "tail_split", "split_k", "reserved")
+              "cta_group", "l2_prefetch", "conv_algo", "tail_split", "split_k", "k_slices", "reserved")
 
     @classmethod
     def from_dict(cls, d):

@@ -54,13 +54,19 @@ bool setup_device(Driver* d) {
   if (prop.major != 10) return false;
   d->sm_count = prop.multiProcessorCount;
   // Opt in to the large dynamic shared-memory carve-out for every kernel instantiation.
-  const void* kernels[9] = {
-      reinterpret_cast<const void*>(&hb::hb_umma_kernel<4, 1, 0>),
-      reinterpret_cast<const void*>(&hb::hb_umma_kernel<2, 1, 0>),
-      reinterpret_cast<const void*>(&hb::hb_umma_kernel<4, 1, 1>),
-      reinterpret_cast<const void*>(&hb::hb_umma_kernel<4, 2, 0>),
-      reinterpret_cast<const void*>(&hb::hb_umma_kernel<2, 2, 0>),
-      reinterpret_cast<const void*>(&hb::hb_umma_kernel<4, 2, 1>),
+  const void* kernels[15] = {
+      reinterpret_cast<const void*>(&hb::hb_umma_kernel<4, 1, 0, 1>),
+      reinterpret_cast<const void*>(&hb::hb_umma_kernel<2, 1, 0, 1>),
+      reinterpret_cast<const void*>(&hb::hb_umma_kernel<4, 1, 1, 1>),
+      reinterpret_cast<const void*>(&hb::hb_umma_kernel<4, 2, 0, 1>),
+      reinterpret_cast<const void*>(&hb::hb_umma_kernel<2, 2, 0, 1>),
+      reinterpret_cast<const void*>(&hb::hb_umma_kernel<4, 2, 1, 1>),
+      reinterpret_cast<const void*>(&hb::hb_umma_kernel<4, 1, 0, 2>),
+      reinterpret_cast<const void*>(&hb::hb_umma_kernel<2, 1, 0, 2>),
+      reinterpret_cast<const void*>(&hb::hb_umma_kernel<4, 1, 1, 2>),
+      reinterpret_cast<const void*>(&hb::hb_umma_kernel<4, 2, 0, 2>),
+      reinterpret_cast<const void*>(&hb::hb_umma_kernel<2, 2, 0, 2>),
+      reinterpret_cast<const void*>(&hb::hb_umma_kernel<4, 2, 1, 2>),
       reinterpret_cast<const void*>(&hb::hb_conv_strip_kernel<4, 0>),
       reinterpret_cast<const void*>(&hb::hb_conv_strip_kernel<2, 0>),
       reinterpret_cast<const void*>(&hb::hb_conv_strip_kernel<4, 1>)};
@@ -237,9 +243,22 @@ void resolve_knobs(const Problem& pr, const hb_knobs* in, int sm_count, hb_knobs
     k.tile_n = best;
   }
   if (k.acc_stages == 0) k.acc_stages = (2 * k.tile_n <= 512) ? 2 : 1;
+  if (k.k_slices == 0) {
+    // Two swizzle spans of K behind one barrier halve what the MMA thread and the producers spend
+    // per span on waits, fences and commits.  Measured on a B200: a gain from 8 spans per tile on
+    // if the ring still holds three such stages (4096^3 fp16 in CTA pairs +3 %, int8 +10 %, tiles
+    // of 64 or 128 columns +25..38 %), a loss with two (4096^3 in single CTAs -9 %, BERT's
+    // 512 x 768 x 768 -14 %) or with 4 spans.
+    const int sw = k.swizzle_bytes;
+    const long long kblocks = (static_cast<long long>(pr.K) * es + sw - 1) / sw;
+    const int epi = k.epilogue == 1 ? hb::kEpiWarps * 2 * hb::kEpiBufBytes : 0;
+    const int wide = 2 * stage_bytes(k.tile_n, k.swizzle_bytes, k.cta_group);
+    const int want = k.stages > 0 ? k.stages : 3;
+    k.k_slices = (kblocks >= 8 && want * wide + epi + kSmemSlack <= kSmemLimit) ? 2 : 1;
+  }
   if (k.stages == 0) {
     const int epi = k.epilogue == 1 ? hb::kEpiWarps * 2 * hb::kEpiBufBytes : 0;
-    int s = (kSmemLimit - kSmemSlack - epi) / stage_bytes(k.tile_n, k.swizzle_bytes, k.cta_group);
+    int s = (kSmemLimit - kSmemSlack - epi) / (k.k_slices * stage_bytes(k.tile_n, k.swizzle_bytes, k.cta_group));
     if (s > 8) s = 8;
     if (s < 1) s = 1;
     k.stages = s;
@@ -272,7 +291,8 @@ int check_knobs(const Problem& pr, const hb_knobs& k, int* smem_bytes, int* tmem
   // whole MN-major chunks in every CTA of the group
   if (b_mn_major(pr) && (k.tile_n / k.cta_group * es) % k.swizzle_bytes != 0) return HB_ERR_KNOB;
   const int epi = k.epilogue == 1 ? hb::kEpiWarps * 2 * hb::kEpiBufBytes : 0;
-  const int smem = k.stages * stage_bytes(k.tile_n, k.swizzle_bytes, k.cta_group) + epi + kSmemSlack;
+  if (k.k_slices != 1 && k.k_slices != 2) return HB_ERR_KNOB;
+  const int smem = k.stages * k.k_slices * stage_bytes(k.tile_n, k.swizzle_bytes, k.cta_group) + epi + kSmemSlack;
   if (smem > kSmemLimit) return HB_ERR_KNOB;
   if (smem_bytes) *smem_bytes = smem;
   if (tmem_cols) *tmem_cols = next_pow2_cols(k.acc_stages * k.tile_n);

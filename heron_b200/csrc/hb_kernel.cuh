@@ -61,6 +61,7 @@ struct KParams {
   int M, N, K, batch;
   int BN, SW, esize_in, esize_out;
   int stages, acc_stages, tmem_cols;
+  int kslices;  // 128-byte (swizzle-span) K slices behind one ring barrier: 1 or 2
   int tiles_m, tiles_n, num_tiles, num_kb;
   int raster, kind, b_mn_major, a_im2col, epilogue, l2_prefetch, probe;
   // Tail balancing: the first `whole_tiles` tiles are 128*CG x BN; each remaining tile is cut into
@@ -114,7 +115,7 @@ __device__ __forceinline__ void mbar_wait_drain(uint32_t bar, uint32_t parity) {
   }
 }
 
-template <int OUT_BYTES, int CG, int KIND>
+template <int OUT_BYTES, int CG, int KIND, int KS>
 __global__ void __launch_bounds__(kUmmaThreads, 1)
 hb_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmB2,
@@ -130,9 +131,10 @@ hb_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   const int a_bytes = kTileM * p.SW;
   const int b_bytes = bn_cta * p.SW;
   const uint32_t sA = smem_base;
-  const uint32_t sB = sA + p.stages * a_bytes;
+  constexpr int G = KS;  // K slices (swizzle spans) behind one ring barrier; equals p.kslices
+  const uint32_t sB = sA + p.stages * G * a_bytes;
   // the epilogue staging buffers are 128-byte swizzled: 1024-byte aligned whatever the ring size
-  const uint32_t sEpi = (sB + p.stages * b_bytes + 1023u) & ~1023u;
+  const uint32_t sEpi = (sB + p.stages * G * b_bytes + 1023u) & ~1023u;
   const int epi_bytes = p.epilogue ? kEpiWarps * 2 * kEpiBufBytes : 0;
   SmemBars* bars = reinterpret_cast<SmemBars*>(smem + (sEpi - smem_base) + epi_bytes);
   volatile int* abort_flag = &bars->abort_flag;
@@ -239,7 +241,8 @@ hb_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         pix_w = x * p.stride_w - p.pad_w;
         pix_h = y * p.stride_h - p.pad_h;
       }
-      for (int kb = kb0; kb < kb1; ++kb) {
+      for (int kbg = kb0; kbg < kb1; kbg += G) {
+        const int g = min(G, kb1 - kbg);  // K slices of this stage
         const uint32_t full_local = smem_u32(&bars->full[stage]);
         const uint32_t full = (CG == 2) ? mapa(full_local, 0) : full_local;  // the leader's barrier
         if (!mbar_wait(smem_u32(&bars->empty[stage]), phase ^ 1u, wctx)) {
@@ -256,40 +259,43 @@ hb_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           }
           continue;
         }
-        if (leader && (part & 1)) mbar_arrive_expect_tx(full_local, tx_bytes);
-        const uint32_t dA = sA + stage * a_bytes;
-        const uint32_t dB = sB + stage * b_bytes;
-        int krow;  // first K index of this block in B's K dimension
-        if (p.a_im2col) {
-          const int tap = kb / p.kb_per_tap;
-          const int cc = kb - tap * p.kb_per_tap;
-          int ryz = tap / p.KW;
-          const int rx = tap - ryz * p.KW;
-          if ((part & 1) && p.a_im2col == 2) {
-            const int rz = ryz / p.KH;
-            const int ry = ryz - rz * p.KH;
-            tma_load_im2col_5d_cg<CG>(dA, &tmA, full, cc * BK, pix_w, pix_h, pix_d, pix_n,
-                                      static_cast<uint16_t>(rx), static_cast<uint16_t>(ry),
-                                      static_cast<uint16_t>(rz));
-          } else if (part & 1) {
-            tma_load_im2col_4d_cg<CG>(dA, &tmA, full, cc * BK, pix_w, pix_h, pix_n,
-                                      static_cast<uint16_t>(rx * p.dil_w), static_cast<uint16_t>(ryz * p.dil_h));
+        if (leader && (part & 1)) mbar_arrive_expect_tx(full_local, tx_bytes * static_cast<uint32_t>(g));
+        for (int j = 0; j < g; ++j) {
+          const int kb = kbg + j;
+          const uint32_t dA = sA + (stage * G + j) * a_bytes;
+          const uint32_t dB = sB + (stage * G + j) * b_bytes;
+          int krow;  // first K index of this block in B's K dimension
+          if (p.a_im2col) {
+            const int tap = kb / p.kb_per_tap;
+            const int cc = kb - tap * p.kb_per_tap;
+            int ryz = tap / p.KW;
+            const int rx = tap - ryz * p.KW;
+            if ((part & 1) && p.a_im2col == 2) {
+              const int rz = ryz / p.KH;
+              const int ry = ryz - rz * p.KH;
+              tma_load_im2col_5d_cg<CG>(dA, &tmA, full, cc * BK, pix_w, pix_h, pix_d, pix_n,
+                                        static_cast<uint16_t>(rx), static_cast<uint16_t>(ry),
+                                        static_cast<uint16_t>(rz));
+            } else if (part & 1) {
+              tma_load_im2col_4d_cg<CG>(dA, &tmA, full, cc * BK, pix_w, pix_h, pix_n,
+                                        static_cast<uint16_t>(rx * p.dil_w), static_cast<uint16_t>(ryz * p.dil_h));
+            }
+            krow = tap * p.CI + cc * BK;
+          } else {
+            if (part & 1) tma_load_3d_cg<CG>(dA, &tmA, full, kb * BK, m0, p.a_shared ? 0 : b);
+            krow = kb * BK;
+            if (p.l2_prefetch > 0 && kb + p.l2_prefetch < kb1) {
+              tma_prefetch_3d(&tmA, (kb + p.l2_prefetch) * BK, m0, b);
+              tma_prefetch_3d(tmBk, (kb + p.l2_prefetch) * BK, n0, b);
+            }
           }
-          krow = tap * p.CI + cc * BK;
-        } else {
-          if (part & 1) tma_load_3d_cg<CG>(dA, &tmA, full, kb * BK, m0, p.a_shared ? 0 : b);
-          krow = kb * BK;
-          if (p.l2_prefetch > 0 && kb + p.l2_prefetch < kb1) {
-            tma_prefetch_3d(&tmA, (kb + p.l2_prefetch) * BK, m0, b);
-            tma_prefetch_3d(tmBk, (kb + p.l2_prefetch) * BK, n0, b);
+          if (!(part & 2)) {
+          } else if (p.b_mn_major) {
+            for (int c = 0; c < n_chunks; ++c)
+              tma_load_3d_cg<CG>(dB + c * (BK * p.SW), &tmB, full, n0 + c * chunk_cols, krow, b);
+          } else {
+            tma_load_3d_cg<CG>(dB, tmBk, full, krow, n0, b);
           }
-        }
-        if (!(part & 2)) {
-        } else if (p.b_mn_major) {
-          for (int j = 0; j < n_chunks; ++j)
-            tma_load_3d_cg<CG>(dB + j * (BK * p.SW), &tmB, full, n0 + j * chunk_cols, krow, b);
-        } else {
-          tma_load_3d_cg<CG>(dB, tmBk, full, krow, n0, b);
         }
         ++issued;
         if (++stage == p.stages) {
@@ -364,30 +370,34 @@ hb_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           const int ks = (t - p.whole_tiles) % p.ksplit;
           n_kb = (ks + 1) * num_kb / p.ksplit - ks * num_kb / p.ksplit;
         }
-        for (int kb = 0; kb < n_kb; ++kb) {
+        for (int kbg = 0; kbg < n_kb; kbg += G) {
+          const int g = min(G, n_kb - kbg);
           if (!mbar_wait(full0 + 8u * stage, phase, wctx)) {
             ok = false;
             break;
           }
           tc_fence_after();
-          uint32_t a_lo = (((sA >> 4) + stage * a16) & 0x3FFFu) | a_lo_fixed;
-          uint64_t a_hi_extra = 0;
-          if (probe >= 16) {
-            // diagnostic: start the A descriptor `shift` rows (128 bytes each) into the tile,
-            // with (probe >= 32) or without the descriptor's base-offset field set
-            const uint32_t shift = static_cast<uint32_t>(probe & 15);
-            const uint32_t addr = sA + stage * a_bytes + shift * 128u;
-            a_lo = ((addr >> 4) & 0x3FFFu) | a_lo_fixed;
-            if (probe >= 32) a_hi_extra = static_cast<uint64_t>((addr >> 7) & 7u) << 49;
-          }
-          const uint32_t b_lo = (((sB >> 4) + stage * b16) & 0x3FFFu) | b_lo_fixed;
-          if (probe != 2) {
-#pragma unroll
-            for (int k = 0; k < 4; ++k) {
-              if (k < n_mma) {
-                umma_cg<CG, KIND>(d_tmem, desc_hi | a_hi_extra | (a_lo + 2u * k), desc_hi | (b_lo + b_step16 * k), idesc_t,
-                                  accum);
-                accum = 1u;
+          for (int j = 0; j < g; ++j) {
+            const int slot = stage * G + j;
+            uint32_t a_lo = (((sA >> 4) + slot * a16) & 0x3FFFu) | a_lo_fixed;
+            uint64_t a_hi_extra = 0;
+            if (probe >= 16) {
+              // diagnostic: start the A descriptor `shift` rows (128 bytes each) into the tile,
+              // with (probe >= 32) or without the descriptor's base-offset field set
+              const uint32_t shift = static_cast<uint32_t>(probe & 15);
+              const uint32_t addr = sA + slot * a_bytes + shift * 128u;
+              a_lo = ((addr >> 4) & 0x3FFFu) | a_lo_fixed;
+              if (probe >= 32) a_hi_extra = static_cast<uint64_t>((addr >> 7) & 7u) << 49;
+            }
+            const uint32_t b_lo = (((sB >> 4) + slot * b16) & 0x3FFFu) | b_lo_fixed;
+            if (probe != 2) {
+  #pragma unroll
+              for (int k = 0; k < 4; ++k) {
+                if (k < n_mma) {
+                  umma_cg<CG, KIND>(d_tmem, desc_hi | a_hi_extra | (a_lo + 2u * k), desc_hi | (b_lo + b_step16 * k), idesc_t,
+                                    accum);
+                  accum = 1u;
+                }
               }
             }
           }

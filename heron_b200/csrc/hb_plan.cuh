@@ -16,7 +16,7 @@ int build_plan(Driver& d, const Problem& pr, const hb_knobs& k, const ConvGeom* 
   KParams& p = plan->p;
   p.M = pr.M; p.N = pr.N; p.K = pr.K; p.batch = pr.batch;
   p.BN = k.tile_n; p.SW = k.swizzle_bytes; p.esize_in = es; p.esize_out = eo;
-  p.stages = k.stages; p.acc_stages = k.acc_stages; p.tmem_cols = tmem_cols;
+  p.stages = k.stages; p.acc_stages = k.acc_stages; p.tmem_cols = tmem_cols; p.kslices = k.k_slices;
   const int cgrp = k.cta_group;
   p.tiles_m = (pr.M + hb::kTileM * cgrp - 1) / (hb::kTileM * cgrp);
   p.tiles_n = (pr.N + k.tile_n - 1) / k.tile_n;
@@ -139,9 +139,10 @@ int build_plan(Driver& d, const Problem& pr, const hb_knobs& k, const ConvGeom* 
     attr.val.clusterDim.x = 2; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
     cfg.attrs = &attr; cfg.numAttrs = 1;
     int clusters = 0;
-    const void* fn = eo == 2 ? reinterpret_cast<const void*>(&hb::hb_umma_kernel<2, 2, 0>)
-                             : (kind == 0 ? reinterpret_cast<const void*>(&hb::hb_umma_kernel<4, 2, 0>)
-                                          : reinterpret_cast<const void*>(&hb::hb_umma_kernel<4, 2, 1>));
+    // (the one- and two-slice instantiations need the same resources per CTA)
+    const void* fn = eo == 2 ? reinterpret_cast<const void*>(&hb::hb_umma_kernel<2, 2, 0, 1>)
+                             : (kind == 0 ? reinterpret_cast<const void*>(&hb::hb_umma_kernel<4, 2, 0, 1>)
+                                          : reinterpret_cast<const void*>(&hb::hb_umma_kernel<4, 2, 1, 1>));
     if (cudaOccupancyMaxActiveClusters(&clusters, fn, &cfg) == cudaSuccess && clusters > 0 &&
         clusters < units)
       units = clusters;
@@ -226,7 +227,7 @@ int build_plan(Driver& d, const Problem& pr, const hb_knobs& k, const ConvGeom* 
   return HB_OK;
 }
 
-template <int OUT_BYTES, int CG, int KIND>
+template <int OUT_BYTES, int CG, int KIND, int KS>
 int launch_kernel(const hb_plan* plan, cudaStream_t stream);
 
 int run_pre(const hb_plan* plan, cudaStream_t stream) {
@@ -319,15 +320,23 @@ int run_main(const hb_plan* plan, cudaStream_t stream) {
   }
   const bool half_out = plan->p.esize_out == 2;
   const bool i8 = plan->p.kind == 1;
-  if (plan->knobs.cta_group == 2) {
-    if (half_out) return launch_kernel<2, 2, 0>(plan, stream);
-    return i8 ? launch_kernel<4, 2, 1>(plan, stream) : launch_kernel<4, 2, 0>(plan, stream);
+  if (plan->p.kslices == 2) {
+    if (plan->knobs.cta_group == 2) {
+      if (half_out) return launch_kernel<2, 2, 0, 2>(plan, stream);
+      return i8 ? launch_kernel<4, 2, 1, 2>(plan, stream) : launch_kernel<4, 2, 0, 2>(plan, stream);
+    }
+    if (half_out) return launch_kernel<2, 1, 0, 2>(plan, stream);
+    return i8 ? launch_kernel<4, 1, 1, 2>(plan, stream) : launch_kernel<4, 1, 0, 2>(plan, stream);
   }
-  if (half_out) return launch_kernel<2, 1, 0>(plan, stream);
-  return i8 ? launch_kernel<4, 1, 1>(plan, stream) : launch_kernel<4, 1, 0>(plan, stream);
+  if (plan->knobs.cta_group == 2) {
+    if (half_out) return launch_kernel<2, 2, 0, 1>(plan, stream);
+    return i8 ? launch_kernel<4, 2, 1, 1>(plan, stream) : launch_kernel<4, 2, 0, 1>(plan, stream);
+  }
+  if (half_out) return launch_kernel<2, 1, 0, 1>(plan, stream);
+  return i8 ? launch_kernel<4, 1, 1, 1>(plan, stream) : launch_kernel<4, 1, 0, 1>(plan, stream);
 }
 
-template <int OUT_BYTES, int CG, int KIND>
+template <int OUT_BYTES, int CG, int KIND, int KS>
 int launch_kernel(const hb_plan* plan, cudaStream_t stream) {
   cudaLaunchConfig_t cfg;
   std::memset(&cfg, 0, sizeof(cfg));
@@ -343,7 +352,7 @@ int launch_kernel(const hb_plan* plan, cudaStream_t stream) {
   attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = follows_own_kernel(plan) ? 2 : 1;
-  const cudaError_t e = cudaLaunchKernelEx(&cfg, hb::hb_umma_kernel<OUT_BYTES, CG, KIND>, plan->tmA,
+  const cudaError_t e = cudaLaunchKernelEx(&cfg, hb::hb_umma_kernel<OUT_BYTES, CG, KIND, KS>, plan->tmA,
                                            plan->tmB, plan->tmC, plan->tmB2, plan->p);
   return e == cudaSuccess ? HB_OK : HB_ERR_LAUNCH;
 }

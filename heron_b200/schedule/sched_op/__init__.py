@@ -130,7 +130,8 @@ class tileOp(SchedOp):
 
 
 class pipelineOp(SchedOp):
-    """Depth of the TMA -> MMA ring and number of TMEM accumulator buffers."""
+    """Depth of the TMA -> MMA ring, swizzle spans of K per ring stage, and number of TMEM
+    accumulator buffers."""
 
     def perform(self, s, stage_name, ctx):
         km = ctx.knob_manager
@@ -140,18 +141,23 @@ class pipelineOp(SchedOp):
         cols = genKey("V", stage_name, "n", var_name="tmem_columns")
         tile_n = genKey("P", stage_name, "n", param_name="tile_n")
         stage_bytes = genKey("V", stage_name, "k", var_name="stage_bytes")
+        slices = genKey("P", stage_name, "k", param_name="k_slices")
         if km.is_building:
             lim = ctx.limits["max_shared_memory_per_block"]
             km.define_value(stages, 1, ctx.limits["max_stages"], 4, True)
+            # swizzle spans of K behind one ring barrier: the stage, and the ring, grow with it
+            km.define_value(slices, 1, 2, 1, True)
             km.define_value(acc, 1, 2, 2, True)
             km.define_value(ring, 1, lim, lim)
             km.define_value(cols, 1, ctx.limits["tmem_columns"], ctx.limits["tmem_columns"])
-            km.addProd([stages, stage_bytes], ring)
+            km.addProd([stages, slices, stage_bytes], ring)
             km.addProd([acc, tile_n], cols)
         ctx.kernel_knobs["stages"] = km.get_val(stages)
         ctx.kernel_knobs["acc_stages"] = km.get_val(acc)
-        ctx.addSchedDesc("## ring of %s stages, %s accumulator buffers\n"
-                         % (ctx.kernel_knobs["stages"], ctx.kernel_knobs["acc_stages"]))
+        ctx.kernel_knobs["k_slices"] = km.get_val(slices)
+        ctx.addSchedDesc("## ring of %s stages of %s K spans, %s accumulator buffers\n"
+                         % (ctx.kernel_knobs["stages"], ctx.kernel_knobs["k_slices"],
+                            ctx.kernel_knobs["acc_stages"]))
 
 
 class epilogueOp(SchedOp):

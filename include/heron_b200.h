@@ -77,6 +77,9 @@ typedef struct {
                         the next ones add (TMA reduce-add or red.global) once the one before has
                         finished, so the order of the additions is fixed.  1 = off, 2..4,
                         0 = library picks.  4-byte outputs only                                   */
+  int k_slices;      /* swizzle spans of K behind one ring barrier (1 or 2): with 2 the MMA thread
+                        waits, fences and commits once per eight MMAs instead of four, at the same
+                        ring size in bytes.  0 = library picks                                     */
   int reserved;      /* diagnostic probe modes; leave 0                                            */
 } hb_knobs;
 

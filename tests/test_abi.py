@@ -60,7 +60,7 @@ def test_default_knobs_are_inside_the_space(hb_lib):
 @pytest.mark.parametrize("bad", [
     dict(tile_n=48), dict(tile_n=288), dict(stages=13), dict(swizzle_bytes=96),
     dict(tile_n=256, stages=12), dict(acc_stages=3), dict(raster=2), dict(epilogue=3), dict(cta_group=3),
-    dict(l2_prefetch=65),
+    dict(l2_prefetch=65), dict(k_slices=3), dict(k_slices=2, stages=4),  # a ring of 4 x 2 x 32 KB plus the staging buffers
 ])
 def test_check_knobs_rejects(hb_lib, bad):
     from heron_b200 import _lib

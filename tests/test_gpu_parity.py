@@ -201,6 +201,32 @@ def test_split_k_conv_and_bmm(K, co):
         check(k_bmm(K, a, b, knobs=knobs), co.bmm_int(a, b), "bmm split-K %s" % (knobs,))
 
 
+@pytest.mark.parametrize("knobs", [
+    dict(k_slices=1), dict(k_slices=2), dict(k_slices=2, cta_group=1), dict(k_slices=2, cta_group=2, stages=1),
+    dict(k_slices=2, stages=2, acc_stages=1), dict(k_slices=2, split_k=2, max_ctas=6),
+    dict(k_slices=2, split_k=3, cta_group=1, max_ctas=5), dict(k_slices=2, tile_n=64, swizzle_bytes=64),
+    dict(k_slices=2, tile_n=128, swizzle_bytes=32, epilogue=2),
+])
+def test_two_k_spans_per_ring_stage(K, co, knobs):
+    """One or two swizzle spans of K behind each ring barrier: K extents of 1, 3, 5 and 9 spans
+    (a last stage that is half full), with split-K slices that cut the K range at odd spans."""
+    rng = np.random.default_rng(sum(knobs.values()))
+    for M, N, Kd in ((300, 200, 128), (300, 200, 384), (520, 328, 640), (129, 72, 1152)):
+        if Kd * 8 < 128 * 8 * knobs.get("split_k", 1):
+            continue  # every split-K slice keeps at least one span
+        a, b = rand_i8(rng, (M, Kd), False), rand_i8(rng, (N, Kd), True)
+        check(k_gemm(K, a, b, knobs=knobs), co.gemm_int(a, b), "k spans int8 %s %s" % ((M, N, Kd), knobs))
+    af = (rng.standard_normal((260, 328)) / np.sqrt(328)).astype(np.float16)
+    bf = rng.standard_normal((136, 328)).astype(np.float16)
+    check(k_gemm(K, af, bf, knobs=knobs), co.gemm_f16(af, bf), "k spans fp16 %s" % (knobs,))
+    ck = {k: v for k, v in knobs.items() if k not in ("split_k", "swizzle_bytes")}
+    x, w = rand_i8(rng, (3, 9, 11, 64), False), rand_i8(rng, (3, 3, 64, 80), True)
+    check(k_conv(K, x, w, (2, 1), 1, 1, knobs=dict(ck, conv_algo=1)), co.conv2d_nhwc_int(x, w, (2, 1), 1, 1),
+          "k spans conv %s" % (ck,))
+    a3, b3 = rand_i8(rng, (5, 200, 320), True), rand_i8(rng, (5, 72, 320), True)
+    check(k_bmm(K, a3, b3, knobs=ck), co.bmm_int(a3, b3), "k spans bmm %s" % (ck,))
+
+
 def test_split_k_rejected_where_it_cannot_add(K):
     from heron_b200._lib import HB_ERR_KNOB, HeronB200Error
     a = torch.zeros(128, 512, dtype=torch.float16, device="cuda")
