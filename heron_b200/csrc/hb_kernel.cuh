@@ -16,6 +16,10 @@
 // Two accumulator buffers in TMEM let the MMA warp start the next tile while the epilogue warps
 // drain the previous one.
 //
+// A ring stage holds KS (1 or 2) swizzle spans of K per operand behind one "full" / "empty"
+// barrier pair: with two, the MMA thread waits, fences and commits once per eight MMAs instead of
+// four and the producers arm half as many barriers, at the same ring size in bytes.
+//
 // With CG = 2 the two CTAs of a cluster share every MMA (tcgen05 cta_group::2): the pair owns a
 // 256 x BN tile, each CTA stages its own 128 rows of A and its own half of B's BN rows, the
 // leader CTA (cluster rank 0) issues the instruction for both and each CTA's TMEM receives its
