@@ -90,7 +90,10 @@ hb_conv_strip_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_cons
 
   if (threadIdx.x == 0) {
     mbar_init(smem_u32(&bars->filt_full), 1);
-    for (int i = 0; i < 4; ++i) {
+    static_assert(sizeof(bars->strip_full) == kMaxStripRing * sizeof(uint64_t) &&
+                      sizeof(bars->strip_empty) == kMaxStripRing * sizeof(uint64_t),
+                  "every ring barrier below is initialised");
+    for (int i = 0; i < kMaxStripRing; ++i) {
       mbar_init(smem_u32(&bars->strip_full[i]), 1);
       mbar_init(smem_u32(&bars->strip_empty[i]), 1);
     }

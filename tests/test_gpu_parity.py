@@ -1,8 +1,10 @@
 """Parity of the sm_100a kernels with the oracle, through the C ABI (ctypes), on a B200.
 
-Bit-exact for the integer paths; for fp16 inputs with fp32 accumulation the bound is a maximum
-error of 1e-2 relative to the largest magnitude of the oracle's output (the benchmark's stated
-tolerance) — observed errors are around 1e-6 (fp32 output) and 5e-4 (fp16 output).
+Bit-exact for the integer paths.  For fp16 inputs with fp32 accumulation two bounds hold at once:
+every element satisfies |got - want| <= 1e-2 * |want| + atol with atol = 1e-3 * RMS(want) (the
+benchmark's stated relative tolerance, with a floor so that sums that cancel to almost nothing are
+not held to a relative bound), and the largest error is at most 1e-2 of the largest magnitude of
+the oracle's output.  Observed errors are around 1e-6 (fp32 output) and 5e-4 (fp16 output).
 """
 import os
 import random
@@ -16,7 +18,8 @@ from oracle import np_oracle as npo
 
 pytestmark = pytest.mark.gpu
 
-FP_TOL = 1e-2
+FP_TOL = 1e-2        # relative, per element and against the largest magnitude
+FP_ATOL_RMS = 1e-3   # absolute floor of the per-element bound, as a fraction of RMS(want)
 
 
 @pytest.fixture(scope="module")
@@ -60,10 +63,14 @@ def check(got_t, want, what=""):
     if want.dtype.kind in "iu":
         assert np.array_equal(got, want), "%s: %d mismatches" % (what, int((got != want).sum()))
     else:
-        scale = max(float(np.abs(want.astype(np.float64)).max()), 1e-30)
-        err = float(np.abs(got.astype(np.float64) - want.astype(np.float64)).max()) / scale
         assert np.isfinite(got.astype(np.float32)).all(), what
-        assert err <= FP_TOL, (what, err)
+        w64, diff = want.astype(np.float64), np.abs(got.astype(np.float64) - want.astype(np.float64))
+        scale = max(float(np.abs(w64).max()), 1e-30)
+        assert float(diff.max()) / scale <= FP_TOL, (what, float(diff.max()) / scale)
+        atol = FP_ATOL_RMS * float(np.sqrt(np.mean(w64 * w64)))
+        excess = diff - (FP_TOL * np.abs(w64) + atol)
+        assert float(excess.max()) <= 0.0, "%s: %d elements outside |d| <= %g|want| + %g" % (
+            what, int((excess > 0).sum()), FP_TOL, atol)
 
 
 def k_gemm(K, a, b, out_dtype=None, knobs=None):
@@ -691,6 +698,21 @@ def test_conv_strip_algorithm_int8(K, co, case):
     rng = np.random.default_rng(sum(case))
     x, w = rand_i8(rng, (N, H, W, CI), False), rand_i8(rng, (KH, KW, CI, CO), True)
     check(k_conv(K, x, w, 1, p, d, knobs=dict(conv_algo=2)), co.conv2d_nhwc_int(x, w, 1, p, d), "strip int8")
+
+
+def test_conv_strip_walks_its_whole_ring(K, co):
+    """One CTA takes every tile in turn, so each barrier of the deepest strip ring is used and
+    reused (14x14 images leave room for six strip buffers)."""
+    rng = np.random.default_rng(1414)
+    x = rng.standard_normal((8, 14, 14, 64)).astype(np.float16)
+    w = (rng.standard_normal((3, 3, 64, 64)) / 24.0).astype(np.float16)
+    out = poison((8, 14, 14, 64), torch.float32)
+    plan = K.plan_conv2d_nhwc(dev(x), dev(w), stride=1, padding=1, dilation=1, out=out,
+                              knobs=dict(conv_algo=2, max_ctas=1))
+    kn = plan.knobs()
+    assert kn["conv_algo"] == 2 and kn["stages"] == 6 and kn["grid"] == 1, kn
+    plan.launch()
+    check(out, co.conv2d_nhwc_f16(x, w, 1, 1, 1, np.float32), "strip ring walk")
 
 
 def test_conv_strip_refused_when_it_does_not_apply(K):
