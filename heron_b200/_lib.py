@@ -39,6 +39,7 @@ EXPORTED_SYMBOLS = (
     "hb_sm_count",
     "hb_default_knobs",
     "hb_check_knobs",
+    "hb_balanced_run",
     "hb_gemm",
     "hb_bmm",
     "hb_conv2d_nhwc",
@@ -91,11 +92,14 @@ class HbKnobs(ctypes.Structure):
         ("tail_split", ctypes.c_int),
         ("split_k", ctypes.c_int),
         ("k_slices", ctypes.c_int),
-        ("reserved", ctypes.c_int),
+        ("balance", ctypes.c_int),
+        ("silent_producer", ctypes.c_int),
+        ("probe", ctypes.c_int),
     ]
 
     FIELDS = ("tile_n", "stages", "swizzle_bytes", "acc_stages", "raster", "epilogue", "max_ctas",
-              "cta_group", "l2_prefetch", "conv_algo", "tail_split", "split_k", "k_slices", "reserved")
+              "cta_group", "l2_prefetch", "conv_algo", "tail_split", "split_k", "k_slices", "balance",
+              "silent_producer", "probe")
 
     @classmethod
     def from_dict(cls, d):
@@ -158,6 +162,8 @@ def load():
     lib.hb_default_knobs.argtypes = [c_int] * 6 + [c_int, c_int, kp]
     lib.hb_check_knobs.restype = c_int
     lib.hb_check_knobs.argtypes = [c_int] * 6 + [c_int, c_int, kp, ip, ip]
+    lib.hb_balanced_run.restype = c_int
+    lib.hb_balanced_run.argtypes = [c_int] * 4 + [ip, ip]
     lib.hb_gemm.restype = c_int
     lib.hb_gemm.argtypes = [c_void_p] * 3 + [c_int] * 3 + [c_int] * 3 + [kp, c_void_p]
     lib.hb_bmm.restype = c_int

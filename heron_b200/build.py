@@ -41,8 +41,12 @@ def is_stale():
 
 
 def build(force=False, verbose=False, extra_flags=()):
+    """Diagnostic probe modes (knob ``probe``) are compiled in only when HB_PROBES=1 is set in the
+    environment; the shipped library has none of their branches."""
     if not force and not is_stale():
         return TARGET
+    if os.environ.get("HB_PROBES") == "1":
+        extra_flags = list(extra_flags) + ["-DHB_PROBES"]
     cmd = [nvcc()] + NVCC_FLAGS + list(extra_flags) + ["-o", TARGET] + SOURCES
     if verbose:
         print(" ".join(cmd))

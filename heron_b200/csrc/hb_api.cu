@@ -70,6 +70,16 @@ int hb_check_knobs(int op, int batch, int M, int N, int K, int k_inner, hb_dtype
   return check_knobs(pr, full, smem_bytes, tmem_cols);
 }
 
+int hb_balanced_run(int tiles, int stages_per_tile, int pairs, int pair, int* first, int* end) {
+  if (tiles <= 0 || stages_per_tile <= 0 || pairs <= 0 || pair < 0 || pair >= pairs || !first || !end)
+    return HB_ERR_SHAPE;
+  const long long total = static_cast<long long>(tiles) * stages_per_tile;
+  if (total > 0x7fffffffLL) return HB_ERR_SHAPE;
+  *first = hb::sk_bound_of(static_cast<int>(total), stages_per_tile, kBalanceMinRun, pair, pairs);
+  *end = hb::sk_bound_of(static_cast<int>(total), stages_per_tile, kBalanceMinRun, pair + 1, pairs);
+  return HB_OK;
+}
+
 int hb_gemm(const void* A, const void* B, void* C, int M, int K, int N, hb_dtype in_a,
             hb_dtype in_b, hb_dtype out, const hb_knobs* knobs, void* stream) {
   hb_plan plan;
@@ -287,7 +297,7 @@ int hb_plan_knobs(const hb_plan* plan, hb_knobs* knobs, int* grid, int* smem_byt
   return HB_OK;
 }
 
-void hb_plan_destroy(hb_plan* plan) { delete plan; }
+void hb_plan_destroy(hb_plan* plan) { destroy_plan(plan); }
 
 int hb_last_status(int* status) {
   if (!status) return HB_ERR_SHAPE;

@@ -113,6 +113,7 @@ hb_conv_strip_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_cons
   tc_fence_after();
   const uint32_t tmem_base = bars->tmem_base;
   griddep_wait();  // input and filter may come from a layout kernel this one was launched behind
+  griddep_launch_dependents();  // the next launch of the stream may set itself up meanwhile
 
   if (warp == 0) {
     // ------------------------------ producer ----------------------------------------------

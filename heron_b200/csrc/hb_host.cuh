@@ -292,6 +292,8 @@ int check_knobs(const Problem& pr, const hb_knobs& k, int* smem_bytes, int* tmem
   if (b_mn_major(pr) && (k.tile_n / k.cta_group * es) % k.swizzle_bytes != 0) return HB_ERR_KNOB;
   const int epi = k.epilogue == 1 ? hb::kEpiWarps * 2 * hb::kEpiBufBytes : 0;
   if (k.k_slices != 1 && k.k_slices != 2) return HB_ERR_KNOB;
+  if (k.balance < 0 || k.balance > 2) return HB_ERR_KNOB;
+  if (k.balance == 2 && eo != 4) return HB_ERR_KNOB;  // partial sums travel through the output
   const int smem = k.stages * k.k_slices * stage_bytes(k.tile_n, k.swizzle_bytes, k.cta_group) + epi + kSmemSlack;
   if (smem > kSmemLimit) return HB_ERR_KNOB;
   if (smem_bytes) *smem_bytes = smem;
@@ -337,6 +339,7 @@ struct hb_plan {
   hb_knobs knobs;
   int grid;
   int smem;
+  int owned_flags;  // hand-over flags (p.flags) this plan holds until it is destroyed; 0: none
   // strip conv (conv_algo 2): its own parameter block; tmA = tiled input map, tmB = filter map
   bool strip;
   hb::StripParams sp;
@@ -368,10 +371,14 @@ struct hb_plan {
 #define HB_STATIC_SCRATCH_BYTES (4u << 20)
 static __device__ __align__(256) int8_t g_hb_static_scratch[HB_STATIC_SCRATCH_BYTES];
 
-// Turn-taking flags of split-K tiles (KParams::flags): one int per sliced tile, zero between
-// launches.  A plan takes a run of slots from a rotating cursor, so launches that overlap on the
-// GPU use different flags unless more than kFlagSlots / 148 of them are in flight at once.
-#define HB_FLAG_SLOTS 16384
+// Hand-over flags (KParams::flags): one int per sliced tile of a split-K plan, or one per (CTA
+// pair, epilogue warp) of a balanced plan; zero between launches.  A plan created with hb_plan_*
+// owns its run of slots until hb_plan_destroy, so two live plans never share flags and may run
+// on different streams at once; one plan must not run concurrently with itself.  The immediate
+// entry points (hb_gemm, ...) take a run from a rotating cursor over the slots no live plan
+// owns: two immediate calls whose kernels overlap on the GPU could share flags only after the
+// cursor has gone round the whole array in between.
+#define HB_FLAG_SLOTS 65536
 static __device__ int g_hb_split_flags[HB_FLAG_SLOTS];
 
 namespace {
@@ -382,11 +389,17 @@ unsigned g_split_flags_cursor = 0;
 void* g_static_scratch_addr[kMaxDevices] = {nullptr};
 std::mutex g_static_scratch_mutex;
 
-// `count` consecutive flags of the current device's flag array (see g_hb_split_flags).
+// Slots owned by live plans (process-wide: a plan's slots are reserved on every device).
+unsigned char g_split_flags_owned[HB_FLAG_SLOTS] = {0};
+// Set while hb_plan_* builds a heap plan: its flags are marked owned and freed on destroy.
+thread_local bool g_plan_owns_flags = false;
+
+// `count` consecutive flags of the current device's flag array (see g_hb_split_flags) that no
+// live plan owns.  HB_ERR_SCRATCH when no such run is left (the caller then plans without them).
 int split_flags(int count, int** out) {
   int dev = -1;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return HB_ERR_DEVICE;
-  if (count <= 0 || count > HB_FLAG_SLOTS) return HB_ERR_SHAPE;
+  if (count <= 0 || count > HB_FLAG_SLOTS) return HB_ERR_SCRATCH;
   std::lock_guard<std::mutex> lock(g_static_scratch_mutex);
   if (g_split_flags_addr[dev] == nullptr) {
     void* ptr = nullptr;
@@ -396,10 +409,39 @@ int split_flags(int count, int** out) {
     }
     g_split_flags_addr[dev] = static_cast<int*>(ptr);
   }
-  if (g_split_flags_cursor + count > HB_FLAG_SLOTS) g_split_flags_cursor = 0;
-  *out = g_split_flags_addr[dev] + g_split_flags_cursor;
-  g_split_flags_cursor += count;
+  // next fit from the cursor, then once more from the start of the array
+  const unsigned n = static_cast<unsigned>(count);
+  auto find = [&](unsigned lo) -> long {
+    unsigned at = lo;
+    while (at + n <= HB_FLAG_SLOTS) {
+      unsigned run = 0;
+      while (run < n && !g_split_flags_owned[at + run]) ++run;
+      if (run == n) return static_cast<long>(at);
+      at += run + 1;  // past the owned slot that ended the run
+    }
+    return -1;
+  };
+  long found = find(g_split_flags_cursor);
+  if (found < 0) found = find(0);
+  if (found < 0) return HB_ERR_SCRATCH;
+  const unsigned start = static_cast<unsigned>(found);
+  if (g_plan_owns_flags)
+    for (int i = 0; i < count; ++i) g_split_flags_owned[start + i] = 1;
+  *out = g_split_flags_addr[dev] + start;
+  g_split_flags_cursor = start + count;
   return HB_OK;
+}
+
+void release_split_flags(const int* flags, int count) {
+  if (!flags || count <= 0) return;
+  std::lock_guard<std::mutex> lock(g_static_scratch_mutex);
+  for (int dev = 0; dev < kMaxDevices; ++dev) {
+    const int* base = g_split_flags_addr[dev];
+    if (base && flags >= base && flags + count <= base + HB_FLAG_SLOTS) {
+      for (int i = 0; i < count; ++i) g_split_flags_owned[(flags - base) + i] = 0;
+      return;
+    }
+  }
 }
 
 // Device address of g_hb_static_scratch on the current device (looked up on first use there).

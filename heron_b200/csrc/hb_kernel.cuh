@@ -44,6 +44,17 @@
 // with B read as (K, N) tiles (a 1x1 NCHW conv on the tensors in place), a third spatial axis
 // (5-D im2col loads), channel-major (NCHW) stores from the direct epilogue.
 //
+// Balanced schedule (KParams::sk): instead of whole tiles dealt out round-robin, the (tile, ring
+// stage) pairs of the whole problem form one line of work units that is cut into equal runs, one
+// per CTA pair.  A run starts and ends inside tiles, so a tile may be shared by two (seldom three)
+// pairs, each holding a K range of it.  The pair that holds the END of a tile's K range meets it
+// first (at the start of its run): it stores its partial sums into the output tile itself and
+// raises a flag per epilogue warp.  The pair that holds the range before it meets the tile last
+// (at the end of its run): its epilogue waits (bounded) for the flag, reads the partial sums back
+// from the output (they are still in L2), adds them to its accumulator and stores the result.
+// No atomics, no workspace, a fixed order of additions, and every pair does the same number of
+// ring stages whatever the tile count.
+//
 // Every wait on an mbarrier is bounded.  When one runs out, the CTA raises a shared abort flag,
 // every role leaves its loop, in-flight TMA loads and MMAs are waited for (bounded again), TMEM
 // is freed and HB_ERR_TIMEOUT is left in the device status word.
@@ -67,7 +78,14 @@ struct KParams {
   int stages, acc_stages, tmem_cols;
   int kslices;  // 128-byte (swizzle-span) K slices behind one ring barrier: 1 or 2
   int tiles_m, tiles_n, num_tiles, num_kb;
-  int raster, kind, b_mn_major, a_im2col, epilogue, l2_prefetch, probe;
+  int raster, kind, b_mn_major, a_im2col, epilogue, l2_prefetch;
+  int probe;            // diagnostic modes; only builds with -DHB_PROBES read it
+  int silent_producer;  // test hook: the producers issue no loads, so the consumers' waits run out
+  // Balanced schedule: work units are ring stages; unit u belongs to tile u / sk_per_tile.  CTA
+  // pair i walks units [bound(i), bound(i+1)), bound(i) = i * sk_total / pairs, moved to the tile
+  // edge when it falls closer to one than sk_min units.  flags then holds one int per (pair,
+  // epilogue warp): "the partial sums of this pair's first, shared tile are in memory".
+  int sk, sk_total, sk_per_tile, sk_min;
   // Tail balancing: the first `whole_tiles` tiles are 128*CG x BN; each remaining tile is cut into
   // `split` column slices of BN/split, so that the last, partly filled wave of the persistent
   // grid is made of shorter work items.  num_tiles counts work items (whole tiles + slices).
@@ -117,6 +135,67 @@ __device__ __forceinline__ void mbar_wait_drain(uint32_t bar, uint32_t parity) {
   while (!mbar_try_wait(bar, parity)) {
     if (clock64() - t0 > (HB_WAIT_LIMIT_CYCLES / 4)) return;
   }
+}
+
+// First work unit of CTA pair `i` of `n` under the balanced schedule: `total` units of
+// `per_tile` ring stages per tile; a cut closer than `min_run` stages to a tile edge moves onto it.
+__host__ __device__ __forceinline__ int sk_bound_of(int total, int per_tile, int min_run, int i, int n) {
+  int b = static_cast<int>(static_cast<long long>(i) * total / n);
+  const int r = b % per_tile;
+  if (r != 0) {
+    if (r < min_run) b -= r;
+    else if (per_tile - r < min_run) b += per_tile - r;
+  }
+  return b;
+}
+__device__ __forceinline__ int sk_bound(const KParams& p, int i, int n) {
+  return sk_bound_of(p.sk_total, p.sk_per_tile, p.sk_min, i, n);
+}
+
+// The work items of one CTA pair, in the order it meets them: whole work items of the static
+// list (index `unit`, `unit + n`, ...), or the tiles its run of the balanced schedule touches.
+struct Walk {
+  int cur, end, step;
+};
+struct Piece {
+  int t;       // work item (static list) or tile (balanced schedule)
+  int s0, s1;  // balanced schedule: ring stages [s0, s1) of the tile
+};
+__device__ __forceinline__ Walk walk_begin(const KParams& p, int unit, int n) {
+  Walk w;
+  if (p.sk) {
+    w.cur = sk_bound(p, unit, n);
+    w.end = sk_bound(p, unit + 1, n);
+    w.step = 0;
+  } else {
+    w.cur = unit;
+    w.end = p.num_tiles;
+    w.step = n;
+  }
+  return w;
+}
+__device__ __forceinline__ bool walk_next(const KParams& p, Walk& w, Piece& pc) {
+  if (w.cur >= w.end) return false;
+  if (p.sk) {
+    pc.t = w.cur / p.sk_per_tile;
+    pc.s0 = w.cur - pc.t * p.sk_per_tile;
+    pc.s1 = min(p.sk_per_tile, pc.s0 + (w.end - w.cur));
+    w.cur += pc.s1 - pc.s0;
+  } else {
+    pc.t = w.cur;
+    pc.s0 = pc.s1 = 0;
+    w.cur += w.step;
+  }
+  return true;
+}
+
+__device__ __forceinline__ uint4 ld_cg_v4(const void* ptr) {
+  uint4 v;
+  asm volatile("ld.global.cg.v4.u32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(ptr)
+               : "memory");
+  return v;
 }
 
 template <int OUT_BYTES, int CG, int KIND, int KS>
@@ -173,19 +252,26 @@ hb_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   // Everything above touched only this CTA's own resources; the operands may still be being
   // written by the layout kernel this one was launched behind.
   griddep_wait();
+  // A launch behind this one in the stream (made with programmatic serialization) may now take
+  // SMs as this grid's CTAs leave them and set itself up; it waits, as above, for this grid to end.
+  griddep_launch_dependents();
 
   const int tiles_per_batch = p.tiles_m * p.tiles_n;
   const int first_tile = blockIdx.x / CG;  // a pair of CTAs walks the tile list together
   const int tile_step = gridDim.x / CG;
   const int tile_rows = kTileM * CG;
   // work item -> (batch, first row of the pair tile, first column, width)
-  auto decode = [&](int t, int& b, int& m_pair, int& n_first, int& bn, int& kb0, int& kb1, int& kslice) {
+  auto decode = [&](const Piece& pc, int& b, int& m_pair, int& n_first, int& bn, int& kb0, int& kb1, int& kslice) {
+    int t = pc.t;
     int slice = 0;
     bn = p.BN;
     kb0 = 0;
     kb1 = p.num_kb;
     kslice = 0;
-    if (t >= p.whole_tiles) {
+    if (p.sk) {
+      kb0 = pc.s0 * KS;
+      kb1 = min(pc.s1 * KS, p.num_kb);
+    } else if (t >= p.whole_tiles) {
       const int h = t - p.whole_tiles;
       if (p.ksplit > 1) {
         const int ks = h % p.ksplit;
@@ -214,11 +300,13 @@ hb_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     long long issued = 0;
     bool ok = true;
     const int chunk_cols = p.SW / p.esize_in;               // MN-major B: columns per chunk
-    // diagnostic 12: the producer stays silent, so the consumers' bounded waits run out and the
-    // abort path (drain, TMEM release, status word) is what the launch exercises
-    for (int t = first_tile; ok && t < p.num_tiles && p.probe != 12; t += tile_step) {
+    // silent_producer (a test hook): nothing is loaded, so the consumers' bounded waits run out
+    // and the abort path (drain, TMEM release, status word) is what the launch exercises
+    Walk walk = walk_begin(p, first_tile, tile_step);
+    Piece pc;
+    while (ok && !p.silent_producer && walk_next(p, walk, pc)) {
       int b, m_pair, n_first, bn, kb0, kb1, kslice;
-      decode(t, b, m_pair, n_first, bn, kb0, kb1, kslice);
+      decode(pc, b, m_pair, n_first, bn, kb0, kb1, kslice);
       const int bn_mine = bn / CG;  // B rows this CTA stages for this work item
       const int n_chunks = p.b_mn_major ? bn_mine / chunk_cols : 1;
       const uint32_t tx_bytes = static_cast<uint32_t>(a_bytes + bn_mine * p.SW) * CG;
@@ -253,6 +341,7 @@ hb_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           ok = false;
           break;
         }
+#ifdef HB_PROBES
         if (p.probe == 1 && issued >= p.stages) {
           // diagnostic: operands stay as first loaded; only the barrier protocol runs
           if (leader && (part & 1)) mbar_arrive(full_local);  // one arrival per stage: the A producer's
@@ -263,6 +352,7 @@ hb_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           }
           continue;
         }
+#endif
         if (leader && (part & 1)) mbar_arrive_expect_tx(full_local, tx_bytes * static_cast<uint32_t>(g));
         for (int j = 0; j < g; ++j) {
           const int kb = kbg + j;
@@ -357,10 +447,16 @@ hb_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       const uint32_t a_lo_fixed = (16u >> 4) << 16;
       const uint32_t b_lo_fixed = ((b_lbo >> 4) & 0x3FFFu) << 16;
       const uint32_t idesc = p.idesc;
-      const int num_kb = p.num_kb, stages = p.stages, acc_stages = p.acc_stages, probe = p.probe;
+      const int num_kb = p.num_kb, stages = p.stages, acc_stages = p.acc_stages;
+#ifdef HB_PROBES
+      const int probe = p.probe;
+#endif
       const uint32_t a16 = static_cast<uint32_t>(a_bytes) >> 4, b16 = static_cast<uint32_t>(b_bytes) >> 4;
       const uint32_t full0 = smem_u32(&bars->full[0]), empty0 = smem_u32(&bars->empty[0]);
-      for (int t = first_tile; ok && t < p.num_tiles; t += tile_step) {
+      Walk walk = walk_begin(p, first_tile, tile_step);
+      Piece pc;
+      while (ok && walk_next(p, walk, pc)) {
+        const int t = pc.t;
         if (!mbar_wait(smem_u32(&bars->tmem_empty[acc]), acc_phase ^ 1u, wctx)) {
           ok = false;
           break;
@@ -370,7 +466,9 @@ hb_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         const uint32_t idesc_t = (t >= p.whole_tiles) ? p.idesc_split : idesc;
         uint32_t accum = 0u;
         int n_kb = num_kb;  // K blocks of this work item
-        if (t >= p.whole_tiles && p.ksplit > 1) {
+        if (p.sk) {
+          n_kb = min(pc.s1 * G, num_kb) - pc.s0 * G;
+        } else if (t >= p.whole_tiles && p.ksplit > 1) {
           const int ks = (t - p.whole_tiles) % p.ksplit;
           n_kb = (ks + 1) * num_kb / p.ksplit - ks * num_kb / p.ksplit;
         }
@@ -385,6 +483,7 @@ hb_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             const int slot = stage * G + j;
             uint32_t a_lo = (((sA >> 4) + slot * a16) & 0x3FFFu) | a_lo_fixed;
             uint64_t a_hi_extra = 0;
+#ifdef HB_PROBES
             if (probe >= 16) {
               // diagnostic: start the A descriptor `shift` rows (128 bytes each) into the tile,
               // with (probe >= 32) or without the descriptor's base-offset field set
@@ -393,15 +492,15 @@ hb_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
               a_lo = ((addr >> 4) & 0x3FFFu) | a_lo_fixed;
               if (probe >= 32) a_hi_extra = static_cast<uint64_t>((addr >> 7) & 7u) << 49;
             }
+            if (probe == 2) continue;  // diagnostic: loads only
+#endif
             const uint32_t b_lo = (((sB >> 4) + slot * b16) & 0x3FFFu) | b_lo_fixed;
-            if (probe != 2) {
-  #pragma unroll
-              for (int k = 0; k < 4; ++k) {
-                if (k < n_mma) {
-                  umma_cg<CG, KIND>(d_tmem, desc_hi | a_hi_extra | (a_lo + 2u * k), desc_hi | (b_lo + b_step16 * k), idesc_t,
-                                    accum);
-                  accum = 1u;
-                }
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              if (k < n_mma) {
+                umma_cg<CG, KIND>(d_tmem, desc_hi | a_hi_extra | (a_lo + 2u * k), desc_hi | (b_lo + b_step16 * k), idesc_t,
+                                  accum);
+                accum = 1u;
               }
             }
           }
@@ -439,9 +538,16 @@ hb_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     uint32_t store_it = 0;
     constexpr int kColsPerStore = 128 / OUT_BYTES;  // 32 (4-byte) or 64 (fp16) columns
     const uint32_t my_buf = sEpi + ew * 2 * kEpiBufBytes;
-    for (int t = first_tile; ok && t < p.num_tiles; t += tile_step) {
+    Walk walk = walk_begin(p, first_tile, tile_step);
+    Piece pc;
+    while (ok && walk_next(p, walk, pc)) {
+      const int t = pc.t;
       int b, m_pair, n0, bn, kb0, kb1, kslice;
-      decode(t, b, m_pair, n0, bn, kb0, kb1, kslice);
+      decode(pc, b, m_pair, n0, bn, kb0, kb1, kslice);
+      // balanced schedule: does another pair hold the K blocks after / before this piece's?
+      const bool sk_later = OUT_BYTES == 4 && p.sk && pc.s1 < p.sk_per_tile;
+      const bool sk_earlier = OUT_BYTES == 4 && p.sk && pc.s0 > 0;
+      const int sk_slot = static_cast<int>(cta_rank) * kEpiWarps + q;
       const bool ksliced = OUT_BYTES == 4 && p.ksplit > 1 && t >= p.whole_tiles && !p.kslab;
       const bool chain = ksliced && p.flags != nullptr;
       const bool reduce = ksliced && (!chain || kslice > 0);
@@ -449,12 +555,34 @@ hb_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       constexpr int kArrivals = kEpiWarps * CG;  // epilogue warps that work on one tile
       const int zc = p.kslab ? kslice : b;  // third coordinate of the output: batch, or workspace slab
       const int row0 = m_pair + static_cast<int>(cta_rank) * kTileM + q * 32;
-      if (!(p.probe == 8 ? mbar_wait(smem_u32(&bars->tmem_full[acc]), acc_phase, wctx)
-                         : mbar_wait_relaxed(smem_u32(&bars->tmem_full[acc]), acc_phase, wctx))) {
+      if (!mbar_wait_relaxed(smem_u32(&bars->tmem_full[acc]), acc_phase, wctx)) {
         ok = false;
         break;
       }
       tc_fence_after();
+      if (sk_later) {
+        // The pair after this one met the tile first and left the sums of the later K blocks in
+        // the output: wait (bounded) until its warp for these 32 rows says they are in memory.
+        const int* f = p.flags + (first_tile + 1) * kArrivals + sk_slot;
+        int got = 1;
+        if (lane == 0) {
+          const long long t0 = clock64();
+          while (ld_acquire_gpu(f) == 0) {
+            if (*abort_flag || clock64() - t0 > wctx.limit_cycles) {
+              *abort_flag = 1;
+              got = 0;
+              break;
+            }
+            __nanosleep(64);
+          }
+        }
+        got = __shfl_sync(0xffffffffu, got, 0);
+        __syncwarp();
+        if (!got) {
+          ok = false;
+          break;
+        }
+      }
       if (chain && kslice > 0) {
         // wait (bounded) for the slice before this one to have written the tile
         int got = 1;
@@ -501,6 +629,31 @@ hb_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             __half2 h = __floats2half2_rn(__uint_as_float(v2[(2 * i) % (OUT_BYTES == 2 ? 32 : 1)]),
                                           __uint_as_float(v2[(2 * i + 1) % (OUT_BYTES == 2 ? 32 : 1)]));
             packed[16 + i] = *reinterpret_cast<uint32_t*>(&h);
+          }
+        }
+        if constexpr (OUT_BYTES == 4) {
+          if (sk_later) {
+            const int row = row0 + lane, col = n0 + c0;
+            if (row < p.M && col < p.N) {
+              const uint8_t* src = static_cast<const uint8_t*>(p.C) +
+                                   (static_cast<long long>(b) * p.batch_stride_c +
+                                    static_cast<long long>(row) * p.ldc + col) * 4;
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                if (col + 4 * j < p.N) {  // rows are 16-byte multiples here: whole vectors or none
+                  const uint4 x = ld_cg_v4(src + 16 * j);
+                  if (KIND == 1) {
+                    packed[4 * j] += x.x; packed[4 * j + 1] += x.y;
+                    packed[4 * j + 2] += x.z; packed[4 * j + 3] += x.w;
+                  } else {
+                    packed[4 * j] = __float_as_uint(__uint_as_float(packed[4 * j]) + __uint_as_float(x.x));
+                    packed[4 * j + 1] = __float_as_uint(__uint_as_float(packed[4 * j + 1]) + __uint_as_float(x.y));
+                    packed[4 * j + 2] = __float_as_uint(__uint_as_float(packed[4 * j + 2]) + __uint_as_float(x.z));
+                    packed[4 * j + 3] = __float_as_uint(__uint_as_float(packed[4 * j + 3]) + __uint_as_float(x.w));
+                  }
+                }
+              }
+            }
           }
         }
         if (c0 + kColsPerStore < bn) {
@@ -608,6 +761,20 @@ hb_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 }
               }
             }
+          }
+        }
+      }
+      if (sk_later || sk_earlier) {
+        // (the partial sums read above are in registers or already stored: the flag that
+        // announced them goes back to zero for the next launch; then, if an earlier K range of
+        // this tile is still to come, this warp's rows are announced in turn)
+        if (sk_earlier && p.epilogue) bulk_wait<0>();
+        __syncwarp();
+        if (lane == 0) {
+          if (sk_later) *(volatile int*)(p.flags + (first_tile + 1) * kArrivals + sk_slot) = 0;
+          if (sk_earlier) {
+            __threadfence();
+            st_release_gpu(p.flags + first_tile * kArrivals + sk_slot, 1);
           }
         }
       }

@@ -4,6 +4,10 @@
 
 namespace {
 
+// Balanced schedule: a cut of the unit line closer than this many ring stages to a tile edge is
+// moved onto the edge (a shared tile costs a partial-sum round trip worth about two stages).
+constexpr int kBalanceMinRun = 2;
+
 int build_plan(Driver& d, const Problem& pr, const hb_knobs& k, const ConvGeom* cg, const void* A,
                const void* B, void* C, hb_plan* plan) {
   const int es = esize(pr.in_a), eo = esize(pr.out);
@@ -12,6 +16,8 @@ int build_plan(Driver& d, const Problem& pr, const hb_knobs& k, const ConvGeom* 
   int rc = check_knobs(pr, k, &smem, &tmem_cols);
   if (rc != HB_OK) return rc;
 
+  // (a heap plan may be built twice: the NCHW operators re-plan with a workspace split)
+  if (g_plan_owns_flags) release_split_flags(plan->p.flags, plan->owned_flags);
   std::memset(plan, 0, sizeof(*plan));
   KParams& p = plan->p;
   p.M = pr.M; p.N = pr.N; p.K = pr.K; p.batch = pr.batch;
@@ -28,8 +34,9 @@ int build_plan(Driver& d, const Problem& pr, const hb_knobs& k, const ConvGeom* 
   p.a_shared = pr.shared_a_b_mn ? 1 : 0;
   p.epilogue = k.epilogue == 1 ? 1 : 0;
   p.l2_prefetch = (!pr.conv && k.l2_prefetch > 0) ? k.l2_prefetch : 0;
-  p.probe = k.reserved;  // diagnostic modes
-  if (k.reserved == 12) p.wait_limit_cycles = 200000000LL;  // ~0.1 s: the timeout test should be quick: 1 = no reloads, 2 = no MMAs (results undefined)
+  p.probe = k.probe;  // diagnostic modes (builds with -DHB_PROBES only)
+  p.silent_producer = k.silent_producer ? 1 : 0;
+  if (p.silent_producer) p.wait_limit_cycles = 200000000LL;  // ~0.1 s: the timeout test should be quick
   p.idesc = make_idesc(kind, pr.in_a, pr.in_b, hb::kTileM * cgrp, k.tile_n, b_mn_major(pr));
   p.C = C; p.ldc = pr.N; p.batch_stride_c = static_cast<long long>(pr.M) * pr.N;
 
@@ -161,13 +168,56 @@ int build_plan(Driver& d, const Problem& pr, const hb_knobs& k, const ConvGeom* 
   const int tiles = p.num_tiles;
   const int tail = tiles % units;
   int split = 1, ksplit = 1;
-  // Split-K first: a slice of the reduction keeps the full-width MMA shape, so its cost falls in
-  // proportion.  The slices of a tile take turns (KParams::flags): the first stores, the others add
-  // through the L2 atomic units (about 0.7 adds per ns on B200) once the one before has finished,
-  // which costs about 2 us of hand-over.  A K block of a full-width tile takes about 0.3 us in the
-  // GEMMs and 0.58 us in the im2col conv.  A partly filled wave also runs faster than a full one
-  // where the kernel is load-bound (the convs), so there the saving has to be a quarter of the
-  // whole launch as well; a tuner may force it either way.
+
+  // Balanced schedule: the (tile, ring stage) units of the whole problem in equal runs, one per
+  // CTA pair (see hb_kernel.cuh).  Decided on counts alone: a pair does ceil(tiles * S / units)
+  // stages instead of ceil(tiles / units) * S, and pays for it with one shared tile at each end
+  // of its run (a partial-sum round trip through L2, about two stages' worth).  Needs 4-byte
+  // row-major output; a boundary closer than sk_min stages to a tile edge moves onto it.
+  const int per_tile = (p.num_kb + k.k_slices - 1) / k.k_slices;
+  const int sk_min = kBalanceMinRun;
+  const long long sk_total = static_cast<long long>(tiles) * per_tile;
+  const bool sk_can = eo == 4 && (static_cast<long long>(pr.N) * eo) % 16 == 0 && !kslab && !p.out_nchw &&
+                      units > 1 && sk_total <= 0x7fffffffLL &&
+                      sk_total >= 2ll * sk_min * units;
+  bool sk = false;
+  if (k.balance == 2) {
+    sk = sk_can;  // (a problem too small to cut keeps the tile list)
+  } else if (k.balance == 0 && sk_can && k.split_k == 0 && k.tail_split == 0 && tail > 0 && per_tile >= 4) {
+    const long long balanced = (sk_total + units - 1) / units + 2;
+    const long long fixed = static_cast<long long>((tiles + units - 1) / units) * per_tile;
+    sk = balanced * 100 <= fixed * 93;
+  }
+  if (sk) {
+    const int per_pair = hb::kEpiWarps * cgrp;
+    const int rc_flags = split_flags(units * per_pair, &p.flags);
+    if (rc_flags == HB_OK) {
+      if (g_plan_owns_flags) plan->owned_flags = units * per_pair;
+    } else if (rc_flags == HB_ERR_SCRATCH) {
+      sk = false;  // every flag slot is held by a live plan: fall back to the tile list
+    } else {
+      return rc_flags;
+    }
+  }
+  if (sk) {
+    p.sk = 1;
+    p.sk_total = static_cast<int>(sk_total);
+    p.sk_per_tile = per_tile;
+    p.sk_min = sk_min;
+    p.split = 1; p.ksplit = 1; p.kslab = 0;
+    p.whole_tiles = tiles;
+    p.idesc_split = p.idesc;
+    plan->tmB2 = plan->tmB;
+    plan->knobs.tail_split = 1;
+    plan->knobs.split_k = 1;
+    plan->knobs.balance = 2;
+    plan->grid = units * cgrp;
+    return HB_OK;
+  }
+  plan->knobs.balance = 1;
+  // Split-K of the tail tiles is an explicit knob only (the turn-taking slices of KParams::flags);
+  // by default a problem whose last wave is partly filled takes the balanced schedule above, or,
+  // where partial sums cannot travel through the output (2-byte elements), column slices.
   auto waves_of = [&](int s) {
     return static_cast<double>((static_cast<long long>(s) * tail + units - 1) / units) / s;
   };
@@ -176,19 +226,6 @@ int build_plan(Driver& d, const Problem& pr, const hb_knobs& k, const ConvGeom* 
   } else if (k.split_k > 1) {
     if (p.num_kb < k.split_k) return HB_ERR_KNOB;
     ksplit = tail > 0 ? k.split_k : 1;
-  } else if (k.split_k == 0 && k.tail_split == 0 && eo == 4 && tail > 0) {
-    const int max_ks = 2;  // more slices wait on one another's epilogues: left to an explicit knob
-    const double kb_us = pr.conv ? 0.58 : 0.30;
-    const double tile_elems = static_cast<double>(hb::kTileM) * cgrp * k.tile_n;
-    double best_gain = 0.0;
-    for (int s2 = 2; s2 <= max_ks; ++s2) {
-      if (p.num_kb < 4 * s2) continue;
-      const double saving = (1.0 - waves_of(s2)) * p.num_kb * kb_us;
-      const double cost = 2.0 + tail * tile_elems * (s2 - 1) / 700e3;
-      const double launch_waves = static_cast<double>((tiles + units - 1) / units);
-      if (pr.conv && (1.0 - waves_of(s2)) < 0.25 * launch_waves) continue;
-      if (saving > 1.25 * cost && saving - cost > best_gain) { best_gain = saving - cost; ksplit = s2; }
-    }
   }
   if (ksplit > 1) {
   } else if (k.tail_split > 1) {
@@ -203,13 +240,19 @@ int build_plan(Driver& d, const Problem& pr, const hb_knobs& k, const ConvGeom* 
       if (t < best - 1e-9) { best = t; split = s2; }
     }
   }
+  if (ksplit > 1 && !kslab) {
+    rc = split_flags(tail, &p.flags);
+    if (rc == HB_ERR_SCRATCH) {
+      ksplit = 1;  // every flag slot is held by a live plan: leave the tail tiles whole
+    } else if (rc != HB_OK) {
+      return rc;
+    } else if (g_plan_owns_flags) {
+      plan->owned_flags = tail;
+    }
+  }
   p.split = split;
   p.ksplit = ksplit;
   p.kslab = kslab ? 1 : 0;
-  if (ksplit > 1 && !kslab) {
-    rc = split_flags(tail, &p.flags);
-    if (rc != HB_OK) return rc;
-  }
   p.whole_tiles = kslab ? 0 : ((split > 1 || ksplit > 1) ? tiles - tail : tiles);
   p.num_tiles = p.whole_tiles + (tiles - p.whole_tiles) * split * ksplit;
   p.idesc_split = make_idesc(kind, pr.in_a, pr.in_b, hb::kTileM * cgrp, k.tile_n / split, b_mn_major(pr));
@@ -249,12 +292,12 @@ int run_pre(const hb_plan* plan, cudaStream_t stream) {
 
 int run_main(const hb_plan* plan, cudaStream_t stream);
 
-// The conv / GEMM kernel of this plan runs right behind another kernel of the same plan (layout
-// glue, filter unpack, the scan operand, split-K zeroing): it is launched with programmatic
-// serialization, sets itself up while that kernel drains and waits for it in griddep_wait().
-bool follows_own_kernel(const hb_plan* plan) {
-  return plan->has_pre || plan->packed_w != nullptr || plan->scan_b != nullptr;
-}
+// Every conv / GEMM kernel is launched with programmatic stream serialization: when the kernel
+// before it in the stream is one of this library's (a glue kernel of the same plan, or the
+// previous launch of a plan in a timed loop), it may take SMs as that kernel's CTAs leave them,
+// set up its barriers, TMEM and tensor-map prefetches meanwhile, and wait for that kernel's end
+// in griddep_wait() before it touches memory.  Behind any other kernel the attribute changes
+// nothing: the launch waits for that kernel to complete, as usual.
 
 int run_plan(const hb_plan* plan, cudaStream_t stream) {
   if (plan->has_pre) {
@@ -308,7 +351,7 @@ int run_main(const hb_plan* plan, cudaStream_t stream) {
     attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr.val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = &attr;
-    cfg.numAttrs = follows_own_kernel(plan) ? 1 : 0;
+    cfg.numAttrs = 1;
     cudaError_t e;
     if (sp.esize_out == 2)
       e = cudaLaunchKernelEx(&cfg, hb::hb_conv_strip_kernel<2, 0>, plan->tmA, plan->tmB, sp);
@@ -347,11 +390,10 @@ int launch_kernel(const hb_plan* plan, cudaStream_t stream) {
   cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = CG; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
-  // behind a layout kernel of the same plan: start early, wait in the kernel (griddep_wait)
   attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = follows_own_kernel(plan) ? 2 : 1;
+  cfg.numAttrs = 2;
   const cudaError_t e = cudaLaunchKernelEx(&cfg, hb::hb_umma_kernel<OUT_BYTES, CG, KIND, KS>, plan->tmA,
                                            plan->tmB, plan->tmC, plan->tmB2, plan->p);
   return e == cudaSuccess ? HB_OK : HB_ERR_LAUNCH;
@@ -393,15 +435,23 @@ int plan_scan(const void* A, void* out, int M, int N, int K, hb_dtype in_a, hb_d
   return HB_OK;
 }
 
+void destroy_plan(hb_plan* plan) {
+  if (!plan) return;
+  release_split_flags(plan->p.flags, plan->owned_flags);
+  delete plan;
+}
+
 template <class BuildFn>
 int new_plan(hb_plan** out, BuildFn build) {
   if (!out) return HB_ERR_SHAPE;
   *out = nullptr;
-  hb_plan* plan = new (std::nothrow) hb_plan;
+  hb_plan* plan = new (std::nothrow) hb_plan();
   if (!plan) return HB_ERR_LAUNCH;
+  g_plan_owns_flags = true;  // hand-over flags taken while building belong to this plan
   const int rc = build(plan);
+  g_plan_owns_flags = false;
   if (rc != HB_OK) {
-    delete plan;
+    destroy_plan(plan);
     return rc;
   }
   *out = plan;

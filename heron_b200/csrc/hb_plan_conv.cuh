@@ -46,6 +46,7 @@ int strip_smem_bytes(const ConvGeom& g, int es, int eo, hb::StripParams* sp) {
 int build_strip_plan(Driver& d, const ConvGeom& g, hb_dtype in_a, hb_dtype in_w, hb_dtype out_t,
                      const hb_knobs& k, const void* in, const void* w, void* out, hb_plan* plan) {
   const int es = esize(in_a), eo = esize(out_t);
+  if (g_plan_owns_flags) release_split_flags(plan->p.flags, plan->owned_flags);
   std::memset(plan, 0, sizeof(*plan));
   hb::StripParams& sp = plan->sp;
   const int smem = strip_smem_bytes(g, es, eo, &sp);
@@ -61,7 +62,7 @@ int build_strip_plan(Driver& d, const ConvGeom& g, hb_dtype in_a, hb_dtype in_w,
   sp.idesc = make_idesc(kind, in_a, in_w, hb::kTileM, g.CO, true);
   sp.out = out;
   sp.out_nchw = g.out_nchw ? 1 : 0;
-  sp.probe = k.reserved;
+  sp.probe = k.probe;
   // input as a tiled (C, W, H, N) tensor: one box = 128 bytes of channels x padded width x strip rows
   cuuint64_t dims[4] = {static_cast<cuuint64_t>(g.CI), static_cast<cuuint64_t>(g.W),
                         static_cast<cuuint64_t>(g.H), static_cast<cuuint64_t>(g.N)};
@@ -169,6 +170,7 @@ int plan_conv(const void* in, const void* w, void* out, int N, int H, int W, int
     if (knobs) k0 = *knobs; else std::memset(&k0, 0, sizeof(k0));
     k0.epilogue = 2;
     k0.split_k = 1;
+    k0.balance = 1;
     resolve_knobs(pr, &k0, d.sm_count, &k);
   } else {
     resolve_knobs(pr, knobs, d.sm_count, &k);
@@ -337,6 +339,7 @@ int plan_conv_nchw(const void* in, const void* w, void* out, int N, int H, int W
     k0.epilogue = 0;
     k0.split_k = 0;
     k0.tail_split = 1;
+    k0.balance = 1;  // the slabs are this plan's split
     if (k0.tile_n != 0 && out_t == HB_F16 && k0.tile_n % 64 != 0) k0.tile_n = 0;
     rc = plan_conv(s_in, s_w, s_ws, N, cH, cW, cCI, CO, KH, cKW, csh, csw, cpad_h, cpad_w, 1, 1, in_a, in_w,
                    acc_t, &k0, plan, &ex);

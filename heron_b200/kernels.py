@@ -43,6 +43,38 @@ def _dev(t, name):
     return ctypes.c_void_p(t.data_ptr())
 
 
+def _out(out, shape, like, name="out"):
+    """A caller-supplied output must be exactly what the kernel will write: a wrong size would put
+    stores past the end of the buffer."""
+    if tuple(out.shape) != tuple(shape):
+        raise ValueError("%s has shape %s, the operator writes %s" % (name, tuple(out.shape), tuple(shape)))
+    if out.dtype not in _TORCH_CODES:
+        raise _lib.HeronB200Error(_lib.HB_ERR_DTYPE, "dtype %s" % out.dtype)
+    if out.device != like.device:
+        raise ValueError("%s is on %s, the inputs are on %s" % (name, out.device, like.device))
+    return out
+
+
+def _same_device(*tensors):
+    """All operands on one device, and that device current: the library launches on the current
+    CUDA device, so a tensor elsewhere would hand it a pointer of another GPU."""
+    dev = tensors[0].device
+    for t in tensors:
+        if t.device != dev:
+            raise ValueError("operands live on different devices: %s and %s" % (dev, t.device))
+    if dev.type == "cuda" and dev.index is not None and dev.index != torch.cuda.current_device():
+        raise ValueError("tensors are on cuda:%d but the current device is cuda:%d; wrap the call in "
+                         "torch.cuda.device(...)" % (dev.index, torch.cuda.current_device()))
+
+
+def _bytes_buf(buf, need, like, name):
+    if buf.numel() * buf.element_size() < need:
+        raise ValueError("%s holds %d bytes, the operator needs %d" % (name, buf.numel() * buf.element_size(), need))
+    if buf.device != like.device:
+        raise ValueError("%s is on %s, the inputs are on %s" % (name, buf.device, like.device))
+    return buf
+
+
 def _knobs(knobs):
     if knobs is None:
         return None
@@ -67,6 +99,7 @@ def gemm(a, b, out=None, out_dtype=None, knobs=None):
         raise ValueError("a is (M,K), b is (N,K): K differs")
     if out is None:
         out = torch.empty((M, N), dtype=out_dtype or default_out_dtype(a.dtype), device=a.device)
+    _same_device(a, b, _out(out, (M, N), a))
     rc = _lib.load().hb_gemm(_dev(a, "a"), _dev(b, "b"), _dev(out, "out"), M, K, N, _code(a),
                              _code(b), _code(out), _knobs(knobs), _stream(a))
     _lib.check(rc, "hb_gemm")
@@ -81,6 +114,7 @@ def bmm(a, b, out=None, out_dtype=None, knobs=None):
         raise ValueError("a is (B,M,K), b is (B,N,K): shapes differ")
     if out is None:
         out = torch.empty((B, M, N), dtype=out_dtype or default_out_dtype(a.dtype), device=a.device)
+    _same_device(a, b, _out(out, (B, M, N), a))
     rc = _lib.load().hb_bmm(_dev(a, "a"), _dev(b, "b"), _dev(out, "out"), B, M, K, N, _code(a),
                             _code(b), _code(out), _knobs(knobs), _stream(a))
     _lib.check(rc, "hb_bmm")
@@ -118,6 +152,7 @@ def conv2d_nhwc(x, w, stride=1, padding=0, dilation=1, out=None, out_dtype=None,
     if out is None:
         out = torch.empty((N, HO, WO, CO), dtype=out_dtype or default_out_dtype(x.dtype),
                           device=x.device)
+    _same_device(x, w, _out(out, (N, HO, WO, CO), x))
     rc = _lib.load().hb_conv2d_nhwc(_dev(x, "x"), _dev(w, "w"), _dev(out, "out"), N, H, W, CI, CO,
                                     KH, KW, sh, sw, int(padding), dh, dw, _code(x), _code(w),
                                     _code(out), _knobs(knobs), _stream(x))
@@ -138,12 +173,24 @@ def conv2d_nhwc_packed(x, w_packed, CO, KH, KW, stride=1, padding=0, dilation=1,
         scratch = torch.empty(need, dtype=torch.int8, device=x.device)
     if out is None:
         out = torch.empty((N, HO, WO, CO // sco, sco), dtype=torch.int32, device=x.device)
+    _packed_checks(x, w_packed, out, scratch, need, (N, HO, WO, CO // sco, sco), (CO // sco, KH, KW, CI // 4, sco, 4))
     rc = lib.hb_conv2d_nhwc_packed(_dev(x, "x"), _dev(w_packed, "w_packed"), _dev(out, "out"), N, H,
                                    W, CI, CO, KH, KW, sh, sw, int(padding), dh, dw, int(sco),
                                    _dev(scratch, "scratch"), scratch.numel(), _knobs(knobs),
                                    _stream(x))
     _lib.check(rc, "hb_conv2d_nhwc_packed")
     return out
+
+
+def _packed_checks(x, w_packed, out, scratch, need, out_shape, w_shape):
+    n_w = 1
+    for d in w_shape:
+        n_w *= d
+    if w_packed.numel() != n_w or w_packed.element_size() != 1:
+        raise ValueError("w_packed holds %d elements, the packed filter %s has %d" % (w_packed.numel(), w_shape, n_w))
+    if tuple(out.shape) == out_shape[:3] + (out_shape[3] * out_shape[4],):
+        out_shape = tuple(out.shape)  # (N, HO, WO, CO): the same bytes as (N, HO, WO, CO/sco, sco)
+    _same_device(x, w_packed, _out(out, out_shape, x), _bytes_buf(scratch, need, x, "scratch"))
 
 
 def _nchw_common(x, w, stride, padding, out, out_dtype, scratch):
@@ -159,6 +206,7 @@ def _nchw_common(x, w, stride, padding, out, out_dtype, scratch):
                                                    _code(out))
     if scratch is None:
         scratch = torch.empty(need, dtype=torch.uint8, device=x.device)
+    _same_device(x, w, _out(out, (N, CO, HO, WO), x), _bytes_buf(scratch, need, x, "scratch"))
     return (N, H, W, CI, CO, KH, KW, sh, sw, int(padding)), out, scratch
 
 
@@ -230,6 +278,7 @@ def plan_gemm(a, b, out=None, out_dtype=None, knobs=None):
         raise ValueError("a is (M,K), b is (N,K): K differs")
     if out is None:
         out = torch.empty((M, N), dtype=out_dtype or default_out_dtype(a.dtype), device=a.device)
+    _same_device(a, b, _out(out, (M, N), a))
     h = ctypes.c_void_p()
     rc = _lib.load().hb_plan_gemm(ctypes.byref(h), _dev(a, "a"), _dev(b, "b"), _dev(out, "out"), M,
                                   K, N, _code(a), _code(b), _code(out), _knobs(knobs))
@@ -244,6 +293,7 @@ def plan_bmm(a, b, out=None, out_dtype=None, knobs=None):
         raise ValueError("a is (B,M,K), b is (B,N,K): shapes differ")
     if out is None:
         out = torch.empty((B, M, N), dtype=out_dtype or default_out_dtype(a.dtype), device=a.device)
+    _same_device(a, b, _out(out, (B, M, N), a))
     h = ctypes.c_void_p()
     rc = _lib.load().hb_plan_bmm(ctypes.byref(h), _dev(a, "a"), _dev(b, "b"), _dev(out, "out"), B,
                                  M, K, N, _code(a), _code(b), _code(out), _knobs(knobs))
@@ -262,6 +312,7 @@ def plan_conv2d_nhwc(x, w, stride=1, padding=0, dilation=1, out=None, out_dtype=
     if out is None:
         out = torch.empty((N, HO, WO, CO), dtype=out_dtype or default_out_dtype(x.dtype),
                           device=x.device)
+    _same_device(x, w, _out(out, (N, HO, WO, CO), x))
     h = ctypes.c_void_p()
     rc = _lib.load().hb_plan_conv2d_nhwc(ctypes.byref(h), _dev(x, "x"), _dev(w, "w"),
                                          _dev(out, "out"), N, H, W, CI, CO, KH, KW, sh, sw,
@@ -278,11 +329,12 @@ def plan_conv2d_nhwc_packed(x, w_packed, CO, KH, KW, stride=1, padding=0, dilati
     dh, dw = _pair(dilation)
     HO, WO = conv_out_hw(H, W, KH, KW, stride, padding, dilation)
     lib = _lib.load()
+    need = lib.hb_conv2d_packed_scratch_bytes(CI, CO, KH, KW)
     if scratch is None:
-        scratch = torch.empty(lib.hb_conv2d_packed_scratch_bytes(CI, CO, KH, KW), dtype=torch.int8,
-                              device=x.device)
+        scratch = torch.empty(need, dtype=torch.int8, device=x.device)
     if out is None:
         out = torch.empty((N, HO, WO, CO // sco, sco), dtype=torch.int32, device=x.device)
+    _packed_checks(x, w_packed, out, scratch, need, (N, HO, WO, CO // sco, sco), (CO // sco, KH, KW, CI // 4, sco, 4))
     h = ctypes.c_void_p()
     rc = lib.hb_plan_conv2d_nhwc_packed(ctypes.byref(h), _dev(x, "x"), _dev(w_packed, "w_packed"),
                                         _dev(out, "out"), N, H, W, CI, CO, KH, KW, sh, sw,

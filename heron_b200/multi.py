@@ -135,3 +135,67 @@ def gather_output(full, rank, world, group=None, check=False):
             if count:
                 dist.broadcast(full[start:start + count], src=r, group=group)
     return full
+
+
+def partition_chunked(extent, rank, world, chunks):
+    """This rank's slices when the leading dimension is first cut into ``chunks`` super-chunks and
+    every super-chunk is split over the ranks: [(start, count)] per super-chunk, plus the
+    super-chunks' own (start, count).  With ``chunks == 1`` this is ``partition``.  Each
+    super-chunk is a contiguous range whose rank slices lie in rank order, so it can be completed
+    by one in-place all-gather while the kernels of the next super-chunk run."""
+    if chunks <= 0:
+        raise ValueError("need chunks > 0")
+    supers = [sc for sc in partition(extent, chunks) if sc[1] > 0]
+    mine = []
+    for (c0, cn) in supers:
+        s, n = partition(cn, world)[rank]
+        mine.append((c0 + s, n))
+    return mine, supers
+
+
+class ChunkedGather:
+    """Compute + gather of a sharded operator's whole output with the two overlapped.
+
+    ``parts`` lists this rank's (start, count) slices of the leading dimension, one per
+    super-chunk.  ``run(plans, full)`` launches ``plans[c]`` (a kernel bound to
+    ``full[start:start+count]`` of slice c) on the current stream and, on a second stream, gathers
+    super-chunk c - 1 in place while it runs; when it returns, the current stream waits for the
+    last gather.  No kernel of this library is handed another GPU's memory: the exchange is the
+    collective library's (NCCL over NVLink on GPUs, gloo on CPU ranks)."""
+
+    def __init__(self, extent, rank, world, chunks=1, group=None):
+        self.rank, self.world, self.group = rank, world, group
+        self.parts, self.supers = partition_chunked(extent, rank, world, chunks)
+        self._comm = None
+
+    def _comm_stream(self, device):
+        import torch
+        if self._comm is None:
+            self._comm = torch.cuda.Stream(device=device)
+        return self._comm
+
+    def gather_super(self, full, c):
+        c0, cn = self.supers[c]
+        gather_output(full[c0:c0 + cn], self.rank, self.world, group=self.group)
+
+    def run(self, plans, full):
+        if len(plans) != len(self.parts):
+            raise ValueError("one plan per super-chunk")
+        if not full.is_cuda:
+            for c, plan in enumerate(plans):  # CPU ranks (tests): no streams to overlap
+                plan()
+                self.gather_super(full, c)
+            return full
+        import torch
+        cur = torch.cuda.current_stream(full.device)
+        comm = self._comm_stream(full.device)
+        comm.wait_stream(cur)  # earlier users of `full` on the compute stream
+        for c, plan in enumerate(plans):
+            plan.launch()
+            done = torch.cuda.Event()
+            done.record(cur)
+            with torch.cuda.stream(comm):
+                comm.wait_event(done)
+                self.gather_super(full, c)
+        cur.wait_stream(comm)
+        return full

@@ -241,6 +241,15 @@ class Solver:
                 cands.insert(0, hint[k])
             return cands
 
+        def pairs_ok(state):
+            # a two-valued `known` entry is a real two-element domain, not the interval between
+            # its values: a state whose interval holds neither value is dead
+            for k, cands in pairs.items():
+                lo, hi = state.lo[k], state.hi[k]
+                if not any(lo <= c <= hi for c in cands):
+                    return False
+            return True
+
         def rec(state):
             nodes[0] += 1
             if nodes[0] > self.node_limit:
@@ -255,6 +264,8 @@ class Solver:
                     _propagate(prims, child)
                 except _Wipeout:
                     continue
+                if not pairs_ok(child):
+                    continue
                 res = rec(child)
                 if res is not None:
                     return res
@@ -263,6 +274,8 @@ class Solver:
         try:
             _propagate(prims, st)
         except _Wipeout:
+            return None
+        if not pairs_ok(st):
             return None
         return rec(st)
 

@@ -266,6 +266,25 @@ class splitKOp(SchedOp):
         ctx.addSchedDesc("## split-K %s\n" % ctx.kernel_knobs["split_k"])
 
 
+class balanceOp(SchedOp):
+    """How work is dealt out to the persistent CTAs: whole tiles round-robin (1), or equal runs
+    of (tile, K stage) units whose end tiles are shared with the neighbouring CTA pair (2).  0
+    leaves the choice to the library.  Partial sums travel through the output, so only 4-byte
+    outputs with 16-byte rows have the second form."""
+
+    def perform(self, s, stage_name, ctx):
+        km = ctx.knob_manager
+        out = _problem(s, stage_name)
+        p = out.op.params
+        eo = ELEM_BYTES[p["out_dtype"]]
+        _, M, N, K, _ = _gemm_view(out)
+        balance = genKey("P", stage_name, "m", param_name="balance")
+        if km.is_building:
+            km.define_value(balance, 0, 2 if (eo == 4 and (N * eo) % 16 == 0) else 1, 0, True)
+        ctx.kernel_knobs["balance"] = km.get_val(balance)
+        ctx.addSchedDesc("## balance %s\n" % ctx.kernel_knobs["balance"])
+
+
 _METHODS = {
     "tileOp": tileOp,
     "pipelineOp": pipelineOp,
@@ -273,6 +292,7 @@ _METHODS = {
     "rasterOp": rasterOp,
     "convAlgoOp": convAlgoOp,
     "splitKOp": splitKOp,
+    "balanceOp": balanceOp,
 }
 
 
@@ -289,5 +309,5 @@ def sched_via_rule(_type, ctx, s):
     that ``Task.instantiate`` can replay them (schedule/sched_op/__init__.py:23-30)."""
     get_op_methods(_type)
     for out in s.outputs:
-        for rule in ("tileOp", "pipelineOp", "epilogueOp", "rasterOp", "convAlgoOp", "splitKOp"):
+        for rule in ("tileOp", "pipelineOp", "epilogueOp", "rasterOp", "convAlgoOp", "splitKOp", "balanceOp"):
             ctx.addSched(rule, out.op.name, s)

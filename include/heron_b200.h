@@ -80,7 +80,17 @@ typedef struct {
   int k_slices;      /* swizzle spans of K behind one ring barrier (1 or 2): with 2 the MMA thread
                         waits, fences and commits once per eight MMAs instead of four, at the same
                         ring size in bytes.  0 = library picks                                     */
-  int reserved;      /* diagnostic probe modes; leave 0                                            */
+  int balance;       /* work distribution over the persistent CTAs (or CTA pairs).  1: whole tiles dealt
+                        out round-robin (with tail_split / split_k for the last wave); 2: the (tile,
+                        K stage) units of the whole problem in equal runs, one per CTA pair: tiles at
+                        the ends of a run are shared with the neighbouring pair, which leaves its
+                        partial sums in the output for this one to add (fixed order, no atomics;
+                        overrides tail_split and split_k).  4-byte outputs with 16-byte rows only;
+                        0 = library picks                                                          */
+  int silent_producer; /* test hook, leave 0.  1: the TMA producers issue nothing, so every consumer's
+                        bounded wait runs out (0.1 s limit for such a launch) and the launch ends
+                        with HB_ERR_TIMEOUT in the status word and the context intact              */
+  int probe;         /* diagnostic modes of builds made with -DHB_PROBES; ignored otherwise         */
 } hb_knobs;
 
 /*
@@ -114,6 +124,16 @@ int hb_default_knobs(int op, int batch, int M, int N, int K, int k_inner, hb_dty
  * resources the configuration needs (either may be NULL). */
 int hb_check_knobs(int op, int batch, int M, int N, int K, int k_inner, hb_dtype in_a,
                    hb_dtype out, const hb_knobs* k, int* smem_bytes, int* tmem_cols);
+
+/*
+ * The partition rule of the balanced schedule (knob `balance` = 2), evaluated on the host: the
+ * problem's `tiles` x `stages_per_tile` ring stages, numbered tile-major, are cut into `pairs`
+ * runs; *first / *end receive the run [first, end) of CTA pair `pair`.  A cut that falls within
+ * two stages of a tile edge is moved onto it.  It is the same function the kernel evaluates; a
+ * tuner's cost model or a test can call it without a GPU.  The reference has no counterpart: its
+ * generated kernels bind one block per output tile (schedule/sched_op/gpu_tensorcore_operator.py).
+ */
+int hb_balanced_run(int tiles, int stages_per_tile, int pairs, int pair, int* first, int* end);
 
 /*
  * GEMM: C[M,N] = sum_k A[M,K] * B[N,K]  (B is stored N-major over K, i.e. C = A * B^T).

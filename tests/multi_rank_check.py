@@ -49,6 +49,19 @@ def main():
     gather_output(full, rank, world)
     ok &= bool(np.array_equal(full.cpu().numpy(), npo.conv2d_nhwc_int(x, w, 1, 1, 1)))
 
+    # the overlapped form: two super-chunks, the gather of the first behind the kernel of the second
+    from heron_b200.multi import ChunkedGather
+    for chunks in (2, 3):
+        cg = ChunkedGather(16, rank, world, chunks)
+        full = torch.full((16, 7, 7, 128), -1, dtype=torch.int32, device=dev)
+        wd = torch.from_numpy(w).to(dev)
+        plans = [K.plan_conv2d_nhwc(torch.from_numpy(x[s:s + n]).to(dev), wd, 1, 1, 1, out=full[s:s + n])
+                 for (s, n) in cg.parts if n]
+        if len(plans) == len(cg.parts):
+            cg.run(plans, full)
+            torch.cuda.synchronize(dev)
+            ok &= bool(np.array_equal(full.cpu().numpy(), npo.conv2d_nhwc_int(x, w, 1, 1, 1)))
+
     ok &= _lib.last_status() == 0
     flag = torch.tensor([1 if ok else 0], device=dev)
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)

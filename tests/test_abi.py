@@ -171,3 +171,76 @@ def test_library_limits_match_the_constraint_model(hb_lib):
                 "smem_slack_bytes"):
         assert lim[key] == B200_LIMITS[key], key
     assert lim["static_scratch_bytes"] == hb_lib.hb_conv2d_packed_noalloc_max_bytes()
+
+
+# ---- the balanced schedule's partition rule (evaluated on the host, no GPU) ----------------------
+def _runs(lib, tiles, per_tile, pairs):
+    import ctypes
+    out = []
+    for i in range(pairs):
+        a, b = ctypes.c_int(-1), ctypes.c_int(-1)
+        assert lib.hb_balanced_run(tiles, per_tile, pairs, i, ctypes.byref(a), ctypes.byref(b)) == 0
+        out.append((a.value, b.value))
+    return out
+
+
+def _pieces(run, per_tile):
+    """The tiles a run touches, in the order the kernel's roles walk them: (tile, s0, s1)."""
+    cur, end = run
+    out = []
+    while cur < end:
+        t, s0 = divmod(cur, per_tile)
+        s1 = min(per_tile, s0 + (end - cur))
+        out.append((t, s0, s1))
+        cur += s1 - s0
+    return out
+
+
+@pytest.mark.parametrize("tiles,per_tile,pairs", [
+    (392, 18, 74), (196, 18, 74), (98, 18, 74), (50, 18, 74), (256, 32, 74), (256, 64, 148),
+    (1, 40, 8), (75, 4, 74), (74, 9, 74), (1000, 1, 148), (5, 1000, 148), (149, 4, 148)])
+def test_balanced_runs_cover_every_stage_once_and_pair_up_their_shared_tiles(hb_lib, tiles, per_tile, pairs):
+    # (the library plans this schedule only when every pair gets at least four stages)
+    assert tiles * per_tile >= 4 * pairs
+    runs = _runs(hb_lib, tiles, per_tile, pairs)
+    total = tiles * per_tile
+    assert runs[0][0] == 0 and runs[-1][1] == total
+    for (a0, a1), (b0, b1) in zip(runs, runs[1:]):
+        assert a0 <= a1 == b0 <= b1, "runs are consecutive and in order"
+    seen = {}
+    for i, run in enumerate(runs):
+        for (t, s0, s1) in _pieces(run, per_tile):
+            assert 0 <= s0 < s1 <= per_tile and 0 <= t < tiles
+            for s in range(s0, s1):
+                assert (t, s) not in seen, "stage walked twice"
+                seen[(t, s)] = i
+    assert len(seen) == total
+    # hand-overs: the pair whose run ENDS inside a tile waits for the flags of the pair after it,
+    # and that pair's FIRST piece must be the continuation of the very same tile
+    for i, run in enumerate(runs):
+        ps = _pieces(run, per_tile)
+        if not ps:
+            continue
+        t, s0, s1 = ps[-1]
+        if s1 < per_tile:  # "later" K blocks are held by another pair
+            nxt = _pieces(runs[i + 1], per_tile)
+            assert nxt and nxt[0][0] == t and nxt[0][1] == s1, (i, ps[-1], nxt[:1])
+        t, s0, s1 = ps[0]
+        if s0 > 0:  # an "earlier" K range is held by the pair before
+            prv = _pieces(runs[i - 1], per_tile)
+            assert prv and prv[-1][0] == t and prv[-1][2] == s0
+        # only the first piece may start inside a tile, only the last may end inside one
+        for (t, s0, s1) in ps[1:]:
+            assert s0 == 0
+        for (t, s0, s1) in ps[:-1]:
+            assert s1 == per_tile
+    # cuts stay two stages clear of tile edges (or sit on them)
+    for a0, _ in runs:
+        r = a0 % per_tile
+        assert r == 0 or (2 <= r <= per_tile - 2)
+
+
+def test_balanced_runs_are_level(hb_lib):
+    runs = _runs(hb_lib, 50, 18, 74)   # 128 images of the int8 ResNet layer: 50 pair tiles, 74 pairs
+    sizes = [b - a for a, b in runs]
+    assert max(sizes) <= 900 // 74 + 1 + 2 and min(sizes) >= 900 // 74 - 2

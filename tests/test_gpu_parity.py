@@ -234,6 +234,95 @@ def test_two_k_spans_per_ring_stage(K, co, knobs):
     check(k_bmm(K, a3, b3, knobs=ck), co.bmm_int(a3, b3), "k spans bmm %s" % (ck,))
 
 
+# ---- balanced schedule (knob balance = 2) --------------------------------------------------------
+BALANCE_KNOBS = [
+    dict(), dict(cta_group=1), dict(cta_group=2), dict(max_ctas=6), dict(max_ctas=10, cta_group=2),
+    dict(k_slices=1, max_ctas=14), dict(k_slices=2, max_ctas=22, cta_group=1), dict(epilogue=2, max_ctas=8),
+    dict(tile_n=64, max_ctas=12), dict(tile_n=128, cta_group=2, max_ctas=20, stages=2),
+    dict(raster=1, max_ctas=18), dict(acc_stages=1, max_ctas=6),
+]
+
+
+@pytest.mark.parametrize("knobs", BALANCE_KNOBS)
+def test_balanced_schedule_gemm_and_bmm(K, co, knobs):
+    """Equal runs of (tile, K stage) units per CTA pair: tiles at the ends of a run are shared with
+    the neighbouring pair through partial sums left in the output.  Integer results are exact;
+    fp32 results equal the oracle within tolerance and are identical from launch to launch."""
+    kn = dict(knobs, balance=2)
+    rng = np.random.default_rng(77 + sum(knobs.values()))
+    for M, N, Kd in ((520, 328, 1152), (1000, 136, 2048), (300, 200, 640), (129, 260, 4096)):
+        a, b = rand_i8(rng, (M, Kd), False), rand_i8(rng, (N, Kd), True)
+        check(k_gemm(K, a, b, knobs=kn), co.gemm_int(a, b), "balanced int8 %s %s" % ((M, N, Kd), kn))
+    af = (rng.standard_normal((700, 1536)) / np.sqrt(1536)).astype(np.float16)
+    bf = rng.standard_normal((392, 1536)).astype(np.float16)
+    first = k_gemm(K, af, bf, knobs=kn)
+    check(first, co.gemm_f16(af, bf), "balanced fp16 %s" % (kn,))
+    for _ in range(3):
+        assert torch.equal(k_gemm(K, af, bf, knobs=kn), first), "the order of the additions is fixed"
+    a3, b3 = rand_i8(rng, (7, 200, 512), True), rand_i8(rng, (7, 136, 512), True)
+    check(k_bmm(K, a3, b3, knobs=kn), co.bmm_int(a3, b3), "balanced bmm %s" % (kn,))
+
+
+@pytest.mark.parametrize("knobs", [dict(), dict(cta_group=1), dict(max_ctas=10), dict(k_slices=1, max_ctas=30),
+                                   dict(epilogue=2, cta_group=2, max_ctas=12)])
+def test_balanced_schedule_conv(K, co, knobs):
+    kn = dict(knobs, balance=2, conv_algo=1)
+    rng = np.random.default_rng(91 + sum(knobs.values()))
+    for case in ((6, 7, 7, 128, 128, 3, 3, 1, 1, 1), (4, 14, 14, 128, 256, 3, 3, 2, 1, 1), (3, 9, 11, 64, 96, 3, 3, (2, 1), 1, 1)):
+        N, H, W, CI, CO, KH, KW, st, p, d = case
+        x, w = rand_i8(rng, (N, H, W, CI), False), rand_i8(rng, (KH, KW, CI, CO), True)
+        check(k_conv(K, x, w, st, p, d, knobs=kn), co.conv2d_nhwc_int(x, w, st, p, d), "balanced conv %s %s" % (case, kn))
+    x = rng.standard_normal((5, 10, 10, 64)).astype(np.float16)
+    w = (rng.standard_normal((3, 3, 64, 64)) / 24.0).astype(np.float16)
+    check(k_conv(K, x, w, 1, 1, 1, out_dtype=np.float32, knobs=kn), co.conv2d_nhwc_f16(x, w, 1, 1, 1, np.float32),
+          "balanced conv fp16 %s" % (kn,))
+
+
+def test_balanced_schedule_is_what_the_sharded_shapes_get(K, co):
+    """The per-GPU shards of the two batch-sharded benchmark configurations at 4 and 8 GPUs (256 and
+    128 images; 48 and 24 batches): the library's own choice of schedule, against the oracle on
+    sampled images / batches and through exact sum identities over every element; split-K forced on
+    for the same shapes as well."""
+    from heron_b200.workloads import make_inputs
+    for count in (128, 256):
+        x, w = make_inputs("cfg5_conv_u8s8_resnet_s4", shard=(512, count))
+        out = poison((count, 7, 7, 512), torch.int32)
+        plan = K.plan_conv2d_nhwc(dev(x), dev(w), stride=1, padding=1, dilation=1, out=out)
+        assert plan.knobs()["balance"] == 2, plan.knobs()
+        plan.launch()
+        for n in (0, 1, count // 2, count - 1):
+            check(out[n:n + 1], co.conv2d_nhwc_int(x[n:n + 1], w, 1, 1, 1), "shard of %d images, image %d" % (count, n))
+        got = out.cpu().numpy().astype(np.int64).sum(axis=3)
+        wsum = w.astype(np.int64).sum(axis=3)
+        xp = np.pad(x.astype(np.int64), ((0, 0), (1, 1), (1, 1), (0, 0)))
+        want = np.zeros(got.shape, dtype=np.int64)
+        for ry in range(3):
+            for rx in range(3):
+                want += (xp[:, ry:ry + 7, rx:rx + 7, :] * wsum[ry, rx]).sum(axis=3)
+        assert np.array_equal(got, want)
+        forced = k_conv(K, x, w, 1, 1, 1, knobs=dict(split_k=2, balance=1))
+        assert torch.equal(forced, out), "split-K and the balanced schedule agree bit for bit"
+    for count in (24, 48):
+        a, b = make_inputs("cfg4_bmm_s8_attention", shard=(96, count))
+        out = k_bmm(K, a, b)
+        for bi in (0, count // 2, count - 1):
+            check(out[bi], co.gemm_int(a[bi], b[bi]), "shard of %d batches, batch %d" % (count, bi))
+        got = out.cpu().numpy().astype(np.int64)
+        a64, b64 = a.astype(np.int64), b.astype(np.int64)
+        assert np.array_equal(got.sum(axis=2), np.einsum("bik,bk->bi", a64, b64.sum(axis=1)))
+        assert np.array_equal(got.sum(axis=1), np.einsum("bjk,bk->bj", b64, a64.sum(axis=1)))
+        assert torch.equal(k_bmm(K, a, b, knobs=dict(balance=2)), out)
+
+
+def test_balanced_schedule_refused_for_two_byte_outputs(K):
+    from heron_b200._lib import HB_ERR_KNOB, HeronB200Error
+    a = torch.zeros(256, 512, dtype=torch.float16, device="cuda")
+    b = torch.zeros(256, 512, dtype=torch.float16, device="cuda")
+    with pytest.raises(HeronB200Error) as e:
+        K.gemm(a, b, out=torch.empty(256, 256, dtype=torch.float16, device="cuda"), knobs=dict(balance=2))
+    assert e.value.status == HB_ERR_KNOB
+
+
 def test_split_k_rejected_where_it_cannot_add(K):
     from heron_b200._lib import HB_ERR_KNOB, HeronB200Error
     a = torch.zeros(128, 512, dtype=torch.float16, device="cuda")
@@ -952,7 +1041,7 @@ def test_bounded_wait_runs_out_cleanly(K, co):
     a, b = rand_i8(rng, (256, 128), False), rand_i8(rng, (256, 128), True)
     ta, tb = dev(a), dev(b)
     out = poison((256, 256), torch.int32)
-    K.gemm(ta, tb, out=out, knobs=dict(cta_group=1, reserved=12))
+    K.gemm(ta, tb, out=out, knobs=dict(cta_group=1, silent_producer=1))
     assert _lib.last_status() == _lib.HB_ERR_TIMEOUT
     assert _lib.last_status() == 0  # reading clears it
     for _ in range(3):  # TMEM was released: full-size allocations succeed again

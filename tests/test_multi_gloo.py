@@ -117,3 +117,61 @@ def test_rank_that_leaves_ends_the_collective_with_an_error():
             p.terminate()
     assert results[1] == "left"
     assert results[0].startswith("error:")
+
+
+def _chunked_worker(rank, world, port, extent, chunks, q):
+    sys.path.insert(0, ROOT)
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from heron_b200.multi import ChunkedGather
+        from oracle import np_oracle as npo
+        rng = np.random.default_rng(321)
+        a = rng.integers(-128, 128, (extent, 16, 32)).astype(np.int8)
+        b = rng.integers(-128, 128, (extent, 8, 32)).astype(np.int8)
+        full = torch.full((extent, 16, 8), -1, dtype=torch.int32)
+        cg = ChunkedGather(extent, rank, world, chunks)
+
+        def kernel_for(start, count):
+            def run():  # the oracle stands in for the kernel bound to this slice of `full`
+                if count:
+                    full[start:start + count].copy_(torch.from_numpy(npo.bmm_int(a[start:start + count],
+                                                                                 b[start:start + count])))
+            return run
+
+        cg.run([kernel_for(s, n) for (s, n) in cg.parts], full)
+        q.put((rank, bool(torch.equal(full, torch.from_numpy(npo.bmm_int(a, b)))), len(cg.parts)))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("extent,chunks", [(8, 2), (12, 3), (7, 2), (9, 4), (3, 4)])
+def test_two_rank_chunked_gather(extent, chunks):
+    """The overlapped form: the leading dimension cut into super-chunks, each split over the ranks
+    and gathered by itself (equal and ragged splits; more chunks than units)."""
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 29500 + (os.getpid() + 300 + 10 * extent + chunks) % 2000
+    procs = [ctx.Process(target=_chunked_worker, args=(r, 2, port, extent, chunks, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=120) for _ in range(2)]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert sorted(r[:2] for r in results) == [(0, True), (1, True)]
+
+
+def test_chunked_partition_covers_the_extent_once():
+    sys.path.insert(0, ROOT)
+    from heron_b200.multi import partition_chunked
+    for extent, world, chunks in [(1024, 8, 4), (192, 8, 2), (10, 4, 3), (5, 8, 2), (1, 2, 1)]:
+        seen = []
+        for r in range(world):
+            mine, supers = partition_chunked(extent, r, world, chunks)
+            assert len(mine) == len(supers)
+            for (s, n), (c0, cn) in zip(mine, supers):
+                assert c0 <= s and s + n <= c0 + cn
+                seen.extend(range(s, s + n))
+        assert sorted(seen) == list(range(extent))
