@@ -40,6 +40,7 @@ EXPORTED_SYMBOLS = (
     "hb_default_knobs",
     "hb_check_knobs",
     "hb_balanced_run",
+    "hb_balanced_pieces",
     "hb_gemm",
     "hb_bmm",
     "hb_conv2d_nhwc",
@@ -164,6 +165,8 @@ def load():
     lib.hb_check_knobs.argtypes = [c_int] * 6 + [c_int, c_int, kp, ip, ip]
     lib.hb_balanced_run.restype = c_int
     lib.hb_balanced_run.argtypes = [c_int] * 4 + [ip, ip]
+    lib.hb_balanced_pieces.restype = c_int
+    lib.hb_balanced_pieces.argtypes = [c_int] * 4 + [ip, c_int]
     lib.hb_gemm.restype = c_int
     lib.hb_gemm.argtypes = [c_void_p] * 3 + [c_int] * 3 + [c_int] * 3 + [kp, c_void_p]
     lib.hb_bmm.restype = c_int

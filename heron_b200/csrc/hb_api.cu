@@ -80,6 +80,31 @@ int hb_balanced_run(int tiles, int stages_per_tile, int pairs, int pair, int* fi
   return HB_OK;
 }
 
+int hb_balanced_pieces(int tiles, int stages_per_tile, int pairs, int pair, int* pieces, int max_pieces) {
+  if (tiles <= 0 || stages_per_tile <= 0 || pairs <= 0 || pair < 0 || pair >= pairs || !pieces || max_pieces < 0)
+    return -HB_ERR_SHAPE;
+  const long long total = static_cast<long long>(tiles) * stages_per_tile;
+  if (total > 0x7fffffffLL) return -HB_ERR_SHAPE;
+  hb::KParams p;
+  std::memset(&p, 0, sizeof(p));
+  p.sk = 1;
+  p.sk_total = static_cast<int>(total);
+  p.sk_per_tile = stages_per_tile;
+  p.sk_min = kBalanceMinRun;
+  hb::Walk w = hb::walk_begin(p, pair, pairs);
+  hb::Piece pc;
+  int n = 0;
+  while (hb::walk_next(p, w, pc)) {
+    if (n < max_pieces) {
+      pieces[3 * n] = pc.t;
+      pieces[3 * n + 1] = pc.s0;
+      pieces[3 * n + 2] = pc.s1;
+    }
+    ++n;
+  }
+  return n;
+}
+
 int hb_gemm(const void* A, const void* B, void* C, int M, int K, int N, hb_dtype in_a,
             hb_dtype in_b, hb_dtype out, const hb_knobs* knobs, void* stream) {
   hb_plan plan;

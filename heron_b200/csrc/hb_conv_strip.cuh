@@ -197,6 +197,18 @@ hb_conv_strip_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_cons
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * p.CO);
         uint32_t accum = 0u;
+#ifdef HB_PROBES
+        if (p.probe == 9) {
+          // diagnostic: the tile's MMA count on fixed descriptors, no address arithmetic in the loop
+          const uint32_t a_lo = (((sStrip + buf * strip_total) >> 4) & 0x3FFFu) | a_lo_fixed;
+          const uint32_t b_lo = ((sFilt >> 4) & 0x3FFFu) | b_lo_fixed;
+          const uint64_t da = desc_hi | a_lo, db = desc_hi | b_lo;
+          const int n = p.KH * p.KW * p.n_cchunks * 4;
+          umma_cg<1, KIND>(d_tmem, da, db, idesc, 0u);
+#pragma unroll 4
+          for (int i = 1; i < n; ++i) umma_cg<1, KIND>(d_tmem, da, db, idesc, 1u);
+        } else
+#endif
         for (int ry = 0; ry < p.KH && p.probe != 2; ++ry)
           for (int rx = 0; rx < p.KW; ++rx) {
             uint32_t row_off = static_cast<uint32_t>(ry * p.dil_h * p.Wp + rx * p.dil_w) * 128u;
@@ -257,7 +269,7 @@ hb_conv_strip_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_cons
           tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(acc * p.CO);
       uint8_t* orow = static_cast<uint8_t*>(p.out) +
                       ((static_cast<long long>(n) * p.HO + y) * p.WO + px) * p.CO * OUT_BYTES;
-      if (p.probe == 3) {
+      if (p.probe == 3 || p.probe == 9) {
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&bars->tmem_empty[acc]));

@@ -8,6 +8,7 @@
 #include "hb_kernel.cuh"
 #include "hb_glue.cuh"
 #include "hb_conv_strip.cuh"
+#include "hb_conv_strip_t.cuh"
 
 #include <cuda.h>
 #include <cuda_runtime.h>
@@ -54,7 +55,9 @@ bool setup_device(Driver* d) {
   if (prop.major != 10) return false;
   d->sm_count = prop.multiProcessorCount;
   // Opt in to the large dynamic shared-memory carve-out for every kernel instantiation.
-  const void* kernels[15] = {
+  const void* kernels[17] = {
+      reinterpret_cast<const void*>(&hb::hb_conv_strip_t_kernel<2>),
+      reinterpret_cast<const void*>(&hb::hb_conv_strip_t_kernel<4>),
       reinterpret_cast<const void*>(&hb::hb_umma_kernel<4, 1, 0, 1>),
       reinterpret_cast<const void*>(&hb::hb_umma_kernel<2, 1, 0, 1>),
       reinterpret_cast<const void*>(&hb::hb_umma_kernel<4, 1, 1, 1>),
@@ -343,6 +346,9 @@ struct hb_plan {
   // strip conv (conv_algo 2): its own parameter block; tmA = tiled input map, tmB = filter map
   bool strip;
   hb::StripParams sp;
+  // wide strip conv (conv_algo 3): channels on the MMA's M axis, up to 256 pixels on N
+  bool strip_t;
+  hb::StripTParams spt;
   // NCHW operators only: one launch that brings input and filter to NHWC / HWIO first (the conv
   // kernel's epilogue writes NCHW itself)
   bool has_pre, pre_is_stem;

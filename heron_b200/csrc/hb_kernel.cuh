@@ -47,13 +47,12 @@
 // Balanced schedule (KParams::sk): instead of whole tiles dealt out round-robin, the (tile, ring
 // stage) pairs of the whole problem form one line of work units that is cut into equal runs, one
 // per CTA pair.  A run starts and ends inside tiles, so a tile may be shared by two (seldom three)
-// pairs, each holding a K range of it.  The pair that holds the END of a tile's K range meets it
-// first (at the start of its run): it stores its partial sums into the output tile itself and
-// raises a flag per epilogue warp.  The pair that holds the range before it meets the tile last
-// (at the end of its run): its epilogue waits (bounded) for the flag, reads the partial sums back
-// from the output (they are still in L2), adds them to its accumulator and stores the result.
-// No atomics, no workspace, a fixed order of additions, and every pair does the same number of
-// ring stages whatever the tile count.
+// pairs, each holding a K range of it.  A pair takes its two shared tiles first (struct Walk).  The
+// pair that holds the START of a tile's K range stores its partial sums into the output tile
+// itself and raises a flag per epilogue warp; the pair that holds the range after it waits
+// (bounded) for the flag, reads the partial sums back (they are still in L2), adds them to its
+// accumulator and stores the result.  No atomics, no workspace, a fixed order of additions, and
+// every pair does the same number of ring stages whatever the tile count.
 //
 // Every wait on an mbarrier is bounded.  When one runs out, the CTA raises a shared abort flag,
 // every role leaves its loop, in-flight TMA loads and MMAs are waited for (bounded again), TMEM
@@ -148,44 +147,81 @@ __host__ __device__ __forceinline__ int sk_bound_of(int total, int per_tile, int
   }
   return b;
 }
-__device__ __forceinline__ int sk_bound(const KParams& p, int i, int n) {
+__host__ __device__ __forceinline__ int sk_bound(const KParams& p, int i, int n) {
   return sk_bound_of(p.sk_total, p.sk_per_tile, p.sk_min, i, n);
 }
 
-// The work items of one CTA pair, in the order it meets them: whole work items of the static
-// list (index `unit`, `unit + n`, ...), or the tiles its run of the balanced schedule touches.
+// The work items of one CTA pair, in the order it takes them.  Static list: work items `unit`,
+// `unit + n`, ...  Balanced schedule: the tiles its run [lo, hi) touches, the two shared ones
+// FIRST — the run's last tile (of which it holds the first K stages: it stores partial sums for
+// the next pair), then the run's first tile (of which it holds the last K stages: it adds what
+// the pair before has stored) — and the whole tiles after them.  Both hand-overs thus happen at
+// the start of a run, hidden behind the main loop of the tiles that follow, and the last thing
+// every pair does is an ordinary tile.
 struct Walk {
-  int cur, end, step;
+  int cur, end, step;  // static list: next item, item count, stride.  balanced: next whole tile, last + 1, phase
+  int lo, hi;          // balanced: the run
 };
 struct Piece {
   int t;       // work item (static list) or tile (balanced schedule)
   int s0, s1;  // balanced schedule: ring stages [s0, s1) of the tile
 };
-__device__ __forceinline__ Walk walk_begin(const KParams& p, int unit, int n) {
+__host__ __device__ __forceinline__ Walk walk_begin(const KParams& p, int unit, int n) {
   Walk w;
   if (p.sk) {
-    w.cur = sk_bound(p, unit, n);
-    w.end = sk_bound(p, unit + 1, n);
-    w.step = 0;
+    w.lo = sk_bound(p, unit, n);
+    w.hi = sk_bound(p, unit + 1, n);
+    w.cur = (w.lo + p.sk_per_tile - 1) / p.sk_per_tile;  // first whole tile
+    w.end = w.hi / p.sk_per_tile;                        // one past the last whole tile
+    w.step = 0;                                          // phase: 0 = run's last tile, 1 = run's first tile, 2 = whole tiles
   } else {
     w.cur = unit;
     w.end = p.num_tiles;
     w.step = n;
+    w.lo = w.hi = 0;
   }
   return w;
 }
-__device__ __forceinline__ bool walk_next(const KParams& p, Walk& w, Piece& pc) {
-  if (w.cur >= w.end) return false;
-  if (p.sk) {
-    pc.t = w.cur / p.sk_per_tile;
-    pc.s0 = w.cur - pc.t * p.sk_per_tile;
-    pc.s1 = min(p.sk_per_tile, pc.s0 + (w.end - w.cur));
-    w.cur += pc.s1 - pc.s0;
-  } else {
+__host__ __device__ __forceinline__ bool walk_next(const KParams& p, Walk& w, Piece& pc) {
+  if (!p.sk) {
+    if (w.cur >= w.end) return false;
     pc.t = w.cur;
     pc.s0 = pc.s1 = 0;
     w.cur += w.step;
+    return true;
   }
+  const int per = p.sk_per_tile;
+  if (w.step == 0) {
+    w.step = 1;
+    if (w.hi <= w.lo) {  // an empty run
+      w.step = 2;
+      w.cur = w.end;
+      return false;
+    }
+    const int t_hi = w.hi / per, s_hi = w.hi - t_hi * per;
+    if (s_hi > 0) {  // the run ends inside tile t_hi
+      const int t_lo = w.lo / per;
+      pc.t = t_hi;
+      pc.s0 = (t_lo == t_hi) ? w.lo - t_lo * per : 0;  // (a run inside one tile is one piece)
+      pc.s1 = s_hi;
+      if (t_lo == t_hi) w.step = 2;
+      return true;
+    }
+  }
+  if (w.step == 1) {
+    w.step = 2;
+    const int t_lo = w.lo / per, s_lo = w.lo - t_lo * per;
+    if (s_lo > 0) {  // the run starts inside tile t_lo
+      pc.t = t_lo;
+      pc.s0 = s_lo;
+      pc.s1 = per;
+      return true;
+    }
+  }
+  if (w.cur >= w.end) return false;
+  pc.t = w.cur++;
+  pc.s0 = 0;
+  pc.s1 = per;
   return true;
 }
 
@@ -544,9 +580,17 @@ hb_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       const int t = pc.t;
       int b, m_pair, n0, bn, kb0, kb1, kslice;
       decode(pc, b, m_pair, n0, bn, kb0, kb1, kslice);
-      // balanced schedule: does another pair hold the K blocks after / before this piece's?
-      const bool sk_later = OUT_BYTES == 4 && p.sk && pc.s1 < p.sk_per_tile;
-      const bool sk_earlier = OUT_BYTES == 4 && p.sk && pc.s0 > 0;
+      // balanced schedule: does another pair hold the K stages after this piece's (it then stores
+      // partial sums for that pair), or the ones before (it then adds that pair's partial sums)?
+#ifdef HB_PROBES
+      // diagnostics (wrong results): 21 = pieces written independently, no hand-over at all;
+      // 22 = flags but no partial-sum loads; 23 = no wait for the partial stores before the flag
+      const bool sk_prod = OUT_BYTES == 4 && p.sk && pc.s1 < p.sk_per_tile && p.probe != 21;
+      const bool sk_cons = OUT_BYTES == 4 && p.sk && pc.s0 > 0 && p.probe != 21;
+#else
+      const bool sk_prod = OUT_BYTES == 4 && p.sk && pc.s1 < p.sk_per_tile;
+      const bool sk_cons = OUT_BYTES == 4 && p.sk && pc.s0 > 0;
+#endif
       const int sk_slot = static_cast<int>(cta_rank) * kEpiWarps + q;
       const bool ksliced = OUT_BYTES == 4 && p.ksplit > 1 && t >= p.whole_tiles && !p.kslab;
       const bool chain = ksliced && p.flags != nullptr;
@@ -560,10 +604,10 @@ hb_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         break;
       }
       tc_fence_after();
-      if (sk_later) {
-        // The pair after this one met the tile first and left the sums of the later K blocks in
+      if (sk_cons) {
+        // The pair before this one took the tile first and left the sums of the earlier K stages in
         // the output: wait (bounded) until its warp for these 32 rows says they are in memory.
-        const int* f = p.flags + (first_tile + 1) * kArrivals + sk_slot;
+        const int* f = p.flags + first_tile * kArrivals + sk_slot;
         int got = 1;
         if (lane == 0) {
           const long long t0 = clock64();
@@ -612,6 +656,30 @@ hb_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       uint32_t v2[OUT_BYTES == 2 ? 32 : 1];
       tmem_ld_32x32(t_addr, v);
       if (OUT_BYTES == 2) tmem_ld_32x32(t_addr + 32, reinterpret_cast<uint32_t(&)[32]>(v2));
+      // balanced schedule, consumer piece: this thread's 128 bytes of the partial sums another
+      // pair left in the output, for the column chunk that starts at tile column c (zeros where
+      // the tile hangs over the edge of C; rows are 16-byte multiples: whole vectors or none)
+      uint4 part[OUT_BYTES == 4 ? 8 : 1];
+      auto load_part = [&](int c) {
+        const int row = row0 + lane, col = n0 + c;
+        const uint8_t* src = static_cast<const uint8_t*>(p.C) +
+                             (static_cast<long long>(b) * p.batch_stride_c +
+                              static_cast<long long>(row) * p.ldc + col) * 4;
+#pragma unroll
+        for (int j = 0; j < (OUT_BYTES == 4 ? 8 : 1); ++j) {
+#ifdef HB_PROBES
+          if (p.probe == 22) {
+            part[j] = make_uint4(0u, 0u, 0u, 0u);
+            continue;
+          }
+#endif
+          if (row < p.M && col + 4 * j < p.N)
+            part[j] = ld_cg_v4(src + 16 * j);
+          else
+            part[j] = make_uint4(0u, 0u, 0u, 0u);
+        }
+      };
+      if (OUT_BYTES == 4 && sk_cons) load_part(0);
       for (int c0 = 0; c0 < bn; c0 += kColsPerStore) {
         uint32_t packed[32];  // 128 bytes of output for this thread's row
         tmem_ld_wait();
@@ -632,28 +700,21 @@ hb_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           }
         }
         if constexpr (OUT_BYTES == 4) {
-          if (sk_later) {
-            const int row = row0 + lane, col = n0 + c0;
-            if (row < p.M && col < p.N) {
-              const uint8_t* src = static_cast<const uint8_t*>(p.C) +
-                                   (static_cast<long long>(b) * p.batch_stride_c +
-                                    static_cast<long long>(row) * p.ldc + col) * 4;
+          if (sk_cons) {
+            // add the other pair's partial sums (fetched one chunk ahead), then start the next fetch
 #pragma unroll
-              for (int j = 0; j < 8; ++j) {
-                if (col + 4 * j < p.N) {  // rows are 16-byte multiples here: whole vectors or none
-                  const uint4 x = ld_cg_v4(src + 16 * j);
-                  if (KIND == 1) {
-                    packed[4 * j] += x.x; packed[4 * j + 1] += x.y;
-                    packed[4 * j + 2] += x.z; packed[4 * j + 3] += x.w;
-                  } else {
-                    packed[4 * j] = __float_as_uint(__uint_as_float(packed[4 * j]) + __uint_as_float(x.x));
-                    packed[4 * j + 1] = __float_as_uint(__uint_as_float(packed[4 * j + 1]) + __uint_as_float(x.y));
-                    packed[4 * j + 2] = __float_as_uint(__uint_as_float(packed[4 * j + 2]) + __uint_as_float(x.z));
-                    packed[4 * j + 3] = __float_as_uint(__uint_as_float(packed[4 * j + 3]) + __uint_as_float(x.w));
-                  }
-                }
+            for (int j = 0; j < 8; ++j) {
+              if (KIND == 1) {
+                packed[4 * j] += part[j].x; packed[4 * j + 1] += part[j].y;
+                packed[4 * j + 2] += part[j].z; packed[4 * j + 3] += part[j].w;
+              } else {
+                packed[4 * j] = __float_as_uint(__uint_as_float(packed[4 * j]) + __uint_as_float(part[j].x));
+                packed[4 * j + 1] = __float_as_uint(__uint_as_float(packed[4 * j + 1]) + __uint_as_float(part[j].y));
+                packed[4 * j + 2] = __float_as_uint(__uint_as_float(packed[4 * j + 2]) + __uint_as_float(part[j].z));
+                packed[4 * j + 3] = __float_as_uint(__uint_as_float(packed[4 * j + 3]) + __uint_as_float(part[j].w));
               }
             }
+            if (c0 + kColsPerStore < bn) load_part(c0 + kColsPerStore);
           }
         }
         if (c0 + kColsPerStore < bn) {
@@ -764,17 +825,24 @@ hb_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           }
         }
       }
-      if (sk_later || sk_earlier) {
+      if (sk_prod || sk_cons) {
         // (the partial sums read above are in registers or already stored: the flag that
-        // announced them goes back to zero for the next launch; then, if an earlier K range of
-        // this tile is still to come, this warp's rows are announced in turn)
-        if (sk_earlier && p.epilogue) bulk_wait<0>();
+        // announced them goes back to zero for the next launch; then, if a later K range of this
+        // tile is another pair's, this warp's rows are announced to it in turn)
+#ifdef HB_PROBES
+        if (sk_prod && p.epilogue && p.probe != 23) {
+#else
+        if (sk_prod && p.epilogue) {
+#endif
+          bulk_wait<0>();
+          fence_proxy_async_all();
+        }
         __syncwarp();
         if (lane == 0) {
-          if (sk_later) *(volatile int*)(p.flags + (first_tile + 1) * kArrivals + sk_slot) = 0;
-          if (sk_earlier) {
+          if (sk_cons) *(volatile int*)(p.flags + first_tile * kArrivals + sk_slot) = 0;
+          if (sk_prod) {
             __threadfence();
-            st_release_gpu(p.flags + first_tile * kArrivals + sk_slot, 1);
+            st_release_gpu(p.flags + (first_tile + 1) * kArrivals + sk_slot, 1);
           }
         }
       }

@@ -169,11 +169,16 @@ int build_plan(Driver& d, const Problem& pr, const hb_knobs& k, const ConvGeom* 
   const int tail = tiles % units;
   int split = 1, ksplit = 1;
 
-  // Balanced schedule: the (tile, ring stage) units of the whole problem in equal runs, one per
-  // CTA pair (see hb_kernel.cuh).  Decided on counts alone: a pair does ceil(tiles * S / units)
-  // stages instead of ceil(tiles / units) * S, and pays for it with one shared tile at each end
-  // of its run (a partial-sum round trip through L2, about two stages' worth).  Needs 4-byte
-  // row-major output; a boundary closer than sk_min stages to a tile edge moves onto it.
+  // Balanced schedule (knob balance = 2): the (tile, ring stage) units of the whole problem in equal
+  // runs, one per CTA pair (see hb_kernel.cuh).  Needs 4-byte row-major output with 16-byte rows; a
+  // cut closer than sk_min stages to a tile edge moves onto it.  It is never picked by default.  On
+  // counts alone it should win wherever the last wave is partly filled (a pair does
+  // ceil(tiles * S / units) stages instead of ceil(tiles / units) * S), but measured on B200 it loses
+  // on every benchmark shape (4096^3 fp16: 119 us against 104; the int8 conv at 1024 / 512 / 256 / 128
+  // images: 97 / 55 / 41 / 43 us against 87 / 48 / 33 / 21), even with the hand-over switched off:
+  // these kernels are bound by operand traffic from L2, and pairs that walk the same K blocks of
+  // neighbouring tiles at the same time (the round-robin tile list) share those reads, while pairs
+  // spread over the unit line do not.
   const int per_tile = (p.num_kb + k.k_slices - 1) / k.k_slices;
   const int sk_min = kBalanceMinRun;
   const long long sk_total = static_cast<long long>(tiles) * per_tile;
@@ -183,10 +188,6 @@ int build_plan(Driver& d, const Problem& pr, const hb_knobs& k, const ConvGeom* 
   bool sk = false;
   if (k.balance == 2) {
     sk = sk_can;  // (a problem too small to cut keeps the tile list)
-  } else if (k.balance == 0 && sk_can && k.split_k == 0 && k.tail_split == 0 && tail > 0 && per_tile >= 4) {
-    const long long balanced = (sk_total + units - 1) / units + 2;
-    const long long fixed = static_cast<long long>((tiles + units - 1) / units) * per_tile;
-    sk = balanced * 100 <= fixed * 93;
   }
   if (sk) {
     const int per_pair = hb::kEpiWarps * cgrp;
@@ -338,6 +339,23 @@ int run_main(const hb_plan* plan, cudaStream_t stream) {
         static_cast<const int8_t*>(plan->packed_w), static_cast<int8_t*>(plan->scratch), plan->p.N,
         plan->KH, plan->p.KW, plan->p.CI, plan->sco);
     if (cudaGetLastError() != cudaSuccess) return HB_ERR_LAUNCH;
+  }
+  if (plan->strip_t) {
+    cudaLaunchConfig_t cfg;
+    std::memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = dim3(plan->grid);
+    cfg.blockDim = dim3(hb::kWideThreads);
+    cfg.dynamicSmemBytes = plan->smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    const cudaError_t e = plan->spt.esize_out == 2
+                              ? cudaLaunchKernelEx(&cfg, hb::hb_conv_strip_t_kernel<2>, plan->tmA, plan->tmB, plan->spt)
+                              : cudaLaunchKernelEx(&cfg, hb::hb_conv_strip_t_kernel<4>, plan->tmA, plan->tmB, plan->spt);
+    return e == cudaSuccess ? HB_OK : HB_ERR_LAUNCH;
   }
   if (plan->strip) {
     const hb::StripParams& sp = plan->sp;

@@ -2,6 +2,7 @@
 // the packed-filter (x86) form and the NCHW operators with their layout glue.
 #pragma once
 #include "hb_plan.cuh"
+#include "hb_plan_strip_t.cuh"
 
 namespace {
 
@@ -145,7 +146,22 @@ int plan_conv(const void* in, const void* w, void* out, int N, int H, int W, int
   // only the im2col kernel reads through custom strides or walks a third spatial axis
   const bool strided_view = cg.w_stride > 0 || is_3d(cg);
   const int algo = knobs ? knobs->conv_algo : 0;
-  if (algo < 0 || algo > 2 || (algo == 2 && strided_view)) return HB_ERR_KNOB;
+  if (algo < 0 || algo > 3 || (algo >= 2 && strided_view)) return HB_ERR_KNOB;
+  {
+    // The wide strip kernel (channels on M, 256 positions on N): asked for, or picked when it applies,
+    // the filter has more than one tap and the reduction is short enough that operand traffic, not
+    // tensor time, bounds the layer (measured on the 56 x 56 x 64 -> 64 layer: 14.6 us against 18.2 us
+    // for the strip kernel and 23.8 us for the im2col kernel).
+    hb_knobs k0;
+    if (knobs) k0 = *knobs; else std::memset(&k0, 0, sizeof(k0));
+    const bool fits_t = !strided_view && !out_nchw && in_w == HB_F16 && !k0.silent_producer &&
+                        strip_t_smem_bytes(cg, in_a, out_t, nullptr, k0.tile_n > 0 && algo == 3 ? k0.tile_n : 256) != 0;
+    if (algo == 3 && !fits_t) return HB_ERR_KNOB;
+    if (algo == 3 || (algo == 0 && fits_t && KH * KW > 1 && K * es <= 2048)) {
+      if (algo == 0) k0.tile_n = 0;  // (tile_n is the GEMM kernels' knob unless this kernel was asked for)
+      return build_strip_t_plan(d, cg, in_a, in_w, out_t, k0, in, w, out, plan);
+    }
+  }
   if (algo != 1 && !strided_view) {
     hb::StripParams probe;
     std::memset(&probe, 0, sizeof(probe));

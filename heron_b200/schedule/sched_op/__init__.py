@@ -193,9 +193,11 @@ class epilogueOp(SchedOp):
 
 
 class convAlgoOp(SchedOp):
-    """conv only: implicit GEMM with one im2col TMA per tap (1), or resident filter + one padded
-    input strip per tile (2).  The second exists only for stride-1 problems whose filter and two
-    strips fit shared memory and whose padded width fits the 128 MMA rows."""
+    """conv only: implicit GEMM with one im2col TMA per tap (1), resident filter + one padded
+    input strip per tile (2), or the same with the output channels on the MMA's M axis and 256
+    positions on N (3).  The second exists only for stride-1 problems whose filter and two strips
+    fit shared memory and whose padded width fits the 128 MMA rows, the third for fp16 problems
+    with 64 or 128 output channels whose filter, strips and output tile fit."""
 
     def perform(self, s, stage_name, ctx):
         km = ctx.knob_manager
@@ -206,7 +208,10 @@ class convAlgoOp(SchedOp):
         algo = genKey("P", stage_name, "m", param_name="conv_algo")
         if km.is_building:
             es, eo = ELEM_BYTES[p["in_dtype"]], ELEM_BYTES[p["out_dtype"]]
-            km.define_value(algo, 1, 2 if strip_applies(p, es, eo, ctx.limits) else 1, 1, True)
+            most = 3 if strip_wide_applies(p, es, eo, ctx.limits) else (2 if strip_applies(p, es, eo, ctx.limits) else 1)
+            km.define_value(algo, 1, most, 1, True)
+            if most == 3 and not strip_applies(p, es, eo, ctx.limits):
+                km.addCandidates(algo, [1, 3])
         ctx.kernel_knobs["conv_algo"] = km.get_val(algo)
         ctx.addSchedDesc("## conv algorithm %s\n" % ctx.kernel_knobs["conv_algo"])
 
@@ -231,6 +236,36 @@ def strip_applies(p, es, eo, limits):
     strip_bytes = (px * 128 + 1023) // 1024 * 1024
     filt = (KH * KW * CI * CO * es + 1023) // 1024 * 1024
     return filt + 2 * (CI * es // 128) * strip_bytes + 1024 + 256 <= limits["max_shared_memory_per_block"]
+
+
+def strip_wide_applies(p, es, eo, limits):
+    """The wide strip kernel's feasibility rule (mirrors the library's check): fp16, stride 1, 64 or
+    128 output channels, and the filter, two input strips and one tile of output in shared memory."""
+    sh, sw = p["stride"]
+    dh, dw = p["dilation"]
+    if (sh, sw) != (1, 1) or es != 2 or p["in_dtype"] != "float16":
+        return False
+    CI, CO, KH, KW, pad = p["CI"], p["CO"], p["KH"], p["KW"], p["padding"]
+    if (CI * 2) % 128 or CO not in (64, 128):
+        return False
+    Wp = p["W"] + 2 * pad
+    if Wp < 1 or Wp > 256:
+        return False
+    HO = (p["H"] - ((KH - 1) * dh + 1) + 2 * pad) + 1
+    WO = (p["W"] - ((KW - 1) * dw + 1) + 2 * pad) + 1
+    if HO <= 0 or WO <= 0:
+        return False
+    P = (HO - 1) * Wp + WO
+    max_off = (KH - 1) * dh * Wp + (KW - 1) * dw
+    filt = (KH * KW * CI * CO * 2 + 1023) // 1024 * 1024
+    for cand in (256, 192, 128, 64):
+        L = cand if P >= cand else (P + 15) // 16 * 16
+        SR = (Wp - 1 + L + max_off + Wp - 1) // Wp
+        strip_bytes = (SR * Wp * 128 + 1023) // 1024 * 1024
+        smem = filt + 2 * (CI * 2 // 128) * strip_bytes + L * CO * eo + 1024 + 512
+        if SR <= 256 and smem <= limits["max_shared_memory_per_block"]:
+            return True
+    return False
 
 
 class rasterOp(SchedOp):

@@ -22,10 +22,17 @@ class KernelHandle:
     repeated launches, which is what the measurement code times.
     """
 
+    # An immediate call on small tensors spends more time encoding its three tensor maps on the
+    # host than the GPU spends on the problem.  Calls whose tensors total at most this many bytes
+    # therefore keep their plan: a later call on the same buffers only launches it.
+    SMALL_CALL_BYTES = 1 << 20
+    PLAN_CACHE_SIZE = 16
+
     def __init__(self, op, knobs):
         self.op = op
         self.knobs = dict(knobs)
         self.entry_name = op.name
+        self._small_plans = {}  # (data_ptr, shape, dtype, device) per tensor -> Plan, oldest first
 
     def _call(self, planned, *tensors):
         from .. import kernels as K
@@ -77,7 +84,19 @@ class KernelHandle:
         raise NotImplementedError(kind)
 
     def __call__(self, *tensors):
-        return self._call(False, *tensors)
+        nbytes = sum(t.numel() * t.element_size() for t in tensors)
+        if nbytes > self.SMALL_CALL_BYTES:
+            return self._call(False, *tensors)
+        # (a cached plan holds references to its tensors, so an address in a key cannot be handed
+        # to another tensor while the entry lives)
+        key = tuple((t.data_ptr(), tuple(t.shape), t.dtype, t.device) for t in tensors)
+        plan = self._small_plans.pop(key, None)
+        if plan is None:
+            plan = self._call(True, *tensors)
+            while len(self._small_plans) >= self.PLAN_CACHE_SIZE:
+                self._small_plans.pop(next(iter(self._small_plans))).close()
+        self._small_plans[key] = plan  # most recently used last
+        return plan.launch()
 
     def plan(self, *tensors):
         return self._call(True, *tensors)

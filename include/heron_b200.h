@@ -68,7 +68,9 @@ typedef struct {
                         L2; 0 = library default, -1 = off (gemm / bmm only)                         */
   int conv_algo;     /* conv only.  1: implicit GEMM, one im2col TMA per filter tap; 2: resident
                         filter + one padded input strip per tile (stride 1, filter fits shared
-                        memory, padded width <= 128); 0 = library picks                           */
+                        memory, padded width <= 128); 3: the same with the operands' places changed:
+                        output channels on the MMA's M axis (64 or 128 of them), 256 consecutive
+                        output positions on N (fp16, stride 1); 0 = library picks                  */
   int tail_split;    /* the tiles of the last, partly filled wave of the persistent grid are cut into
                         this many column slices (1, 2 or 4); 0 = library picks                      */
   int split_k;       /* work items that do not fill a wave of the persistent grid (the tiles of the
@@ -134,6 +136,10 @@ int hb_check_knobs(int op, int batch, int M, int N, int K, int k_inner, hb_dtype
  * generated kernels bind one block per output tile (schedule/sched_op/gpu_tensorcore_operator.py).
  */
 int hb_balanced_run(int tiles, int stages_per_tile, int pairs, int pair, int* first, int* end);
+/* The pieces of that run in the order the kernel's roles take them (the kernel's own walker,
+ * compiled for the host): up to max_pieces triples (tile, first stage, end stage) are written to
+ * `pieces`; returns the number of pieces of the run, or a negative status. */
+int hb_balanced_pieces(int tiles, int stages_per_tile, int pairs, int pair, int* pieces, int max_pieces);
 
 /*
  * GEMM: C[M,N] = sum_k A[M,K] * B[N,K]  (B is stored N-major over K, i.e. C = A * B^T).

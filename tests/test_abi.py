@@ -185,14 +185,21 @@ def _runs(lib, tiles, per_tile, pairs):
 
 
 def _pieces(run, per_tile):
-    """The tiles a run touches, in the order the kernel's roles walk them: (tile, s0, s1)."""
-    cur, end = run
+    """The tiles a run touches, in the order the kernel's roles take them: the run's last tile (if
+    the run ends inside it), the run's first tile (if it starts inside it), then the whole tiles."""
+    lo, hi = run
+    if hi <= lo:
+        return []
+    t_lo, s_lo = divmod(lo, per_tile)
+    t_hi, s_hi = divmod(hi, per_tile)
     out = []
-    while cur < end:
-        t, s0 = divmod(cur, per_tile)
-        s1 = min(per_tile, s0 + (end - cur))
-        out.append((t, s0, s1))
-        cur += s1 - s0
+    if s_hi > 0:
+        if t_lo == t_hi:
+            return [(t_hi, s_lo, s_hi)]
+        out.append((t_hi, 0, s_hi))
+    if s_lo > 0:
+        out.append((t_lo, s_lo, per_tile))
+    out.extend((t, 0, per_tile) for t in range(-(-lo // per_tile), t_hi))
     return out
 
 
@@ -207,6 +214,14 @@ def test_balanced_runs_cover_every_stage_once_and_pair_up_their_shared_tiles(hb_
     assert runs[0][0] == 0 and runs[-1][1] == total
     for (a0, a1), (b0, b1) in zip(runs, runs[1:]):
         assert a0 <= a1 == b0 <= b1, "runs are consecutive and in order"
+    # the kernel's own walker (compiled for the host) takes the pieces in the order restated above
+    import ctypes
+    for i, run in enumerate(runs):
+        buf = (ctypes.c_int * (3 * 64))()
+        n = hb_lib.hb_balanced_pieces(tiles, per_tile, pairs, i, buf, 64)
+        want = _pieces(run, per_tile)
+        assert n == len(want)
+        assert [tuple(buf[3 * j:3 * j + 3]) for j in range(min(n, 64))] == want[:64]
     seen = {}
     for i, run in enumerate(runs):
         for (t, s0, s1) in _pieces(run, per_tile):
@@ -215,25 +230,23 @@ def test_balanced_runs_cover_every_stage_once_and_pair_up_their_shared_tiles(hb_
                 assert (t, s) not in seen, "stage walked twice"
                 seen[(t, s)] = i
     assert len(seen) == total
-    # hand-overs: the pair whose run ENDS inside a tile waits for the flags of the pair after it,
-    # and that pair's FIRST piece must be the continuation of the very same tile
+    # hand-overs: a piece that stops short of its tile's last stage stores partial sums and raises
+    # the flags of the NEXT pair, whose run must hold the continuation of the very same tile; a
+    # piece that starts inside a tile waits for its own pair's flags, raised by the pair before
     for i, run in enumerate(runs):
         ps = _pieces(run, per_tile)
-        if not ps:
-            continue
-        t, s0, s1 = ps[-1]
-        if s1 < per_tile:  # "later" K blocks are held by another pair
-            nxt = _pieces(runs[i + 1], per_tile)
-            assert nxt and nxt[0][0] == t and nxt[0][1] == s1, (i, ps[-1], nxt[:1])
-        t, s0, s1 = ps[0]
-        if s0 > 0:  # an "earlier" K range is held by the pair before
-            prv = _pieces(runs[i - 1], per_tile)
-            assert prv and prv[-1][0] == t and prv[-1][2] == s0
-        # only the first piece may start inside a tile, only the last may end inside one
-        for (t, s0, s1) in ps[1:]:
-            assert s0 == 0
-        for (t, s0, s1) in ps[:-1]:
-            assert s1 == per_tile
+        producers = [pc for pc in ps if pc[2] < per_tile]
+        consumers = [pc for pc in ps if pc[1] > 0]
+        assert len(producers) <= 1 and len(consumers) <= 1
+        for (t, s0, s1) in producers:
+            nxt = [pc for pc in _pieces(runs[i + 1], per_tile) if pc[1] > 0]
+            assert nxt == [(t, s1, nxt[0][2])], (i, (t, s0, s1), nxt)
+        for (t, s0, s1) in consumers:
+            prv = [pc for pc in _pieces(runs[i - 1], per_tile) if pc[2] < per_tile]
+            assert prv and prv[0][0] == t and prv[0][2] == s0
+        # shared tiles come first: the producer piece, then the consumer piece, then whole tiles
+        kinds = ["p" if pc[2] < per_tile else ("c" if pc[1] > 0 else "w") for pc in ps]
+        assert kinds == sorted(kinds, key="pcw".index), kinds
     # cuts stay two stages clear of tile edges (or sit on them)
     for a0, _ in runs:
         r = a0 % per_tile

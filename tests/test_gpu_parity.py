@@ -278,16 +278,16 @@ def test_balanced_schedule_conv(K, co, knobs):
           "balanced conv fp16 %s" % (kn,))
 
 
-def test_balanced_schedule_is_what_the_sharded_shapes_get(K, co):
+def test_schedules_agree_on_the_sharded_shapes(K, co):
     """The per-GPU shards of the two batch-sharded benchmark configurations at 4 and 8 GPUs (256 and
-    128 images; 48 and 24 batches): the library's own choice of schedule, against the oracle on
-    sampled images / batches and through exact sum identities over every element; split-K forced on
-    for the same shapes as well."""
+    128 images; 48 and 24 batches) under the balanced schedule, against the oracle on sampled
+    images / batches and through exact sum identities over every element; the library's default
+    schedule and split-K forced on give the same bits."""
     from heron_b200.workloads import make_inputs
     for count in (128, 256):
         x, w = make_inputs("cfg5_conv_u8s8_resnet_s4", shard=(512, count))
         out = poison((count, 7, 7, 512), torch.int32)
-        plan = K.plan_conv2d_nhwc(dev(x), dev(w), stride=1, padding=1, dilation=1, out=out)
+        plan = K.plan_conv2d_nhwc(dev(x), dev(w), stride=1, padding=1, dilation=1, out=out, knobs=dict(balance=2))
         assert plan.knobs()["balance"] == 2, plan.knobs()
         plan.launch()
         for n in (0, 1, count // 2, count - 1):
@@ -302,6 +302,7 @@ def test_balanced_schedule_is_what_the_sharded_shapes_get(K, co):
         assert np.array_equal(got, want)
         forced = k_conv(K, x, w, 1, 1, 1, knobs=dict(split_k=2, balance=1))
         assert torch.equal(forced, out), "split-K and the balanced schedule agree bit for bit"
+        assert torch.equal(k_conv(K, x, w, 1, 1, 1), out), "and so does the default"
     for count in (24, 48):
         a, b = make_inputs("cfg4_bmm_s8_attention", shard=(96, count))
         out = k_bmm(K, a, b)
@@ -599,6 +600,31 @@ def test_quick_start_config_through_x86_interface(K, co):
     check(out, co.gemm_int(a, b), "cfg1")
 
 
+def test_small_immediate_calls_reuse_their_plan(K, co):
+    """A built operator called again on the same small buffers launches the plan of the first call
+    (no tensor maps re-encoded); new contents in those buffers give new results, other buffers
+    get a plan of their own."""
+    from heron_b200.ops import x86 as heron_cpu
+    t = _task(heron_cpu, "gemm", [64, 64, 64, "uint8", "int32"], "CPU")
+    t.knob_manager.randSample()
+    handle, args = t.instantiate(t.knob_manager)
+    rng = np.random.default_rng(64)
+    a, b = rand_i8(rng, (64, 64), False), rand_i8(rng, (64, 64), True)
+    ta, tb, out = dev(a), dev(b), poison((64, 64), torch.int32)
+    handle(ta, tb, out)
+    check(out, co.gemm_int(a, b), "first call")
+    assert len(handle._small_plans) == 1
+    a2 = rand_i8(rng, (64, 64), False)
+    ta.copy_(torch.from_numpy(a2))
+    handle(ta, tb, out)
+    check(out, co.gemm_int(a2, b), "second call, same buffers")
+    assert len(handle._small_plans) == 1
+    out2 = poison((64, 64), torch.int32)
+    handle(ta, tb, out2)
+    check(out2, co.gemm_int(a2, b), "other output buffer")
+    assert len(handle._small_plans) == 2
+
+
 # ---- the benchmark configurations at full size -----------------------------------------------
 def test_cfg2_gemm_fp16_4096_full_size(K, co):
     """Full 4096^3: 48 sampled rows against the oracle, every element through a row-sum identity
@@ -818,10 +844,13 @@ def test_conv_strip_refused_when_it_does_not_apply(K):
     K.conv2d_nhwc(x, w, 2, 1, 1)  # the default falls back to the implicit-GEMM kernel
 
 
-def test_default_picks_strip_for_resnet_stage2(K):
+def test_default_picks_a_strip_kernel_for_resnet_stage2(K):
     x = torch.zeros(8, 56, 56, 64, dtype=torch.float16, device="cuda")
     w = torch.zeros(3, 3, 64, 64, dtype=torch.float16, device="cuda")
-    assert K.plan_conv2d_nhwc(x, w, 1, 1, 1).knobs()["conv_algo"] == 2
+    assert K.plan_conv2d_nhwc(x, w, 1, 1, 1).knobs()["conv_algo"] == 3   # fp16, 64 channels out: the wide one
+    xi = torch.zeros(4, 28, 28, 128, dtype=torch.uint8, device="cuda")
+    wi = torch.zeros(3, 3, 128, 128, dtype=torch.int8, device="cuda")
+    assert K.plan_conv2d_nhwc(xi, wi, 1, 1, 1).knobs()["conv_algo"] == 2  # integer operands: pixels on M
     x = torch.zeros(16, 7, 7, 512, dtype=torch.uint8, device="cuda")
     w = torch.zeros(3, 3, 512, 512, dtype=torch.int8, device="cuda")
     assert K.plan_conv2d_nhwc(x, w, 1, 1, 1).knobs()["conv_algo"] == 1
