@@ -173,12 +173,12 @@ int build_plan(Driver& d, const Problem& pr, const hb_knobs& k, const ConvGeom* 
   // runs, one per CTA pair (see hb_kernel.cuh).  Needs 4-byte row-major output with 16-byte rows; a
   // cut closer than sk_min stages to a tile edge moves onto it.  It is never picked by default.  On
   // counts alone it should win wherever the last wave is partly filled (a pair does
-  // ceil(tiles * S / units) stages instead of ceil(tiles / units) * S), but measured on B200 it loses
-  // on every benchmark shape (4096^3 fp16: 119 us against 104; the int8 conv at 1024 / 512 / 256 / 128
-  // images: 97 / 55 / 41 / 43 us against 87 / 48 / 33 / 21), even with the hand-over switched off:
-  // these kernels are bound by operand traffic from L2, and pairs that walk the same K blocks of
-  // neighbouring tiles at the same time (the round-robin tile list) share those reads, while pairs
-  // spread over the unit line do not.
+  // ceil(tiles * S / units) stages instead of ceil(tiles / units) * S), but measured on B200 it does
+  // not: with the hand-over switched off (a diagnostic build) it runs level with the tile list
+  // (84.2 us against 85.8 for the int8 conv at 1024 images, 20.9 against 20.3 at 128) because these
+  // kernels' time is the total operand traffic through L2, which another deal of the same tiles does
+  // not change; and the hand-over then costs 4 to 22 us (waiting for the neighbour's partial sums,
+  // and reading them back with one 16-byte access per lane and row).
   const int per_tile = (p.num_kb + k.k_slices - 1) / k.k_slices;
   const int sk_min = kBalanceMinRun;
   const long long sk_total = static_cast<long long>(tiles) * per_tile;
