@@ -39,7 +39,8 @@ struct StripParams {
   int tmem_cols;
   int ring;   // strip buffers in flight (2..kMaxStripRing)
   long long wait_limit_cycles;
-  int probe;  // diagnostic: 2 = no MMAs, 3 = epilogue only hands the accumulator back, 4 = strips loaded once
+  int probe;  // diagnostic modes of -DHB_PROBES builds: 2 = no MMAs, 3 = the epilogue only hands the accumulator
+              // back, 4 = strips loaded once, 9 = the tile's MMAs on fixed descriptors (and 3)
   uint32_t idesc;
   void* out;
   int out_nchw;  // output is (N, CO, HO, WO) instead of (N, HO, WO, CO)
@@ -142,6 +143,7 @@ hb_conv_strip_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_cons
           break;
         }
         const uint32_t full = smem_u32(&bars->strip_full[buf]);
+#ifdef HB_PROBES
         if (p.probe == 4 && issued >= p.ring) {
           mbar_arrive(full);
           ++issued;
@@ -151,6 +153,7 @@ hb_conv_strip_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_cons
           }
           continue;
         }
+#endif
         mbar_arrive_expect_tx(full, tx);
         for (int cc = 0; cc < p.n_cchunks; ++cc)
           tma_load_4d(sStrip + buf * strip_total + cc * p.strip_bytes, &tmIn, full, cc * BK, -p.pad_w,
@@ -207,13 +210,11 @@ hb_conv_strip_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_cons
           umma_cg<1, KIND>(d_tmem, da, db, idesc, 0u);
 #pragma unroll 4
           for (int i = 1; i < n; ++i) umma_cg<1, KIND>(d_tmem, da, db, idesc, 1u);
-        } else
+        } else if (p.probe != 2)
 #endif
-        for (int ry = 0; ry < p.KH && p.probe != 2; ++ry)
+        for (int ry = 0; ry < p.KH; ++ry)
           for (int rx = 0; rx < p.KW; ++rx) {
-            uint32_t row_off = static_cast<uint32_t>(ry * p.dil_h * p.Wp + rx * p.dil_w) * 128u;
-            if (p.probe == 5) row_off &= ~1023u;  // diagnostic: 8-row aligned starts (wrong results)
-            if (p.probe == 6) row_off = 0;
+            const uint32_t row_off = static_cast<uint32_t>(ry * p.dil_h * p.Wp + rx * p.dil_w) * 128u;
             for (int cc = 0; cc < p.n_cchunks; ++cc) {
               const uint32_t a_addr = sStrip + buf * strip_total + cc * p.strip_bytes + row_off;
               const uint32_t b_addr = sFilt + ((ry * p.KW + rx) * p.n_cchunks + cc) * tap_bytes;
@@ -221,9 +222,7 @@ hb_conv_strip_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_cons
               const uint32_t b_lo = ((b_addr >> 4) & 0x3FFFu) | b_lo_fixed;
 #pragma unroll
               for (int k = 0; k < 4; ++k) {
-                // diagnostic 7: alternate between two accumulators per instruction (wrong results)
-                const uint32_t d_sel = (p.probe == 7 && (k & 1)) ? (d_tmem ^ static_cast<uint32_t>(2 * p.CO)) : d_tmem;
-                umma_cg<1, KIND>(d_sel, desc_hi | (a_lo + 2u * k), desc_hi | (b_lo + b_step16 * k), idesc,
+                umma_cg<1, KIND>(d_tmem, desc_hi | (a_lo + 2u * k), desc_hi | (b_lo + b_step16 * k), idesc,
                                  accum);
                 accum = 1u;
               }
@@ -269,6 +268,7 @@ hb_conv_strip_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_cons
           tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(acc * p.CO);
       uint8_t* orow = static_cast<uint8_t*>(p.out) +
                       ((static_cast<long long>(n) * p.HO + y) * p.WO + px) * p.CO * OUT_BYTES;
+#ifdef HB_PROBES
       if (p.probe == 3 || p.probe == 9) {
         tc_fence_before();
         __syncwarp();
@@ -279,6 +279,7 @@ hb_conv_strip_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_cons
         }
         continue;
       }
+#endif
       for (int c0 = 0; c0 < p.CO; c0 += kColsPerStep) {
         uint32_t v[32];
         uint32_t packed[32];
