@@ -364,12 +364,10 @@ def roofline_of(name, work, alg_bytes, per_launch_s, sustained, peaks, traffic):
 
 def is_sustained(elapsed_ms, clocks):
     """Which measured peak a timed region is held against: the sustained one when the region was
-    long (over half a second) or ran power-capped well below the maximum SM clock, else the burst
-    one (the two cuBLAS figures in MEASURED_PEAKS.json were taken in exactly these two regimes)."""
-    if elapsed_ms > 500.0:
-        return True
-    mhz, top = clocks.get("sm_mhz"), clocks.get("sm_max_mhz")
-    return bool(mhz and top and "sw_power_cap" in clocks.get("reasons", []) and mhz < 0.93 * top)
+    long (over half a second) or ran under the power cap (`sw_power_cap` active in its clock
+    record: on this part the cap bites after some 50 ms of tensor work and costs 10-15 %), else the
+    burst one.  The two cuBLAS figures in MEASURED_PEAKS.json were taken in exactly these regimes."""
+    return elapsed_ms > 500.0 or "sw_power_cap" in clocks.get("reasons", [])
 
 
 def unit_of(cfg):
