@@ -15,10 +15,19 @@
 // address, so a descriptor may start at any 128-byte row.  One tile = R = floor(128 / Wp) output
 // rows of one image = one 128-row MMA per (tap, 32 bytes of channels).
 //
-// Roles as in hb_umma_kernel: warp 0 loads (filter once, then strips into a ring of two to six buffers),
-// warp 1 issues MMAs into one of two TMEM accumulators, warps 2..5 read the accumulator and store
-// the valid positions straight to global memory (each thread owns one output pixel: CO
-// contiguous elements).  All waits are bounded, with the same abort protocol.
+// Roles as in hb_umma_kernel: warp 0 loads (the first strip, then the filter tap by tap, each tap
+// on a barrier of its own, then strips into a ring of two to six buffers), warp 1 issues MMAs into
+// one of two TMEM accumulators (descriptor words advance by running additions: the issuing thread
+// is one lane, and every integer instruction between two MMAs is on the tensor pipe's critical
+// path: 47 ns per MMA with address arithmetic, 30 ns without), warps 2..5 read the accumulator.
+// Each epilogue thread owns one output pixel (CO contiguous elements).  Staged epilogue (NHWC
+// output whose tile fits shared memory): the thread writes its pixel, 128 bytes of channels at a
+// time, into a 128-byte-swizzled staging buffer laid out [row][x][channels] with the junk positions
+// squeezed out (conflict-free 16-byte stores), the four warps meet at a barrier and one thread
+// sends the tile out with one tiled TMA store per 128-byte channel chunk: box (channels, WO, R),
+// rows past the image clipped by TMA.  Direct epilogue (channel-major output, or no room): the
+// thread stores its pixel itself, which touches 32 lines per warp instruction and runs at about
+// one sector per 2 ns and SM.  All waits are bounded, with the same abort protocol.
 #pragma once
 #include "hb_kernel.cuh"
 
@@ -44,10 +53,16 @@ struct StripParams {
   uint32_t idesc;
   void* out;
   int out_nchw;  // output is (N, CO, HO, WO) instead of (N, HO, WO, CO)
+  int staged;    // 1: the epilogue goes through the staging buffer and TMA stores (see above)
+  int stage_chunk_bytes;  // staging bytes per 128-byte channel chunk: R * WO * 128, rounded up to 1024
 };
 
+constexpr int kStripFiltBars = 16;  // filter taps with a barrier of their own (later taps share the last)
+
 struct StripBars {
-  uint64_t filt_full;
+  uint64_t filt_full[kStripFiltBars];
+  uint64_t stage;       // the epilogue warps: "my pixels of this tile are in the staging buffer"
+  uint64_t stage_free;  // the copying thread: "the TMA stores have read the staging buffer"
   uint64_t strip_full[kMaxStripRing];
   uint64_t strip_empty[kMaxStripRing];
   uint64_t tmem_full[2];
@@ -67,10 +82,19 @@ __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* m, 
       : "memory");
 }
 
+// Tiled 4-D store from shared memory (bulk-group completion); elements past the tensor are dropped.
+__device__ __forceinline__ void tma_store_4d(const CUtensorMap* m, uint32_t src, int c, int w, int h, int n) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];" ::"l"(
+          reinterpret_cast<uint64_t>(m)),
+      "r"(src), "r"(c), "r"(w), "r"(h), "r"(n)
+      : "memory");
+}
+
 template <int OUT_BYTES, int KIND>
 __global__ void __launch_bounds__(kThreads, 1)
 hb_conv_strip_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constant__ CUtensorMap tmW,
-                     const StripParams p) {
+                     const __grid_constant__ CUtensorMap tmOut, const StripParams p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -82,7 +106,10 @@ hb_conv_strip_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_cons
   const int strip_total = p.n_cchunks * p.strip_bytes;
   const uint32_t sFilt = smem_base;
   const uint32_t sStrip = sFilt + ((filt_bytes + 1023) & ~1023);
-  StripBars* bars = reinterpret_cast<StripBars*>(smem + (sStrip - smem_base) + p.ring * strip_total);
+  const uint32_t sStage = sStrip + p.ring * strip_total;  // 1024-byte aligned: strips are multiples of 1024
+  const int n_ochunks = p.CO * OUT_BYTES / 128;           // 128-byte channel chunks of an output pixel
+  const int stage_bytes = p.staged ? n_ochunks * p.stage_chunk_bytes : 0;
+  StripBars* bars = reinterpret_cast<StripBars*>(smem + (sStage - smem_base) + stage_bytes);
   volatile int* abort_flag = &bars->abort_flag;
   const WaitCtx wctx{abort_flag, p.wait_limit_cycles > 0 ? p.wait_limit_cycles : HB_WAIT_LIMIT_CYCLES};
 
@@ -90,7 +117,9 @@ hb_conv_strip_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_cons
   const int lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
-    mbar_init(smem_u32(&bars->filt_full), 1);
+    for (int i = 0; i < kStripFiltBars; ++i) mbar_init(smem_u32(&bars->filt_full[i]), 1);
+    mbar_init(smem_u32(&bars->stage), kEpiWarps);
+    mbar_init(smem_u32(&bars->stage_free), 1);
     static_assert(sizeof(bars->strip_full) == kMaxStripRing * sizeof(uint64_t) &&
                       sizeof(bars->strip_empty) == kMaxStripRing * sizeof(uint64_t),
                   "every ring barrier below is initialised");
@@ -107,6 +136,7 @@ hb_conv_strip_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_cons
     fence_mbar_init();
     prefetch_tmap(&tmIn);
     prefetch_tmap(&tmW);
+    if (p.staged) prefetch_tmap(&tmOut);
   }
   if (warp == 1) tmem_alloc_cg<1>(smem_u32(&bars->tmem_base), static_cast<uint32_t>(p.tmem_cols));
   tc_fence_before();
@@ -124,13 +154,24 @@ hb_conv_strip_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_cons
       // fetched as CO*esize/128 boxes of 128 bytes of output channels
       const int chunk_cols = 128 / p.esize_in;
       const int n_nchunks = p.CO / chunk_cols;
-      const uint32_t ff = smem_u32(&bars->filt_full);
-      mbar_arrive_expect_tx(ff, static_cast<uint32_t>(filt_bytes));
-      for (int tap = 0; tap < n_taps; ++tap)
-        for (int cc = 0; cc < p.n_cchunks; ++cc)
-          for (int j = 0; j < n_nchunks; ++j)
-            tma_load_3d(sFilt + (tap * p.n_cchunks + cc) * tap_bytes + j * (BK * 128), &tmW, ff,
-                        j * chunk_cols, tap * p.CI + cc * BK, 0);
+      auto load_filter = [&]() {
+        for (int tap = 0; tap < n_taps; ++tap) {
+          const int fb = tap < kStripFiltBars ? tap : kStripFiltBars - 1;
+          const uint32_t ff = smem_u32(&bars->filt_full[fb]);
+          // (the last barrier takes every tap from kStripFiltBars - 1 on: armed once, with all their bytes)
+          if (tap < kStripFiltBars)
+            mbar_arrive_expect_tx(ff, static_cast<uint32_t>(p.n_cchunks * tap_bytes) *
+                                          static_cast<uint32_t>(tap == kStripFiltBars - 1 ? n_taps - tap : 1));
+          for (int cc = 0; cc < p.n_cchunks; ++cc)
+            for (int j = 0; j < n_nchunks; ++j)
+              tma_load_3d(sFilt + (tap * p.n_cchunks + cc) * tap_bytes + j * (BK * 128), &tmW, ff,
+                          j * chunk_cols, tap * p.CI + cc * BK, 0);
+        }
+        // barriers of taps the filter does not have complete at once, so that every wait on them passes
+        for (int fb = n_taps; fb < kStripFiltBars; ++fb) mbar_arrive(smem_u32(&bars->filt_full[fb]));
+      };
+      // (the first tile's strip goes out before the filter: TMA serves its requests in order, and the
+      // first MMA needs the strip and one tap, not the whole filter)
       int buf = 0;
       uint32_t phase = 0;
       int issued = 0;
@@ -158,14 +199,16 @@ hb_conv_strip_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_cons
         for (int cc = 0; cc < p.n_cchunks; ++cc)
           tma_load_4d(sStrip + buf * strip_total + cc * p.strip_bytes, &tmIn, full, cc * BK, -p.pad_w,
                       y0 - p.pad_h, n);
+        if (issued == 0) load_filter();
         ++issued;
         if (++buf == p.ring) {
           buf = 0;
           phase ^= 1u;
         }
       }
+      if (issued == 0) load_filter();  // (a CTA without tiles: its barriers still complete)
       if (!ok) {
-        mbar_wait_drain(smem_u32(&bars->filt_full), 0u);
+        for (int fb = 0; fb < kStripFiltBars; ++fb) mbar_wait_drain(smem_u32(&bars->filt_full[fb]), 0u);
         const int pending = issued < p.ring ? issued : p.ring;
         for (int i = 0; i < pending; ++i) {
           if (--buf < 0) {
@@ -180,7 +223,8 @@ hb_conv_strip_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_cons
   } else if (warp == 1) {
     // ------------------------------ MMA issuer --------------------------------------------
     if (elect_one()) {
-      bool ok = mbar_wait(smem_u32(&bars->filt_full), 0u, wctx);
+      bool ok = true;
+      bool filter_in = false;  // after the first tile every tap has been waited for
       int buf = 0, acc = 0;
       uint32_t phase = 0, acc_phase = 0;
       const int umma_k = 32 / p.esize_in;
@@ -191,6 +235,12 @@ hb_conv_strip_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_cons
       const uint32_t b_lo_fixed = ((static_cast<uint32_t>(BK * 128) >> 4) & 0x3FFFu) << 16;
       const uint32_t b_step16 = static_cast<uint32_t>(umma_k * 128) >> 4;
       const uint32_t idesc = p.idesc;
+      // running steps of the descriptor low words, in 16-byte units (shared memory is < 256 KiB, so
+      // the 14-bit address field cannot wrap)
+      const uint32_t slab16 = static_cast<uint32_t>(tap_bytes) >> 4;            // next (tap, chunk) slab of B
+      const uint32_t chunk16 = static_cast<uint32_t>(p.strip_bytes) >> 4;       // next channel chunk of A
+      const uint32_t tap_step16 = static_cast<uint32_t>(p.dil_w) * 8u;          // next tap of a filter row
+      const uint32_t row_step16 = static_cast<uint32_t>(p.dil_h * p.Wp) * 8u;   // next filter row
       for (int t = blockIdx.x; ok && t < p.num_tiles; t += gridDim.x) {
         if (!mbar_wait(smem_u32(&bars->tmem_empty[acc]), acc_phase ^ 1u, wctx) ||
             !mbar_wait(smem_u32(&bars->strip_full[buf]), phase, wctx)) {
@@ -212,22 +262,33 @@ hb_conv_strip_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_cons
           for (int i = 1; i < n; ++i) umma_cg<1, KIND>(d_tmem, da, db, idesc, 1u);
         } else if (p.probe != 2)
 #endif
-        for (int ry = 0; ry < p.KH; ++ry)
-          for (int rx = 0; rx < p.KW; ++rx) {
-            const uint32_t row_off = static_cast<uint32_t>(ry * p.dil_h * p.Wp + rx * p.dil_w) * 128u;
-            for (int cc = 0; cc < p.n_cchunks; ++cc) {
-              const uint32_t a_addr = sStrip + buf * strip_total + cc * p.strip_bytes + row_off;
-              const uint32_t b_addr = sFilt + ((ry * p.KW + rx) * p.n_cchunks + cc) * tap_bytes;
-              const uint32_t a_lo = ((a_addr >> 4) & 0x3FFFu) | a_lo_fixed;
-              const uint32_t b_lo = ((b_addr >> 4) & 0x3FFFu) | b_lo_fixed;
+        {
+          uint32_t b_lo = (sFilt >> 4) | b_lo_fixed;
+          uint32_t a_row = ((sStrip + buf * strip_total) >> 4) | a_lo_fixed;
+          int tap = 0;
+          for (int ry = 0; ry < p.KH && ok; ++ry, a_row += row_step16) {
+            uint32_t a_tap = a_row;
+            for (int rx = 0; rx < p.KW; ++rx, ++tap, a_tap += tap_step16) {
+              if (!filter_in) {
+                if (tap < kStripFiltBars && !mbar_wait(smem_u32(&bars->filt_full[tap]), 0u, wctx)) {
+                  ok = false;
+                  break;
+                }
+                tc_fence_after();
+              }
+              uint32_t a_lo = a_tap;
+              for (int cc = 0; cc < p.n_cchunks; ++cc, a_lo += chunk16, b_lo += slab16) {
 #pragma unroll
-              for (int k = 0; k < 4; ++k) {
-                umma_cg<1, KIND>(d_tmem, desc_hi | (a_lo + 2u * k), desc_hi | (b_lo + b_step16 * k), idesc,
-                                 accum);
-                accum = 1u;
+                for (int k = 0; k < 4; ++k) {
+                  umma_cg<1, KIND>(d_tmem, desc_hi | (a_lo + 2u * k), desc_hi | (b_lo + b_step16 * k), idesc, accum);
+                  accum = 1u;
+                }
               }
             }
           }
+        }
+        if (!ok) break;
+        filter_in = true;
         umma_commit(smem_u32(&bars->strip_empty[buf]));
         umma_commit(smem_u32(&bars->tmem_full[acc]));
         if (++buf == p.ring) {
@@ -249,16 +310,27 @@ hb_conv_strip_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_cons
     // ------------------------------ epilogue ----------------------------------------------
     const int q = warp & 3;
     int acc = 0;
-    uint32_t acc_phase = 0;
+    uint32_t acc_phase = 0, stage_phase = 0, free_phase = 0;
     bool ok = true;
+    bool copies_pending = false;
+    const bool copier = threadIdx.x == 64;         // lane 0 of the first epilogue warp issues the TMA stores
     constexpr int kColsPerStep = 128 / OUT_BYTES;  // 32 or 64 output channels = 128 bytes
     const int pos = q * 32 + lane;                 // padded-linear position inside the tile
     const int py = pos / p.Wp;
     const int px = pos - py * p.Wp;
+    const int r2 = py * p.WO + px;                 // the pixel's row in the squeezed [R][WO] staging tile
+    const uint32_t stage_bar = smem_u32(&bars->stage), free_bar = smem_u32(&bars->stage_free);
     for (int t = blockIdx.x; ok && t < p.num_tiles; t += gridDim.x) {
       const int n = t / p.groups;
-      const int y = (t - n * p.groups) * p.R + py;
+      const int y0 = (t - n * p.groups) * p.R;
+      const int y = y0 + py;
       const bool valid = py < p.R && y < p.HO && px < p.WO;
+      if (copier && copies_pending) {
+        // the previous tile's stores have read the staging buffer: it may be overwritten
+        bulk_wait_read<0>();
+        mbar_arrive(free_bar);
+        copies_pending = false;
+      }
       if (!mbar_wait(smem_u32(&bars->tmem_full[acc]), acc_phase, wctx)) {
         ok = false;
         break;
@@ -280,6 +352,14 @@ hb_conv_strip_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_cons
         continue;
       }
 #endif
+      if (p.staged) {
+        // (free_phase counts tiles: the buffer starts out free, so the first wait passes at once)
+        if (!mbar_wait(free_bar, free_phase ^ 1u, wctx)) {
+          ok = false;
+          break;
+        }
+        free_phase ^= 1u;
+      }
       for (int c0 = 0; c0 < p.CO; c0 += kColsPerStep) {
         uint32_t v[32];
         uint32_t packed[32];
@@ -307,7 +387,20 @@ hb_conv_strip_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_cons
           __syncwarp();
           if (lane == 0) mbar_arrive(smem_u32(&bars->tmem_empty[acc]));
         }
-        if (valid && p.out_nchw) {
+        if (p.staged) {
+          // this pixel's 128 bytes of channels, into row r2 of the chunk's swizzled staging tile
+          if (valid) {
+            const uint32_t row_addr =
+                sStage + static_cast<uint32_t>((c0 / kColsPerStep) * p.stage_chunk_bytes + r2 * 128);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const uint32_t a = row_addr + ((j ^ (r2 & 7)) << 4);
+              asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(a), "r"(packed[4 * j]),
+                           "r"(packed[4 * j + 1]), "r"(packed[4 * j + 2]), "r"(packed[4 * j + 3])
+                           : "memory");
+            }
+          }
+        } else if (valid && p.out_nchw) {
           // channel-major output: consecutive lanes are consecutive pixels of one image row
           const long long plane = static_cast<long long>(p.HO) * p.WO;
           uint8_t* o = static_cast<uint8_t*>(p.out) +
@@ -327,11 +420,32 @@ hb_conv_strip_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_cons
                 make_uint4(packed[4 * j], packed[4 * j + 1], packed[4 * j + 2], packed[4 * j + 3]);
         }
       }
+      if (p.staged) {
+        fence_proxy_async_smem();  // the staging writes above are read by TMA stores (async proxy)
+        __syncwarp();
+        if (lane == 0) mbar_arrive(stage_bar);
+        if (copier) {
+          // every warp's pixels of this tile are staged: one tiled store per 128-byte channel chunk,
+          // box (channels, WO, R); rows past the image's last are clipped by TMA
+          if (!mbar_wait(stage_bar, stage_phase, wctx)) {
+            ok = false;
+          } else {
+            for (int c = 0; c < n_ochunks; ++c)
+              tma_store_4d(&tmOut, sStage + static_cast<uint32_t>(c * p.stage_chunk_bytes), c * kColsPerStep, 0,
+                           y0, n);
+            bulk_commit();
+            copies_pending = true;
+          }
+        }
+        stage_phase ^= 1u;
+        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;  // (the copier's verdict counts for its warp)
+      }
       if (++acc == 2) {
         acc = 0;
         acc_phase ^= 1u;
       }
     }
+    if (copier) bulk_wait_read<0>();  // shared memory must outlive the stores' reads of it
     __syncwarp();
   }
 

@@ -372,11 +372,11 @@ int run_main(const hb_plan* plan, cudaStream_t stream) {
     cfg.numAttrs = 1;
     cudaError_t e;
     if (sp.esize_out == 2)
-      e = cudaLaunchKernelEx(&cfg, hb::hb_conv_strip_kernel<2, 0>, plan->tmA, plan->tmB, sp);
+      e = cudaLaunchKernelEx(&cfg, hb::hb_conv_strip_kernel<2, 0>, plan->tmA, plan->tmB, plan->tmC, sp);
     else if (sp.esize_in == 2)
-      e = cudaLaunchKernelEx(&cfg, hb::hb_conv_strip_kernel<4, 0>, plan->tmA, plan->tmB, sp);
+      e = cudaLaunchKernelEx(&cfg, hb::hb_conv_strip_kernel<4, 0>, plan->tmA, plan->tmB, plan->tmC, sp);
     else
-      e = cudaLaunchKernelEx(&cfg, hb::hb_conv_strip_kernel<4, 1>, plan->tmA, plan->tmB, sp);
+      e = cudaLaunchKernelEx(&cfg, hb::hb_conv_strip_kernel<4, 1>, plan->tmA, plan->tmB, plan->tmC, sp);
     return e == cudaSuccess ? HB_OK : HB_ERR_LAUNCH;
   }
   const bool half_out = plan->p.esize_out == 2;

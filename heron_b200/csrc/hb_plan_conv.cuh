@@ -29,8 +29,14 @@ int strip_smem_bytes(const ConvGeom& g, int es, int eo, hb::StripParams* sp) {
   const int strip_bytes = (px * 128 + 1023) & ~1023;
   const int n_cchunks = g.CI * es / 128;
   const long long filt = static_cast<long long>(g.KH) * g.KW * g.CI * g.CO * es;
-  long long smem = ((filt + 1023) & ~1023LL) + 2LL * n_cchunks * strip_bytes + 1024 + 256;
+  long long smem = ((filt + 1023) & ~1023LL) + 2LL * n_cchunks * strip_bytes + 1024 + 512;
   if (smem > kSmemLimit) return 0;
+  // Staged epilogue (row-major output): one squeezed [R][WO] tile of 128-byte rows per 128-byte
+  // channel chunk of the output, sent out by TMA.  It takes precedence over a deeper strip ring.
+  const int stage_chunk = (R * g.WO * 128 + 1023) & ~1023;
+  const long long stage = static_cast<long long>(g.CO) * eo / 128 * stage_chunk;
+  const bool staged = !g.out_nchw && g.WO <= 256 && R <= 256 && smem + stage <= kSmemLimit;
+  if (staged) smem += stage;
   int ring = 2;  // deeper when shared memory allows: more strips in flight hide HBM latency
   while (ring < hb::kMaxStripRing && smem + static_cast<long long>(n_cchunks) * strip_bytes <= kSmemLimit) {
     smem += static_cast<long long>(n_cchunks) * strip_bytes;
@@ -40,6 +46,7 @@ int strip_smem_bytes(const ConvGeom& g, int es, int eo, hb::StripParams* sp) {
     sp->ring = ring;
     sp->Wp = Wp; sp->R = R; sp->strip_rows = strip_rows; sp->strip_bytes = strip_bytes;
     sp->n_cchunks = n_cchunks; sp->groups = (g.HO + R - 1) / R;
+    sp->staged = staged ? 1 : 0; sp->stage_chunk_bytes = stage_chunk;
   }
   return static_cast<int>(smem);
 }
@@ -80,6 +87,19 @@ int build_strip_plan(Driver& d, const ConvGeom& g, hb_dtype in_a, hb_dtype in_w,
   const uint64_t rowB = static_cast<uint64_t>(g.CO) * es;
   int rc = encode_tiled3(d, &plan->tmB, in_w, w, g.CO, K, 1, rowB, rowB * K, 128 / es, 128 / es, 128);
   if (rc != HB_OK) return rc;
+  plan->tmC = plan->tmA;  // (a valid map in every case; the staged epilogue gets the output's below)
+  if (sp.staged) {
+    // output as a tiled (C, W, H, N) tensor: one box = 128 bytes of channels x WO x R rows
+    cuuint64_t odims[4] = {static_cast<cuuint64_t>(g.CO), static_cast<cuuint64_t>(g.WO),
+                           static_cast<cuuint64_t>(g.HO), static_cast<cuuint64_t>(g.N)};
+    cuuint64_t ostrides[3] = {static_cast<cuuint64_t>(g.CO) * eo, static_cast<cuuint64_t>(g.WO) * g.CO * eo,
+                              static_cast<cuuint64_t>(g.HO) * g.WO * g.CO * eo};
+    cuuint32_t obox[4] = {static_cast<cuuint32_t>(128 / eo), static_cast<cuuint32_t>(g.WO),
+                          static_cast<cuuint32_t>(sp.R), 1};
+    r = d.tiled(&plan->tmC, tmap_dtype(out_t), 4, out, odims, ostrides, obox, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return HB_ERR_LAUNCH;
+  }
   int grid = d.sm_count;
   if (k.max_ctas > 0 && k.max_ctas < grid) grid = k.max_ctas;
   if (sp.num_tiles < grid) grid = sp.num_tiles;

@@ -235,7 +235,7 @@ def strip_applies(p, es, eo, limits):
     px = max(strip_rows * Wp, (KH - 1) * dh * Wp + (KW - 1) * dw + 128)
     strip_bytes = (px * 128 + 1023) // 1024 * 1024
     filt = (KH * KW * CI * CO * es + 1023) // 1024 * 1024
-    return filt + 2 * (CI * es // 128) * strip_bytes + 1024 + 256 <= limits["max_shared_memory_per_block"]
+    return filt + 2 * (CI * es // 128) * strip_bytes + 1024 + 512 <= limits["max_shared_memory_per_block"]
 
 
 def strip_wide_applies(p, es, eo, limits):
