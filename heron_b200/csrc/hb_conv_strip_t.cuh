@@ -253,11 +253,9 @@ hb_conv_strip_t_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_co
           for (int i = 1; i < nm; ++i) umma_cg<1, 0>(d_tmem, da, db, idesc, 1u);
         }
 #endif
-        // The issuing thread is one lane of one warp: every integer instruction between two MMAs is
-        // on the tensor pipe's critical path.  Descriptor low words therefore advance by running
-        // additions (16-byte units; shared memory is < 256 KiB, so the 14-bit address field cannot
-        // wrap): per tap B moves on by dil_w pixels, per filter row by dil_h padded rows, A by one
-        // (tap, chunk) slab.
+        // Descriptor low words advance by running additions (16-byte units; shared memory is
+        // < 256 KiB, so the 14-bit address field cannot wrap): per tap B moves on by dil_w pixels, per
+        // filter row by dil_h padded rows, A by one (tap, chunk) slab.
         uint32_t a_lo = (sFilt >> 4) | a_lo_fixed;
         uint32_t b_row = (((sStrip + buf * strip_total) >> 4) + static_cast<uint32_t>(x0) * 8u) | b_lo_fixed;
         int tap = 0;

@@ -816,8 +816,8 @@ def test_conv_strip_algorithm_int8(K, co, case):
 
 
 def test_conv_strip_walks_its_whole_ring(K, co):
-    """One CTA takes every tile in turn, so each barrier of the deepest strip ring is used and
-    reused (14x14 images leave room for six strip buffers)."""
+    """One CTA takes every tile in turn, so each barrier of a deep strip ring is used and reused
+    (14x14 images leave room for five strip buffers beside the filter and the staging tile)."""
     rng = np.random.default_rng(1414)
     x = rng.standard_normal((8, 14, 14, 64)).astype(np.float16)
     w = (rng.standard_normal((3, 3, 64, 64)) / 24.0).astype(np.float16)
@@ -825,7 +825,7 @@ def test_conv_strip_walks_its_whole_ring(K, co):
     plan = K.plan_conv2d_nhwc(dev(x), dev(w), stride=1, padding=1, dilation=1, out=out,
                               knobs=dict(conv_algo=2, max_ctas=1))
     kn = plan.knobs()
-    assert kn["conv_algo"] == 2 and kn["stages"] == 6 and kn["grid"] == 1, kn
+    assert kn["conv_algo"] == 2 and kn["stages"] >= 5 and kn["grid"] == 1, kn
     plan.launch()
     check(out, co.conv2d_nhwc_f16(x, w, 1, 1, 1, np.float32), "strip ring walk")
 
