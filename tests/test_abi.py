@@ -257,3 +257,32 @@ def test_balanced_runs_are_level(hb_lib):
     runs = _runs(hb_lib, 50, 18, 74)   # 128 images of the int8 ResNet layer: 50 pair tiles, 74 pairs
     sizes = [b - a for a, b in runs]
     assert max(sizes) <= 900 // 74 + 1 + 2 and min(sizes) >= 900 // 74 - 2
+
+
+def test_balanced_walker_random_shapes(hb_lib):
+    """The kernel's walker over random (tiles, stages per tile, pairs): every stage exactly once,
+    at most one piece per run that starts inside a tile and one that ends inside one, shared tiles
+    first."""
+    import ctypes
+    import random
+    rnd = random.Random(7)
+    for _ in range(300):
+        pairs = rnd.choice([1, 2, 3, 37, 74, 148])
+        per_tile = rnd.randint(1, 80)
+        tiles = rnd.randint(max(1, -(-4 * pairs // per_tile)), max(2, -(-4 * pairs // per_tile)) + rnd.randint(0, 400))
+        seen = set()
+        buf = (ctypes.c_int * (3 * 512))()
+        for i in range(pairs):
+            n = hb_lib.hb_balanced_pieces(tiles, per_tile, pairs, i, buf, 512)
+            assert 0 <= n <= 512
+            kinds = []
+            for j in range(n):
+                t, s0, s1 = buf[3 * j], buf[3 * j + 1], buf[3 * j + 2]
+                assert 0 <= t < tiles and 0 <= s0 < s1 <= per_tile
+                for st in range(s0, s1):
+                    assert (t, st) not in seen
+                    seen.add((t, st))
+                kinds.append("p" if s1 < per_tile else ("c" if s0 > 0 else "w"))
+            assert kinds.count("p") <= 1 and kinds.count("c") <= 1
+            assert kinds == sorted(kinds, key="pcw".index), (tiles, per_tile, pairs, i, kinds)
+        assert len(seen) == tiles * per_tile, (tiles, per_tile, pairs)
