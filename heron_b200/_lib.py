@@ -94,12 +94,13 @@ class HbKnobs(ctypes.Structure):
         ("split_k", ctypes.c_int),
         ("k_slices", ctypes.c_int),
         ("balance", ctypes.c_int),
+        ("epi_warps", ctypes.c_int),
         ("silent_producer", ctypes.c_int),
         ("probe", ctypes.c_int),
     ]
 
     FIELDS = ("tile_n", "stages", "swizzle_bytes", "acc_stages", "raster", "epilogue", "max_ctas",
-              "cta_group", "l2_prefetch", "conv_algo", "tail_split", "split_k", "k_slices", "balance",
+              "cta_group", "l2_prefetch", "conv_algo", "tail_split", "split_k", "k_slices", "balance", "epi_warps",
               "silent_producer", "probe")
 
     @classmethod

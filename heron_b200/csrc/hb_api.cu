@@ -39,7 +39,7 @@ int hb_kernel_limits(hb_limits* out) {
   out->tmem_columns = 512;
   out->tile_m = hb::kTileM;
   out->max_stages = hb::kMaxStages;
-  out->epilogue_staging_bytes = hb::kEpiWarps * 2 * hb::kEpiBufBytes;
+  out->epilogue_staging_bytes = hb::kUmmaEpiBytes;
   out->smem_slack_bytes = kSmemSlack;
   out->static_scratch_bytes = static_cast<int>(HB_STATIC_SCRATCH_BYTES);
   out->reserved = 0;

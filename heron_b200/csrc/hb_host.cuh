@@ -254,17 +254,28 @@ void resolve_knobs(const Problem& pr, const hb_knobs* in, int sm_count, hb_knobs
     // 512 x 768 x 768 -14 %) or with 4 spans.
     const int sw = k.swizzle_bytes;
     const long long kblocks = (static_cast<long long>(pr.K) * es + sw - 1) / sw;
-    const int epi = k.epilogue == 1 ? hb::kEpiWarps * 2 * hb::kEpiBufBytes : 0;
+    const int epi = k.epilogue == 1 ? hb::kUmmaEpiBytes : 0;
     const int wide = 2 * stage_bytes(k.tile_n, k.swizzle_bytes, k.cta_group);
     const int want = k.stages > 0 ? k.stages : 3;
     k.k_slices = (kblocks >= 8 && want * wide + epi + kSmemSlack <= kSmemLimit) ? 2 : 1;
   }
   if (k.stages == 0) {
-    const int epi = k.epilogue == 1 ? hb::kEpiWarps * 2 * hb::kEpiBufBytes : 0;
+    const int epi = k.epilogue == 1 ? hb::kUmmaEpiBytes : 0;
     int s = (kSmemLimit - kSmemSlack - epi) / (k.k_slices * stage_bytes(k.tile_n, k.swizzle_bytes, k.cta_group));
     if (s > 8) s = 8;
     if (s < 1) s = 1;
     k.stages = s;
+  }
+  if (k.epi_warps == 0) {
+    // Eight epilogue warps where a tile's K loop is shorter than its drain (fewer swizzle spans of
+    // K than 128-byte column chunks of output: the MMA warp then waits for TMEM), if that leaves
+    // each warp at least two chunks.  Measured on a B200 (four warps against eight): 192 batches of
+    // 512 x 512 x 64 int8 -> s32 40.3 against 38.7 us, 24 batches 9.25 against 8.85 us; long-K
+    // shapes are level or lose up to 0.5 % with eight (4096^3 fp16 108.2 against 108.8 us, the
+    // 512-channel 3x3 int8 conv over 1024 images 89.0 against 89.3 us), so they keep four.
+    const long long spans = (static_cast<long long>(pr.K) * es + k.swizzle_bytes - 1) / k.swizzle_bytes;
+    const int chunks = k.tile_n * eo / 128;
+    k.epi_warps = (chunks >= 4 && spans < chunks) ? 8 : 4;
   }
   if (k.l2_prefetch == 0) k.l2_prefetch = -1;
   *out = k;
@@ -293,8 +304,9 @@ int check_knobs(const Problem& pr, const hb_knobs& k, int* smem_bytes, int* tmem
   if (pr.conv && (pr.CI * es) % k.swizzle_bytes != 0) return HB_ERR_KNOB;
   // whole MN-major chunks in every CTA of the group
   if (b_mn_major(pr) && (k.tile_n / k.cta_group * es) % k.swizzle_bytes != 0) return HB_ERR_KNOB;
-  const int epi = k.epilogue == 1 ? hb::kEpiWarps * 2 * hb::kEpiBufBytes : 0;
+  const int epi = k.epilogue == 1 ? hb::kUmmaEpiBytes : 0;
   if (k.k_slices != 1 && k.k_slices != 2) return HB_ERR_KNOB;
+  if (k.epi_warps != 4 && k.epi_warps != 8) return HB_ERR_KNOB;
   if (k.balance < 0 || k.balance > 2) return HB_ERR_KNOB;
   if (k.balance == 2 && eo != 4) return HB_ERR_KNOB;  // partial sums travel through the output
   const int smem = k.stages * k.k_slices * stage_bytes(k.tile_n, k.swizzle_bytes, k.cta_group) + epi + kSmemSlack;

@@ -6,13 +6,15 @@
 // warps have fixed roles:
 //   warp 0      one elected lane issues the A-operand TMA loads into a ring of shared-memory
 //               stages (and arms each stage's barrier with the bytes both operands will bring);
-//   warp 6      one elected lane issues the B-operand loads of the same stages (two issuing
+//   last warp   one elected lane issues the B-operand loads of the same stages (two issuing
 //               threads keep more loads in flight than one: +12 % on the int8 conv);
 //   warp 1      allocates TMEM; one elected lane issues tcgen05.mma into a TMEM accumulator and
 //               commits stage-free / accumulator-full events to mbarriers;
-//   warps 2..5  epilogue: tcgen05.ld the accumulator (each warp owns the 32 TMEM lanes its
-//               position in the warpgroup may touch), convert, and write the tile either through
-//               swizzled shared memory + TMA store or with direct vector stores.
+//   warps 2..   epilogue, four or eight warps (chosen per launch): tcgen05.ld the accumulator
+//               (a warp may touch the 32 TMEM lanes of its position in its warpgroup; with eight
+//               warps the two of a position split a tile's 128-byte column chunks), convert, and
+//               write the tile either through swizzled shared memory + TMA store or with direct
+//               vector stores.  Eight pay where a tile's K loop is shorter than its drain.
 // Two accumulator buffers in TMEM let the MMA warp start the next tile while the epilogue warps
 // drain the previous one.
 //
@@ -60,6 +62,7 @@
 #pragma once
 #include "hb_ptx.cuh"
 #include <cuda_fp16.h>
+#include <type_traits>
 
 namespace hb {
 
@@ -67,8 +70,14 @@ constexpr int kMaxStages = 12;
 constexpr int kTileM = 128;
 constexpr int kEpiWarps = 4;
 constexpr int kThreads = 32 * (2 + kEpiWarps);       // strip conv kernel: producer, MMA, epilogue
-constexpr int kUmmaThreads = kThreads + 32;          // GEMM kernel: a second producer warp
 constexpr int kEpiBufBytes = 4096;  // 32 rows x 128 bytes
+// GEMM kernel: four epilogue warps (one per TMEM lane quadrant, two staging buffers each) or
+// eight (two per quadrant, each with half of a tile's column chunks and one staging buffer),
+// chosen per launch, and a second producer warp after them
+constexpr int kUmmaEpiWarpsMax = 8;
+constexpr int kUmmaEpiBytes = kUmmaEpiWarpsMax * kEpiBufBytes;
+constexpr int kUmmaThreadsMax = 32 * (3 + kUmmaEpiWarpsMax);
+__host__ __device__ constexpr int umma_threads(int epi_warps) { return 32 * (3 + epi_warps); }
 constexpr int kErrTimeout = 5;      // HB_ERR_TIMEOUT
 
 struct KParams {
@@ -79,6 +88,7 @@ struct KParams {
   int tiles_m, tiles_n, num_tiles, num_kb;
   int raster, kind, b_mn_major, a_im2col, epilogue, l2_prefetch;
   int probe;            // diagnostic modes; only builds with -DHB_PROBES read it
+  int epi_warps;        // epilogue warps of a CTA: 4 or 8
   int silent_producer;  // test hook: the producers issue no loads, so the consumers' waits run out
   // Balanced schedule: work units are ring stages; unit u belongs to tile u / sk_per_tile.  CTA
   // pair i walks units [bound(i), bound(i+1)), bound(i) = i * sk_total / pairs, moved to the tile
@@ -235,7 +245,7 @@ __device__ __forceinline__ uint4 ld_cg_v4(const void* ptr) {
 }
 
 template <int OUT_BYTES, int CG, int KIND, int KS>
-__global__ void __launch_bounds__(kUmmaThreads, 1)
+__global__ void __launch_bounds__(kUmmaThreadsMax, 1)
 hb_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmB2,
                const KParams p) {
@@ -254,7 +264,7 @@ hb_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   const uint32_t sB = sA + p.stages * G * a_bytes;
   // the epilogue staging buffers are 128-byte swizzled: 1024-byte aligned whatever the ring size
   const uint32_t sEpi = (sB + p.stages * G * b_bytes + 1023u) & ~1023u;
-  const int epi_bytes = p.epilogue ? kEpiWarps * 2 * kEpiBufBytes : 0;
+  const int epi_bytes = p.epilogue ? kUmmaEpiBytes : 0;
   SmemBars* bars = reinterpret_cast<SmemBars*>(smem + (sEpi - smem_base) + epi_bytes);
   volatile int* abort_flag = &bars->abort_flag;
   const WaitCtx wctx{abort_flag, p.wait_limit_cycles > 0 ? p.wait_limit_cycles : HB_WAIT_LIMIT_CYCLES};
@@ -270,7 +280,7 @@ hb_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(smem_u32(&bars->tmem_full[a]), 1);
-      mbar_init(smem_u32(&bars->tmem_empty[a]), kEpiWarps * CG);
+      mbar_init(smem_u32(&bars->tmem_empty[a]), p.epi_warps * CG);
     }
     mbar_init(smem_u32(&bars->drain), 1);
     bars->abort_flag = 0;
@@ -560,20 +570,27 @@ hb_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       }
     }
     __syncwarp();
-  } else if (warp >= 6) {
+  } else if (warp >= 2 + p.epi_warps) {
     // ------------------------------ second TMA producer: the B operand ---------------------
     if (elect_one()) produce(2);
     __syncwarp();
   } else {
     // ------------------------------ epilogue ----------------------------------------------
+    // (one body per warp count: the drain loop of a short-K shape is the kernel's critical path,
+    // and with the count a compile-time constant the four-warp form costs nothing for the other)
+    auto epilogue = [&](auto eight_tag) {
+    constexpr bool kEight = decltype(eight_tag)::value;
+    constexpr int kWarps = kEight ? 8 : 4;
     const int q = warp & 3;  // TMEM lane quadrant this warp may read
     const int ew = warp - 2;
+    const int half = kEight ? (ew >> 2) : 0;  // with eight warps: which half of a tile's column chunks
+    constexpr uint32_t n_bufs = kUmmaEpiWarpsMax / kWarps;  // staging buffers of a warp
+    uint32_t store_it = 0;
     int acc = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
-    uint32_t store_it = 0;
     constexpr int kColsPerStore = 128 / OUT_BYTES;  // 32 (4-byte) or 64 (fp16) columns
-    const uint32_t my_buf = sEpi + ew * 2 * kEpiBufBytes;
+    const uint32_t my_buf = sEpi + ew * n_bufs * kEpiBufBytes;
     Walk walk = walk_begin(p, first_tile, tile_step);
     Piece pc;
     while (ok && walk_next(p, walk, pc)) {
@@ -591,12 +608,12 @@ hb_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       const bool sk_prod = OUT_BYTES == 4 && p.sk && pc.s1 < p.sk_per_tile;
       const bool sk_cons = OUT_BYTES == 4 && p.sk && pc.s0 > 0;
 #endif
-      const int sk_slot = static_cast<int>(cta_rank) * kEpiWarps + q;
+      const int sk_slot = static_cast<int>(cta_rank) * kWarps + ew;
       const bool ksliced = OUT_BYTES == 4 && p.ksplit > 1 && t >= p.whole_tiles && !p.kslab;
       const bool chain = ksliced && p.flags != nullptr;
       const bool reduce = ksliced && (!chain || kslice > 0);
       int* const flag = chain ? p.flags + (t - p.whole_tiles) / p.ksplit : nullptr;
-      constexpr int kArrivals = kEpiWarps * CG;  // epilogue warps that work on one tile
+      constexpr int kArrivals = kWarps * CG;  // epilogue warps that work on one tile
       const int zc = p.kslab ? kslice : b;  // third coordinate of the output: batch, or workspace slab
       const int row0 = m_pair + static_cast<int>(cta_rank) * kTileM + q * 32;
       if (!mbar_wait_relaxed(smem_u32(&bars->tmem_full[acc]), acc_phase, wctx)) {
@@ -652,10 +669,28 @@ hb_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                               static_cast<uint32_t>(acc * p.BN);
       // Software pipeline over 128-byte column chunks: the TMEM load of chunk i+1 is in flight
       // while chunk i goes through shared memory to its TMA store.
+      // Two warps of a quadrant split the chunks: the first takes the lower half (the larger
+      // one when the count is odd), the second the rest, which may be nothing.
+      const int n_chunks = (bn + kColsPerStore - 1) / kColsPerStore;
+      const int c_mid = !kEight ? bn : min(bn, ((n_chunks + 1) >> 1) * kColsPerStore);
+      const int c_lo = half ? c_mid : 0;
+      const int c_hi = half ? bn : c_mid;
       uint32_t v[32];
       uint32_t v2[OUT_BYTES == 2 ? 32 : 1];
-      tmem_ld_32x32(t_addr, v);
-      if (OUT_BYTES == 2) tmem_ld_32x32(t_addr + 32, reinterpret_cast<uint32_t(&)[32]>(v2));
+      if (!kEight || c_lo < c_hi) {
+        tmem_ld_32x32(t_addr + c_lo, v);
+        if (OUT_BYTES == 2) tmem_ld_32x32(t_addr + c_lo + 32, reinterpret_cast<uint32_t(&)[32]>(v2));
+      } else {
+        // no chunk for this warp: the accumulator is handed back at once
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) {
+          if (CG == 2)
+            mbar_arrive_cluster(mapa(smem_u32(&bars->tmem_empty[acc]), 0));
+          else
+            mbar_arrive(smem_u32(&bars->tmem_empty[acc]));
+        }
+      }
       // balanced schedule, consumer piece: this thread's 128 bytes of the partial sums another
       // pair left in the output, for the column chunk that starts at tile column c (zeros where
       // the tile hangs over the edge of C; rows are 16-byte multiples: whole vectors or none)
@@ -679,8 +714,8 @@ hb_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             part[j] = make_uint4(0u, 0u, 0u, 0u);
         }
       };
-      if (OUT_BYTES == 4 && sk_cons) load_part(0);
-      for (int c0 = 0; c0 < bn; c0 += kColsPerStore) {
+      if (OUT_BYTES == 4 && sk_cons && c_lo < c_hi) load_part(c_lo);
+      for (int c0 = c_lo; c0 < c_hi; c0 += kColsPerStore) {
         uint32_t packed[32];  // 128 bytes of output for this thread's row
         tmem_ld_wait();
         if (OUT_BYTES == 4) {
@@ -714,15 +749,15 @@ hb_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 packed[4 * j + 3] = __float_as_uint(__uint_as_float(packed[4 * j + 3]) + __uint_as_float(part[j].w));
               }
             }
-            if (c0 + kColsPerStore < bn) load_part(c0 + kColsPerStore);
+            if (c0 + kColsPerStore < c_hi) load_part(c0 + kColsPerStore);
           }
         }
-        if (c0 + kColsPerStore < bn) {
+        if (c0 + kColsPerStore < c_hi) {
           tmem_ld_32x32(t_addr + c0 + kColsPerStore, v);
           if (OUT_BYTES == 2)
             tmem_ld_32x32(t_addr + c0 + kColsPerStore + 32, reinterpret_cast<uint32_t(&)[32]>(v2));
         }
-        if (c0 + kColsPerStore >= bn) {
+        if (c0 + kColsPerStore >= c_hi) {
           // Last read of this accumulator: hand it back to the MMA warp before storing.
           tc_fence_before();
           __syncwarp();
@@ -736,10 +771,15 @@ hb_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         const int col = n0 + c0;
         if (p.epilogue) {
           if (col < p.N && row0 < p.M) {
-            const uint32_t buf = my_buf + (store_it & 1u) * kEpiBufBytes;
+            const uint32_t buf = my_buf + (n_bufs == 2 ? (store_it & 1u) * kEpiBufBytes : 0u);
             ++store_it;
             const bool issuer = elect_one();
-            if (issuer) bulk_wait_read<1>();  // the store that last used this buffer has read it
+            // the store that last used this buffer has read it (every lane waits: only the one
+            // that issued stores has groups to wait for)
+            if (n_bufs == 2)
+              bulk_wait_read<1>();
+            else
+              bulk_wait_read<0>();
             __syncwarp();
             const uint32_t row_addr = buf + lane * 128;
 #pragma unroll
@@ -861,10 +901,15 @@ hb_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         acc_phase ^= 1u;
       }
     }
-    // every lane may have been the elected issuer of some store: each drains its own groups
+    // the lane that issued this warp's stores drains their groups (a no-op for the others):
     // shared memory must outlive the stores' reads of it; their writes complete with the grid
     if (p.epilogue) bulk_wait_read<0>();
     __syncwarp();
+    };
+    if (p.epi_warps == 8)
+      epilogue(std::true_type{});
+    else
+      epilogue(std::false_type{});
   }
 
   tc_fence_before();

@@ -34,6 +34,7 @@ int build_plan(Driver& d, const Problem& pr, const hb_knobs& k, const ConvGeom* 
   p.a_shared = pr.shared_a_b_mn ? 1 : 0;
   p.epilogue = k.epilogue == 1 ? 1 : 0;
   p.l2_prefetch = (!pr.conv && k.l2_prefetch > 0) ? k.l2_prefetch : 0;
+  p.epi_warps = k.epi_warps;
   p.probe = k.probe;  // diagnostic modes (builds with -DHB_PROBES only)
   p.silent_producer = k.silent_producer ? 1 : 0;
   if (p.silent_producer) p.wait_limit_cycles = 200000000LL;  // ~0.1 s: the timeout test should be quick
@@ -139,7 +140,7 @@ int build_plan(Driver& d, const Problem& pr, const hb_knobs& k, const ConvGeom* 
     cudaLaunchConfig_t cfg;
     std::memset(&cfg, 0, sizeof(cfg));
     cfg.gridDim = dim3(d.sm_count / 2 * 2);
-    cfg.blockDim = dim3(hb::kUmmaThreads);
+    cfg.blockDim = dim3(hb::umma_threads(k.epi_warps));
     cfg.dynamicSmemBytes = smem;
     cudaLaunchAttribute attr;
     attr.id = cudaLaunchAttributeClusterDimension;
@@ -190,7 +191,7 @@ int build_plan(Driver& d, const Problem& pr, const hb_knobs& k, const ConvGeom* 
     sk = sk_can;  // (a problem too small to cut keeps the tile list)
   }
   if (sk) {
-    const int per_pair = hb::kEpiWarps * cgrp;
+    const int per_pair = k.epi_warps * cgrp;
     const int rc_flags = split_flags(units * per_pair, &p.flags);
     if (rc_flags == HB_OK) {
       if (g_plan_owns_flags) plan->owned_flags = units * per_pair;
@@ -402,7 +403,7 @@ int launch_kernel(const hb_plan* plan, cudaStream_t stream) {
   cudaLaunchConfig_t cfg;
   std::memset(&cfg, 0, sizeof(cfg));
   cfg.gridDim = dim3(plan->grid);
-  cfg.blockDim = dim3(hb::kUmmaThreads);
+  cfg.blockDim = dim3(hb::umma_threads(plan->p.epi_warps));
   cfg.dynamicSmemBytes = plan->smem;
   cfg.stream = stream;
   cudaLaunchAttribute attr[2];

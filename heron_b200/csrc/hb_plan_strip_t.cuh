@@ -100,7 +100,7 @@ int build_strip_t_plan(Driver& d, const ConvGeom& g, hb_dtype in_a, hb_dtype in_
   // fields hb_plan_knobs reports
   plan->knobs.tile_n = sp.L; plan->knobs.swizzle_bytes = 128; plan->knobs.stages = sp.ring;
   plan->knobs.acc_stages = 2; plan->knobs.cta_group = 1; plan->knobs.epilogue = 2;
-  plan->knobs.balance = 1; plan->knobs.split_k = 1; plan->knobs.tail_split = 1; plan->knobs.k_slices = 1;
+  plan->knobs.epi_warps = hb::kWideEpiWarps; plan->knobs.balance = 1; plan->knobs.split_k = 1; plan->knobs.tail_split = 1; plan->knobs.k_slices = 1;
   plan->p.N = g.CO; plan->p.KW = g.KW; plan->p.CI = g.CI; plan->p.esize_out = sp.esize_out;
   return HB_OK;
 }

@@ -320,6 +320,20 @@ class balanceOp(SchedOp):
         ctx.addSchedDesc("## balance %s\n" % ctx.kernel_knobs["balance"])
 
 
+class epilogueWarpsOp(SchedOp):
+    """Warps that drain a CTA's accumulators: four (one per 32 TMEM lanes) or eight (two per 32
+    lanes, half of a tile's column chunks each)."""
+
+    def perform(self, s, stage_name, ctx):
+        km = ctx.knob_manager
+        warps = genKey("P", stage_name, "n", param_name="epi_warps")
+        if km.is_building:
+            km.define_value(warps, 4, 8, 4, True)
+            km.addCandidates(warps, [4, 8])
+        ctx.kernel_knobs["epi_warps"] = km.get_val(warps)
+        ctx.addSchedDesc("## epilogue warps %s\n" % ctx.kernel_knobs["epi_warps"])
+
+
 _METHODS = {
     "tileOp": tileOp,
     "pipelineOp": pipelineOp,
@@ -328,6 +342,7 @@ _METHODS = {
     "convAlgoOp": convAlgoOp,
     "splitKOp": splitKOp,
     "balanceOp": balanceOp,
+    "epilogueWarpsOp": epilogueWarpsOp,
 }
 
 
@@ -344,5 +359,6 @@ def sched_via_rule(_type, ctx, s):
     that ``Task.instantiate`` can replay them (schedule/sched_op/__init__.py:23-30)."""
     get_op_methods(_type)
     for out in s.outputs:
-        for rule in ("tileOp", "pipelineOp", "epilogueOp", "rasterOp", "convAlgoOp", "splitKOp", "balanceOp"):
+        for rule in ("tileOp", "pipelineOp", "epilogueOp", "rasterOp", "convAlgoOp", "splitKOp", "balanceOp",
+                     "epilogueWarpsOp"):
             ctx.addSched(rule, out.op.name, s)

@@ -89,6 +89,10 @@ typedef struct {
                         partial sums in the output for this one to add (fixed order, no atomics;
                         overrides tail_split and split_k).  4-byte outputs with 16-byte rows only;
                         0 = library picks                                                          */
+  int epi_warps;     /* warps that drain a CTA's accumulators: 4 (one per 32 TMEM lanes, two staging
+                        buffers each) or 8 (two per 32 lanes, each with half of a tile's column
+                        chunks and one staging buffer); 0 = library picks (8 where a tile's K loop
+                        is shorter than its drain)                                                */
   int silent_producer; /* test hook, leave 0.  1: the TMA producers issue nothing, so every consumer's
                         bounded wait runs out (0.1 s limit for such a launch) and the launch ends
                         with HB_ERR_TIMEOUT in the status word and the context intact              */

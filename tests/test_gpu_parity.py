@@ -155,6 +155,9 @@ def test_gemm_fp16(K, co, M, N, Kd, out_dtype):
     dict(raster=1), dict(max_ctas=3), dict(tile_n=224, stages=3, raster=1),
     dict(cta_group=1), dict(cta_group=2), dict(cta_group=2, tile_n=64, swizzle_bytes=64), dict(cta_group=1, tile_n=256),
     dict(cta_group=2, epilogue=2, acc_stages=1), dict(cta_group=2, l2_prefetch=3), dict(cta_group=2, max_ctas=5),
+    dict(epi_warps=4), dict(epi_warps=8), dict(epi_warps=8, tile_n=32), dict(epi_warps=8, tile_n=96, epilogue=2),
+    dict(epi_warps=8, cta_group=2), dict(epi_warps=8, cta_group=2, tile_n=160, acc_stages=1), dict(epi_warps=8, max_ctas=2),
+    dict(epi_warps=4, tile_n=256, cta_group=1), dict(epi_warps=8, tile_n=224, raster=1, epilogue=2),
 ])
 def test_gemm_every_knob_gives_the_same_bits(K, co, knobs):
     rng = np.random.default_rng(42)
@@ -167,6 +170,7 @@ def test_gemm_every_knob_gives_the_same_bits(K, co, knobs):
     dict(split_k=2), dict(split_k=3), dict(split_k=4), dict(split_k=2, epilogue=2), dict(split_k=4, epilogue=2),
     dict(split_k=3, cta_group=1, tile_n=128), dict(split_k=2, cta_group=2, tile_n=64, swizzle_bytes=64),
     dict(split_k=4, max_ctas=6), dict(split_k=2, raster=1, max_ctas=10),
+    dict(split_k=3, epi_warps=8), dict(split_k=2, epi_warps=8, epilogue=2, cta_group=2), dict(split_k=4, epi_warps=4),
 ])
 @pytest.mark.parametrize("M,N,Kd", [(300, 200, 1040), (1024, 520, 512)])
 def test_split_k_int8_exact(K, co, knobs, M, N, Kd):
@@ -234,12 +238,49 @@ def test_two_k_spans_per_ring_stage(K, co, knobs):
     check(k_bmm(K, a3, b3, knobs=ck), co.bmm_int(a3, b3), "k spans bmm %s" % (ck,))
 
 
+@pytest.mark.parametrize("knobs", [
+    dict(epi_warps=8), dict(epi_warps=8, cta_group=2), dict(epi_warps=8, epilogue=2), dict(epi_warps=8, tile_n=64),
+    dict(epi_warps=8, tile_n=192, acc_stages=2, max_ctas=3), dict(epi_warps=4),
+])
+def test_eight_epilogue_warps(K, co, knobs):
+    """Two warps per 32 TMEM lanes, each draining half of a tile's 128-byte column chunks (an odd
+    count leaves the first warp one more, a single chunk leaves the second none): fp16 and fp32
+    outputs, ragged edges, conv through im2col loads, batched GEMM, and the library's own pick
+    on a short-K shape."""
+    rng = np.random.default_rng(11 + sum(knobs.values()))
+    for M, N, Kd in ((300, 200, 64), (640, 488, 192), (129, 1000, 320)):
+        a, b = rand_i8(rng, (M, Kd), False), rand_i8(rng, (N, Kd), True)
+        check(k_gemm(K, a, b, knobs=knobs), co.gemm_int(a, b), "epi warps int8 %s %s" % ((M, N, Kd), knobs))
+    af = (rng.standard_normal((260, 328)) / np.sqrt(328)).astype(np.float16)
+    bf = rng.standard_normal((392, 328)).astype(np.float16)
+    for od in (np.float32, np.float16):
+        check(k_gemm(K, af, bf, out_dtype=od, knobs=knobs), co.gemm_f16(af, bf).astype(od), "epi warps fp16 %s" % (knobs,))
+    ck = {k: v for k, v in knobs.items() if k != "tile_n"}
+    x, w = rand_i8(rng, (3, 9, 11, 64), False), rand_i8(rng, (3, 3, 64, 80), True)
+    check(k_conv(K, x, w, (2, 1), 1, 1, knobs=dict(ck, conv_algo=1)), co.conv2d_nhwc_int(x, w, (2, 1), 1, 1),
+          "epi warps conv %s" % (ck,))
+    a3, b3 = rand_i8(rng, (5, 200, 64), True), rand_i8(rng, (5, 264, 64), True)
+    check(k_bmm(K, a3, b3, knobs=ck), co.bmm_int(a3, b3), "epi warps bmm %s" % (ck,))
+
+
+def test_short_k_shapes_take_eight_epilogue_warps(K):
+    """The library's pick: eight where a tile has fewer swizzle spans of K than column chunks."""
+    a = torch.zeros((1024, 64), dtype=torch.int8, device="cuda")
+    b = torch.zeros((512, 64), dtype=torch.int8, device="cuda")
+    assert K.plan_gemm(a.view(torch.uint8), b, knobs=dict(tile_n=256)).knobs()["epi_warps"] == 8
+    a = torch.zeros((1024, 4096), dtype=torch.int8, device="cuda")
+    b = torch.zeros((512, 4096), dtype=torch.int8, device="cuda")
+    assert K.plan_gemm(a.view(torch.uint8), b, knobs=dict(tile_n=256)).knobs()["epi_warps"] == 4
+
+
 # ---- balanced schedule (knob balance = 2) --------------------------------------------------------
 BALANCE_KNOBS = [
     dict(), dict(cta_group=1), dict(cta_group=2), dict(max_ctas=6), dict(max_ctas=10, cta_group=2),
     dict(k_slices=1, max_ctas=14), dict(k_slices=2, max_ctas=22, cta_group=1), dict(epilogue=2, max_ctas=8),
     dict(tile_n=64, max_ctas=12), dict(tile_n=128, cta_group=2, max_ctas=20, stages=2),
     dict(raster=1, max_ctas=18), dict(acc_stages=1, max_ctas=6),
+    dict(epi_warps=8, max_ctas=10), dict(epi_warps=8, cta_group=2, max_ctas=14), dict(epi_warps=8, tile_n=96, epilogue=2, max_ctas=7),
+    dict(epi_warps=4, max_ctas=9),
 ]
 
 

@@ -156,7 +156,7 @@ def test_task_knob_space_and_instantiate(hb_lib):
     from heron_b200 import _lib
     t = _task("gemm", [4096, 4096, 4096, "float16", "float32"])
     km = t.knob_manager
-    assert not km.is_building and len(km.knob_names) == 10
+    assert not km.is_building and len(km.knob_names) == 11
     random.seed(3)
     distinct = set()
     for _ in range(40):
