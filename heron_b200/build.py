@@ -47,10 +47,17 @@ def build(force=False, verbose=False, extra_flags=()):
         return TARGET
     if os.environ.get("HB_PROBES") == "1":
         extra_flags = list(extra_flags) + ["-DHB_PROBES"]
-    cmd = [nvcc()] + NVCC_FLAGS + list(extra_flags) + ["-o", TARGET] + SOURCES
+    # (built beside the target and moved into place, so a reader never sees a half-written library)
+    tmp = TARGET + ".tmp.%d" % os.getpid()
+    cmd = [nvcc()] + NVCC_FLAGS + list(extra_flags) + ["-o", tmp] + SOURCES
     if verbose:
         print(" ".join(cmd))
-    subprocess.check_call(cmd)
+    try:
+        subprocess.check_call(cmd)
+        os.replace(tmp, TARGET)
+    finally:
+        if os.path.exists(tmp):
+            os.remove(tmp)
     return TARGET
 
 

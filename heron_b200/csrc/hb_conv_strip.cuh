@@ -56,7 +56,15 @@ struct StripParams {
   int out_nchw;  // output is (N, CO, HO, WO) instead of (N, HO, WO, CO)
   int staged;    // 1: the epilogue goes through the staging buffer and TMA stores (see above)
   int stage_chunk_bytes;  // staging bytes per 128-byte channel chunk: R * WO * 128, rounded up to 1024
+  int fuse_kw;   // 1: the KW taps of a filter row share one MMA of N = KW * CO columns (see FUSE below)
+  int acc_cols;  // TMEM columns from one accumulator to the other: CO, or KW * CO when fused
 };
+
+// Shared memory of the fused form's boundary exchange: per tile parity, per epilogue warp, the
+// second and third column groups of the warp's first position and the third of its second.
+constexpr int kStripXchRows = 3;
+__host__ __device__ constexpr int strip_xch_bytes(int co) { return 2 * kEpiWarps * kStripXchRows * co * 4; }
+
 
 constexpr int kStripFiltBars = 16;  // filter taps with a barrier of their own (later taps share the last)
 
@@ -64,6 +72,7 @@ struct StripBars {
   uint64_t filt_full[kStripFiltBars];
   uint64_t stage;       // the epilogue warps: "my pixels of this tile are in the staging buffer"
   uint64_t stage_free;  // the copying thread: "the TMA stores have read the staging buffer"
+  uint64_t xch;         // fused form: "my first positions' column groups of this tile are published"
   uint64_t strip_full[kMaxStripRing];
   uint64_t strip_empty[kMaxStripRing];
   uint64_t tmem_full[2];
@@ -92,7 +101,19 @@ __device__ __forceinline__ void tma_store_4d(const CUtensorMap* m, uint32_t src,
       : "memory");
 }
 
-template <int OUT_BYTES, int KIND>
+// FUSE = 1 (fp16, one 128-byte chunk of output channels, KW = 3, dilation 1 along W): the three
+// taps of a filter row are consecutive slabs of the resident filter, so one MN-major descriptor
+// with the slab distance as its column-chunk stride reads them as one B operand of 3 * CO
+// columns.  The MMA of filter row ry then takes the strip at the row's first tap as A and leaves,
+// in column group g, tap (ry, g) applied to the pixel g places to the LEFT of where it belongs:
+//   out[pos] = G0[pos] + G1[pos + 1] + G2[pos + 2].
+// A tile is whole padded rows and an output row ends KW - 1 pixels before its padded row, so the
+// shifted reads never leave the tile.  A third of the MMAs, each fetching 10 KB of operands for
+// 128 x 192 x 16 products instead of 6 KB for 128 x 64 x 16.  Positions are TMEM lanes: the
+// epilogue shifts with warp shuffles, and a warp's last two lanes take the next warp's first two
+// positions from a small shared-memory exchange (double-buffered by tile parity, published
+// behind an mbarrier so that the wait is bounded like every other).
+template <int OUT_BYTES, int KIND, int FUSE = 0>
 __global__ void __launch_bounds__(kThreads, 1)
 hb_conv_strip_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constant__ CUtensorMap tmW,
                      const __grid_constant__ CUtensorMap tmOut, const StripParams p) {
@@ -111,6 +132,7 @@ hb_conv_strip_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_cons
   const int n_ochunks = p.CO * OUT_BYTES / 128;           // 128-byte channel chunks of an output pixel
   const int stage_bytes = p.staged ? n_ochunks * p.stage_chunk_bytes : 0;
   StripBars* bars = reinterpret_cast<StripBars*>(smem + (sStage - smem_base) + stage_bytes);
+  float* const xch_base = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(bars) + 512);  // fused form only
   volatile int* abort_flag = &bars->abort_flag;
   const WaitCtx wctx{abort_flag, p.wait_limit_cycles > 0 ? p.wait_limit_cycles : HB_WAIT_LIMIT_CYCLES};
 
@@ -121,6 +143,7 @@ hb_conv_strip_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_cons
     for (int i = 0; i < kStripFiltBars; ++i) mbar_init(smem_u32(&bars->filt_full[i]), 1);
     mbar_init(smem_u32(&bars->stage), kEpiWarps);
     mbar_init(smem_u32(&bars->stage_free), 1);
+    mbar_init(smem_u32(&bars->xch), kEpiWarps);
     static_assert(sizeof(bars->strip_full) == kMaxStripRing * sizeof(uint64_t) &&
                       sizeof(bars->strip_empty) == kMaxStripRing * sizeof(uint64_t),
                   "every ring barrier below is initialised");
@@ -249,7 +272,7 @@ hb_conv_strip_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_cons
           break;
         }
         tc_fence_after();
-        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * p.CO);
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * p.acc_cols);
         uint32_t accum = 0u;
 #ifdef HB_PROBES
         if (p.probe == 9) {
@@ -263,7 +286,32 @@ hb_conv_strip_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_cons
           for (int i = 1; i < n; ++i) umma_cg<1, KIND>(d_tmem, da, db, idesc, 1u);
         } else if (p.probe != 2)
 #endif
-        {
+        if constexpr (FUSE) {
+          // one MMA per (filter row, channel chunk, 32 bytes of K): B's column chunks are the row's
+          // taps, n_cchunks slabs apart
+          const uint32_t b_fused = ((static_cast<uint32_t>(p.n_cchunks * tap_bytes) >> 4) & 0x3FFFu) << 16;
+          uint32_t b_row = (sFilt >> 4) | b_fused;
+          uint32_t a_row = ((sStrip + buf * strip_total) >> 4) | a_lo_fixed;
+          const uint32_t b_row_step16 = static_cast<uint32_t>(p.KW * p.n_cchunks) * slab16;
+          for (int ry = 0; ry < p.KH && ok; ++ry, a_row += row_step16, b_row += b_row_step16) {
+            if (!filter_in) {
+              for (int rx = 0; rx < p.KW && ok; ++rx) {
+                const int tap = ry * p.KW + rx;
+                if (tap < kStripFiltBars && !mbar_wait(smem_u32(&bars->filt_full[tap]), 0u, wctx)) ok = false;
+              }
+              if (!ok) break;
+              tc_fence_after();
+            }
+            uint32_t a_lo = a_row, b_lo = b_row;
+            for (int cc = 0; cc < p.n_cchunks; ++cc, a_lo += chunk16, b_lo += slab16) {
+#pragma unroll
+              for (int k = 0; k < 4; ++k) {
+                umma_cg<1, KIND>(d_tmem, desc_hi | (a_lo + 2u * k), desc_hi | (b_lo + b_step16 * k), idesc, accum);
+                accum = 1u;
+              }
+            }
+          }
+        } else {
           uint32_t b_lo = (sFilt >> 4) | b_lo_fixed;
           uint32_t a_row = ((sStrip + buf * strip_total) >> 4) | a_lo_fixed;
           int tap = 0;
@@ -311,7 +359,7 @@ hb_conv_strip_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_cons
     // ------------------------------ epilogue ----------------------------------------------
     const int q = warp & 3;
     int acc = 0;
-    uint32_t acc_phase = 0, stage_phase = 0, free_phase = 0;
+    uint32_t acc_phase = 0, stage_phase = 0, free_phase = 0, xch_phase = 0;
     bool ok = true;
     bool copies_pending = false;
     const bool copier = threadIdx.x == 64;         // lane 0 of the first epilogue warp issues the TMA stores
@@ -338,7 +386,37 @@ hb_conv_strip_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_cons
       }
       tc_fence_after();
       const uint32_t t_addr =
-          tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(acc * p.CO);
+          tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(acc * p.acc_cols);
+      // fused form: this tile's exchange rows of this warp and of the next one (the last warp's
+      // last two lanes are never output pixels; they read the first warp's rows and drop the sum)
+      float* const xch_mine = xch_base + ((xch_phase * kEpiWarps + q) * kStripXchRows) * p.CO;
+      const float* const xch_next = xch_base + ((xch_phase * kEpiWarps + ((q + 1) & 3)) * kStripXchRows) * p.CO;
+      if constexpr (FUSE) {
+        for (int c = 0; c < p.CO; c += 32) {
+          uint32_t v[32];
+          tmem_ld_32x32(t_addr + p.CO + c, v);
+          tmem_ld_wait();
+          // (rows of the exchange are CO * 4 = 256 bytes and start 256-byte aligned: vector stores)
+          if (lane == 0) {
+            uint4* dst = reinterpret_cast<uint4*>(xch_mine + c);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) dst[i] = make_uint4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+          }
+          tmem_ld_32x32(t_addr + 2 * p.CO + c, v);
+          tmem_ld_wait();
+          if (lane < 2) {
+            uint4* dst = reinterpret_cast<uint4*>(xch_mine + (1 + lane) * p.CO + c);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) dst[i] = make_uint4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+          }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&bars->xch));
+        if (!mbar_wait(smem_u32(&bars->xch), xch_phase, wctx)) {
+          ok = false;
+          break;
+        }
+      }
       uint8_t* orow = static_cast<uint8_t*>(p.out) +
                       ((static_cast<long long>(n) * p.HO + y) * p.WO + px) * p.CO * OUT_BYTES;
 #ifdef HB_PROBES
@@ -364,12 +442,43 @@ hb_conv_strip_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_cons
       for (int c0 = 0; c0 < p.CO; c0 += kColsPerStep) {
         uint32_t v[32];
         uint32_t packed[32];
-        tmem_ld_32x32(t_addr + c0, v);
-        tmem_ld_wait();
-        if (OUT_BYTES == 4) {
+        if constexpr (FUSE) {
+#pragma unroll
+          for (int h = 0; h < kColsPerStep / 16; ++h) {
+            const int c = c0 + 16 * h;
+            uint32_t g0[16], g1[16], g2[16];
+            tmem_ld_32x16(t_addr + c, g0);
+            tmem_ld_32x16(t_addr + p.CO + c, g1);
+            tmem_ld_32x16(t_addr + 2 * p.CO + c, g2);
+            tmem_ld_wait();
+            float s[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              float a1 = __shfl_down_sync(0xffffffffu, __uint_as_float(g1[i]), 1);
+              float a2 = __shfl_down_sync(0xffffffffu, __uint_as_float(g2[i]), 2);
+              if (lane == 31) a1 = xch_next[c + i];
+              if (lane >= 30) a2 = xch_next[(1 + lane - 30) * p.CO + c + i];
+              s[i] = (__uint_as_float(g0[i]) + a1) + a2;
+            }
+            if (OUT_BYTES == 4) {
+#pragma unroll
+              for (int i = 0; i < 16; ++i) packed[(16 * h + i) % 32] = __float_as_uint(s[i]);
+            } else {
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                __half2 hh = __floats2half2_rn(s[2 * i], s[2 * i + 1]);
+                packed[(8 * h + i) % 32] = *reinterpret_cast<uint32_t*>(&hh);
+              }
+            }
+          }
+        } else if (OUT_BYTES == 4) {
+          tmem_ld_32x32(t_addr + c0, v);
+          tmem_ld_wait();
 #pragma unroll
           for (int i = 0; i < 32; ++i) packed[i] = v[i];
         } else {
+          tmem_ld_32x32(t_addr + c0, v);
+          tmem_ld_wait();
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
             __half2 h = __floats2half2_rn(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1]));
@@ -441,6 +550,7 @@ hb_conv_strip_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_cons
         stage_phase ^= 1u;
         ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;  // (the copier's verdict counts for its warp)
       }
+      if (FUSE) xch_phase ^= 1u;
       if (++acc == 2) {
         acc = 0;
         acc_phase ^= 1u;

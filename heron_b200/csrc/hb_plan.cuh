@@ -372,7 +372,11 @@ int run_main(const hb_plan* plan, cudaStream_t stream) {
     cfg.attrs = &attr;
     cfg.numAttrs = 1;
     cudaError_t e;
-    if (sp.esize_out == 2)
+    if (sp.fuse_kw)
+      e = sp.esize_out == 2
+              ? cudaLaunchKernelEx(&cfg, hb::hb_conv_strip_kernel<2, 0, 1>, plan->tmA, plan->tmB, plan->tmC, sp)
+              : cudaLaunchKernelEx(&cfg, hb::hb_conv_strip_kernel<4, 0, 1>, plan->tmA, plan->tmB, plan->tmC, sp);
+    else if (sp.esize_out == 2)
       e = cudaLaunchKernelEx(&cfg, hb::hb_conv_strip_kernel<2, 0>, plan->tmA, plan->tmB, plan->tmC, sp);
     else if (sp.esize_in == 2)
       e = cudaLaunchKernelEx(&cfg, hb::hb_conv_strip_kernel<4, 0>, plan->tmA, plan->tmB, plan->tmC, sp);

@@ -13,9 +13,12 @@ int conv_out_extent(int in, int k, int stride, int pad, int dil) {
 
 
 
-// Shared-memory need of the strip algorithm for a geometry, or 0 when it does not apply.
-int strip_smem_bytes(const ConvGeom& g, int es, int eo, hb::StripParams* sp) {
+// Shared-memory need of the strip algorithm for a geometry, or 0 when it does not apply.  `fuse`:
+// the form whose MMAs take the three taps of a filter row at once (fp16, 64 output channels,
+// KW = 3, no dilation along W).
+int strip_smem_bytes(const ConvGeom& g, int es, int eo, hb::StripParams* sp, bool fuse = false) {
   if (g.stride_h != 1 || g.stride_w != 1) return 0;
+  if (fuse && (es != 2 || g.CO * es != 128 || g.KW != 3 || g.dil_w != 1)) return 0;
   if ((g.CI * es) % 128 != 0 || (g.CO * es) % 128 != 0) return 0;
   if (g.CO > 256 || g.CO % (128 / eo) != 0 || g.CO % 16 != 0) return 0;
   const int Wp = g.W + 2 * g.pad_w;
@@ -30,6 +33,7 @@ int strip_smem_bytes(const ConvGeom& g, int es, int eo, hb::StripParams* sp) {
   const int n_cchunks = g.CI * es / 128;
   const long long filt = static_cast<long long>(g.KH) * g.KW * g.CI * g.CO * es;
   long long smem = ((filt + 1023) & ~1023LL) + 2LL * n_cchunks * strip_bytes + 1024 + 512;
+  if (fuse) smem += hb::strip_xch_bytes(g.CO);
   if (smem > kSmemLimit) return 0;
   // Staged epilogue (row-major output): one squeezed [R][WO] tile of 128-byte rows per 128-byte
   // channel chunk of the output, sent out by TMA.  It takes precedence over a deeper strip ring.
@@ -47,6 +51,7 @@ int strip_smem_bytes(const ConvGeom& g, int es, int eo, hb::StripParams* sp) {
     sp->Wp = Wp; sp->R = R; sp->strip_rows = strip_rows; sp->strip_bytes = strip_bytes;
     sp->n_cchunks = n_cchunks; sp->groups = (g.HO + R - 1) / R;
     sp->staged = staged ? 1 : 0; sp->stage_chunk_bytes = stage_chunk;
+    sp->fuse_kw = fuse ? 1 : 0; sp->acc_cols = fuse ? g.KW * g.CO : g.CO;
   }
   return static_cast<int>(smem);
 }
@@ -57,17 +62,18 @@ int build_strip_plan(Driver& d, const ConvGeom& g, hb_dtype in_a, hb_dtype in_w,
   if (g_plan_owns_flags) release_split_flags(plan->p.flags, plan->owned_flags);
   std::memset(plan, 0, sizeof(*plan));
   hb::StripParams& sp = plan->sp;
-  const int smem = strip_smem_bytes(g, es, eo, &sp);
-  if (smem == 0) return HB_ERR_KNOB;
+  const bool fuse = k.conv_algo == 4;
+  const int smem = strip_smem_bytes(g, es, eo, &sp, fuse);
+  if (smem == 0 || (fuse && in_w != HB_F16)) return HB_ERR_KNOB;
   const long long tiles = static_cast<long long>(g.N) * sp.groups;
   if (tiles > 0x7fffffffLL) return HB_ERR_SHAPE;
   sp.N = g.N; sp.H = g.H; sp.W = g.W; sp.CI = g.CI; sp.CO = g.CO; sp.KH = g.KH; sp.KW = g.KW;
   sp.pad_h = g.pad_h; sp.pad_w = g.pad_w; sp.dil_h = g.dil_h; sp.dil_w = g.dil_w; sp.HO = g.HO; sp.WO = g.WO;
   sp.num_tiles = static_cast<int>(tiles);
   sp.esize_in = es; sp.esize_out = eo;
-  sp.tmem_cols = next_pow2_cols(2 * g.CO);
+  sp.tmem_cols = next_pow2_cols(2 * sp.acc_cols);
   const int kind = mma_kind(in_a, in_w, out_t);
-  sp.idesc = make_idesc(kind, in_a, in_w, hb::kTileM, g.CO, true);
+  sp.idesc = make_idesc(kind, in_a, in_w, hb::kTileM, sp.acc_cols, true);
   sp.out = out;
   sp.out_nchw = g.out_nchw ? 1 : 0;
   sp.probe = k.probe;
@@ -107,9 +113,9 @@ int build_strip_plan(Driver& d, const ConvGeom& g, hb_dtype in_a, hb_dtype in_w,
   plan->grid = grid;
   plan->smem = smem;
   plan->knobs = k;
-  plan->knobs.conv_algo = 2;
+  plan->knobs.conv_algo = fuse ? 4 : 2;
   // fields hb_plan_knobs reports
-  plan->knobs.tile_n = g.CO; plan->knobs.swizzle_bytes = 128; plan->knobs.stages = sp.ring;
+  plan->knobs.tile_n = sp.acc_cols; plan->knobs.swizzle_bytes = 128; plan->knobs.stages = sp.ring;
   plan->knobs.acc_stages = 2; plan->knobs.cta_group = 1; plan->knobs.epilogue = 2; plan->knobs.epi_warps = hb::kEpiWarps;
   // the packed-filter wrapper reads these from the GEMM-view parameter block
   plan->p.N = g.CO; plan->p.KW = g.KW; plan->p.CI = g.CI; plan->p.esize_out = eo;
@@ -166,7 +172,7 @@ int plan_conv(const void* in, const void* w, void* out, int N, int H, int W, int
   // only the im2col kernel reads through custom strides or walks a third spatial axis
   const bool strided_view = cg.w_stride > 0 || is_3d(cg);
   const int algo = knobs ? knobs->conv_algo : 0;
-  if (algo < 0 || algo > 3 || (algo >= 2 && strided_view)) return HB_ERR_KNOB;
+  if (algo < 0 || algo > 4 || (algo >= 2 && strided_view)) return HB_ERR_KNOB;
   {
     // The wide strip kernel (channels on M, 256 positions on N): asked for, or picked when it applies,
     // the filter has more than one tap and the reduction is short enough that operand traffic, not
@@ -192,9 +198,15 @@ int plan_conv(const void* in, const void* w, void* out, int N, int H, int W, int
     const bool rows_used = fits && static_cast<long long>(HO) * probe.Wp * 4 >= static_cast<long long>(probe.groups) * 128 * 3;
     const bool wanted = algo == 2 || (KH * KW > 1 && rows_used && K * es <= 2048);
     if (algo == 2 && !fits) return HB_ERR_KNOB;
+    if (algo == 4) {
+      if (in_w != HB_F16 || strip_smem_bytes(cg, es, esize(out_t), nullptr, true) == 0) return HB_ERR_KNOB;
+      hb_knobs k0 = *knobs;
+      return build_strip_plan(d, cg, in_a, in_w, out_t, k0, in, w, out, plan);
+    }
     if (fits && wanted) {
       hb_knobs k0;
       if (knobs) k0 = *knobs; else std::memset(&k0, 0, sizeof(k0));
+      k0.conv_algo = 2;
       return build_strip_plan(d, cg, in_a, in_w, out_t, k0, in, w, out, plan);
     }
   }

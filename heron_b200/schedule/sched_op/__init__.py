@@ -194,10 +194,12 @@ class epilogueOp(SchedOp):
 
 class convAlgoOp(SchedOp):
     """conv only: implicit GEMM with one im2col TMA per tap (1), resident filter + one padded
-    input strip per tile (2), or the same with the output channels on the MMA's M axis and 256
-    positions on N (3).  The second exists only for stride-1 problems whose filter and two strips
-    fit shared memory and whose padded width fits the 128 MMA rows, the third for fp16 problems
-    with 64 or 128 output channels whose filter, strips and output tile fit."""
+    input strip per tile (2), the same with the output channels on the MMA's M axis and 256
+    positions on N (3), or the second with the three taps of a filter row taken by one MMA (4).
+    The second exists only for stride-1 problems whose filter and two strips fit shared memory and
+    whose padded width fits the 128 MMA rows, the third for fp16 problems with 64 or 128 output
+    channels whose filter, strips and output tile fit, the fourth for fp16 problems with 64 output
+    channels and an undilated three-tap filter row."""
 
     def perform(self, s, stage_name, ctx):
         km = ctx.knob_manager
@@ -208,10 +210,16 @@ class convAlgoOp(SchedOp):
         algo = genKey("P", stage_name, "m", param_name="conv_algo")
         if km.is_building:
             es, eo = ELEM_BYTES[p["in_dtype"]], ELEM_BYTES[p["out_dtype"]]
-            most = 3 if strip_wide_applies(p, es, eo, ctx.limits) else (2 if strip_applies(p, es, eo, ctx.limits) else 1)
-            km.define_value(algo, 1, most, 1, True)
-            if most == 3 and not strip_applies(p, es, eo, ctx.limits):
-                km.addCandidates(algo, [1, 3])
+            cands = [1]
+            if strip_applies(p, es, eo, ctx.limits):
+                cands.append(2)
+            if strip_wide_applies(p, es, eo, ctx.limits):
+                cands.append(3)
+            if strip_fused_applies(p, es, eo, ctx.limits):
+                cands.append(4)
+            km.define_value(algo, 1, cands[-1], 1, True)
+            if cands != list(range(1, cands[-1] + 1)):
+                km.addCandidates(algo, cands)
         ctx.kernel_knobs["conv_algo"] = km.get_val(algo)
         ctx.addSchedDesc("## conv algorithm %s\n" % ctx.kernel_knobs["conv_algo"])
 
@@ -236,6 +244,15 @@ def strip_applies(p, es, eo, limits):
     strip_bytes = (px * 128 + 1023) // 1024 * 1024
     filt = (KH * KW * CI * CO * es + 1023) // 1024 * 1024
     return filt + 2 * (CI * es // 128) * strip_bytes + 1024 + 512 <= limits["max_shared_memory_per_block"]
+
+
+def strip_fused_applies(p, es, eo, limits):
+    """The fused-row form of the strip kernel (mirrors the library's check): the strip kernel's own
+    rule with the exchange buffer added, fp16, 64 output channels, KW = 3, no dilation along W."""
+    if p["in_dtype"] != "float16" or p["CO"] != 64 or p["KW"] != 3 or p["dilation"][1] != 1:
+        return False
+    shrunk = dict(limits, max_shared_memory_per_block=limits["max_shared_memory_per_block"] - 2 * 4 * 3 * 64 * 4)
+    return strip_applies(p, es, eo, shrunk)
 
 
 def strip_wide_applies(p, es, eo, limits):

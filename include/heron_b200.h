@@ -70,7 +70,10 @@ typedef struct {
                         filter + one padded input strip per tile (stride 1, filter fits shared
                         memory, padded width <= 128); 3: the same with the operands' places changed:
                         output channels on the MMA's M axis (64 or 128 of them), 256 consecutive
-                        output positions on N (fp16, stride 1); 0 = library picks                  */
+                        output positions on N (fp16, stride 1); 4: algorithm 2 with the three taps
+                        of a filter row taken by one MMA of 192 columns, the epilogue adding the
+                        column groups shifted by one and two pixels (fp16, 64 output channels,
+                        KW = 3, no dilation along W); 0 = library picks                            */
   int tail_split;    /* the tiles of the last, partly filled wave of the persistent grid are cut into
                         this many column slices (1, 2 or 4); 0 = library picks                      */
   int split_k;       /* work items that do not fill a wave of the persistent grid (the tiles of the
