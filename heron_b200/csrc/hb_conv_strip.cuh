@@ -50,7 +50,8 @@ struct StripParams {
   int ring;   // strip buffers in flight (2..kMaxStripRing)
   long long wait_limit_cycles;
   int probe;  // diagnostic modes of -DHB_PROBES builds: 2 = no MMAs, 3 = the epilogue only hands the accumulator
-              // back, 4 = strips loaded once, 9 = the tile's MMAs on fixed descriptors (and 3)
+              // back, 4 = strips loaded once, 9 = the tile's MMAs on fixed descriptors (and 3); fused form
+              // only: 5 = no boundary exchange, 6 = no shifted adds, 7 = no staging writes and no TMA stores
   uint32_t idesc;
   void* out;
   int out_nchw;  // output is (N, CO, HO, WO) instead of (N, HO, WO, CO)
@@ -60,19 +61,24 @@ struct StripParams {
   int acc_cols;  // TMEM columns from one accumulator to the other: CO, or KW * CO when fused
 };
 
-// Shared memory of the fused form's boundary exchange: per tile parity, per epilogue warp, the
-// second and third column groups of the warp's first position and the third of its second.
+// Shared memory of the fused form's boundary exchange: per warp group and tile parity, per 32
+// TMEM lanes, the second and third column groups of their first position and the third of
+// their second (two parities: a fast warp publishes for the group's next tile while a slow one
+// still reads this tile's rows).
 constexpr int kStripXchRows = 3;
-__host__ __device__ constexpr int strip_xch_bytes(int co) { return 2 * kEpiWarps * kStripXchRows * co * 4; }
+constexpr int kStripFusedEpiWarps = 8;  // two groups of four: one drains a tile while the other drains the next
+constexpr int kStripFusedThreads = 32 * (2 + kStripFusedEpiWarps);
+__host__ __device__ constexpr int strip_xch_bytes(int co) { return 2 * 2 * 4 * kStripXchRows * co * 4; }
 
 
 constexpr int kStripFiltBars = 16;  // filter taps with a barrier of their own (later taps share the last)
 
 struct StripBars {
   uint64_t filt_full[kStripFiltBars];
-  uint64_t stage;       // the epilogue warps: "my pixels of this tile are in the staging buffer"
-  uint64_t stage_free;  // the copying thread: "the TMA stores have read the staging buffer"
-  uint64_t xch;         // fused form: "my first positions' column groups of this tile are published"
+  // (one of each per epilogue warp group: the fused form has two groups that take tiles in turn)
+  uint64_t stage[2];       // the epilogue warps: "my pixels of this tile are in the staging buffer"
+  uint64_t stage_free[2];  // the copying thread: "the TMA stores have read the staging buffer"
+  uint64_t xch[2];         // fused form: "my first positions' column groups of this tile are published"
   uint64_t strip_full[kMaxStripRing];
   uint64_t strip_empty[kMaxStripRing];
   uint64_t tmem_full[2];
@@ -114,7 +120,7 @@ __device__ __forceinline__ void tma_store_4d(const CUtensorMap* m, uint32_t src,
 // positions from a small shared-memory exchange (double-buffered by tile parity, published
 // behind an mbarrier so that the wait is bounded like every other).
 template <int OUT_BYTES, int KIND, int FUSE = 0>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(FUSE ? kStripFusedThreads : kThreads, 1)
 hb_conv_strip_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constant__ CUtensorMap tmW,
                      const __grid_constant__ CUtensorMap tmOut, const StripParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -131,7 +137,8 @@ hb_conv_strip_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_cons
   const uint32_t sStage = sStrip + p.ring * strip_total;  // 1024-byte aligned: strips are multiples of 1024
   const int n_ochunks = p.CO * OUT_BYTES / 128;           // 128-byte channel chunks of an output pixel
   const int stage_bytes = p.staged ? n_ochunks * p.stage_chunk_bytes : 0;
-  StripBars* bars = reinterpret_cast<StripBars*>(smem + (sStage - smem_base) + stage_bytes);
+  // (the fused form has a staging buffer per epilogue warp group)
+  StripBars* bars = reinterpret_cast<StripBars*>(smem + (sStage - smem_base) + (FUSE ? 2 : 1) * stage_bytes);
   float* const xch_base = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(bars) + 512);  // fused form only
   volatile int* abort_flag = &bars->abort_flag;
   const WaitCtx wctx{abort_flag, p.wait_limit_cycles > 0 ? p.wait_limit_cycles : HB_WAIT_LIMIT_CYCLES};
@@ -141,9 +148,11 @@ hb_conv_strip_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_cons
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < kStripFiltBars; ++i) mbar_init(smem_u32(&bars->filt_full[i]), 1);
-    mbar_init(smem_u32(&bars->stage), kEpiWarps);
-    mbar_init(smem_u32(&bars->stage_free), 1);
-    mbar_init(smem_u32(&bars->xch), kEpiWarps);
+    for (int g = 0; g < 2; ++g) {
+      mbar_init(smem_u32(&bars->stage[g]), kEpiWarps);
+      mbar_init(smem_u32(&bars->stage_free[g]), 1);
+      mbar_init(smem_u32(&bars->xch[g]), kEpiWarps);
+    }
     static_assert(sizeof(bars->strip_full) == kMaxStripRing * sizeof(uint64_t) &&
                       sizeof(bars->strip_empty) == kMaxStripRing * sizeof(uint64_t),
                   "every ring barrier below is initialised");
@@ -358,23 +367,38 @@ hb_conv_strip_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_cons
   } else {
     // ------------------------------ epilogue ----------------------------------------------
     const int q = warp & 3;
-    int acc = 0;
+    // Fused form: two groups of four warps; group g drains the CTA's tiles g, g + 2, ... from
+    // accumulator g into its own staging buffer, so one tile's drain overlaps the next one's.
+    const int grp = FUSE ? (warp - 2) >> 2 : 0;
+    int acc = grp;
     uint32_t acc_phase = 0, stage_phase = 0, free_phase = 0, xch_phase = 0;
     bool ok = true;
     bool copies_pending = false;
-    const bool copier = threadIdx.x == 64;         // lane 0 of the first epilogue warp issues the TMA stores
+    const bool copier = threadIdx.x == 64 + 128 * grp;  // lane 0 of the group's first warp issues the TMA stores
+    const uint32_t sStageG = sStage + static_cast<uint32_t>(grp * stage_bytes);
     constexpr int kColsPerStep = 128 / OUT_BYTES;  // 32 or 64 output channels = 128 bytes
     const int pos = q * 32 + lane;                 // padded-linear position inside the tile
     const int py = pos / p.Wp;
     const int px = pos - py * p.Wp;
     const int r2 = py * p.WO + px;                 // the pixel's row in the squeezed [R][WO] staging tile
-    const uint32_t stage_bar = smem_u32(&bars->stage), free_bar = smem_u32(&bars->stage_free);
-    for (int t = blockIdx.x; ok && t < p.num_tiles; t += gridDim.x) {
+    const uint32_t stage_bar = smem_u32(&bars->stage[grp]), free_bar = smem_u32(&bars->stage_free[grp]);
+    const uint32_t xch_bar = smem_u32(&bars->xch[grp]);
+    auto next_acc = [&]() {
+      if (FUSE) {
+        acc_phase ^= 1u;  // (a group keeps its accumulator)
+      } else if (++acc == 2) {
+        acc = 0;
+        acc_phase ^= 1u;
+      }
+    };
+    int it = 0;
+    for (int t = blockIdx.x; ok && t < p.num_tiles; t += gridDim.x, ++it) {
+      if (FUSE && (it & 1) != grp) continue;
       const int n = t / p.groups;
       const int y0 = (t - n * p.groups) * p.R;
       const int y = y0 + py;
       const bool valid = py < p.R && y < p.HO && px < p.WO;
-      if (copier && copies_pending) {
+      if (!FUSE && copier && copies_pending) {
         // the previous tile's stores have read the staging buffer: it may be overwritten
         bulk_wait_read<0>();
         mbar_arrive(free_bar);
@@ -389,34 +413,8 @@ hb_conv_strip_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_cons
           tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(acc * p.acc_cols);
       // fused form: this tile's exchange rows of this warp and of the next one (the last warp's
       // last two lanes are never output pixels; they read the first warp's rows and drop the sum)
-      float* const xch_mine = xch_base + ((xch_phase * kEpiWarps + q) * kStripXchRows) * p.CO;
-      const float* const xch_next = xch_base + ((xch_phase * kEpiWarps + ((q + 1) & 3)) * kStripXchRows) * p.CO;
-      if constexpr (FUSE) {
-        for (int c = 0; c < p.CO; c += 32) {
-          uint32_t v[32];
-          tmem_ld_32x32(t_addr + p.CO + c, v);
-          tmem_ld_wait();
-          // (rows of the exchange are CO * 4 = 256 bytes and start 256-byte aligned: vector stores)
-          if (lane == 0) {
-            uint4* dst = reinterpret_cast<uint4*>(xch_mine + c);
-#pragma unroll
-            for (int i = 0; i < 8; ++i) dst[i] = make_uint4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
-          }
-          tmem_ld_32x32(t_addr + 2 * p.CO + c, v);
-          tmem_ld_wait();
-          if (lane < 2) {
-            uint4* dst = reinterpret_cast<uint4*>(xch_mine + (1 + lane) * p.CO + c);
-#pragma unroll
-            for (int i = 0; i < 8; ++i) dst[i] = make_uint4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
-          }
-        }
-        __syncwarp();
-        if (lane == 0) mbar_arrive(smem_u32(&bars->xch));
-        if (!mbar_wait(smem_u32(&bars->xch), xch_phase, wctx)) {
-          ok = false;
-          break;
-        }
-      }
+      float* const xch_mine = xch_base + (((grp * 2 + xch_phase) * 4 + q) * kStripXchRows) * p.CO;
+      const float* const xch_next = xch_base + (((grp * 2 + xch_phase) * 4 + ((q + 1) & 3)) * kStripXchRows) * p.CO;
       uint8_t* orow = static_cast<uint8_t*>(p.out) +
                       ((static_cast<long long>(n) * p.HO + y) * p.WO + px) * p.CO * OUT_BYTES;
 #ifdef HB_PROBES
@@ -424,14 +422,11 @@ hb_conv_strip_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_cons
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&bars->tmem_empty[acc]));
-        if (++acc == 2) {
-          acc = 0;
-          acc_phase ^= 1u;
-        }
+        next_acc();
         continue;
       }
 #endif
-      if (p.staged) {
+      if (!FUSE && p.staged) {
         // (free_phase counts tiles: the buffer starts out free, so the first wait passes at once)
         if (!mbar_wait(free_bar, free_phase ^ 1u, wctx)) {
           ok = false;
@@ -439,39 +434,153 @@ hb_conv_strip_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_cons
         }
         free_phase ^= 1u;
       }
-      for (int c0 = 0; c0 < p.CO; c0 += kColsPerStep) {
-        uint32_t v[32];
-        uint32_t packed[32];
-        if constexpr (FUSE) {
+      if constexpr (FUSE) {
+        // out[pos] = G0[pos] + G1[pos + 1] + G2[pos + 2].  Shuffles inside the warp; its last two
+        // lanes need the next warp's first two positions: every warp first puts the second and
+        // third column groups of its own first two positions into the exchange rows of its 32
+        // lanes, the group meets at a barrier, and every lane reads the next warp's rows (one or
+        // two addresses per instruction: broadcasts) and selects without a branch: a divergent
+        // branch per channel costs more than the rest of the drain.  (Publishing from the registers
+        // of the main pass instead, with a barrier per half, measured 1.7 us slower on the
+        // 56 x 56 x 64 layer: the group waits twice.)
+        uint32_t g0[32], g1[32], g2[32];
+#ifdef HB_PROBES
+        // diagnostics (wrong results): 5 = no boundary exchange, 6 = no shifted adds, 7 = no staging
+        // writes and no TMA stores
+        if (p.probe != 5)
+#endif
 #pragma unroll
-          for (int h = 0; h < kColsPerStep / 16; ++h) {
-            const int c = c0 + 16 * h;
-            uint32_t g0[16], g1[16], g2[16];
-            tmem_ld_32x16(t_addr + c, g0);
-            tmem_ld_32x16(t_addr + p.CO + c, g1);
-            tmem_ld_32x16(t_addr + 2 * p.CO + c, g2);
-            tmem_ld_wait();
-            float s[16];
+        for (int cb = 0; cb < 64; cb += 32) {
+          tmem_ld_32x32(t_addr + p.CO + cb, g1);
+          tmem_ld_32x32(t_addr + 2 * p.CO + cb, g2);
+          tmem_ld_wait();
+          // (rows of the exchange are CO * 4 = 256 bytes and start 256-byte aligned: vector stores)
+          if (lane == 0) {
+            uint4* dst = reinterpret_cast<uint4*>(xch_mine + cb);
 #pragma unroll
-            for (int i = 0; i < 16; ++i) {
-              float a1 = __shfl_down_sync(0xffffffffu, __uint_as_float(g1[i]), 1);
-              float a2 = __shfl_down_sync(0xffffffffu, __uint_as_float(g2[i]), 2);
-              if (lane == 31) a1 = xch_next[c + i];
-              if (lane >= 30) a2 = xch_next[(1 + lane - 30) * p.CO + c + i];
-              s[i] = (__uint_as_float(g0[i]) + a1) + a2;
+            for (int i = 0; i < 8; ++i) dst[i] = make_uint4(g1[4 * i], g1[4 * i + 1], g1[4 * i + 2], g1[4 * i + 3]);
+          }
+          if (lane < 2) {
+            uint4* dst = reinterpret_cast<uint4*>(xch_mine + (1 + lane) * p.CO + cb);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) dst[i] = make_uint4(g2[4 * i], g2[4 * i + 1], g2[4 * i + 2], g2[4 * i + 3]);
+          }
+        }
+        __syncwarp();
+#ifdef HB_PROBES
+        if (p.probe != 5)
+#endif
+        if (lane == 0) mbar_arrive(xch_bar);
+        // (the first half's columns are in flight while the other warps publish)
+        tmem_ld_32x32(t_addr, g0);
+        tmem_ld_32x32(t_addr + p.CO, g1);
+        tmem_ld_32x32(t_addr + 2 * p.CO, g2);
+        if (copier && copies_pending) {
+          // the stores of this group's previous tile have read its staging buffer (the wait sits
+          // here, behind the exchange, so that it costs the group nothing when the stores are done)
+          bulk_wait_read<0>();
+          mbar_arrive(free_bar);
+          copies_pending = false;
+        }
+#ifdef HB_PROBES
+        if ((p.probe != 5 && !mbar_wait(xch_bar, xch_phase, wctx)) ||
+#else
+        if (!mbar_wait(xch_bar, xch_phase, wctx) ||
+#endif
+            (p.staged && !mbar_wait(free_bar, free_phase ^ 1u, wctx))) {
+          tmem_ld_wait();
+          ok = false;
+          break;
+        }
+        if (p.staged) free_phase ^= 1u;
+        const bool last = lane == 31, last2 = lane >= 30;
+#pragma unroll
+        for (int cb = 0; cb < 64; cb += 32) {
+          const float4* r1 = reinterpret_cast<const float4*>(xch_next + cb);
+          const float4* r2v = reinterpret_cast<const float4*>(xch_next + (1 + (lane & 1)) * p.CO + cb);
+          uint32_t packed[32 * OUT_BYTES / 4];  // this position's 32 channels: 64 or 128 bytes
+          tmem_ld_wait();
+          if (cb == 32) {
+            // Last read of this accumulator: hand it back to the MMA warp at once.
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&bars->tmem_empty[acc]));
+          }
+#pragma unroll
+          for (int i4 = 0; i4 < 8; ++i4) {
+            const float4 u = r1[i4], w = r2v[i4];
+            const float n1[4] = {u.x, u.y, u.z, u.w}, n2[4] = {w.x, w.y, w.z, w.w};
+            float sum[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              const int i = 4 * i4 + k;
+#ifdef HB_PROBES
+              if (p.probe == 6) {
+                sum[k] = __uint_as_float(g0[i]) + __uint_as_float(g1[i]) + __uint_as_float(g2[i]) + n1[k] + n2[k];
+                continue;
+              }
+#endif
+              const float a1 = __shfl_down_sync(0xffffffffu, __uint_as_float(g1[i]), 1);
+              const float a2 = __shfl_down_sync(0xffffffffu, __uint_as_float(g2[i]), 2);
+              sum[k] = (__uint_as_float(g0[i]) + (last ? n1[k] : a1)) + (last2 ? n2[k] : a2);
             }
             if (OUT_BYTES == 4) {
 #pragma unroll
-              for (int i = 0; i < 16; ++i) packed[(16 * h + i) % 32] = __float_as_uint(s[i]);
+              for (int k = 0; k < 4; ++k) packed[(4 * i4 + k) % (32 * OUT_BYTES / 4)] = __float_as_uint(sum[k]);
             } else {
-#pragma unroll
-              for (int i = 0; i < 8; ++i) {
-                __half2 hh = __floats2half2_rn(s[2 * i], s[2 * i + 1]);
-                packed[(8 * h + i) % 32] = *reinterpret_cast<uint32_t*>(&hh);
-              }
+              __half2 h0 = __floats2half2_rn(sum[0], sum[1]), h1 = __floats2half2_rn(sum[2], sum[3]);
+              packed[(2 * i4) % (32 * OUT_BYTES / 4)] = *reinterpret_cast<uint32_t*>(&h0);
+              packed[(2 * i4 + 1) % (32 * OUT_BYTES / 4)] = *reinterpret_cast<uint32_t*>(&h1);
             }
           }
-        } else if (OUT_BYTES == 4) {
+          if (cb == 0) {
+            // (the second half's columns load while the first half is stored)
+            tmem_ld_32x32(t_addr + 32, g0);
+            tmem_ld_32x32(t_addr + p.CO + 32, g1);
+            tmem_ld_32x32(t_addr + 2 * p.CO + 32, g2);
+          }
+          constexpr int kVecs = 32 * OUT_BYTES / 16;  // 16-byte pieces of these 32 channels: 4 or 8
+          const int byte0 = cb * OUT_BYTES;           // where they start in the pixel's output
+#ifdef HB_PROBES
+          if (p.probe == 7) continue;
+#endif
+          if (p.staged) {
+            if (valid) {
+              const uint32_t row_addr =
+                  sStageG + static_cast<uint32_t>((byte0 >> 7) * p.stage_chunk_bytes + r2 * 128);
+              const int j0 = (byte0 & 127) >> 4;
+#pragma unroll
+              for (int j = 0; j < kVecs; ++j) {
+                const uint32_t a = row_addr + (((j0 + j) ^ (r2 & 7)) << 4);
+                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(a), "r"(packed[4 * j]),
+                             "r"(packed[4 * j + 1]), "r"(packed[4 * j + 2]), "r"(packed[4 * j + 3])
+                             : "memory");
+              }
+            }
+          } else if (valid && p.out_nchw) {
+            const long long plane = static_cast<long long>(p.HO) * p.WO;
+            uint8_t* o = static_cast<uint8_t*>(p.out) +
+                         ((static_cast<long long>(n) * p.CO + cb) * plane + static_cast<long long>(y) * p.WO + px) * OUT_BYTES;
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              if (OUT_BYTES == 4)
+                *reinterpret_cast<uint32_t*>(o + i * plane * OUT_BYTES) = packed[i % (32 * OUT_BYTES / 4)];
+              else
+                *reinterpret_cast<uint16_t*>(o + i * plane * OUT_BYTES) =
+                    static_cast<uint16_t>(packed[(i >> 1) % (32 * OUT_BYTES / 4)] >> (16 * (i & 1)));
+            }
+          } else if (valid) {
+#pragma unroll
+            for (int j = 0; j < kVecs; ++j)
+              *reinterpret_cast<uint4*>(orow + byte0 + 16 * j) =
+                  make_uint4(packed[4 * j], packed[4 * j + 1], packed[4 * j + 2], packed[4 * j + 3]);
+          }
+        }
+      }
+      for (int c0 = 0; !FUSE && c0 < p.CO; c0 += kColsPerStep) {
+        uint32_t v[32];
+        uint32_t packed[32];
+        if (OUT_BYTES == 4) {
           tmem_ld_32x32(t_addr + c0, v);
           tmem_ld_wait();
 #pragma unroll
@@ -540,8 +649,11 @@ hb_conv_strip_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_cons
           if (!mbar_wait(stage_bar, stage_phase, wctx)) {
             ok = false;
           } else {
+#ifdef HB_PROBES
+            if (p.probe != 7)
+#endif
             for (int c = 0; c < n_ochunks; ++c)
-              tma_store_4d(&tmOut, sStage + static_cast<uint32_t>(c * p.stage_chunk_bytes), c * kColsPerStep, 0,
+              tma_store_4d(&tmOut, sStageG + static_cast<uint32_t>(c * p.stage_chunk_bytes), c * kColsPerStep, 0,
                            y0, n);
             bulk_commit();
             copies_pending = true;
@@ -551,10 +663,7 @@ hb_conv_strip_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_cons
         ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;  // (the copier's verdict counts for its warp)
       }
       if (FUSE) xch_phase ^= 1u;
-      if (++acc == 2) {
-        acc = 0;
-        acc_phase ^= 1u;
-      }
+      next_acc();
     }
     if (copier) bulk_wait_read<0>();  // shared memory must outlive the stores' reads of it
     __syncwarp();

@@ -363,7 +363,7 @@ int run_main(const hb_plan* plan, cudaStream_t stream) {
     cudaLaunchConfig_t cfg;
     std::memset(&cfg, 0, sizeof(cfg));
     cfg.gridDim = dim3(plan->grid);
-    cfg.blockDim = dim3(hb::kThreads);
+    cfg.blockDim = dim3(sp.fuse_kw ? hb::kStripFusedThreads : hb::kThreads);
     cfg.dynamicSmemBytes = plan->smem;
     cfg.stream = stream;
     cudaLaunchAttribute attr;

@@ -39,8 +39,10 @@ int strip_smem_bytes(const ConvGeom& g, int es, int eo, hb::StripParams* sp, boo
   // channel chunk of the output, sent out by TMA.  It takes precedence over a deeper strip ring.
   const int stage_chunk = (R * g.WO * 128 + 1023) & ~1023;
   const long long stage = static_cast<long long>(g.CO) * eo / 128 * stage_chunk;
-  const bool staged = !g.out_nchw && g.WO <= 256 && R <= 256 && smem + stage <= kSmemLimit;
-  if (staged) smem += stage;
+  // (the fused form drains two tiles at a time: a staging tile per epilogue warp group)
+  const long long stage_all = (fuse ? 2 : 1) * stage;
+  const bool staged = !g.out_nchw && g.WO <= 256 && R <= 256 && smem + stage_all <= kSmemLimit;
+  if (staged) smem += stage_all;
   int ring = 2;  // deeper when shared memory allows: more strips in flight hide HBM latency
   while (ring < hb::kMaxStripRing && smem + static_cast<long long>(n_cchunks) * strip_bytes <= kSmemLimit) {
     smem += static_cast<long long>(n_cchunks) * strip_bytes;

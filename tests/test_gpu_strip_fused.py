@@ -67,8 +67,9 @@ def test_fused_row_strip_random_geometry(K, co, N, H, W, CI, KH, pad, dh, half_o
     try:
         got = k_conv(K, x, w, 1, pad, (dh, 1), out_dtype=od, knobs=dict(conv_algo=4, max_ctas=max_ctas))
     except HeronB200Error as e:
-        # the padded row must fit the 128 MMA rows; a three-row filter over 128 input channels leaves no room for two strips
-        assert e.status == HB_ERR_KNOB and (W + 2 * pad > 128 or (CI == 128 and KH == 3))
+        # the padded row must fit the 128 MMA rows; the filter, two strips of 128 input channels and
+        # the staging tile can exceed shared memory
+        assert e.status == HB_ERR_KNOB and (W + 2 * pad > 128 or (CI == 128 and KH >= 2))
         return
     check(got, co.conv2d_nhwc_f16(x, w, 1, pad, (dh, 1), od), "fused-row strip %s" % ((N, H, W, CI, KH, pad, dh),))
 
