@@ -175,17 +175,44 @@ int plan_conv(const void* in, const void* w, void* out, int N, int H, int W, int
   const bool strided_view = cg.w_stride > 0 || is_3d(cg);
   const int algo = knobs ? knobs->conv_algo : 0;
   if (algo < 0 || algo > 4 || (algo >= 2 && strided_view)) return HB_ERR_KNOB;
+  if (algo == 0 && !strided_view && !out_nchw && in_w == HB_F16 && !(knobs && knobs->silent_producer)) {
+    // The strip kernel's fused-row form: picked where it applies and the filter has at least two
+    // rows; with a 2-byte output where tiles fill three quarters of the MMA rows, with a 4-byte
+    // output up to a padded width of 100.  Measured on a B200, 3x3, 64 -> 64 channels, fp16 out
+    // (im2col / strip / wide strip / fused, us): 32 x 56 x 56: 24.2 / 18.7 / 15.5 / 14.2;
+    // 64 x 28 x 28: 14.0 / 12.2 / 12.2 / 9.8; 16 x 96 x 96: 31.2 / 26.7 / 20.4 / 18.8;
+    // 16 x 112 x 112: 41.6 / 30.6 / 51.4 / 21.2; but 32 x 64 x 64 (half of the MMA rows idle):
+    // 27.8 / 32.6 / 18.5 / 21.9 and 16 x 80 x 80: 24.3 / 22.7 / 15.6 / 16.8.  fp32 out:
+    // 32 x 56 x 56: 25.4 / 18.0 / 19.7 / 15.1; 16 x 80 x 80: 25.6 / 21.7 / 20.5 / 17.7;
+    // 16 x 96 x 96: 32.6 / 25.5 / 38.7 / 20.5; but 16 x 112 x 112: 43.3 / 29.6 / 51.8 / 35.1.
+    // A one-row filter is level with the strip kernel.
+    hb::StripParams pf;
+    std::memset(&pf, 0, sizeof(pf));
+    const int eo = esize(out_t);
+    const bool fits_f = strip_smem_bytes(cg, es, eo, &pf, true) != 0;
+    const bool rows_used = fits_f && static_cast<long long>(HO) * pf.Wp * 4 >= static_cast<long long>(pf.groups) * 128 * 3;
+    if (fits_f && KH >= 2 && K * es <= 2048 && (eo == 2 ? rows_used : pf.Wp <= 100)) {
+      hb_knobs k0;
+      if (knobs) k0 = *knobs; else std::memset(&k0, 0, sizeof(k0));
+      k0.conv_algo = 4;
+      return build_strip_plan(d, cg, in_a, in_w, out_t, k0, in, w, out, plan);
+    }
+  }
   {
     // The wide strip kernel (channels on M, 256 positions on N): asked for, or picked when it applies,
     // the filter has more than one tap and the reduction is short enough that operand traffic, not
     // tensor time, bounds the layer (measured on the 56 x 56 x 64 -> 64 layer: 14.6 us against 18.2 us
-    // for the strip kernel and 23.8 us for the im2col kernel).
+    // for the strip kernel and 23.8 us for the im2col kernel).  Not picked for padded rows wider
+    // than 90 pixels (a strip of 256 positions plus the taps' reach is then many image rows:
+    // 16 x 112 x 112 x 64 -> 64 measured 51.4 us against 30.6 us for the strip kernel), nor for
+    // 64 output channels with a 4-byte output (19.7 against 18.0 us on the 56 x 56 layer).
     hb_knobs k0;
     if (knobs) k0 = *knobs; else std::memset(&k0, 0, sizeof(k0));
     const bool fits_t = !strided_view && !out_nchw && in_w == HB_F16 && !k0.silent_producer &&
                         strip_t_smem_bytes(cg, in_a, out_t, nullptr, k0.tile_n > 0 && algo == 3 ? k0.tile_n : 256) != 0;
+    const bool wide_pays = W + 2 * pad_w <= 90 && (CO != 64 || esize(out_t) == 2);
     if (algo == 3 && !fits_t) return HB_ERR_KNOB;
-    if (algo == 3 || (algo == 0 && fits_t && KH * KW > 1 && K * es <= 2048)) {
+    if (algo == 3 || (algo == 0 && fits_t && wide_pays && KH * KW > 1 && K * es <= 2048)) {
       if (algo == 0) k0.tile_n = 0;  // (tile_n is the GEMM kernels' knob unless this kernel was asked for)
       return build_strip_t_plan(d, cg, in_a, in_w, out_t, k0, in, w, out, plan);
     }

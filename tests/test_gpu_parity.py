@@ -888,7 +888,20 @@ def test_conv_strip_refused_when_it_does_not_apply(K):
 def test_default_picks_a_strip_kernel_for_resnet_stage2(K):
     x = torch.zeros(8, 56, 56, 64, dtype=torch.float16, device="cuda")
     w = torch.zeros(3, 3, 64, 64, dtype=torch.float16, device="cuda")
-    assert K.plan_conv2d_nhwc(x, w, 1, 1, 1).knobs()["conv_algo"] == 3   # fp16, 64 channels out: the wide one
+    assert K.plan_conv2d_nhwc(x, w, 1, 1, 1).knobs()["conv_algo"] == 4   # fp16, 64 channels out, 3x3: filter rows fused
+    assert K.plan_conv2d_nhwc(x, w, 1, 1, 1, out_dtype=torch.float32).knobs()["conv_algo"] == 4
+    xw = torch.zeros(2, 112, 112, 64, dtype=torch.float16, device="cuda")
+    assert K.plan_conv2d_nhwc(xw, w, 1, 1, 1, out_dtype=torch.float16).knobs()["conv_algo"] == 4
+    # (one image row per tile and a 4-byte output: the plain strip kernel)
+    assert K.plan_conv2d_nhwc(xw, w, 1, 1, 1, out_dtype=torch.float32).knobs()["conv_algo"] == 2
+    w22 = torch.zeros(2, 2, 64, 64, dtype=torch.float16, device="cuda")
+    assert K.plan_conv2d_nhwc(x, w22, 1, 1, 1, out_dtype=torch.float16).knobs()["conv_algo"] == 3  # not a three-tap row: the wide one
+    x80 = torch.zeros(2, 80, 80, 64, dtype=torch.float16, device="cuda")
+    assert K.plan_conv2d_nhwc(x80, w, 1, 1, 1, out_dtype=torch.float16).knobs()["conv_algo"] == 3  # 64 % of the MMA rows: the wide one
+    assert K.plan_conv2d_nhwc(x80, w, 1, 1, 1, out_dtype=torch.float32).knobs()["conv_algo"] == 4
+    w128 = torch.zeros(3, 3, 64, 128, dtype=torch.float16, device="cuda")
+    x28 = torch.zeros(4, 28, 28, 64, dtype=torch.float16, device="cuda")
+    assert K.plan_conv2d_nhwc(x28, w128, 1, 1, 1, out_dtype=torch.float16).knobs()["conv_algo"] == 3  # 128 channels out: the wide one
     xi = torch.zeros(4, 28, 28, 128, dtype=torch.uint8, device="cuda")
     wi = torch.zeros(3, 3, 128, 128, dtype=torch.int8, device="cuda")
     assert K.plan_conv2d_nhwc(xi, wi, 1, 1, 1).knobs()["conv_algo"] == 2  # integer operands: pixels on M
