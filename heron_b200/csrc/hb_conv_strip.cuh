@@ -118,7 +118,9 @@ __device__ __forceinline__ void tma_store_4d(const CUtensorMap* m, uint32_t src,
 // 128 x 192 x 16 products instead of 6 KB for 128 x 64 x 16.  Positions are TMEM lanes: the
 // epilogue shifts with warp shuffles, and a warp's last two lanes take the next warp's first two
 // positions from a small shared-memory exchange (double-buffered by tile parity, published
-// behind an mbarrier so that the wait is bounded like every other).
+// behind an mbarrier so that the wait is bounded like every other).  Eight epilogue warps in two
+// groups of four: group g drains the CTA's tiles g, g + 2, ... from accumulator g through its own
+// staging tile, barriers and copying thread, so that one tile's drain overlaps the next one's.
 template <int OUT_BYTES, int KIND, int FUSE = 0>
 __global__ void __launch_bounds__(FUSE ? kStripFusedThreads : kThreads, 1)
 hb_conv_strip_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constant__ CUtensorMap tmW,
@@ -441,8 +443,9 @@ hb_conv_strip_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_cons
         // lanes, the group meets at a barrier, and every lane reads the next warp's rows (one or
         // two addresses per instruction: broadcasts) and selects without a branch: a divergent
         // branch per channel costs more than the rest of the drain.  (Publishing from the registers
-        // of the main pass instead, with a barrier per half, measured 1.7 us slower on the
-        // 56 x 56 x 64 layer: the group waits twice.)
+        // of the main pass instead measured slower on the 56 x 56 x 64 layer: by 1.7 us with a
+        // barrier per half, and by 2.1 us with one barrier after the main pass and the two boundary
+        // lanes finishing their pixels from parked partial sums afterwards.)
         uint32_t g0[32], g1[32], g2[32];
 #ifdef HB_PROBES
         // diagnostics (wrong results): 5 = no boundary exchange, 6 = no shifted adds, 7 = no staging

@@ -251,7 +251,7 @@ def strip_fused_applies(p, es, eo, limits):
     rule with the exchange buffer added, fp16, 64 output channels, KW = 3, no dilation along W."""
     if p["in_dtype"] != "float16" or p["CO"] != 64 or p["KW"] != 3 or p["dilation"][1] != 1:
         return False
-    shrunk = dict(limits, max_shared_memory_per_block=limits["max_shared_memory_per_block"] - 2 * 4 * 3 * 64 * 4)
+    shrunk = dict(limits, max_shared_memory_per_block=limits["max_shared_memory_per_block"] - 2 * 2 * 4 * 3 * 64 * 4)
     return strip_applies(p, es, eo, shrunk)
 
 
