@@ -209,7 +209,7 @@ int plan_conv(const void* in, const void* w, void* out, int N, int H, int W, int
     hb_knobs k0;
     if (knobs) k0 = *knobs; else std::memset(&k0, 0, sizeof(k0));
     const bool fits_t = !strided_view && !out_nchw && in_w == HB_F16 && !k0.silent_producer &&
-                        strip_t_smem_bytes(cg, in_a, out_t, nullptr, k0.tile_n > 0 && algo == 3 ? k0.tile_n : 256) != 0;
+                        strip_t_smem_bytes(cg, in_a, out_t, nullptr, strip_t_max_l(algo == 3 ? k0.tile_n : 0)) != 0;
     const bool wide_pays = W + 2 * pad_w <= 90 && (CO != 64 || esize(out_t) == 2);
     if (algo == 3 && !fits_t) return HB_ERR_KNOB;
     if (algo == 3 || (algo == 0 && fits_t && wide_pays && KH * KW > 1 && K * es <= 2048)) {

@@ -50,13 +50,21 @@ int strip_t_smem_bytes(const ConvGeom& g, hb_dtype in_a, hb_dtype out_t, hb::Str
   return static_cast<int>(smem);
 }
 
+// The positions per tile the knob tile_n asks of the wide strip kernel: a multiple of 64 between
+// 64 and 256 (the knob's own grid is multiples of 32: those round down), 256 when unset.
+int strip_t_max_l(int tile_n) {
+  if (tile_n <= 0) return 256;
+  const int l = tile_n / 64 * 64;
+  return l < 64 ? 64 : (l > 256 ? 256 : l);
+}
+
 int build_strip_t_plan(Driver& d, const ConvGeom& g, hb_dtype in_a, hb_dtype in_w, hb_dtype out_t,
                        const hb_knobs& k, const void* in, const void* w, void* out, hb_plan* plan) {
   if (g_plan_owns_flags) release_split_flags(plan->p.flags, plan->owned_flags);
   std::memset(plan, 0, sizeof(*plan));
   hb::StripTParams& sp = plan->spt;
   // (knob tile_n caps the positions per tile: 64, 128, 192 or 256)
-  const int smem = strip_t_smem_bytes(g, in_a, out_t, &sp, k.tile_n > 0 ? k.tile_n : 256);
+  const int smem = strip_t_smem_bytes(g, in_a, out_t, &sp, strip_t_max_l(k.tile_n));
   if (smem == 0 || in_w != HB_F16) return HB_ERR_KNOB;
   const long long tiles = static_cast<long long>(g.N) * sp.tiles_per_img;
   if (tiles > 0x7fffffffLL) return HB_ERR_SHAPE;

@@ -70,7 +70,8 @@ typedef struct {
                         filter + one padded input strip per tile (stride 1, filter fits shared
                         memory, padded width <= 128); 3: the same with the operands' places changed:
                         output channels on the MMA's M axis (64 or 128 of them), 256 consecutive
-                        output positions on N (fp16, stride 1); 4: algorithm 2 with the three taps
+                        output positions on N (fp16, stride 1; tile_n then caps the positions per
+                        tile, rounded down to a multiple of 64); 4: algorithm 2 with the three taps
                         of a filter row taken by one MMA of 192 columns, the epilogue adding the
                         column groups shifted by one and two pixels (fp16, 64 output channels,
                         KW = 3, no dilation along W); 0 = library picks                            */

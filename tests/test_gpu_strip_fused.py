@@ -64,13 +64,18 @@ def test_fused_row_strip_random_geometry(K, co, N, H, W, CI, KH, pad, dh, half_o
     x = rng.standard_normal((N, H, W, CI)).astype(np.float16)
     w = (rng.standard_normal((KH, 3, CI, 64)) / np.sqrt(KH * 3 * CI)).astype(np.float16)
     od = np.float16 if half_out else np.float32
+    # the constraint model's own rule (the padded row within the 128 MMA rows; filter, two strips
+    # and the exchange within shared memory) says which geometries the library takes
+    from heron_b200.schedule.context.context import B200_LIMITS
+    from heron_b200.schedule.sched_op import strip_fused_applies
+    geom = dict(stride=(1, 1), dilation=(dh, 1), CI=CI, CO=64, KH=KH, KW=3, padding=pad, H=H, W=W, in_dtype="float16")
+    feasible = strip_fused_applies(geom, 2, 2 if half_out else 4, B200_LIMITS)
     try:
         got = k_conv(K, x, w, 1, pad, (dh, 1), out_dtype=od, knobs=dict(conv_algo=4, max_ctas=max_ctas))
     except HeronB200Error as e:
-        # the padded row must fit the 128 MMA rows; the filter, two strips of 128 input channels and
-        # the staging tile can exceed shared memory
-        assert e.status == HB_ERR_KNOB and (W + 2 * pad > 128 or (CI == 128 and KH >= 2))
+        assert e.status == HB_ERR_KNOB and not feasible
         return
+    assert feasible
     check(got, co.conv2d_nhwc_f16(x, w, 1, pad, (dh, 1), od), "fused-row strip %s" % ((N, H, W, CI, KH, pad, dh),))
 
 
@@ -132,3 +137,40 @@ def test_cfg3_full_size_on_the_fused_row_strip_kernel(K, co):
     out = k_conv(K, x, w, 1, 1, 1, out_dtype=np.float16, knobs=dict(conv_algo=4))
     for n in (0, 13, 31):
         check(out[n:n + 1], co.conv2d_nhwc_f16(x[n:n + 1], w, 1, 1, 1, np.float16), "cfg3 image %d" % n)
+
+
+@pytest.mark.parametrize("args", [
+    [16, 20, 20, 64, 64, 3, 3, 1, 1, 1, "float16", "float16"],
+    [16, 12, 70, 64, 64, 3, 3, 1, 1, 1, "float16", "float32"],
+])
+def test_knob_space_reaches_every_conv_algorithm(K, co, args):
+    """Random feasible points of the operator's knob space (the constraint model's conv-algorithm
+    rule lists the fused-row form where the library accepts it): every point runs and matches the
+    oracle, and the sweep meets the fused-row form and at least two of the others."""
+    import random
+    from heron_b200.ops import cuda as heron_cuda
+    from test_gpu_parity import _task
+    t = _task(heron_cuda, "c2d_nhwc", args, "GPU_TENSOR_CORE")
+    N, H, W, CI, CO = args[:5]
+    rng = np.random.default_rng(H)
+    x = rng.standard_normal((N, H, W, CI)).astype(np.float16)
+    w = (rng.standard_normal((3, 3, CI, CO)) / np.sqrt(9 * CI)).astype(np.float16)
+    od = np.float16 if args[-1] == "float16" else np.float32
+    want = co.conv2d_nhwc_f16(x, w, 1, 1, 1, od)
+    tin = [dev(x), dev(w)]
+    random.seed(23)
+    seen, algos = set(), set()
+    for _ in range(150):
+        if len(seen) >= 40:
+            break
+        t.knob_manager.randSample()
+        handle, targs = t.instantiate(t.knob_manager)
+        key = tuple(sorted(handle.knobs.items()))
+        if key in seen:
+            continue
+        seen.add(key)
+        algos.add(handle.knobs.get("conv_algo"))
+        out = poison(targs[-1].shape, torch.float16 if od == np.float16 else torch.float32)
+        handle(*tin, out)
+        check(out, want, str(handle.knobs))
+    assert 4 in algos and len(algos) >= 3, algos
