@@ -821,6 +821,51 @@ def test_many_random_knob_points(K, co, op, args):
     assert len(seen) >= 40
 
 
+@pytest.mark.parametrize("op,args", [
+    ("gemm", [300, 328, 264, "float16", "float32"]),
+    ("bmm", [16, 64, 64, 320, "float16", "float16"]),
+    ("c2d_nhwc", [16, 14, 14, 64, 128, 3, 3, 1, 1, 1, "float16", "float16"]),
+    ("c2d_nhwc", [16, 9, 9, 64, 96, 3, 3, 2, 1, 1, "float16", "float32"]),
+])
+def test_many_random_knob_points_fp16(K, co, op, args):
+    """Forty distinct feasible points of the knob space per operator, fp16 operands with fp16 and
+    fp32 outputs: every point the constraint model calls feasible runs and stays within the bounds."""
+    from heron_b200.ops import cuda as heron_cuda
+    t = _task(heron_cuda, op, args, "GPU_TENSOR_CORE")
+    rng = np.random.default_rng(len(args) + args[1])
+    od = np.float16 if args[-1] == "float16" else np.float32
+    if op == "gemm":
+        M, Kd, N = args[:3]
+        ins = [(rng.standard_normal((M, Kd)) / np.sqrt(Kd)).astype(np.float16), rng.standard_normal((N, Kd)).astype(np.float16)]
+        want = co.gemm_f16(*ins).astype(od)
+    elif op == "bmm":
+        B, M, Kd, N = args[:4]
+        ins = [(rng.standard_normal((B, M, Kd)) / np.sqrt(Kd)).astype(np.float16),
+               rng.standard_normal((B, N, Kd)).astype(np.float16)]
+        want = co.bmm_f16(*ins).astype(od)
+    else:
+        N, H, W, CI, CO, KH, KW, s, p, d = args[:10]
+        ins = [rng.standard_normal((N, H, W, CI)).astype(np.float16),
+               (rng.standard_normal((KH, KW, CI, CO)) / np.sqrt(KH * KW * CI)).astype(np.float16)]
+        want = co.conv2d_nhwc_f16(ins[0], ins[1], s, p, d, od)
+    tin = [dev(i) for i in ins]
+    random.seed(29)
+    seen = set()
+    for _ in range(160):
+        if len(seen) >= 40:
+            break
+        t.knob_manager.randSample()
+        handle, targs = t.instantiate(t.knob_manager)
+        key = tuple(sorted(handle.knobs.items()))
+        if key in seen:
+            continue
+        seen.add(key)
+        out = poison(targs[-1].shape, torch.float16 if od == np.float16 else torch.float32)
+        handle(*tin, out)
+        check(out, want, str(handle.knobs))
+    assert len(seen) >= 25
+
+
 STRIP_CASES = [
     # N, H, W, CI, CO, KH, KW, pad, dil  (stride 1; filter + two strips fit shared memory)
     (2, 8, 8, 64, 64, 3, 3, 1, 1),
