@@ -399,7 +399,16 @@ hb_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           continue;
         }
 #endif
+#ifdef HB_PROBES
+        // diagnostic (wrong results): 3 = every other stage keeps the B operand of its previous use:
+        // a quarter less operand traffic from L2 for the same MMA work
+        const bool skip_b = p.probe == 3 && (issued & 1) && issued >= p.stages;
+        if (leader && (part & 1))
+          mbar_arrive_expect_tx(full_local, (skip_b ? static_cast<uint32_t>(a_bytes) * CG : tx_bytes) * static_cast<uint32_t>(g));
+#else
+        constexpr bool skip_b = false;
         if (leader && (part & 1)) mbar_arrive_expect_tx(full_local, tx_bytes * static_cast<uint32_t>(g));
+#endif
         for (int j = 0; j < g; ++j) {
           const int kb = kbg + j;
           const uint32_t dA = sA + (stage * G + j) * a_bytes;
@@ -429,7 +438,7 @@ hb_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
               tma_prefetch_3d(tmBk, (kb + p.l2_prefetch) * BK, n0, b);
             }
           }
-          if (!(part & 2)) {
+          if (!(part & 2) || skip_b) {
           } else if (p.b_mn_major) {
             for (int c = 0; c < n_chunks; ++c)
               tma_load_3d_cg<CG>(dB + c * (BK * p.SW), &tmB, full, n0 + c * chunk_cols, krow, b);
