@@ -174,3 +174,19 @@ def test_knob_space_reaches_every_conv_algorithm(K, co, args):
         handle(*tin, out)
         check(out, want, str(handle.knobs))
     assert 4 in algos and len(algos) >= 3, algos
+
+
+@pytest.mark.parametrize("case", [(2, 64, 14, 14), (3, 64, 30, 41), (2, 64, 9, 100), (16, 64, 56, 56)])
+def test_fused_row_strip_channel_major_output(K, co, case):
+    """The NCHW operator on the fused-row form: the epilogue's channel-major stores (no staging
+    tile, each lane writes its pixel's channels plane by plane), fp16 and fp32 outputs."""
+    N, CI, H, W = case
+    rng = np.random.default_rng(sum(case))
+    x = rng.standard_normal((N, CI, H, W)).astype(np.float16)
+    w = (rng.standard_normal((64, CI, 3, 3)) / np.sqrt(9 * CI)).astype(np.float16)
+    for od, td in ((np.float16, torch.float16), (np.float32, torch.float32)):
+        out = poison((N, 64, H, W), td)
+        plan = K.plan_conv2d_nchw(dev(x), dev(w), stride=1, padding=1, out=out, knobs=dict(conv_algo=4))
+        assert plan.knobs()["conv_algo"] == 4
+        plan.launch()
+        check(out, co.conv2d_nchw(x, w, 1, 1, od), "fused-row strip, NCHW %s" % (case,))
