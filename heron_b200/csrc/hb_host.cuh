@@ -55,7 +55,7 @@ bool setup_device(Driver* d) {
   if (prop.major != 10) return false;
   d->sm_count = prop.multiProcessorCount;
   // Opt in to the large dynamic shared-memory carve-out for every kernel instantiation.
-  const void* kernels[19] = {
+  const void* kernels[31] = {
       reinterpret_cast<const void*>(&hb::hb_conv_strip_t_kernel<2>),
       reinterpret_cast<const void*>(&hb::hb_conv_strip_t_kernel<4>),
       reinterpret_cast<const void*>(&hb::hb_umma_kernel<4, 1, 0, 1>),
@@ -70,6 +70,18 @@ bool setup_device(Driver* d) {
       reinterpret_cast<const void*>(&hb::hb_umma_kernel<4, 2, 0, 2>),
       reinterpret_cast<const void*>(&hb::hb_umma_kernel<2, 2, 0, 2>),
       reinterpret_cast<const void*>(&hb::hb_umma_kernel<4, 2, 1, 2>),
+      reinterpret_cast<const void*>(&hb::hb_umma_kernel<4, 1, 0, 1, 8>),
+      reinterpret_cast<const void*>(&hb::hb_umma_kernel<2, 1, 0, 1, 8>),
+      reinterpret_cast<const void*>(&hb::hb_umma_kernel<4, 1, 1, 1, 8>),
+      reinterpret_cast<const void*>(&hb::hb_umma_kernel<4, 2, 0, 1, 8>),
+      reinterpret_cast<const void*>(&hb::hb_umma_kernel<2, 2, 0, 1, 8>),
+      reinterpret_cast<const void*>(&hb::hb_umma_kernel<4, 2, 1, 1, 8>),
+      reinterpret_cast<const void*>(&hb::hb_umma_kernel<4, 1, 0, 2, 8>),
+      reinterpret_cast<const void*>(&hb::hb_umma_kernel<2, 1, 0, 2, 8>),
+      reinterpret_cast<const void*>(&hb::hb_umma_kernel<4, 1, 1, 2, 8>),
+      reinterpret_cast<const void*>(&hb::hb_umma_kernel<4, 2, 0, 2, 8>),
+      reinterpret_cast<const void*>(&hb::hb_umma_kernel<2, 2, 0, 2, 8>),
+      reinterpret_cast<const void*>(&hb::hb_umma_kernel<4, 2, 1, 2, 8>),
       reinterpret_cast<const void*>(&hb::hb_conv_strip_kernel<4, 0>),
       reinterpret_cast<const void*>(&hb::hb_conv_strip_kernel<2, 0>),
       reinterpret_cast<const void*>(&hb::hb_conv_strip_kernel<4, 1>),

@@ -244,8 +244,11 @@ __device__ __forceinline__ uint4 ld_cg_v4(const void* ptr) {
   return v;
 }
 
-template <int OUT_BYTES, int CG, int KIND, int KS>
-__global__ void __launch_bounds__(kUmmaThreadsMax, 1)
+// EW: epilogue warps of a CTA, 4 or 8.  A template parameter so that each form has its own launch
+// bounds and drain loop: with the count a run-time value (or the drain in a generic lambda under
+// the larger form's launch bounds) the four-warp form lost 10-30 % on short-K shapes.
+template <int OUT_BYTES, int CG, int KIND, int KS, int EW = 4>
+__global__ void __launch_bounds__(umma_threads(EW), 1)
 hb_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmB2,
                const KParams p) {
@@ -280,7 +283,7 @@ hb_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(smem_u32(&bars->tmem_full[a]), 1);
-      mbar_init(smem_u32(&bars->tmem_empty[a]), p.epi_warps * CG);
+      mbar_init(smem_u32(&bars->tmem_empty[a]), EW * CG);
     }
     mbar_init(smem_u32(&bars->drain), 1);
     bars->abort_flag = 0;
@@ -579,17 +582,14 @@ hb_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       }
     }
     __syncwarp();
-  } else if (warp >= 2 + p.epi_warps) {
+  } else if (warp >= 2 + EW) {
     // ------------------------------ second TMA producer: the B operand ---------------------
     if (elect_one()) produce(2);
     __syncwarp();
   } else {
     // ------------------------------ epilogue ----------------------------------------------
-    // (one body per warp count: the drain loop of a short-K shape is the kernel's critical path,
-    // and with the count a compile-time constant the four-warp form costs nothing for the other)
-    auto epilogue = [&](auto eight_tag) {
-    constexpr bool kEight = decltype(eight_tag)::value;
-    constexpr int kWarps = kEight ? 8 : 4;
+    constexpr bool kEight = EW == 8;
+    constexpr int kWarps = EW;
     const int q = warp & 3;  // TMEM lane quadrant this warp may read
     const int ew = warp - 2;
     const int half = kEight ? (ew >> 2) : 0;  // with eight warps: which half of a tile's column chunks
@@ -914,11 +914,6 @@ hb_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     // shared memory must outlive the stores' reads of it; their writes complete with the grid
     if (p.epilogue) bulk_wait_read<0>();
     __syncwarp();
-    };
-    if (p.epi_warps == 8)
-      epilogue(std::true_type{});
-    else
-      epilogue(std::false_type{});
   }
 
   tc_fence_before();

@@ -148,9 +148,13 @@ int build_plan(Driver& d, const Problem& pr, const hb_knobs& k, const ConvGeom* 
     cfg.attrs = &attr; cfg.numAttrs = 1;
     int clusters = 0;
     // (the one- and two-slice instantiations need the same resources per CTA)
-    const void* fn = eo == 2 ? reinterpret_cast<const void*>(&hb::hb_umma_kernel<2, 2, 0, 1>)
-                             : (kind == 0 ? reinterpret_cast<const void*>(&hb::hb_umma_kernel<4, 2, 0, 1>)
-                                          : reinterpret_cast<const void*>(&hb::hb_umma_kernel<4, 2, 1, 1>));
+    const void* fn4 = eo == 2 ? reinterpret_cast<const void*>(&hb::hb_umma_kernel<2, 2, 0, 1>)
+                              : (kind == 0 ? reinterpret_cast<const void*>(&hb::hb_umma_kernel<4, 2, 0, 1>)
+                                           : reinterpret_cast<const void*>(&hb::hb_umma_kernel<4, 2, 1, 1>));
+    const void* fn8 = eo == 2 ? reinterpret_cast<const void*>(&hb::hb_umma_kernel<2, 2, 0, 1, 8>)
+                              : (kind == 0 ? reinterpret_cast<const void*>(&hb::hb_umma_kernel<4, 2, 0, 1, 8>)
+                                           : reinterpret_cast<const void*>(&hb::hb_umma_kernel<4, 2, 1, 1, 8>));
+    const void* fn = k.epi_warps == 8 ? fn8 : fn4;
     if (cudaOccupancyMaxActiveClusters(&clusters, fn, &cfg) == cudaSuccess && clusters > 0 &&
         clusters < units)
       units = clusters;
@@ -402,12 +406,21 @@ int run_main(const hb_plan* plan, cudaStream_t stream) {
   return i8 ? launch_kernel<4, 1, 1, 1>(plan, stream) : launch_kernel<4, 1, 0, 1>(plan, stream);
 }
 
+template <int OUT_BYTES, int CG, int KIND, int KS, int EW>
+int launch_kernel_ew(const hb_plan* plan, cudaStream_t stream);
+
 template <int OUT_BYTES, int CG, int KIND, int KS>
 int launch_kernel(const hb_plan* plan, cudaStream_t stream) {
+  return plan->p.epi_warps == 8 ? launch_kernel_ew<OUT_BYTES, CG, KIND, KS, 8>(plan, stream)
+                                : launch_kernel_ew<OUT_BYTES, CG, KIND, KS, 4>(plan, stream);
+}
+
+template <int OUT_BYTES, int CG, int KIND, int KS, int EW>
+int launch_kernel_ew(const hb_plan* plan, cudaStream_t stream) {
   cudaLaunchConfig_t cfg;
   std::memset(&cfg, 0, sizeof(cfg));
   cfg.gridDim = dim3(plan->grid);
-  cfg.blockDim = dim3(hb::umma_threads(plan->p.epi_warps));
+  cfg.blockDim = dim3(hb::umma_threads(EW));
   cfg.dynamicSmemBytes = plan->smem;
   cfg.stream = stream;
   cudaLaunchAttribute attr[2];
@@ -417,7 +430,7 @@ int launch_kernel(const hb_plan* plan, cudaStream_t stream) {
   attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 2;
-  const cudaError_t e = cudaLaunchKernelEx(&cfg, hb::hb_umma_kernel<OUT_BYTES, CG, KIND, KS>, plan->tmA,
+  const cudaError_t e = cudaLaunchKernelEx(&cfg, hb::hb_umma_kernel<OUT_BYTES, CG, KIND, KS, EW>, plan->tmA,
                                            plan->tmB, plan->tmC, plan->tmB2, plan->p);
   return e == cudaSuccess ? HB_OK : HB_ERR_LAUNCH;
 }
