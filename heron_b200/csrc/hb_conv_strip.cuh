@@ -663,7 +663,7 @@ hb_conv_strip_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_cons
           }
         }
         stage_phase ^= 1u;
-        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;  // (the copier's verdict counts for its warp)
+        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;  // (the copier's result counts for its warp)
       }
       if (FUSE) xch_phase ^= 1u;
       next_acc();

@@ -424,7 +424,7 @@ hb_conv_strip_t_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_co
         }
       }
       stage_phase ^= 1u;
-      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;  // (the copier's verdict counts for its warp)
+      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;  // (the copier's result counts for its warp)
       if (++acc == 2) {
         acc = 0;
         acc_phase ^= 1u;
