@@ -188,6 +188,38 @@ def test_conv_knob_space_respects_channel_bytes(hb_lib):
         assert hb_lib.hb_check_knobs(2, 1, 16 * 81, 64, 144, 16, _lib.HB_F16, _lib.HB_F32, ctypes.byref(k), None, None) == 0
 
 
+def test_conv_algorithm_candidates_follow_the_feasibility_rules():
+    """The constraint model offers a conv algorithm only where its rule holds: the fused-row form is
+    a subset of the strip kernel's space (same strips plus 12 KiB of exchange), needs fp16, 64
+    output channels, a three-tap undilated filter row; a task's candidate list is what the rules say."""
+    from heron_b200.schedule.context.context import B200_LIMITS
+    from heron_b200.schedule.sched_op import strip_applies, strip_fused_applies, strip_wide_applies
+    rnd = random.Random(5)
+    seen_fused = 0
+    for _ in range(400):
+        g = dict(stride=(rnd.choice([1, 1, 2]),) * 2, dilation=(rnd.randint(1, 2), rnd.choice([1, 1, 2])),
+                 CI=rnd.choice([64, 128]), CO=rnd.choice([64, 128]), KH=rnd.randint(1, 3), KW=rnd.randint(1, 3),
+                 padding=rnd.randint(0, 2), H=rnd.randint(1, 60), W=rnd.randint(1, 140), in_dtype="float16")
+        eo = rnd.choice([2, 4])
+        fused = strip_fused_applies(g, 2, eo, B200_LIMITS)
+        if fused:
+            seen_fused += 1
+            assert strip_applies(g, 2, eo, B200_LIMITS)
+            assert g["CO"] == 64 and g["KW"] == 3 and g["dilation"][1] == 1 and g["stride"] == (1, 1)
+            assert g["W"] + 2 * g["padding"] <= 128
+    assert seen_fused > 10
+    assert not strip_fused_applies(dict(stride=(1, 1), dilation=(1, 1), CI=64, CO=64, KH=3, KW=3, padding=1, H=8, W=8,
+                                        in_dtype="uint8"), 1, 4, B200_LIMITS)
+    t = _task("c2d_nhwc", [16, 20, 20, 64, 64, 3, 3, 1, 1, 1, "float16", "float16"])
+    name = [k for k in t.knob_manager.knob_names if "conv_algo" in k][0]
+    assert sorted(t.knob_manager.get_knob_candidates(name)) == [1, 2, 3, 4]
+    t = _task("c2d_nhwc", [16, 20, 20, 64, 128, 3, 3, 1, 1, 1, "float16", "float16"])
+    name = [k for k in t.knob_manager.knob_names if "conv_algo" in k][0]
+    assert 4 not in t.knob_manager.get_knob_candidates(name)
+    assert strip_wide_applies(dict(stride=(1, 1), dilation=(1, 1), CI=64, CO=128, KH=3, KW=3, padding=1, H=20, W=20,
+                                   in_dtype="float16"), 2, 2, B200_LIMITS)
+
+
 def test_nchw_first_layer_knob_space_is_the_row_packed_form(hb_lib):
     """3 input channels, 7x7 filter: the library reads a whole filter row (8 taps of 16 bytes) as one
     128-byte K block, and the tuner's space must offer that block size, not the 32 bytes of the
