@@ -118,7 +118,7 @@ int build_strip_plan(Driver& d, const ConvGeom& g, hb_dtype in_a, hb_dtype in_w,
   plan->knobs.conv_algo = fuse ? 4 : 2;
   // fields hb_plan_knobs reports
   plan->knobs.tile_n = sp.acc_cols; plan->knobs.swizzle_bytes = 128; plan->knobs.stages = sp.ring;
-  plan->knobs.acc_stages = 2; plan->knobs.cta_group = 1; plan->knobs.epilogue = 2; plan->knobs.epi_warps = hb::kEpiWarps;
+  plan->knobs.acc_stages = 2; plan->knobs.cta_group = 1; plan->knobs.epilogue = 2; plan->knobs.epi_warps = fuse ? hb::kStripFusedEpiWarps : hb::kEpiWarps;
   // the packed-filter wrapper reads these from the GEMM-view parameter block
   plan->p.N = g.CO; plan->p.KW = g.KW; plan->p.CI = g.CI; plan->p.esize_out = eo;
   return HB_OK;
