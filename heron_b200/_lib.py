@@ -70,6 +70,7 @@ EXPORTED_SYMBOLS = (
     "hb_plan_conv2d_nhwc_packed",
     "hb_plan_launch",
     "hb_plan_knobs",
+    "hb_plan_set_peer_outputs",
     "hb_plan_destroy",
     "hb_last_status",
     "hb_status_string",
@@ -229,6 +230,8 @@ def load():
     lib.hb_plan_launch.argtypes = [c_void_p, c_void_p]
     lib.hb_plan_knobs.restype = c_int
     lib.hb_plan_knobs.argtypes = [c_void_p, kp, ip, ip]
+    lib.hb_plan_set_peer_outputs.restype = c_int
+    lib.hb_plan_set_peer_outputs.argtypes = [c_void_p, c_int, ctypes.POINTER(c_void_p)]
     lib.hb_plan_destroy.restype = None
     lib.hb_plan_destroy.argtypes = [c_void_p]
     lib.hb_last_status.restype = c_int

@@ -322,6 +322,8 @@ int hb_plan_knobs(const hb_plan* plan, hb_knobs* knobs, int* grid, int* smem_byt
   return HB_OK;
 }
 
+int hb_plan_set_peer_outputs(hb_plan* plan, int n, void* const* outs) { return set_peer_outputs(plan, n, outs); }
+
 void hb_plan_destroy(hb_plan* plan) { destroy_plan(plan); }
 
 int hb_last_status(int* status) {

@@ -369,6 +369,9 @@ struct hb_plan {
   int grid;
   int smem;
   int owned_flags;  // hand-over flags (p.flags) this plan holds until it is destroyed; 0: none
+  // what the output's tensor map was encoded from (TMA-store epilogue), for maps of further outputs
+  int out_dt; long long out_d0, out_d1, out_d2;
+  void* peer_maps_dev;  // device array of those maps (hb_plan_set_peer_outputs); freed with the plan
   // strip conv (conv_algo 2): its own parameter block; tmA = tiled input map, tmB = filter map
   bool strip;
   hb::StripParams sp;

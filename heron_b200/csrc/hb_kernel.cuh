@@ -89,6 +89,10 @@ struct KParams {
   int raster, kind, b_mn_major, a_im2col, epilogue, l2_prefetch;
   int probe;            // diagnostic modes; only builds with -DHB_PROBES read it
   int epi_warps;        // epilogue warps of a CTA: 4 or 8
+  // TMA-store epilogue: the same tile also goes to these outputs (other GPUs' copies of the output
+  // buffer, reached over NVLink); tensor maps in this device's global memory
+  const CUtensorMap* peer_maps;
+  int n_peers;
   int silent_producer;  // test hook: the producers issue no loads, so the consumers' waits run out
   // Balanced schedule: work units are ring stages; unit u belongs to tile u / sk_per_tile.  CTA
   // pair i walks units [bound(i), bound(i+1)), bound(i) = i * sk_total / pairs, moved to the tile
@@ -805,6 +809,8 @@ hb_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 tma_reduce_add_3d(&tmC, buf, col, row0, zc);
               else
                 tma_store_3d(&tmC, buf, col, row0, zc);
+              // (plain stores into other GPUs' memory: nothing here waits on a peer)
+              for (int r = 0; r < p.n_peers; ++r) tma_store_3d(p.peer_maps + r, buf, col, row0, zc);
               bulk_commit();
             }
           }

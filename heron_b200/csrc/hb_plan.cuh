@@ -133,6 +133,8 @@ int build_plan(Driver& d, const Problem& pr, const hb_knobs& k, const ConvGeom* 
     rc = encode_tiled3(d, &tmC, pr.out, C, pr.N, pr.M, kslab ? kslab : pr.batch, rowC, rowC * pr.M,
                        128 / eo, 32, 128);
     if (rc != HB_OK) return rc;
+    plan->out_dt = static_cast<int>(pr.out);
+    plan->out_d0 = pr.N; plan->out_d1 = pr.M; plan->out_d2 = kslab ? kslab : pr.batch;
   }
 
   int units = d.sm_count / cgrp;  // CTAs, or CTA pairs, resident at once
@@ -471,8 +473,47 @@ int plan_scan(const void* A, void* out, int M, int N, int K, hb_dtype in_a, hb_d
   return HB_OK;
 }
 
+// Further outputs of a plan whose epilogue is the TMA store: every tile is also stored to each of
+// `outs` (same shape and layout as the plan's own output; typically the same slice of the other
+// GPUs' output buffers, mapped into this process).  n = 0 takes them away again.
+int set_peer_outputs(hb_plan* plan, int n, void* const* outs) {
+  if (!plan || n < 0 || n > 15 || (n > 0 && !outs)) return HB_ERR_SHAPE;
+  if (plan->strip || plan->strip_t || !plan->p.epilogue || plan->p.kslab || plan->p.ksplit > 1 || plan->p.sk ||
+      plan->has_post)
+    return HB_ERR_KNOB;
+  Driver& d = driver();
+  if (d.status != HB_OK) return d.status;
+  if (plan->peer_maps_dev) {
+    cudaFree(plan->peer_maps_dev);
+    plan->peer_maps_dev = nullptr;
+  }
+  plan->p.peer_maps = nullptr;
+  plan->p.n_peers = 0;
+  if (n == 0) return HB_OK;
+  CUtensorMap maps[15];
+  const hb_dtype dt = static_cast<hb_dtype>(plan->out_dt);
+  const uint64_t row = static_cast<uint64_t>(plan->out_d0) * esize(dt);
+  for (int i = 0; i < n; ++i) {
+    if (!outs[i] || !aligned16(outs[i])) return HB_ERR_ALIGN;
+    const int rc = encode_tiled3(d, &maps[i], dt, outs[i], plan->out_d0, plan->out_d1, plan->out_d2, row,
+                                 row * plan->out_d1, 128 / esize(dt), 32, 128);
+    if (rc != HB_OK) return rc;
+  }
+  void* dev = nullptr;
+  if (cudaMalloc(&dev, sizeof(CUtensorMap) * n) != cudaSuccess) return HB_ERR_SCRATCH;
+  if (cudaMemcpy(dev, maps, sizeof(CUtensorMap) * n, cudaMemcpyHostToDevice) != cudaSuccess) {
+    cudaFree(dev);
+    return HB_ERR_LAUNCH;
+  }
+  plan->peer_maps_dev = dev;
+  plan->p.peer_maps = static_cast<const CUtensorMap*>(dev);
+  plan->p.n_peers = n;
+  return HB_OK;
+}
+
 void destroy_plan(hb_plan* plan) {
   if (!plan) return;
+  if (plan->peer_maps_dev) cudaFree(plan->peer_maps_dev);
   release_split_flags(plan->p.flags, plan->owned_flags);
   delete plan;
 }

@@ -259,6 +259,18 @@ class Plan:
         d["grid"], d["smem_bytes"] = grid.value, smem.value
         return d
 
+    def set_peer_outputs(self, outs):
+        """Every tile the kernel stores to this plan's output also goes to each tensor of `outs`
+        (same shape, dtype and layout; typically this rank's slice of the other GPUs' output
+        buffers, mapped into this process).  An empty list removes them."""
+        outs = list(outs)
+        for o in outs:
+            if tuple(o.shape) != tuple(self.out.shape) or o.dtype != self.out.dtype or not o.is_contiguous():
+                raise ValueError("a peer output must have the plan's output shape, dtype and a dense layout")
+        arr = (ctypes.c_void_p * max(len(outs), 1))(*[o.data_ptr() for o in outs])
+        _lib.check(_lib.load().hb_plan_set_peer_outputs(self._handle, len(outs), arr), "hb_plan_set_peer_outputs")
+        self._peer_outs = outs  # (kept alive with the plan)
+
     def close(self):
         if self._handle is not None:
             _lib.load().hb_plan_destroy(self._handle)

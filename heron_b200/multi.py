@@ -199,3 +199,41 @@ class ChunkedGather:
                 self.gather_super(full, c)
         cur.wait_stream(comm)
         return full
+
+
+class PeerStoreOutput:
+    """The whole output of a sharded operator on every GPU of one box with no collective at all:
+    each rank's kernel stores its tiles into its slice of EVERY rank's output buffer (TMA stores
+    from the kernel's staging buffer, over NVLink for the other GPUs), so the transfer rides on
+    the kernel's own epilogue.
+
+    The buffer is symmetric memory (torch.distributed._symmetric_memory: the same allocation on
+    every rank, each rank's copy mapped into all processes).  ``attach(plan, start, count)`` hands
+    the plan this rank's slice of the other ranks' buffers (`hb_plan_set_peer_outputs`); the plan
+    itself must have been built on ``mine(start, count)``.  After every rank's launch,
+    ``barrier()`` (a device-side barrier on the current stream) says that all slices have arrived.
+    Only plain stores cross NVLink; nothing in the kernel waits on another GPU.  NVLink multicast
+    is switched off for the allocation (a rank that dies while its memory is bound to a multicast
+    object disturbs the other GPUs of the box)."""
+
+    def __init__(self, shape, dtype, device, group=None):
+        import os
+        import torch.distributed as dist
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        import torch.distributed._symmetric_memory as symm_mem
+        self.group = group if group is not None else dist.group.WORLD
+        self.rank, self.world = dist.get_rank(self.group), dist.get_world_size(self.group)
+        self.shape, self.dtype = tuple(shape), dtype
+        self.full = symm_mem.empty(*self.shape, dtype=dtype, device=device)
+        self._hdl = symm_mem.rendezvous(self.full, self.group)
+        self._peers = [self._hdl.get_buffer(r, self.shape, dtype) for r in range(self.world) if r != self.rank]
+
+    def mine(self, start, count):
+        return self.full[start:start + count]
+
+    def attach(self, plan, start, count):
+        plan.set_peer_outputs([p[start:start + count] for p in self._peers])
+        return plan
+
+    def barrier(self):
+        self._hdl.barrier()

@@ -340,6 +340,19 @@ int hb_plan_conv1d_nwc_packed(hb_plan** plan, const void* in, const void* w_pack
 int hb_plan_launch(const hb_plan* plan, void* stream);
 /* The knobs after defaults were resolved, the persistent grid and the dynamic shared memory. */
 int hb_plan_knobs(const hb_plan* plan, hb_knobs* knobs, int* grid, int* smem_bytes);
+/*
+ * Further outputs of a gemm / bmm / conv2d_nhwc plan whose epilogue is the TMA store (`epilogue` 1,
+ * no split-K, not the balanced schedule, not a strip kernel): every tile the kernel stores to the
+ * plan's output is stored to each of `outs[0..n)` as well, straight from the same shared-memory
+ * staging buffer.  Meant for the sharded operators (batches / images over the GPUs of one box,
+ * heron_b200/multi.py): `outs` are this rank's slice of the other GPUs' full-size output buffers,
+ * mapped into this process (CUDA IPC or symmetric memory), so the whole output is complete on
+ * every GPU when every rank's kernel has finished and no collective runs afterwards.  The caller
+ * orders "every rank has finished" itself (a barrier on the stream).  Each pointer 16-byte
+ * aligned, same shape and layout as the plan's output; n <= 15; n = 0 removes them.  Allocates a
+ * small device array for the tensor maps (freed by hb_plan_destroy).
+ */
+int hb_plan_set_peer_outputs(hb_plan* plan, int n, void* const* outs);
 void hb_plan_destroy(hb_plan* plan);
 
 /*

@@ -1,7 +1,8 @@
 """Body of the multi-GPU check, one process per GPU (launched by tests/test_gpu_multi.py under
 torch.distributed.run).  Each rank computes its shard of a batched GEMM and of an NHWC conv with
 the sm_100a kernels, writing straight into its slice of a full-size output buffer; one in-place
-NCCL all-gather completes the buffer; every rank compares the whole result with the oracle."""
+NCCL all-gather completes the buffer; every rank compares the whole result with the oracle.  Then
+the form without a collective: each rank's kernel stores its shard into every rank's buffer."""
 import os
 import sys
 
@@ -61,6 +62,46 @@ def main():
             cg.run(plans, full)
             torch.cuda.synchronize(dev)
             ok &= bool(np.array_equal(full.cpu().numpy(), npo.conv2d_nhwc_int(x, w, 1, 1, 1)))
+
+    # no collective at all: every rank's kernel stores its shard into every rank's buffer
+    from heron_b200.multi import PeerStoreOutput
+    for batch in (12, 7):
+        a = rng.integers(-128, 128, (batch, 192, 64)).astype(np.int8)
+        b = rng.integers(-128, 128, (batch, 160, 64)).astype(np.int8)
+        start, count = partition(batch, world)[rank]
+        po = PeerStoreOutput((batch, 192, 160), torch.int32, dev)
+        po.full.fill_(-1)
+        po.barrier()
+        if count:
+            plan = K.plan_bmm(torch.from_numpy(a[start:start + count]).to(dev),
+                              torch.from_numpy(b[start:start + count]).to(dev), out=po.mine(start, count))
+            po.attach(plan, start, count)
+            plan.launch()
+            plan.launch()  # (a second launch stores the same bits again)
+        po.barrier()
+        torch.cuda.synchronize(dev)
+        ok &= bool(np.array_equal(po.full.cpu().numpy(), npo.bmm_int(a, b)))
+        po.barrier()
+    start, count = partition(16, world)[rank]
+    po = PeerStoreOutput((16, 7, 7, 128), torch.int32, dev)
+    po.full.fill_(-1)
+    po.barrier()
+    plan = K.plan_conv2d_nhwc(torch.from_numpy(x[start:start + count]).to(dev), torch.from_numpy(w).to(dev), 1, 1, 1,
+                              out=po.mine(start, count), knobs=dict(conv_algo=1))
+    po.attach(plan, start, count)
+    plan.launch()
+    po.barrier()
+    torch.cuda.synchronize(dev)
+    ok &= bool(np.array_equal(po.full.cpu().numpy(), npo.conv2d_nhwc_int(x, w, 1, 1, 1)))
+    po.barrier()
+    # (the strip kernels and the direct-store epilogue have no such outputs: refused, not ignored)
+    try:
+        K.plan_conv2d_nhwc(torch.from_numpy(x[start:start + count]).to(dev), torch.from_numpy(w).to(dev), 1, 1, 1,
+                           out=po.mine(start, count), knobs=dict(conv_algo=1, epilogue=2)).set_peer_outputs(
+                               [po.mine(start, count)])
+        ok = False
+    except _lib.HeronB200Error as e:
+        ok &= e.status == _lib.HB_ERR_KNOB
 
     ok &= _lib.last_status() == 0
     flag = torch.tensor([1 if ok else 0], device=dev)
