@@ -464,12 +464,51 @@ def run_sharded(env, name, steps):
             out["compute_value"] = round(work_and_bytes(name)[0] / (cms * 1e-3) / 1e12, 3)
             out["gathered_mb"] = round(full.numel() * full.element_size() / 1e6, 1)
         del plans, full
+    # No collective: every rank's kernel stores its shard into every rank's copy of the output
+    # (symmetric memory; TMA stores from the kernel's staging buffer over NVLink), then a
+    # device-side barrier on the stream.
+    try:
+        from heron_b200.multi import PeerStoreOutput, partition
+        start, count = partition(total, env.world)[env.rank]
+        handle, hargs = build_handle(name, count)
+        po = PeerStoreOutput((total,) + tuple(hargs[-1].shape[1:]), TORCH_DTYPES[hargs[-1].dtype], env.device)
+        po.full.view(torch.uint8).fill_(0xCD)
+        po.barrier()
+        ins = [to_dev(h, env.device) for h in make_inputs(name, shard=(start, count))]
+        plan = po.attach(handle.plan(*ins, po.mine(start, count)), start, count)
+        plan.launch()
+        po.barrier()
+        env.barrier()
+        ok = True
+        if env.rank == env.world - 1:  # (a rank other than the one that checked the gathered form)
+            ok = sum_identity_check(name, po.full.cpu().numpy())
+        flag = torch.tensor([1 if ok else 0], device=env.device)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        out["peer_store_check"] = "pass" if int(flag[0]) == 1 else "fail"
+        gsteps = max(3, min(steps, 50))
+        for _ in range(3):
+            plan.launch()
+            po.barrier()
+        env.barrier()
+        p0, p1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        p0.record()
+        for _ in range(gsteps):
+            plan.launch()
+            po.barrier()
+        p1.record()
+        env.barrier()
+        out["with_peer_stores_ms"] = round(env.max_over_ranks([p0.elapsed_time(p1) / gsteps])[0], 5)
+        del plan, po
+    except Exception as e:  # symmetric memory unavailable on this box: the gathered form stands
+        out["with_peer_stores_ms"] = None
+        out["peer_store_note"] = "%s: %s" % (type(e).__name__, str(e)[:160])
     best = min(v for k, v in out.items() if k.startswith("with_all_gather_ms"))
     out["with_all_gather_ms"] = best
     out["unit"] = unit_of(cfg)
     out["note"] = ("compute_ms: this configuration's shard kernel alone (L2-warm, same buffers every launch); "
                    "with_all_gather_ms: kernels write their shards into the full buffer, in-place NCCL all-gather, "
-                   "best of 1 / 2 / 4 overlapped super-chunks")
+                   "best of 1 / 2 / 4 overlapped super-chunks; with_peer_stores_ms: no collective, every rank's kernel "
+                   "stores its tiles into every rank's buffer (hb_plan_set_peer_outputs) + a device-side barrier")
     return out
 
 
