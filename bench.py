@@ -466,7 +466,7 @@ def run_sharded(env, name, steps):
         del plans, full
     # No collective: every rank's kernel stores its shard into every rank's copy of the output
     # (symmetric memory; TMA stores from the kernel's staging buffer over NVLink), then a
-    # device-side barrier on the stream.
+    # one-element all-reduce on the stream as the barrier.
     try:
         from heron_b200.multi import PeerStoreOutput, partition
         start, count = partition(total, env.world)[env.rank]
@@ -508,7 +508,7 @@ def run_sharded(env, name, steps):
     out["note"] = ("compute_ms: this configuration's shard kernel alone (L2-warm, same buffers every launch); "
                    "with_all_gather_ms: kernels write their shards into the full buffer, in-place NCCL all-gather, "
                    "best of 1 / 2 / 4 overlapped super-chunks; with_peer_stores_ms: no collective, every rank's kernel "
-                   "stores its tiles into every rank's buffer (hb_plan_set_peer_outputs) + a device-side barrier")
+                   "stores its tiles into every rank's buffer (hb_plan_set_peer_outputs) + a one-element all-reduce as the barrier")
     return out
 
 

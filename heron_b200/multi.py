@@ -211,7 +211,11 @@ class PeerStoreOutput:
     every rank, each rank's copy mapped into all processes).  ``attach(plan, start, count)`` hands
     the plan this rank's slice of the other ranks' buffers (`hb_plan_set_peer_outputs`); the plan
     itself must have been built on ``mine(start, count)``.  After every rank's launch,
-    ``barrier()`` (a device-side barrier on the current stream) says that all slices have arrived.
+    ``barrier()`` says on the current stream that all slices have arrived: a one-element all-reduce
+    of the collective library, ordered behind this rank's kernel, which completes only when every
+    rank's kernel (and with it its stores into this rank's buffer) has.  A rank that never arrives
+    ends that collective through the process group's timeout with an error on the host; the
+    symmetric-memory library's own device-side barrier would spin on the GPU instead.
     Only plain stores cross NVLink; nothing in the kernel waits on another GPU.  NVLink multicast
     is switched off for the allocation (a rank that dies while its memory is bound to a multicast
     object disturbs the other GPUs of the box)."""
@@ -227,6 +231,8 @@ class PeerStoreOutput:
         self.full = symm_mem.empty(*self.shape, dtype=dtype, device=device)
         self._hdl = symm_mem.rendezvous(self.full, self.group)
         self._peers = [self._hdl.get_buffer(r, self.shape, dtype) for r in range(self.world) if r != self.rank]
+        import torch
+        self._token = torch.zeros(1, dtype=torch.int32, device=device)
 
     def mine(self, start, count):
         return self.full[start:start + count]
@@ -236,4 +242,5 @@ class PeerStoreOutput:
         return plan
 
     def barrier(self):
-        self._hdl.barrier()
+        import torch.distributed as dist
+        dist.all_reduce(self._token, group=self.group)
