@@ -248,6 +248,11 @@ __device__ __forceinline__ uint4 ld_cg_v4(const void* ptr) {
   return v;
 }
 
+// The tile in `buf` to every further output of the plan (tensor maps in global memory).
+__device__ __noinline__ void tma_store_peers(const CUtensorMap* maps, int n, uint32_t buf, int col, int row, int z) {
+  for (int r = 0; r < n; ++r) tma_store_3d(maps + r, buf, col, row, z);
+}
+
 // EW: epilogue warps of a CTA, 4 or 8.  A template parameter so that each form has its own launch
 // bounds and drain loop: with the count a run-time value (or the drain in a generic lambda under
 // the larger form's launch bounds) the four-warp form lost 10-30 % on short-K shapes.
@@ -809,9 +814,14 @@ hb_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 tma_reduce_add_3d(&tmC, buf, col, row0, zc);
               else
                 tma_store_3d(&tmC, buf, col, row0, zc);
-              // (plain stores into other GPUs' memory: nothing here waits on a peer)
-              for (int r = 0; r < p.n_peers; ++r) tma_store_3d(p.peer_maps + r, buf, col, row0, zc);
               bulk_commit();
+              // (plain stores into other GPUs' memory, a bulk group of their own: nothing here waits
+              // on a peer; the waits on this buffer's earlier groups count groups in order, so one
+              // more group per chunk only makes them wait for more)
+              if (p.n_peers) {
+                tma_store_peers(p.peer_maps, p.n_peers, buf, col, row0, zc);
+                bulk_commit();
+              }
             }
           }
         } else {
