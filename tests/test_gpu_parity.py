@@ -1299,3 +1299,56 @@ def test_conv3d_random_geometry(K, co, N, CI, D, H, W, CO8, KD, KH, KW, sd, sh, 
     want = co.conv3d_ncdhw(x, w, (sd, sh, sw), pad)
     got = K.conv3d_ncdhw(dev(x), dev(w), (sd, sh, sw), pad)
     check(got, want, "c3d %s" % ((N, CI, D, H, W, CO, KD, KH, KW, sd, sh, sw, pad, int8),))
+
+
+def test_further_outputs_of_a_plan(K, co):
+    """hb_plan_set_peer_outputs on one GPU: every tile goes to the plan's output and to each
+    further output (here ordinary buffers of the same device; across GPUs they are the other
+    ranks' buffers, tests/multi_rank_check.py).  GEMM in CTA pairs with a ragged edge, a batched
+    GEMM with eight epilogue warps, an fp16 conv through im2col loads; taking the outputs away
+    again; the refusals."""
+    from heron_b200._lib import HB_ERR_KNOB, HeronB200Error
+    rng = np.random.default_rng(99)
+    a, b = rand_i8(rng, (520, 1152), False), rand_i8(rng, (328, 1152), True)
+    out = poison((520, 328), torch.int32)
+    extra = [poison((520, 328), torch.int32) for _ in range(3)]
+    plan = K.plan_gemm(dev(a), dev(b), out=out, knobs=dict(cta_group=2))
+    plan.set_peer_outputs(extra)
+    plan.launch()
+    want = co.gemm_int(a, b)
+    for t in [out] + extra:
+        check(t, want, "gemm, further outputs")
+    for t in extra:
+        t.fill_(-7)
+    plan.set_peer_outputs([])
+    out.fill_(0)
+    plan.launch()
+    check(out, want, "gemm, outputs removed")
+    assert all(bool((t == -7).all()) for t in extra)
+
+    a3, b3 = rand_i8(rng, (5, 200, 64), True), rand_i8(rng, (5, 264, 64), True)
+    out3 = poison((5, 200, 264), torch.int32)
+    more = [poison((5, 200, 264), torch.int32) for _ in range(2)]
+    plan3 = K.plan_bmm(dev(a3), dev(b3), out=out3, knobs=dict(epi_warps=8))
+    plan3.set_peer_outputs(more)
+    plan3.launch()
+    for t in [out3] + more:
+        check(t, co.bmm_int(a3, b3), "bmm, further outputs")
+
+    x = rng.standard_normal((3, 9, 11, 64)).astype(np.float16)
+    w = (rng.standard_normal((3, 3, 64, 128)) / 24.0).astype(np.float16)
+    outc = poison((3, 9, 11, 128), torch.float16)
+    morec = [poison((3, 9, 11, 128), torch.float16)]
+    planc = K.plan_conv2d_nhwc(dev(x), dev(w), 1, 1, 1, out=outc, knobs=dict(conv_algo=1))
+    planc.set_peer_outputs(morec)
+    planc.launch()
+    for t in [outc] + morec:
+        check(t, co.conv2d_nhwc_f16(x, w, 1, 1, 1, np.float16), "conv, further outputs")
+
+    for knobs in (dict(conv_algo=1, epilogue=2), dict(conv_algo=2), dict(conv_algo=1, split_k=2)):
+        p2 = K.plan_conv2d_nhwc(dev(x), dev(w), 1, 1, 1, out_dtype=torch.float32, knobs=knobs)
+        with pytest.raises(HeronB200Error) as e:
+            p2.set_peer_outputs([torch.empty_like(p2.out)])
+        assert e.value.status == HB_ERR_KNOB
+    with pytest.raises(ValueError):
+        plan.set_peer_outputs([torch.empty((520, 320), dtype=torch.int32, device="cuda")])
