@@ -30,6 +30,10 @@ import sys
 import threading
 import time
 
+# (before torch is imported: the symmetric-memory allocations of the sharded block bind nothing to
+# an NVLink multicast object; a rank that dies while bound to one disturbs the box's other GPUs)
+os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+
 ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
@@ -485,6 +489,7 @@ def run_sharded(env, name, steps):
         flag = torch.tensor([1 if ok else 0], device=env.device)
         dist.all_reduce(flag, op=dist.ReduceOp.MIN)
         out["peer_store_check"] = "pass" if int(flag[0]) == 1 else "fail"
+        out["peer_store_multicast_bound"] = bool(getattr(po._hdl, "multicast_ptr", 0))
         gsteps = max(3, min(steps, 50))
         for _ in range(3):
             plan.launch()

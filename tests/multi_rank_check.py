@@ -6,6 +6,8 @@ the form without a collective: each rank's kernel stores its shard into every ra
 import os
 import sys
 
+os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")  # (before torch is imported)
+
 import numpy as np
 import torch
 import torch.distributed as dist
